@@ -1,0 +1,314 @@
+#!/usr/bin/env python
+"""Benchmark of the GPT-2 decode hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload: GPT-2 medium (24 layers, d_model 1024, 16 heads, d_ff 4096, vocab 50257), FP32
+random-init N(0, 0.02) weights (seed 0), 64 independent sequences per GPU with 128-token seeded
+uniform prompts, greedy decode. A step is one batched decode step: every sequence of the rank
+advances by one token. Weights and KV cache (> 1.4 GB per step) are far larger than L2, so no
+explicit L2 flush is needed between steps. For N > 1 (launched by torchrun, one rank per GPU)
+every rank holds a full weight replica and its own 64 sequences; there is no collective on the
+token path (weak scaling).
+
+One JSON line is printed by rank 0; see the keys `value`, `e2e`, `roofline`, `cpu_baseline`.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "gpt2_decode_tokens_per_sec"
+UNIT = "tokens/s"
+MODEL = "medium"
+SEQS_PER_GPU = 64
+PROMPT_LEN = 128
+WEIGHT_SEED = 0
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device, self.proc, self.lines = device, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.device)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower() == "active":
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def make_prompts(cfg, rank):
+    from puppygrad_b200 import synthetic
+    base = rank * SEQS_PER_GPU
+    return [synthetic.uniform_prompt(base + i + 1, PROMPT_LEN, cfg["vocab_size"]) for i in range(SEQS_PER_GPU)]
+
+
+def kv_bytes_per_step(cfg, lens):
+    # each sequence reads K and V of all cached positions (plus the new one) in every layer, and
+    # writes one K row and one V row per layer
+    c, L = cfg["n_embd"], cfg["n_layer"]
+    return sum(2 * L * (t + 1) * c * 4 + 2 * L * c * 4 for t in lens)
+
+
+# ---------------------------------------------------------------------------------------------
+def cpu_baseline_sample(cfg, weights, tokens: int, prompt_len: int, threads: int):
+    """Times the CPU oracle (the port of the reference path) on one sequence of the workload:
+    prefill `prompt_len` tokens untimed, then `tokens` greedy decode steps timed."""
+    from oracle import oracle
+    from puppygrad_b200 import synthetic
+    model = oracle.Model(cfg, weights, threads=threads)
+    cache = model.new_kv_cache()
+    prompt = synthetic.uniform_prompt(1, prompt_len, cfg["vocab_size"])
+    logits = model.prefill(prompt, cache)
+    t0 = time.perf_counter()
+    for _ in range(tokens):
+        logits = model.forward_one(oracle.argmax_logits(logits), cache)
+    dt = time.perf_counter() - t0
+    return tokens / dt, dt
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the path (its C++ port: the reference is Rust and no
+    Rust toolchain exists on these machines), all host threads, one sequence at a time as the
+    reference serves them. A step is one decode token of one sequence of the workload."""
+    rank, world, local = dist_env()
+    if rank != 0:
+        return
+    from oracle import oracle
+    from puppygrad_b200 import synthetic
+    cfg = synthetic.preset(MODEL)
+    weights = synthetic.random_init_weights(cfg, WEIGHT_SEED)
+    threads = os.cpu_count() or 1
+    model = oracle.Model(cfg, weights, threads=threads)
+    cache = model.new_kv_cache()
+    # a short prompt keeps the untimed prefill bounded; decode cost is dominated by the weights
+    prompt = synthetic.uniform_prompt(1, PROMPT_LEN, cfg["vocab_size"])[:16]
+    logits = model.prefill(prompt, cache)
+    for _ in range(args.warmup):
+        logits = model.forward_one(oracle.argmax_logits(logits), cache)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        if cache.seq_len >= cfg["n_positions"]:
+            cache.clear()
+            logits = model.prefill(prompt, cache)
+        logits = model.forward_one(oracle.argmax_logits(logits), cache)
+    dt = time.perf_counter() - t0
+    value = args.steps / dt
+    sample = (f"1 sequence, {args.steps} greedy decode tokens after a 16-token prompt, {threads} threads, "
+              "C++ port of the reference CPU path")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"gpt2-{MODEL} fp32 greedy decode, one sequence at a time on host cores"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0}))
+
+
+# ---------------------------------------------------------------------------------------------
+def run_ours(args):
+    rank, world, local = dist_env()
+    import torch
+    import torch.distributed as dist
+
+    import puppygrad_b200 as pg
+    from puppygrad_b200 import synthetic
+
+    if world > 1:
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    cfg = synthetic.preset(MODEL)
+    weights = synthetic.random_init_weights(cfg, WEIGHT_SEED)
+    model = pg.Gpt2Model(cfg, weights, pg.Gpt2CudaConfig(device=local))
+    cache = model.new_kv_cache(max_batch=SEQS_PER_GPU)
+    prompts = make_prompts(cfg, rank)
+    B, K, W = SEQS_PER_GPU, args.steps, args.warmup
+    if PROMPT_LEN + W + K + 1 > cfg["n_positions"]:
+        raise SystemExit("steps + warmup exceed the context window")
+
+    # ---- device-resident throughput: tokens fed back on the device, timed with CUDA events on
+    # the library's stream
+    _, first = model.prefill_batch(prompts, cache)
+    if W:
+        warm = model.decode_greedy(first, cache, W)
+        first = warm[-1]
+    clocks = ClockSampler(local)
+    launches0 = cache.kernel_launches()
+    barrier()
+    clocks.start()
+    cache.time_begin()
+    toks = model.decode_greedy(first, cache, K)
+    sec = cache.time_end()
+    barrier()
+    clock_info = clocks.stop()
+    launches = cache.kernel_launches() - launches0
+    lens_mid = [PROMPT_LEN + W + K // 2] * B
+
+    t = torch.tensor([sec], dtype=torch.float64, device=f"cuda:{local}")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    sec_max = float(t.item())
+    value = world * B * K / sec_max
+
+    # ---- end to end through the public API: host token ids in, host argmax out, every step
+    _, cur = model.prefill_batch(prompts, cache)
+    for _ in range(W):
+        _, cur, _, _ = model.forward_one_batch(cur, cache)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        _, cur, _, _ = model.forward_one_batch(cur, cache)
+    e2e_sec = time.perf_counter() - t0
+    barrier()
+    t = torch.tensor([e2e_sec], dtype=torch.float64, device=f"cuda:{local}")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = world * B * K / float(t.item())
+
+    # ---- per-operation device time of one step (kernel by kernel), for the roofline line
+    _, cur = model.prefill_batch(prompts, cache)
+    for _ in range(max(W, 3)):
+        _, cur, _, _ = model.forward_one_batch(cur, cache)
+    prof = {}
+    reps = 3
+    for _ in range(reps):
+        p = model.profile_forward_one(cur, cache)
+        for k, (s, n) in p.items():
+            prof[k] = (prof.get(k, (0.0, 0))[0] + s / reps, n)
+        _, cur, _, _ = model.forward_one_batch(cur, cache)
+    t_prof = cache.seq_len_of(0) - 1
+
+    if rank == 0:
+        peak, peak_src = measured_peaks()
+        c, f, L = cfg["n_embd"], cfg["n_inner"], cfg["n_layer"]
+        # dominant kernel class by device time, its algorithmic bytes per launch
+        alg = {
+            "qkv_projection": 4 * (3 * c * c + 3 * c + B * c + B * 3 * c + 2 * c),
+            "attention_projection": 4 * (c * c + c + 3 * B * c),
+            "mlp_fc_projection": 4 * (c * f + f + B * c + B * f + 2 * c),
+            "mlp_projection": 4 * (c * f + c + B * f + 2 * B * c),
+            "final_logits": 4 * (cfg["vocab_size"] * c + B * c + B * cfg["vocab_size"] + 2 * c),
+            "attention": kv_bytes_per_step(cfg, [t_prof] * B) / L + 4 * B * 4 * c,
+        }
+        dom = max(alg, key=lambda k: prof[k][0])
+        dom_sec, dom_n = prof[dom]
+        per_launch = dom_sec / max(dom_n, 1)
+        launches_per_step_dom = dom_n
+        achieved = alg[dom] * (L if dom != "final_logits" else 1) / launches_per_step_dom / per_launch / 1e9
+        step_bytes = model.weight_bytes_per_step() + kv_bytes_per_step(cfg, lens_mid)
+        step_achieved = step_bytes / (sec_max / K) / 1e9
+
+        cpu_tokens = 24
+        cpu_val, cpu_dt = cpu_baseline_sample(cfg, weights, cpu_tokens, 16, os.cpu_count() or 1)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": sec_max / K * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"gpt2-{MODEL} fp32, {B} sequences per GPU, {PROMPT_LEN}-token prompts, "
+                                   f"greedy decode; step = one batched decode step ({B} tokens per GPU)",
+                       "l2": "inputs larger than L2 (1.4 GB weights + KV per step)", "parallelism": f"replicas x{world}"},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
+            "gpu_launches": int(launches),
+            "clocks": clock_info,
+            "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "per_launch_us": per_launch * 1e6},
+            "step_roofline": {"bound": "hbm", "bytes_per_step": step_bytes, "achieved": step_achieved,
+                              "peak": peak, "frac": step_achieved / peak},
+            "profile_us": {k: round(v[0] * 1e6, 1) for k, v in prof.items()},
+            "cpu_baseline": {"value": cpu_val, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
+                             "sample": f"1 sequence, {cpu_tokens} greedy decode tokens after a 16-token prompt "
+                                       f"({cpu_dt:.1f} s)"},
+            "check": {"tokens_last_step": [int(x) for x in toks[-1][:4]]},
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

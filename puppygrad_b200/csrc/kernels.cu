@@ -1,0 +1,1074 @@
+// sm_100a CUDA kernels of the GPT-2 inference path (FP32 parity path).
+//
+// Decode is HBM-bound weight streaming: every linear reads its [out, in] matrix once with 128-bit
+// non-allocating loads, keeps the few activation rows on chip, and fuses LayerNorm (prologue) and
+// bias / GELU / residual (epilogue). Kernels of one decode step are chained with programmatic
+// dependent launch: each CTA issues its first weight loads *before* griddepcontrol.wait, so the
+// weight stream of kernel N+1 overlaps the tail of kernel N.
+#include <cfloat>
+#include <climits>
+
+#include "kernels.cuh"
+
+namespace pg {
+namespace {
+
+constexpr unsigned FULL = 0xffffffffu;
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// 128-bit streaming load of read-only weights: bypass L1 allocation so activations stay cached.
+__device__ __forceinline__ float4 ldg_stream(const float4* p) {
+  float4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ float dot4(float4 a, float4 b, float acc) {
+  acc = fmaf(a.x, b.x, acc);
+  acc = fmaf(a.y, b.y, acc);
+  acc = fmaf(a.z, b.z, acc);
+  acc = fmaf(a.w, b.w, acc);
+  return acc;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(FULL, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(FULL, v, o));
+  return v;
+}
+
+// Reduces N (power of two, <= 32) per-lane values across the warp with N-1 + log2(32/N)
+// shuffles. Afterwards v[0] of lane l holds the total of value index l >> (5 - log2 N).
+template <int N, int OFF>
+struct WarpMultiReduce {
+  static __device__ __forceinline__ void run(float* v, int lane) {
+    const bool up = (lane & OFF) != 0;
+#pragma unroll
+    for (int j = 0; j < N / 2; ++j) {
+      float send = up ? v[j] : v[j + N / 2];
+      float keep = up ? v[j + N / 2] : v[j];
+      v[j] = keep + __shfl_xor_sync(FULL, send, OFF);
+    }
+    WarpMultiReduce<N / 2, OFF / 2>::run(v, lane);
+  }
+};
+template <int OFF>
+struct WarpMultiReduce<1, OFF> {
+  static __device__ __forceinline__ void run(float* v, int lane) {
+    v[0] += __shfl_xor_sync(FULL, v[0], OFF);
+    WarpMultiReduce<1, OFF / 2>::run(v, lane);
+  }
+};
+template <>
+struct WarpMultiReduce<1, 0> {
+  static __device__ __forceinline__ void run(float*, int) {}
+};
+
+// tanh-GELU in the reference's evaluation order (src/models/cpu.rs:145-150)
+__device__ __forceinline__ float gelu_ref(float x) {
+  return 0.5f * x * (1.0f + tanhf(0.7978846f * (x + 0.044715f * x * x * x)));
+}
+
+constexpr int LIN_THREADS = 128;
+constexpr int LIN_WARPS = LIN_THREADS / 32;
+constexpr int LIN_ROWS = 4;
+
+// ------------------------------------------------------------------ decode linear
+// CTA: LIN_ROWS weight rows per group, the 128 threads split K; grid-stride over row groups.
+// Replaces linear_block_into / transposed_dense_projection_into / logits_from_hidden_into
+// (src/models/gpt2/rust.rs:1481-1532, 1767-1813; src/models/cpu.rs:58-75) and, fused,
+// layer_norm_in_place, gelu_in_place, add_in_place (cpu.rs:119-171).
+template <int MT, int EPI, bool LN>
+__global__ void __launch_bounds__(LIN_THREADS) linear_decode_kernel(LinearArgs a) {
+  extern __shared__ float4 dyn_smem4[];
+  float* xs = reinterpret_cast<float*>(dyn_smem4);  // [MT][k] normalised rows (LN only)
+  __shared__ float red[LIN_WARPS][LIN_ROWS * MT];
+  __shared__ float best_v[LIN_ROWS * MT];
+  __shared__ int best_i[LIN_ROWS * MT];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int k4 = a.k >> 2;
+  const int groups = (a.n + LIN_ROWS - 1) / LIN_ROWS;
+  const float4* w4 = reinterpret_cast<const float4*>(a.w);
+  constexpr int NV = LIN_ROWS * MT;
+
+  pdl_launch();
+
+  // First chunk of this CTA's first row group: issued before the dependency wait.
+  float4 wpre[LIN_ROWS];
+  {
+    const int g0 = blockIdx.x;
+#pragma unroll
+    for (int r = 0; r < LIN_ROWS; ++r) {
+      int row = min(g0 * LIN_ROWS + r, a.n - 1);
+      wpre[r] = (g0 < groups && tid < k4) ? ldg_stream(w4 + (size_t)row * k4 + tid) : make_float4(0, 0, 0, 0);
+    }
+  }
+
+  pdl_wait();
+
+  if (LN) {
+    // rows of x -> LayerNorm -> shared memory; warp w handles rows w, w+4
+    for (int m = warp; m < MT; m += LIN_WARPS) {
+      float* dst = xs + (size_t)m * a.k;
+      if (m < a.m) {
+        const float4* xr = reinterpret_cast<const float4*>(a.x + (size_t)m * a.k);
+        float s = 0.f;
+        for (int c = lane; c < k4; c += 32) {
+          float4 v = xr[c];
+          reinterpret_cast<float4*>(dst)[c] = v;
+          s += (v.x + v.y) + (v.z + v.w);
+        }
+        s = warp_sum(s);
+        const float mean = s / (float)a.k;
+        float q = 0.f;
+        for (int c = lane; c < k4; c += 32) {
+          float4 v = reinterpret_cast<float4*>(dst)[c];
+          float d0 = v.x - mean, d1 = v.y - mean, d2 = v.z - mean, d3 = v.w - mean;
+          q += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+        }
+        q = warp_sum(q);
+        const float inv_std = 1.0f / sqrtf(q / (float)a.k + a.eps);
+        const float4* g4 = reinterpret_cast<const float4*>(a.ln_g);
+        const float4* b4 = reinterpret_cast<const float4*>(a.ln_b);
+        for (int c = lane; c < k4; c += 32) {
+          float4 v = reinterpret_cast<float4*>(dst)[c];
+          float4 g = g4[c], b = b4[c];
+          v.x = (v.x - mean) * inv_std * g.x + b.x;
+          v.y = (v.y - mean) * inv_std * g.y + b.y;
+          v.z = (v.z - mean) * inv_std * g.z + b.z;
+          v.w = (v.w - mean) * inv_std * g.w + b.w;
+          reinterpret_cast<float4*>(dst)[c] = v;
+        }
+      } else {
+        for (int c = lane; c < k4; c += 32) reinterpret_cast<float4*>(dst)[c] = make_float4(0, 0, 0, 0);
+      }
+    }
+    __syncthreads();
+  }
+
+  float run_best = -INFINITY;  // lm_head argmax partial of this thread's (row-in-group, m) pair
+  int run_idx = INT_MAX;
+
+  for (int g = blockIdx.x; g < groups; g += gridDim.x) {
+    const int row0 = g * LIN_ROWS;
+    const float4* wrow[LIN_ROWS];
+#pragma unroll
+    for (int r = 0; r < LIN_ROWS; ++r) wrow[r] = w4 + (size_t)min(row0 + r, a.n - 1) * k4;
+
+    for (int m0 = 0; m0 < a.m; m0 += MT) {
+      float acc[NV];
+#pragma unroll
+      for (int i = 0; i < NV; ++i) acc[i] = 0.f;
+      const float* xbase = LN ? xs : a.x + (size_t)m0 * a.k;
+
+      bool first = (g == (int)blockIdx.x) && (m0 == 0);
+#pragma unroll 2
+      for (int c = tid; c < k4; c += LIN_THREADS) {
+        float4 w[LIN_ROWS];
+        if (first && c == tid) {
+#pragma unroll
+          for (int r = 0; r < LIN_ROWS; ++r) w[r] = wpre[r];
+        } else {
+#pragma unroll
+          for (int r = 0; r < LIN_ROWS; ++r) w[r] = ldg_stream(wrow[r] + c);
+        }
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          float4 xv;
+          if (LN) {
+            xv = reinterpret_cast<const float4*>(xbase + (size_t)m * a.k)[c];
+          } else {
+            xv = (m0 + m < a.m) ? reinterpret_cast<const float4*>(xbase + (size_t)m * a.k)[c]
+                                : make_float4(0, 0, 0, 0);
+          }
+#pragma unroll
+          for (int r = 0; r < LIN_ROWS; ++r) acc[r * MT + m] = dot4(w[r], xv, acc[r * MT + m]);
+        }
+      }
+
+      WarpMultiReduce<NV, 16>::run(acc, lane);
+      constexpr int SH = (NV == 32) ? 0 : (NV == 16) ? 1 : (NV == 8) ? 2 : 3;  // 5 - log2(NV)
+      if ((lane & ((1 << SH) - 1)) == 0) red[warp][lane >> SH] = acc[0];
+      __syncthreads();
+      if (tid < NV) {
+        const int r = tid / MT, m = m0 + tid % MT, row = row0 + r;
+        if (row < a.n && m < a.m) {
+          float dotv = ((red[0][tid] + red[1][tid]) + red[2][tid]) + red[3][tid];
+          float v = a.bias ? a.bias[row] + dotv : dotv;
+          if (EPI == EPI_GELU) v = gelu_ref(v);
+          if (EPI == EPI_RESID) v = a.resid[(size_t)m * a.n + row] + v;
+          a.out[(size_t)m * a.n + row] = v;
+          if (a.part_val && v > run_best) {
+            run_best = v;
+            run_idx = row;
+          }
+        }
+      }
+      __syncthreads();
+    }
+  }
+
+  if (a.part_val) {  // m <= MT here: one (r, m) pair per thread
+    if (tid < NV) {
+      best_v[tid] = run_best;
+      best_i[tid] = run_idx;
+    }
+    __syncthreads();
+    if (tid < MT && tid < a.m) {
+      float bv = -INFINITY;
+      int bi = INT_MAX;
+#pragma unroll
+      for (int r = 0; r < LIN_ROWS; ++r) {
+        float v = best_v[r * MT + tid];
+        int i = best_i[r * MT + tid];
+        if (v > bv || (v == bv && i < bi)) {
+          bv = v;
+          bi = i;
+        }
+      }
+      a.part_val[(size_t)tid * gridDim.x + blockIdx.x] = bv;
+      a.part_idx[(size_t)tid * gridDim.x + blockIdx.x] = bi;
+    }
+  }
+}
+
+// Any k (no alignment requirement): one thread per output element. Only shapes whose inner
+// dimension is not a multiple of 4 take this path.
+__global__ void linear_generic_kernel(LinearArgs a, int epi) {
+  pdl_launch();
+  pdl_wait();
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)a.m * a.n) return;
+  int m = (int)(idx / a.n), o = (int)(idx % a.n);
+  const float* xr = a.x + (size_t)m * a.k;
+  const float* wr = a.w + (size_t)o * a.k;
+  float acc = 0.f;
+  for (int i = 0; i < a.k; ++i) acc = fmaf(xr[i], wr[i], acc);
+  float v = a.bias ? a.bias[o] + acc : acc;
+  if (epi == EPI_GELU) v = gelu_ref(v);
+  if (epi == EPI_RESID) v = a.resid[idx] + v;
+  a.out[idx] = v;
+}
+
+// ------------------------------------------------------------------ small row kernels
+__global__ void embed_kernel(const float* __restrict__ wte, const float* __restrict__ wpe, const int* ids,
+                             const int* pos, float* out, int rows, int c) {
+  pdl_launch();
+  pdl_wait();
+  int r = blockIdx.x;
+  if (r >= rows) return;
+  const float* t = wte + (size_t)ids[r] * c;
+  const float* p = wpe + (size_t)pos[r] * c;
+  for (int i = threadIdx.x; i < c; i += blockDim.x) out[(size_t)r * c + i] = t[i] + p[i];
+}
+
+// One warp per row (src/models/cpu.rs:119-143 with tree sums).
+__global__ void layernorm_rows_kernel(const float* x, const float* __restrict__ g, const float* __restrict__ b,
+                                      float eps, float* out, int rows, int c) {
+  pdl_launch();
+  pdl_wait();
+  int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  int lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const float* xr = x + (size_t)r * c;
+  float s = 0.f;
+  for (int i = lane; i < c; i += 32) s += xr[i];
+  s = warp_sum(s);
+  float mean = s / (float)c;
+  float q = 0.f;
+  for (int i = lane; i < c; i += 32) {
+    float d = xr[i] - mean;
+    q += d * d;
+  }
+  q = warp_sum(q);
+  float inv_std = 1.0f / sqrtf(q / (float)c + eps);
+  for (int i = lane; i < c; i += 32) out[(size_t)r * c + i] = (xr[i] - mean) * inv_std * g[i] + b[i];
+}
+
+__global__ void transpose_kernel(const float* __restrict__ src, float* __restrict__ dst, int in_f, int out_f) {
+  __shared__ float tile[32][33];
+  int o0 = blockIdx.x * 32, i0 = blockIdx.y * 32;
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    int i = i0 + j, o = o0 + threadIdx.x;
+    if (i < in_f && o < out_f) tile[j][threadIdx.x] = src[(size_t)i * out_f + o];
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    int o = o0 + j, i = i0 + threadIdx.x;
+    if (i < in_f && o < out_f) dst[(size_t)o * in_f + i] = tile[threadIdx.x][j];
+  }
+}
+
+__global__ void gather_rows_kernel(const float* src, const int* rows, float* dst, int n, int c) {
+  int r = blockIdx.x;
+  if (r >= n) return;
+  const float* s = src + (size_t)rows[r] * c;
+  for (int i = threadIdx.x; i < c; i += blockDim.x) dst[(size_t)r * c + i] = s[i];
+}
+
+// ------------------------------------------------------------------ FP32 GEMM (prefill parity path)
+// 128x128x8 tiles, 256 threads, 8x8 outputs per thread.
+constexpr int GB = 128, GK = 8;
+__global__ void __launch_bounds__(256) gemm_f32_kernel(LinearArgs a, int epi) {
+  __shared__ __align__(16) float As[GK][GB + 4];
+  __shared__ __align__(16) float Ws[GK][GB + 4];
+  const int tid = threadIdx.x;
+  const int m0 = blockIdx.y * GB, n0 = blockIdx.x * GB;
+  const int lr = tid >> 1, lk = (tid & 1) * 4;  // loader: row within tile, k offset
+  const int ty = tid >> 4, tx = tid & 15;
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+
+  const bool arow_ok = (m0 + lr) < a.m, wrow_ok = (n0 + lr) < a.n;
+  const float* ap = a.x + (size_t)(m0 + lr) * a.k + lk;
+  const float* wp = a.w + (size_t)(n0 + lr) * a.k + lk;
+  for (int k0 = 0; k0 < a.k; k0 += GK) {
+    float4 av = make_float4(0, 0, 0, 0), wv = make_float4(0, 0, 0, 0);
+    if (k0 + lk < a.k) {  // k is a multiple of 4
+      if (arow_ok) av = *reinterpret_cast<const float4*>(ap + k0);
+      if (wrow_ok) wv = *reinterpret_cast<const float4*>(wp + k0);
+    }
+    As[lk + 0][lr] = av.x; As[lk + 1][lr] = av.y; As[lk + 2][lr] = av.z; As[lk + 3][lr] = av.w;
+    Ws[lk + 0][lr] = wv.x; Ws[lk + 1][lr] = wv.y; Ws[lk + 2][lr] = wv.z; Ws[lk + 3][lr] = wv.w;
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < GK; ++kk) {
+      float4 a0 = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
+      float4 a1 = *reinterpret_cast<const float4*>(&As[kk][64 + ty * 4]);
+      float4 b0 = *reinterpret_cast<const float4*>(&Ws[kk][tx * 4]);
+      float4 b1 = *reinterpret_cast<const float4*>(&Ws[kk][64 + tx * 4]);
+      float af[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      float bf[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(af[i], bf[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    int m = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+    if (m >= a.m) continue;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      int n = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + (j - 4));
+      if (n >= a.n) continue;
+      float v = a.bias ? a.bias[n] + acc[i][j] : acc[i][j];
+      if (epi == EPI_GELU) v = gelu_ref(v);
+      if (epi == EPI_RESID) v = a.resid[(size_t)m * a.n + n] + v;
+      a.out[(size_t)m * a.n + n] = v;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ paged KV helpers
+__device__ __forceinline__ size_t kv_row_offset(const KvLayout& kv, int page, int which, int head, int off) {
+  // [page][2][head][page_tokens][head_dim]
+  return ((((size_t)page * 2 + which) * kv.n_head + head) * kv.page_tokens + off) * kv.head_dim;
+}
+
+__global__ void kv_scatter_kernel(const float* qkv, const int* row_slot, const int* row_pos, float* pool,
+                                  const int* page_table, KvLayout kv, int rows) {
+  int r = blockIdx.x;
+  if (r >= rows) return;
+  const int c = kv.n_head * kv.head_dim;
+  const int slot = row_slot[r], pos = row_pos[r];
+  const int page = page_table[(size_t)slot * kv.pages_per_seq + pos / kv.page_tokens];
+  const int off = pos % kv.page_tokens;
+  for (int i = threadIdx.x; i < 2 * c; i += blockDim.x) {
+    int which = i / c, j = i % c, h = j / kv.head_dim, d = j % kv.head_dim;
+    pool[kv_row_offset(kv, page, which, h, off) + d] = qkv[(size_t)r * 3 * c + c + i];
+  }
+}
+
+__global__ void kv_gather_kernel(const float* pool, const int* page_table, KvLayout kv, int slot, int seq_len,
+                                 int n_positions, float* keys, float* values) {
+  // output layout (head * n_positions + pos) * head_dim + dim
+  size_t total = (size_t)kv.n_head * n_positions * kv.head_dim;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    int d = (int)(idx % kv.head_dim);
+    int pos = (int)((idx / kv.head_dim) % n_positions);
+    int h = (int)(idx / ((size_t)kv.head_dim * n_positions));
+    float k = 0.f, v = 0.f;
+    if (pos < seq_len) {
+      int page = page_table[(size_t)slot * kv.pages_per_seq + pos / kv.page_tokens];
+      int off = pos % kv.page_tokens;
+      k = pool[kv_row_offset(kv, page, 0, h, off) + d];
+      v = pool[kv_row_offset(kv, page, 1, h, off) + d];
+    }
+    keys[idx] = k;
+    values[idx] = v;
+  }
+}
+
+// ------------------------------------------------------------------ decode attention
+// cached_self_attention_into (src/models/gpt2/rust.rs:1662-1741): append K,V of the new token,
+// scores over the cached keys, softmax, weighted sum of values. One CTA per (head, sequence,
+// split); the split partials are merged by whichever CTA of the (head, sequence) finishes last.
+constexpr int ATT_THREADS = 128;
+
+__device__ __forceinline__ float block_max_128(float v, float* sm) {
+  v = warp_max(v);
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = fmaxf(fmaxf(sm[0], sm[1]), fmaxf(sm[2], sm[3]));
+  __syncthreads();
+  return r;
+}
+__device__ __forceinline__ float block_sum_128(float v, float* sm) {
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = (sm[0] + sm[1]) + (sm[2] + sm[3]);
+  __syncthreads();
+  return r;
+}
+
+// Merges split partials (m, l, acc[D]) in split order and writes the normalised head output.
+__device__ void merge_splits(const float* part, int splits, int d_len, float* out_head) {
+  for (int d = threadIdx.x; d < d_len; d += blockDim.x) {
+    float mx = -INFINITY;
+    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, part[(size_t)s * (d_len + 2)]);
+    float l = 0.f, o = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float* p = part + (size_t)s * (d_len + 2);
+      float sc = (p[0] == -INFINITY) ? 0.f : expf(p[0] - mx);
+      l += p[1] * sc;
+      o += p[2 + d] * sc;
+    }
+    out_head[d] = o / l;
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(DecodeAttnArgs a) {
+  static_assert(D == 64, "fast path is written for head_dim 64");
+  extern __shared__ float4 dyn_smem4[];
+  float* scores = reinterpret_cast<float*>(dyn_smem4);  // [keys of this split]
+  __shared__ float red4[4];
+  __shared__ __align__(16) float pv[8][D];
+  __shared__ int is_last;
+
+  const int h = blockIdx.x, b = blockIdx.y, sp = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int c = a.kv.n_head * D;
+  pdl_launch();
+  pdl_wait();
+
+  const int pos = a.pos[b];
+  const int nkeys = pos + 1;
+  const int per = (nkeys + a.splits - 1) / a.splits;
+  const int k0 = min(sp * per, nkeys), k1 = min(k0 + per, nkeys);
+  const int* table = a.page_table + (size_t)b * a.kv.pages_per_seq;
+  const float* row = a.qkv + (size_t)b * 3 * c;
+
+  if (k0 <= pos && pos < k1) {  // this split owns the new position: append K,V
+    if (tid < 32) {
+      const int page = table[pos / a.kv.page_tokens], off = pos % a.kv.page_tokens;
+      const int which = tid >> 4, j = tid & 15;
+      float4 v = reinterpret_cast<const float4*>(row + c + which * c + h * D)[j];
+      reinterpret_cast<float4*>(a.kv_pool + kv_row_offset(a.kv, page, which, h, off))[j] = v;
+    }
+    __syncthreads();
+  }
+
+  // scores: four lanes per key, lane part p owns float4 i*4+p (i = 0..3) of the 64 dims
+  const int part = lane & 3;
+  float4 q[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) q[i] = reinterpret_cast<const float4*>(row + h * D)[i * 4 + part];
+  const float scale = 1.0f / sqrtf((float)D);
+  float lmax = -INFINITY;
+  for (int kb = k0 + warp * 8; kb < k1; kb += 32) {
+    const int key = kb + (lane >> 2);
+    float s = 0.f;
+    if (key < k1) {
+      const int page = table[key / a.kv.page_tokens], off = key % a.kv.page_tokens;
+      const float4* kr = reinterpret_cast<const float4*>(a.kv_pool + kv_row_offset(a.kv, page, 0, h, off));
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s = dot4(q[i], kr[i * 4 + part], s);
+    }
+    s += __shfl_xor_sync(FULL, s, 1);
+    s += __shfl_xor_sync(FULL, s, 2);
+    s *= scale;
+    if (key < k1) {
+      if (part == 0) scores[key - k0] = s;
+      lmax = fmaxf(lmax, s);
+    }
+  }
+  const float mx = block_max_128(lmax, red4);  // also orders the score writes
+  float lsum = 0.f;
+  for (int k = k0 + tid; k < k1; k += ATT_THREADS) {
+    float e = expf(scores[k - k0] - mx);
+    scores[k - k0] = e;
+    lsum += e;
+  }
+  const float total = block_sum_128(lsum, red4);
+
+  // weighted values: 16 lanes cover one 64-float row, 8 key groups
+  const int dg = tid & 15, kg = tid >> 4;
+  float4 acc = make_float4(0, 0, 0, 0);
+  for (int k = k0 + kg; k < k1; k += 8) {
+    const int page = table[k / a.kv.page_tokens], off = k % a.kv.page_tokens;
+    const float4 v = reinterpret_cast<const float4*>(a.kv_pool + kv_row_offset(a.kv, page, 1, h, off))[dg];
+    const float p = scores[k - k0];
+    acc.x = fmaf(p, v.x, acc.x);
+    acc.y = fmaf(p, v.y, acc.y);
+    acc.z = fmaf(p, v.z, acc.z);
+    acc.w = fmaf(p, v.w, acc.w);
+  }
+  reinterpret_cast<float4*>(&pv[kg][0])[dg] = acc;
+  __syncthreads();
+  float o = 0.f;
+  if (tid < D) {
+#pragma unroll
+    for (int g = 0; g < 8; ++g) o += pv[g][tid];
+  }
+
+  if (a.splits == 1) {
+    if (tid < D) a.out[(size_t)b * c + h * D + tid] = o / total;
+    return;
+  }
+  float* mypart = a.part + ((size_t)(b * a.kv.n_head + h) * a.splits + sp) * (D + 2);
+  if (tid < D) mypart[2 + tid] = o;
+  if (tid == 0) {
+    mypart[0] = (k1 > k0) ? mx : -INFINITY;
+    mypart[1] = (k1 > k0) ? total : 0.f;
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    unsigned old = atomicAdd(&a.counters[b * a.kv.n_head + h], 1u);
+    is_last = (old == (unsigned)a.splits - 1);
+  }
+  __syncthreads();
+  if (is_last) {
+    __threadfence();
+    merge_splits(a.part + (size_t)(b * a.kv.n_head + h) * a.splits * (D + 2), a.splits, D,
+                 a.out + (size_t)b * c + h * D);
+    if (tid == 0) a.counters[b * a.kv.n_head + h] = 0;
+  }
+}
+
+// Any head_dim, one CTA per (head, sequence), no split. Same arithmetic, simple indexing.
+__global__ void decode_attention_generic_kernel(DecodeAttnArgs a) {
+  extern __shared__ float4 dyn_smem4[];
+  float* scores = reinterpret_cast<float*>(dyn_smem4);
+  __shared__ float red4[4];
+  const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+  const int D = a.kv.head_dim, c = a.kv.n_head * D;
+  pdl_launch();
+  pdl_wait();
+  const int pos = a.pos[b], nkeys = pos + 1;
+  const int* table = a.page_table + (size_t)b * a.kv.pages_per_seq;
+  const float* row = a.qkv + (size_t)b * 3 * c;
+  {
+    const int page = table[pos / a.kv.page_tokens], off = pos % a.kv.page_tokens;
+    for (int i = tid; i < 2 * D; i += blockDim.x) {
+      int which = i / D, d = i % D;
+      a.kv_pool[kv_row_offset(a.kv, page, which, h, off) + d] = row[c + which * c + h * D + d];
+    }
+  }
+  __syncthreads();
+  const float scale = 1.0f / sqrtf((float)D);
+  float lmax = -INFINITY;
+  for (int k = tid; k < nkeys; k += blockDim.x) {
+    const int page = table[k / a.kv.page_tokens], off = k % a.kv.page_tokens;
+    const float* kr = a.kv_pool + kv_row_offset(a.kv, page, 0, h, off);
+    float s = 0.f;
+    for (int d = 0; d < D; ++d) s = fmaf(row[h * D + d], kr[d], s);
+    s *= scale;
+    scores[k] = s;
+    lmax = fmaxf(lmax, s);
+  }
+  const float mx = block_max_128(lmax, red4);
+  float lsum = 0.f;
+  for (int k = tid; k < nkeys; k += blockDim.x) {
+    float e = expf(scores[k] - mx);
+    scores[k] = e;
+    lsum += e;
+  }
+  const float total = block_sum_128(lsum, red4);
+  for (int d = tid; d < D; d += blockDim.x) {
+    float o = 0.f;
+    for (int k = 0; k < nkeys; ++k) {
+      const int page = table[k / a.kv.page_tokens], off = k % a.kv.page_tokens;
+      o = fmaf(scores[k], a.kv_pool[kv_row_offset(a.kv, page, 1, h, off) + d], o);
+    }
+    a.out[(size_t)b * c + h * D + d] = o / total;
+  }
+}
+
+// ------------------------------------------------------------------ prefill attention
+// causal_self_attention (src/models/gpt2/rust.rs:1580-1659) over concatenated sequences.
+// CTA = 32 queries of one (head, sequence); four threads per query, each owning 16 of 64 dims;
+// keys/values staged through shared memory in tiles of 32; online softmax per tile.
+constexpr int PA_Q = 32, PA_K = 32;
+template <int D>
+__global__ void __launch_bounds__(128) prefill_attention_kernel(PrefillAttnArgs a) {
+  static_assert(D == 64, "fast path is written for head_dim 64");
+  __shared__ float4 Ks[PA_K][D / 4];
+  __shared__ float4 Vs[PA_K][D / 4];
+  const int h = blockIdx.x, qb = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, part = tid & 3, qi = tid >> 2;
+  const int c = a.n_head * D;
+  const int r0 = a.seq_start[b], len = a.seq_start[b + 1] - r0;
+  const int q0 = qb * PA_Q;
+  if (q0 >= len) return;
+  const int qpos = q0 + qi;
+  const bool qok = qpos < len;
+  float4 q[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    q[i] = qok ? reinterpret_cast<const float4*>(a.qkv + (size_t)(r0 + qpos) * 3 * c + h * D)[i * 4 + part]
+               : make_float4(0, 0, 0, 0);
+  const float scale = 1.0f / sqrtf((float)D);
+  float m = -INFINITY, l = 0.f;
+  float4 acc[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) acc[i] = make_float4(0, 0, 0, 0);
+
+  const int kend = min(len, q0 + PA_Q);  // keys needed by the last query of this CTA
+  for (int kt = 0; kt < kend; kt += PA_K) {
+    __syncthreads();
+    for (int i = tid; i < PA_K * (D / 4); i += 128) {
+      int j = i / (D / 4), d4 = i % (D / 4);
+      int kp = kt + j;
+      float4 kv = make_float4(0, 0, 0, 0), vv = kv;
+      if (kp < len) {
+        const float* base = a.qkv + (size_t)(r0 + kp) * 3 * c + h * D;
+        kv = reinterpret_cast<const float4*>(base + c)[d4];
+        vv = reinterpret_cast<const float4*>(base + 2 * c)[d4];
+      }
+      Ks[j][d4] = kv;
+      Vs[j][d4] = vv;
+    }
+    __syncthreads();
+    float s[PA_K];
+    float tmax = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < PA_K; ++j) {
+      float d = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) d = dot4(q[i], Ks[j][i * 4 + part], d);
+      d += __shfl_xor_sync(FULL, d, 1);
+      d += __shfl_xor_sync(FULL, d, 2);
+      d *= scale;
+      const bool ok = qok && (kt + j <= qpos);
+      s[j] = ok ? d : -INFINITY;
+      tmax = fmaxf(tmax, s[j]);
+    }
+    if (tmax == -INFINITY) continue;  // whole tile masked for this query (uniform within the quad)
+    const float mn = fmaxf(m, tmax);
+    const float corr = expf(m - mn);  // m = -inf on the first tile: expf(-inf) = 0
+    l *= corr;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc[i].x *= corr; acc[i].y *= corr; acc[i].z *= corr; acc[i].w *= corr;
+    }
+#pragma unroll
+    for (int j = 0; j < PA_K; ++j) {
+      const float p = (s[j] == -INFINITY) ? 0.f : expf(s[j] - mn);
+      l += p;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float4 v = Vs[j][i * 4 + part];
+        acc[i].x = fmaf(p, v.x, acc[i].x);
+        acc[i].y = fmaf(p, v.y, acc[i].y);
+        acc[i].z = fmaf(p, v.z, acc[i].z);
+        acc[i].w = fmaf(p, v.w, acc[i].w);
+      }
+    }
+    m = mn;
+  }
+  if (qok) {
+    const float inv = 1.0f / l;
+    float4* o = reinterpret_cast<float4*>(a.out + (size_t)(r0 + qpos) * c + h * D);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      o[i * 4 + part] = make_float4(acc[i].x * inv, acc[i].y * inv, acc[i].z * inv, acc[i].w * inv);
+  }
+}
+
+// Any head_dim <= 128: one thread per query, two passes over the keys.
+__global__ void prefill_attention_generic_kernel(PrefillAttnArgs a) {
+  const int h = blockIdx.x, b = blockIdx.z;
+  const int D = a.head_dim, c = a.n_head * D;
+  const int r0 = a.seq_start[b], len = a.seq_start[b + 1] - r0;
+  const int qpos = blockIdx.y * blockDim.x + threadIdx.x;
+  if (qpos >= len) return;
+  const float* qr = a.qkv + (size_t)(r0 + qpos) * 3 * c + h * D;
+  const float scale = 1.0f / sqrtf((float)D);
+  float mx = -INFINITY;
+  for (int k = 0; k <= qpos; ++k) {
+    const float* kr = a.qkv + (size_t)(r0 + k) * 3 * c + c + h * D;
+    float s = 0.f;
+    for (int d = 0; d < D; ++d) s = fmaf(qr[d], kr[d], s);
+    mx = fmaxf(mx, s * scale);
+  }
+  float acc[128];
+  for (int d = 0; d < D; ++d) acc[d] = 0.f;
+  float l = 0.f;
+  for (int k = 0; k <= qpos; ++k) {
+    const float* kr = a.qkv + (size_t)(r0 + k) * 3 * c + c + h * D;
+    const float* vr = kr + c;
+    float s = 0.f;
+    for (int d = 0; d < D; ++d) s = fmaf(qr[d], kr[d], s);
+    float p = expf(s * scale - mx);
+    l += p;
+    for (int d = 0; d < D; ++d) acc[d] = fmaf(p, vr[d], acc[d]);
+  }
+  for (int d = 0; d < D; ++d) a.out[(size_t)(r0 + qpos) * c + h * D + d] = acc[d] / l;
+}
+
+// ------------------------------------------------------------------ argmax / top-k
+// argmax_logits (src/models/generation.rs:269-279): first strict maximum from -inf.
+__global__ void finalize_kernel(FinalizeArgs a) {
+  pdl_launch();
+  pdl_wait();
+  const int m = blockIdx.x;
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  float bv = -INFINITY;
+  int bi = INT_MAX;
+  for (int p = threadIdx.x; p < a.parts; p += blockDim.x) {
+    float v = a.part_val[(size_t)m * a.parts + p];
+    int i = a.part_idx[(size_t)m * a.parts + p];
+    if (v > bv || (v == bv && i < bi)) {
+      bv = v;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(FULL, bv, o);
+    int oi = __shfl_xor_sync(FULL, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) {
+      bv = ov;
+      bi = oi;
+    }
+  }
+  if ((threadIdx.x & 31) == 0) {
+    sv[threadIdx.x >> 5] = bv;
+    si[threadIdx.x >> 5] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+      if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) {
+        bv = sv[w];
+        bi = si[w];
+      }
+    int tok;
+    if (a.part_val) {
+      tok = (bi == INT_MAX) ? 0 : bi;
+      a.argmax_out[m] = tok;
+    } else {
+      tok = a.argmax_out[m];
+    }
+    a.next_ids[m] = tok;
+    const int np = a.pos[m] + 1;
+    a.pos[m] = np;
+    if (np < a.n_positions) a.token_log[(size_t)m * a.n_positions + np] = tok;
+  }
+}
+
+__global__ void argmax_rows_kernel(const float* logits, int m, int n, int* out) {
+  const int r = blockIdx.x;
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const float* row = logits + (size_t)r * n;
+  float bv = -INFINITY;
+  int bi = INT_MAX;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = row[i];
+    if (v > bv) {  // increasing i per thread: strict > keeps the lowest index
+      bv = v;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(FULL, bv, o);
+    int oi = __shfl_xor_sync(FULL, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) {
+      bv = ov;
+      bi = oi;
+    }
+  }
+  if ((threadIdx.x & 31) == 0) {
+    sv[threadIdx.x >> 5] = bv;
+    si[threadIdx.x >> 5] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+      if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) {
+        bv = sv[w];
+        bi = si[w];
+      }
+    out[r] = (bi == INT_MAX) ? 0 : bi;
+  }
+}
+
+// Order of f32::total_cmp as a signed key; larger key = larger value.
+__device__ __forceinline__ int total_key(float f) {
+  int b = __float_as_int(f);
+  return b ^ (int)(((unsigned)(b >> 31)) >> 1);
+}
+
+// k rounds of block-wide arg-max over the row held in shared memory. Candidates are the finite
+// logits; order is descending total_cmp, ties by lower index (the stable sort of sample_logits,
+// src/models/generation.rs:305-318). Rows shorter than k are padded with -inf / -1.
+__global__ void __launch_bounds__(1024) topk_rows_kernel(const float* logits, int m, int n, int k, float* vals,
+                                                         int* idx) {
+  extern __shared__ float4 dyn_smem4[];
+  int* keys = reinterpret_cast<int*>(dyn_smem4);  // [n] total-order keys, INT_MIN = removed
+  __shared__ int sk[32];
+  __shared__ int si[32];
+  __shared__ int win_i;
+  const int r = blockIdx.x;
+  const float* row = logits + (size_t)r * n;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = row[i];
+    keys[i] = isfinite(v) ? total_key(v) : INT_MIN;
+  }
+  __syncthreads();
+  for (int round = 0; round < k; ++round) {
+    int bk = INT_MIN, bi = INT_MAX;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      int kk = keys[i];
+      if (kk > bk) {
+        bk = kk;
+        bi = i;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      int ok = __shfl_xor_sync(FULL, bk, o);
+      int oi = __shfl_xor_sync(FULL, bi, o);
+      if (ok > bk || (ok == bk && oi < bi)) {
+        bk = ok;
+        bi = oi;
+      }
+    }
+    if ((threadIdx.x & 31) == 0) {
+      sk[threadIdx.x >> 5] = bk;
+      si[threadIdx.x >> 5] = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+        if (sk[w] > bk || (sk[w] == bk && si[w] < bi)) {
+          bk = sk[w];
+          bi = si[w];
+        }
+      if (bk == INT_MIN) {
+        vals[(size_t)r * k + round] = -INFINITY;
+        idx[(size_t)r * k + round] = -1;
+        win_i = -1;
+      } else {
+        vals[(size_t)r * k + round] = row[bi];
+        idx[(size_t)r * k + round] = bi;
+        win_i = bi;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && win_i >= 0) keys[win_i] = INT_MIN;
+    __syncthreads();
+  }
+}
+
+// ------------------------------------------------------------------ launch helper
+template <typename... KArgs, typename... Args>
+cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool pdl,
+                   Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+template <int MT, int EPI>
+cudaError_t launch_linear_mt(const LinearArgs& a, bool ln, int grid, bool pdl, cudaStream_t s) {
+  if (ln) {
+    size_t smem = (size_t)MT * a.k * sizeof(float);
+    auto kern = linear_decode_kernel<MT, EPI, true>;
+    return launch(kern, dim3(grid), dim3(LIN_THREADS), smem, s, pdl, a);
+  }
+  return launch(linear_decode_kernel<MT, EPI, false>, dim3(grid), dim3(LIN_THREADS), 0, s, pdl, a);
+}
+
+template <int EPI>
+cudaError_t launch_linear_epi(const LinearArgs& a, bool ln, int mt, int grid, bool pdl, cudaStream_t s) {
+  switch (mt) {
+    case 1: return launch_linear_mt<1, EPI>(a, ln, grid, pdl, s);
+    case 2: return launch_linear_mt<2, EPI>(a, ln, grid, pdl, s);
+    case 4: return launch_linear_mt<4, EPI>(a, ln, grid, pdl, s);
+    default: return launch_linear_mt<8, EPI>(a, ln, grid, pdl, s);
+  }
+}
+
+int g_num_sms = 0;
+int num_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+}  // namespace
+
+int linear_decode_grid(int n, int sms) {
+  int groups = (n + LIN_ROWS - 1) / LIN_ROWS;
+  int cap = sms * 8;  // eight 128-thread CTAs per SM keep >= 32 KB of weight loads in flight
+  return groups < cap ? groups : cap;
+}
+
+cudaError_t launch_linear_decode(const LinearArgs& a, int epilogue, bool pdl, cudaStream_t s, int* grid_out) {
+  if (a.k % 4 != 0 || (a.ln_g && (a.m > 8 || a.k > 2048)) || (a.part_val && a.m > 8)) {
+    if (a.ln_g || a.part_val) return cudaErrorInvalidValue;  // callers un-fuse these cases
+    size_t total = (size_t)a.m * a.n;
+    if (grid_out) *grid_out = 0;
+    return launch(linear_generic_kernel, dim3((unsigned)((total + 127) / 128)), dim3(128), 0, s, pdl, a, epilogue);
+  }
+  int mt = a.m <= 1 ? 1 : a.m <= 2 ? 2 : a.m <= 4 ? 4 : 8;
+  int grid = linear_decode_grid(a.n, num_sms());
+  if (grid_out) *grid_out = grid;
+  bool ln = a.ln_g != nullptr;
+  switch (epilogue) {
+    case EPI_GELU: return launch_linear_epi<EPI_GELU>(a, ln, mt, grid, pdl, s);
+    case EPI_RESID: return launch_linear_epi<EPI_RESID>(a, ln, mt, grid, pdl, s);
+    default: return launch_linear_epi<EPI_NONE>(a, ln, mt, grid, pdl, s);
+  }
+}
+
+cudaError_t launch_embed(const float* wte, const float* wpe, const int* ids, const int* pos, float* out, int rows,
+                         int c, bool pdl, cudaStream_t s) {
+  return launch(embed_kernel, dim3(rows), dim3(256), 0, s, pdl, wte, wpe, ids, pos, out, rows, c);
+}
+
+cudaError_t launch_layernorm_rows(const float* x, const float* g, const float* b, float eps, float* out, int rows,
+                                  int c, bool pdl, cudaStream_t s) {
+  return launch(layernorm_rows_kernel, dim3((rows + 3) / 4), dim3(128), 0, s, pdl, x, g, b, eps, out, rows, c);
+}
+
+cudaError_t launch_gemm_f32(const LinearArgs& a, int epilogue, cudaStream_t s) {
+  if (a.k % 4 != 0) {
+    size_t total = (size_t)a.m * a.n;
+    return launch(linear_generic_kernel, dim3((unsigned)((total + 127) / 128)), dim3(128), 0, s, false, a, epilogue);
+  }
+  dim3 grid((a.n + GB - 1) / GB, (a.m + GB - 1) / GB);
+  return launch(gemm_f32_kernel, grid, dim3(256), 0, s, false, a, epilogue);
+}
+
+cudaError_t launch_transpose(const float* src, float* dst, int in_f, int out_f, cudaStream_t s) {
+  dim3 grid((out_f + 31) / 32, (in_f + 31) / 32);
+  transpose_kernel<<<grid, dim3(32, 8), 0, s>>>(src, dst, in_f, out_f);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_decode_attention(const DecodeAttnArgs& a, bool pdl, cudaStream_t s) {
+  const int max_keys = a.kv.pages_per_seq * a.kv.page_tokens;
+  if (a.kv.head_dim == 64) {
+    size_t smem = (size_t)((max_keys + a.splits - 1) / a.splits + 1) * sizeof(float);
+    smem = (smem + 15) & ~(size_t)15;
+    auto kern = decode_attention_kernel<64>;
+    if (smem > 64 * 1024) return cudaErrorInvalidValue;
+    return launch(kern, dim3(a.kv.n_head, a.batch, a.splits), dim3(ATT_THREADS), smem, s, pdl, a);
+  }
+  size_t smem = ((size_t)max_keys * sizeof(float) + 15) & ~(size_t)15;
+  auto kern = decode_attention_generic_kernel;
+  if (smem > 64 * 1024) return cudaErrorInvalidValue;
+  return launch(kern, dim3(a.kv.n_head, a.batch, 1), dim3(ATT_THREADS), smem, s, pdl, a);
+}
+
+cudaError_t launch_prefill_attention(const PrefillAttnArgs& a, cudaStream_t s) {
+  if (a.head_dim == 64) {
+    dim3 grid(a.n_head, (a.max_len + PA_Q - 1) / PA_Q, a.batch);
+    prefill_attention_kernel<64><<<grid, 128, 0, s>>>(a);
+  } else {
+    if (a.head_dim > 128) return cudaErrorInvalidValue;
+    dim3 grid(a.n_head, (a.max_len + 63) / 64, a.batch);
+    prefill_attention_generic_kernel<<<grid, 64, 0, s>>>(a);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_kv_scatter(const float* qkv, const int* row_slot, const int* row_pos, float* kv_pool,
+                              const int* page_table, KvLayout kv, int rows, cudaStream_t s) {
+  kv_scatter_kernel<<<rows, 256, 0, s>>>(qkv, row_slot, row_pos, kv_pool, page_table, kv, rows);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_kv_gather(const float* kv_pool, const int* page_table, KvLayout kv, int slot, int seq_len,
+                             int n_positions, float* keys, float* values, cudaStream_t s) {
+  kv_gather_kernel<<<296, 256, 0, s>>>(kv_pool, page_table, kv, slot, seq_len, n_positions, keys, values);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gather_rows(const float* src, const int* rows, float* dst, int n, int c, cudaStream_t s) {
+  gather_rows_kernel<<<n, 256, 0, s>>>(src, rows, dst, n, c);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_finalize(const FinalizeArgs& a, bool pdl, cudaStream_t s) {
+  return launch(finalize_kernel, dim3(a.m), dim3(256), 0, s, pdl, a);
+}
+
+cudaError_t init_kernel_attributes() {
+  const int ln_smem = 8 * 2048 * (int)sizeof(float);
+  cudaError_t e;
+#define PG_SET(kern, bytes)                                                                 \
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(bytes)); \
+  if (e != cudaSuccess) return e;
+  PG_SET((linear_decode_kernel<8, EPI_NONE, true>), ln_smem)
+  PG_SET((linear_decode_kernel<8, EPI_GELU, true>), ln_smem)
+  PG_SET((linear_decode_kernel<8, EPI_RESID, true>), ln_smem)
+  PG_SET((linear_decode_kernel<4, EPI_NONE, true>), ln_smem / 2)
+  PG_SET((linear_decode_kernel<4, EPI_GELU, true>), ln_smem / 2)
+  PG_SET((linear_decode_kernel<4, EPI_RESID, true>), ln_smem / 2)
+  PG_SET(decode_attention_kernel<64>, 64 * 1024)
+  PG_SET(decode_attention_generic_kernel, 64 * 1024)
+  PG_SET(topk_rows_kernel, 227 * 1024)
+#undef PG_SET
+  return cudaSuccess;
+}
+
+cudaError_t launch_argmax_rows(const float* logits, int m, int n, int* out, cudaStream_t s) {
+  argmax_rows_kernel<<<m, 1024, 0, s>>>(logits, m, n, out);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_topk_rows(const float* logits, int m, int n, int k, float* vals, int* idx, cudaStream_t s) {
+  size_t smem = ((size_t)n * sizeof(int) + 15) & ~(size_t)15;
+  if (smem > 227 * 1024) return cudaErrorInvalidValue;
+  topk_rows_kernel<<<m, 1024, smem, s>>>(logits, m, n, k, vals, idx);
+  return cudaGetLastError();
+}
+
+}  // namespace pg

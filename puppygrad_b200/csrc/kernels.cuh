@@ -1,0 +1,101 @@
+// Launch wrappers of the sm_100a kernels (definitions in kernels.cu). Pointers are device
+// pointers. Every wrapper returns the cudaError_t of its launch.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace pg {
+
+enum Epilogue { EPI_NONE = 0, EPI_GELU = 1, EPI_RESID = 2 };
+
+// KV page pool of one layer: [page][2 (K,V)][head][page_tokens][head_dim] floats.
+struct KvLayout {
+  int n_head, head_dim, page_tokens, pages_per_seq;  // pages_per_seq = ceil(n_positions / page_tokens)
+};
+
+struct LinearArgs {
+  const float* w;      // [n, k] row-major ([out, in])
+  const float* bias;   // [n] or nullptr
+  const float* x;      // [m, k]
+  float* out;          // [m, n]
+  const float* resid;  // [m, n], EPI_RESID only (may alias out)
+  const float* ln_g;   // LayerNorm gamma/beta over k, or nullptr for no LayerNorm prologue
+  const float* ln_b;
+  float eps;
+  int m, n, k;
+  float* part_val;     // optional per-CTA argmax partials: [m][grid] (lm_head)
+  int* part_idx;
+};
+
+// Decode-time linear for a few activation rows (m <= 64): streams W once per 8 rows of x with
+// 128-bit loads, optional fused LayerNorm prologue (m <= 8, k <= 2048) and bias/GELU/residual
+// epilogue. `pdl` launches with programmatic dependent launch. Returns the grid size used in
+// *grid_out (the stride of part_val / part_idx).
+cudaError_t launch_linear_decode(const LinearArgs& a, int epilogue, bool pdl, cudaStream_t s, int* grid_out);
+int linear_decode_grid(int n, int num_sms);
+
+// out[r, :] = wte[ids[r]] + wpe[pos[r]]
+cudaError_t launch_embed(const float* wte, const float* wpe, const int* ids, const int* pos, float* out,
+                         int rows, int c, bool pdl, cudaStream_t s);
+// out = LayerNorm(x) row-wise
+cudaError_t launch_layernorm_rows(const float* x, const float* g, const float* b, float eps, float* out,
+                                  int rows, int c, bool pdl, cudaStream_t s);
+// General FP32 GEMM out[m,n] = x[m,k] . w[n,k]^T (+bias)(+GELU | +resid), CUDA-core FMA.
+cudaError_t launch_gemm_f32(const LinearArgs& a, int epilogue, cudaStream_t s);
+// dst[o, i] = src[i, o]
+cudaError_t launch_transpose(const float* src, float* dst, int in_f, int out_f, cudaStream_t s);
+
+struct DecodeAttnArgs {
+  const float* qkv;       // [batch, 3c]
+  float* out;             // [batch, c]
+  float* kv_pool;         // this layer's page pool
+  const int* page_table;  // [max_batch, pages_per_seq]
+  const int* pos;         // [batch]: position of the new token (= keys already cached)
+  float* part;            // split-K partials [batch*head][splits][head_dim + 2]
+  unsigned* counters;     // [batch*head], zero between launches
+  KvLayout kv;
+  int batch, splits;
+};
+// Causal attention of one new token per sequence over the paged cache; also appends the new K,V.
+cudaError_t launch_decode_attention(const DecodeAttnArgs& a, bool pdl, cudaStream_t s);
+
+struct PrefillAttnArgs {
+  const float* qkv;      // [rows, 3c], sequences concatenated
+  float* out;            // [rows, c]
+  const int* seq_start;  // [batch + 1] row offsets
+  int n_head, head_dim, batch, max_len;
+};
+cudaError_t launch_prefill_attention(const PrefillAttnArgs& a, cudaStream_t s);
+// Copies K,V of every prompt row into the paged cache.
+cudaError_t launch_kv_scatter(const float* qkv, const int* row_slot, const int* row_pos, float* kv_pool,
+                              const int* page_table, KvLayout kv, int rows, cudaStream_t s);
+// Reads one slot's K,V of one layer back in [head][n_positions][head_dim] order.
+cudaError_t launch_kv_gather(const float* kv_pool, const int* page_table, KvLayout kv, int slot, int seq_len,
+                             int n_positions, float* keys, float* values, cudaStream_t s);
+// dst[r, :] = src[rows[r], :]
+cudaError_t launch_gather_rows(const float* src, const int* rows, float* dst, int n, int c, cudaStream_t s);
+
+// End of a decode step. Reduces the per-CTA argmax partials of the lm_head into argmax_out[m]
+// (when part_val is nullptr, argmax_out already holds the row argmax), feeds the token back as
+// next_ids[m], advances pos[m] by one and records the token at its position in
+// token_log[m * n_positions + new_pos].
+struct FinalizeArgs {
+  const float* part_val;
+  const int* part_idx;
+  int parts, m;
+  int* argmax_out;  // [m]
+  int* next_ids;    // [m]
+  int* pos;         // [m]
+  int* token_log;   // [m][n_positions]
+  int n_positions;
+};
+// Sets the opt-in shared-memory limits of the kernels; once per device before the first launch.
+cudaError_t init_kernel_attributes();
+cudaError_t launch_finalize(const FinalizeArgs& a, bool pdl, cudaStream_t s);
+// Plain argmax over rows of a [m, n] matrix (first strict maximum).
+cudaError_t launch_argmax_rows(const float* logits, int m, int n, int* out, cudaStream_t s);
+// k largest per row, descending, ties by lower index; k <= 64.
+cudaError_t launch_topk_rows(const float* logits, int m, int n, int k, float* vals, int* idx, cudaStream_t s);
+
+}  // namespace pg

@@ -1,0 +1,122 @@
+"""Sampling configuration and the logits sampler, mirroring puppygrad src/models/generation.rs.
+The arithmetic runs in the native library (csrc/sampler.cpp); nothing here touches the GPU."""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import _native as N
+from .errors import Gpt2Error, check
+
+GPT2_EOS_TOKEN_ID = 50_256  # src/models/gpt2/options.rs:8
+
+
+@dataclass
+class TextGenerationConfig:
+    """generation.rs:60-116; defaults of TextGenerationConfig::new."""
+    max_new_tokens: int = 32
+    eos_token_id: Optional[int] = None
+    temperature: float = 0.0
+    top_p: Optional[float] = None
+    top_k: Optional[int] = None
+    seed: int = 299_792_458
+    repeat_penalty: float = 1.0
+    repeat_last_n: int = 128
+
+    def with_eos_token_id(self, eos_token_id: Optional[int]) -> "TextGenerationConfig":
+        self.eos_token_id = eos_token_id
+        return self
+
+    def to_native(self) -> N.PgGenerationConfig:
+        return N.PgGenerationConfig(self.max_new_tokens, -1 if self.eos_token_id is None else self.eos_token_id,
+                                    self.temperature, -1.0 if self.top_p is None else self.top_p,
+                                    -1 if self.top_k is None else self.top_k, self.seed, self.repeat_penalty,
+                                    self.repeat_last_n)
+
+    def validate(self) -> None:
+        g = self.to_native()
+        check(N.lib.pg_generation_config_validate(C.byref(g)))
+
+
+def gpt2_generation_config(max_new_tokens: int) -> TextGenerationConfig:
+    """Gpt2GenerationConfig::new (options.rs:156-162): EOS 50256."""
+    return TextGenerationConfig(max_new_tokens).with_eos_token_id(GPT2_EOS_TOKEN_ID)
+
+
+@dataclass
+class GenerationStats:
+    """generation.rs:129-180"""
+    prompt_tokens: int = 0
+    generated_tokens: int = 0
+    tokenize_time: float = 0.0
+    prefill_time: float = 0.0
+    decode_time: float = 0.0
+    total_generation_time: float = 0.0
+    first_token_time: Optional[float] = None
+
+    @staticmethod
+    def _rate(tokens: int, seconds: float) -> float:
+        return 0.0 if seconds == 0.0 else tokens / seconds
+
+    def total_model_tokens(self) -> int:
+        return self.prompt_tokens + self.generated_tokens
+
+    def prefill_tokens_per_second(self) -> float:
+        return self._rate(self.prompt_tokens, self.prefill_time)
+
+    def decode_tokens_per_second(self) -> float:
+        return self._rate(self.generated_tokens, self.decode_time)
+
+    def total_tokens_per_second(self) -> float:
+        return self._rate(self.total_model_tokens(), self.total_generation_time)
+
+    def average_decode_token_time(self) -> Optional[float]:
+        if self.generated_tokens == 0:
+            return None
+        return self.decode_time / self.generated_tokens
+
+
+def argmax_logits(values: Sequence[float]) -> int:
+    """generation.rs:269-279"""
+    v = np.ascontiguousarray(values, np.float32)
+    return int(N.lib.pg_argmax_logits(v.ctypes.data_as(C.POINTER(C.c_float)), v.size))
+
+
+class LogitsSampler:
+    """generation.rs:209-241"""
+
+    def __init__(self, seed: int):
+        self._h = C.c_void_p()
+        check(N.lib.pg_sampler_new(seed, C.byref(self._h)))
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            N.lib.pg_sampler_free(self._h)
+            self._h = None
+
+    def select_next_token(self, logits, history, config: TextGenerationConfig) -> int:
+        v = np.ascontiguousarray(logits, np.float32)
+        h = np.ascontiguousarray(history, np.uint64)
+        g = config.to_native()
+        out = C.c_uint64()
+        check(N.lib.pg_sampler_select_next_token(self._h, v.ctypes.data_as(C.POINTER(C.c_float)), v.size,
+                                                 h.ctypes.data_as(C.POINTER(C.c_uint64)), h.size, C.byref(g),
+                                                 C.byref(out)))
+        return int(out.value)
+
+    def select_from_topk(self, vals, idx, config: TextGenerationConfig) -> int:
+        v = np.ascontiguousarray(vals, np.float32)
+        i = np.ascontiguousarray(idx, np.int32)
+        g = config.to_native()
+        out = C.c_uint64()
+        check(N.lib.pg_sampler_select_from_topk(self._h, v.ctypes.data_as(C.POINTER(C.c_float)),
+                                                i.ctypes.data_as(C.POINTER(C.c_int32)), v.size, C.byref(g),
+                                                C.byref(out)))
+        return int(out.value)
+
+
+__all__ = ["TextGenerationConfig", "GenerationStats", "LogitsSampler", "argmax_logits", "Gpt2Error",
+           "gpt2_generation_config", "GPT2_EOS_TOKEN_ID"]

@@ -1,0 +1,327 @@
+"""Host-side mirror of the reference's GPT-2 model API over the CUDA library.
+
+Names, argument meaning and error behaviour follow puppygrad src/models/gpt2/rust.rs:
+`Gpt2Config` (31-100), `Gpt2Model` (798-1027), `Gpt2KvCache` (178-249), `Gpt2Output` (150-175) and
+the `AutoregressiveDecoder` impl (1253-1277). Batched calls (`*_batch`, `decode_greedy`) are
+additions; with one sequence they reduce to the reference calls.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence
+
+import numpy as np
+
+from . import _native as N
+from .errors import Gpt2Error, check
+from .generation import GenerationStats, TextGenerationConfig
+
+_MATH = {"fp32": 0, "tf32x3": 1, "tf32": 2, "bf16": 3}
+
+
+@dataclass
+class Gpt2Config:
+    vocab_size: int
+    n_positions: int
+    n_embd: int
+    n_layer: int
+    n_head: int
+    n_inner: int = 0
+    layer_norm_epsilon: float = 1e-5
+
+    def __post_init__(self):
+        if not self.n_inner:
+            self.n_inner = 4 * self.n_embd
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "Gpt2Config":
+        return cls(d["vocab_size"], d["n_positions"], d["n_embd"], d["n_layer"], d["n_head"],
+                   d.get("n_inner") or 0, d.get("layer_norm_epsilon", 1e-5))
+
+    @classmethod
+    def from_json(cls, path: str) -> "Gpt2Config":
+        """load_config, rust.rs:696-711"""
+        c = N.PgConfig()
+        check(N.lib.pg_config_load_json(str(path).encode(), C.byref(c)))
+        return cls._from_native(c)
+
+    @classmethod
+    def _from_native(cls, c: N.PgConfig) -> "Gpt2Config":
+        return cls(c.vocab_size, c.n_positions, c.n_embd, c.n_layer, c.n_head, c.n_inner, c.layer_norm_epsilon)
+
+    def to_native(self) -> N.PgConfig:
+        return N.PgConfig(self.vocab_size, self.n_positions, self.n_embd, self.n_layer, self.n_head,
+                          self.n_inner, self.layer_norm_epsilon)
+
+    def validate(self) -> None:
+        c = self.to_native()
+        check(N.lib.pg_config_validate(C.byref(c)))
+
+    def head_dim(self) -> int:
+        return self.n_embd // self.n_head
+
+
+@dataclass
+class Gpt2CudaConfig:
+    """Knobs of this backend; stands where `Gpt2RustConfig` stands in the reference
+    (src/models/gpt2/options.rs:52-96)."""
+    device: int = 0
+    math_mode: str = "fp32"
+    page_tokens: int = 32
+    use_graphs: bool = True
+    attn_splits: int = 0
+
+    def to_native(self) -> N.PgBackendConfig:
+        if self.math_mode not in _MATH:
+            raise Gpt2Error("InvalidConfig", f"cuda math_mode {self.math_mode!r} must be one of {sorted(_MATH)}")
+        b = N.PgBackendConfig()
+        b.device, b.math_mode, b.page_tokens = self.device, _MATH[self.math_mode], self.page_tokens
+        b.use_graphs, b.attn_splits = (1 if self.use_graphs else 2), self.attn_splits
+        return b
+
+
+@dataclass
+class Gpt2Output:
+    logits: np.ndarray  # [seq_len, vocab_size]
+    seq_len: int
+    vocab_size: int
+
+    def logits_for_position(self, pos: int) -> np.ndarray:
+        if pos >= self.seq_len:
+            raise Gpt2Error("InvalidInput", f"position {pos} out of range for seq_len {self.seq_len}")
+        return self.logits[pos]
+
+    def last_logits(self) -> np.ndarray:
+        if self.seq_len == 0:
+            raise Gpt2Error("InvalidInput", "empty sequence")
+        return self.logits_for_position(self.seq_len - 1)
+
+
+def _i32(a) -> np.ndarray:
+    arr = np.asarray(a)
+    if arr.size and (arr.min() < -2**31 or arr.max() >= 2**31):
+        # keep the id visible to the range check in the library's message
+        arr = np.clip(arr, -1, 2**31 - 1)
+    return np.ascontiguousarray(arr, np.int32)
+
+
+def _ip(a: np.ndarray):
+    return a.ctypes.data_as(C.POINTER(C.c_int32))
+
+
+def _fp(a: Optional[np.ndarray]):
+    return a.ctypes.data_as(C.POINTER(C.c_float)) if a is not None else None
+
+
+class Gpt2KvCache:
+    """Paged device-resident KV cache for `max_batch` independent sequences."""
+
+    def __init__(self, model: "Gpt2Model", max_batch: int = 1):
+        self._h = C.c_void_p()
+        self.model = model
+        check(N.lib.pg_cache_new(model._h, max_batch, C.byref(self._h)))
+        self.max_batch = max_batch
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            N.lib.pg_cache_free(self._h)
+            self._h = None
+
+    def seq_len_of(self, slot: int) -> int:
+        out = C.c_uint64()
+        check(N.lib.pg_cache_seq_len(self._h, slot, C.byref(out)))
+        return int(out.value)
+
+    @property
+    def seq_len(self) -> int:
+        return self.seq_len_of(0)
+
+    @property
+    def max_seq_len(self) -> int:
+        return int(N.lib.pg_cache_max_seq_len(self._h))
+
+    def clear(self) -> None:
+        check(N.lib.pg_cache_clear(self._h))
+
+    def clear_slot(self, slot: int) -> None:
+        check(N.lib.pg_cache_clear_slot(self._h, slot))
+
+    def time_begin(self) -> None:
+        """Starts the device-side stopwatch on this cache's stream."""
+        check(N.lib.pg_cache_time_begin(self._h))
+
+    def time_end(self) -> float:
+        """Seconds of device time since `time_begin` (waits for the queued work)."""
+        out = C.c_double()
+        check(N.lib.pg_cache_time_end(self._h, C.byref(out)))
+        return float(out.value)
+
+    def kernel_launches(self) -> int:
+        return int(N.lib.pg_cache_kernel_launches(self._h))
+
+    def read_layer(self, layer: int, slot: int = 0):
+        """Keys and values in the reference layout [head][max_seq_len][head_dim]."""
+        cfg = self.model.config
+        n = cfg.n_positions * cfg.n_embd
+        k = np.empty(n, np.float32)
+        v = np.empty(n, np.float32)
+        check(N.lib.pg_cache_read_layer(self._h, slot, layer, _fp(k), _fp(v)))
+        shape = (cfg.n_head, cfg.n_positions, cfg.head_dim())
+        return k.reshape(shape), v.reshape(shape)
+
+
+class Gpt2Model:
+    def __init__(self, config, weights, cuda_config: Optional[Gpt2CudaConfig] = None):
+        """Gpt2Model::new_with_rust_config (rust.rs:803-825). `weights` maps Hugging Face tensor
+        names to float32 arrays (dense matrices `[in, out]`), or is the flat list in ABI order."""
+        from .synthetic import tensor_names
+        self.config = config if isinstance(config, Gpt2Config) else Gpt2Config.from_dict(config)
+        self.cuda_config = cuda_config or Gpt2CudaConfig()
+        if isinstance(weights, dict):
+            names = tensor_names({"n_layer": self.config.n_layer})
+            missing = [n for n in names if n not in weights]
+            if missing:
+                raise Gpt2Error("Asset", f"tensor {missing[0]} not found")
+            weights = [weights[n] for n in names]
+        tensors = [np.ascontiguousarray(t, np.float32).reshape(-1) for t in weights]
+        n = len(tensors)
+        ptrs = (C.POINTER(C.c_float) * n)(*[_fp(t) for t in tensors])
+        lens = np.array([t.size for t in tensors], np.uint64)
+        c, b = self.config.to_native(), self.cuda_config.to_native()
+        self._h = C.c_void_p()
+        check(N.lib.pg_model_from_host_weights(C.byref(c), ptrs, lens.ctypes.data_as(C.POINTER(C.c_uint64)), n,
+                                               C.byref(b), C.byref(self._h)))
+
+    @classmethod
+    def from_dir(cls, model_dir: str, cuda_config: Optional[Gpt2CudaConfig] = None) -> "Gpt2Model":
+        """The model half of Gpt2Runtime::from_dir_with_backend (rust.rs:382-396)."""
+        self = cls.__new__(cls)
+        self.cuda_config = cuda_config or Gpt2CudaConfig()
+        b = self.cuda_config.to_native()
+        self._h = C.c_void_p()
+        check(N.lib.pg_model_load_dir(str(model_dir).encode(), C.byref(b), C.byref(self._h)))
+        c = N.PgConfig()
+        check(N.lib.pg_model_config(self._h, C.byref(c)))
+        self.config = Gpt2Config._from_native(c)
+        return self
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            N.lib.pg_model_free(self._h)
+            self._h = None
+
+    # ---- AutoregressiveDecoder (rust.rs:1253-1277)
+    def max_context_len(self) -> int:
+        return int(N.lib.pg_model_max_context_len(self._h))
+
+    def new_cache(self) -> Gpt2KvCache:
+        return self.new_kv_cache()
+
+    def select_next_token(self, logits) -> int:
+        from .generation import argmax_logits
+        return argmax_logits(logits)
+
+    def weight_bytes_per_step(self) -> int:
+        return int(N.lib.pg_model_weight_bytes_per_step(self._h))
+
+    # ---- reference single-sequence API
+    def new_kv_cache(self, max_batch: int = 1) -> Gpt2KvCache:
+        return Gpt2KvCache(self, max_batch)
+
+    def forward(self, input_ids: Sequence[int]) -> Gpt2Output:
+        ids = _i32(input_ids)
+        v = self.config.vocab_size
+        out = np.empty((max(ids.size, 1), v), np.float32)
+        check(N.lib.pg_forward(self._h, _ip(ids), ids.size, _fp(out)))
+        return Gpt2Output(out, ids.size, v)
+
+    def generate_greedy(self, input_ids: Sequence[int], max_new_tokens: int) -> List[int]:
+        ids = _i32(input_ids)
+        out = np.empty(ids.size + max_new_tokens + 1, np.int32)
+        n = C.c_uint64()
+        check(N.lib.pg_generate_greedy(self._h, _ip(ids), ids.size, max_new_tokens, _ip(out), C.byref(n)))
+        return [int(t) for t in out[:n.value]]
+
+    def prefill(self, input_ids: Sequence[int], cache: Gpt2KvCache) -> np.ndarray:
+        ids = _i32(input_ids)
+        lens = np.array([ids.size], np.int32)
+        out = np.empty(self.config.vocab_size, np.float32)
+        check(N.lib.pg_prefill(self._h, cache._h, _ip(ids), _ip(lens), 1, _fp(out), None))
+        return out
+
+    def forward_one(self, token_id: int, cache: Gpt2KvCache) -> np.ndarray:
+        ids = _i32([token_id])
+        out = np.empty(self.config.vocab_size, np.float32)
+        check(N.lib.pg_forward_one(self._h, cache._h, _ip(ids), 1, _fp(out), None, None, None, 0))
+        return out
+
+    def generate_greedy_cached(self, input_ids: Sequence[int], max_new_tokens: int) -> List[int]:
+        return self.stream_greedy_tokens(input_ids, max_new_tokens, None)
+
+    def stream_greedy_tokens(self, input_ids: Sequence[int], max_new_tokens: int,
+                             on_token: Optional[Callable[[int], Optional[bool]]] = None) -> List[int]:
+        """rust.rs:1016-1027. `on_token` may return True to abort (the closure returning Err)."""
+        ids = _i32(input_ids)
+        out = np.empty(ids.size + max_new_tokens + 1, np.int32)
+        n = C.c_uint64()
+        cb = N.TOKEN_CALLBACK(lambda tok, _u: int(bool(on_token(int(tok))))) if on_token else N.TOKEN_CALLBACK()
+        check(N.lib.pg_stream_greedy_tokens(self._h, _ip(ids), ids.size, max_new_tokens, cb, None, _ip(out),
+                                            C.byref(n)))
+        return [int(t) for t in out[:n.value]]
+
+    def generate_with_config(self, input_ids: Sequence[int], config: TextGenerationConfig,
+                             on_token: Optional[Callable[[int], Optional[bool]]] = None):
+        """The token-id loop of Gpt2Runtime::stream_token_ids_with_stats (rust.rs:548-635).
+        Returns (generated ids, GenerationStats)."""
+        ids = _i32(input_ids)
+        g = config.to_native()
+        out = np.empty(max(config.max_new_tokens, 1), np.int32)
+        n = C.c_uint64()
+        st = N.PgGenerationStats()
+        cb = N.TOKEN_CALLBACK(lambda tok, _u: int(bool(on_token(int(tok))))) if on_token else N.TOKEN_CALLBACK()
+        check(N.lib.pg_generate_with_config(self._h, _ip(ids), ids.size, C.byref(g), cb, None, _ip(out),
+                                            C.byref(n), C.byref(st)))
+        stats = GenerationStats(st.prompt_tokens, st.generated_tokens, st.tokenize_time, st.prefill_time,
+                                st.decode_time, st.total_generation_time,
+                                None if st.first_token_time < 0 else st.first_token_time)
+        return [int(t) for t in out[:n.value]], stats
+
+    # ---- batched additions
+    def prefill_batch(self, prompts: Sequence[Sequence[int]], cache: Gpt2KvCache, want_logits: bool = False):
+        lens = np.array([len(p) for p in prompts], np.int32)
+        ids = _i32(np.concatenate([np.asarray(p, np.int64) for p in prompts]) if len(prompts) else [])
+        b = len(prompts)
+        logits = np.empty((b, self.config.vocab_size), np.float32) if want_logits else None
+        am = np.empty(b, np.int32)
+        check(N.lib.pg_prefill(self._h, cache._h, _ip(ids), _ip(lens), b, _fp(logits), _ip(am)))
+        return logits, am
+
+    def forward_one_batch(self, token_ids: Sequence[int], cache: Gpt2KvCache, want_logits: bool = False,
+                          top_k: int = 0):
+        ids = _i32(token_ids)
+        b = ids.size
+        logits = np.empty((b, self.config.vocab_size), np.float32) if want_logits else None
+        am = np.empty(b, np.int32)
+        tv = np.empty((b, top_k), np.float32) if top_k else None
+        ti = np.empty((b, top_k), np.int32) if top_k else None
+        check(N.lib.pg_forward_one(self._h, cache._h, _ip(ids), b, _fp(logits), _ip(am), _fp(tv),
+                                   _ip(ti) if top_k else None, top_k))
+        return logits, am, tv, ti
+
+    def profile_forward_one(self, token_ids: Sequence[int], cache: Gpt2KvCache) -> dict:
+        """One decode step timed per operation class (Gpt2OperationProfile, rust.rs:336-347).
+        Returns {bucket: (seconds, kernel launches)}."""
+        ids = _i32(token_ids)
+        p = N.PgOperationProfile()
+        check(N.lib.pg_profile_forward_one(self._h, cache._h, _ip(ids), ids.size, C.byref(p)))
+        names = ("layer_norm", "qkv_projection", "attention", "attention_projection", "mlp_fc_projection",
+                 "mlp_projection", "final_logits", "other")
+        return {n: (getattr(p, n), int(p.launches[i])) for i, n in enumerate(names)}
+
+    def decode_greedy(self, first_ids: Sequence[int], cache: Gpt2KvCache, steps: int) -> np.ndarray:
+        """`steps` greedy steps with the token fed back on the device; returns [steps, batch]."""
+        ids = _i32(first_ids)
+        out = np.empty((steps, ids.size), np.int32)
+        check(N.lib.pg_decode_greedy(self._h, cache._h, _ip(ids), ids.size, steps, _ip(out)))
+        return out
