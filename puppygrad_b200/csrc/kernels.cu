@@ -1054,7 +1054,7 @@ cudaError_t init_kernel_attributes() {
   PG_SET((linear_decode_kernel<4, EPI_RESID, true>), ln_smem / 2)
   PG_SET(decode_attention_kernel<64>, 64 * 1024)
   PG_SET(decode_attention_generic_kernel, 64 * 1024)
-  PG_SET(topk_rows_kernel, 227 * 1024)
+  PG_SET(topk_rows_kernel, 220 * 1024)
 #undef PG_SET
   return cudaSuccess;
 }
@@ -1066,7 +1066,7 @@ cudaError_t launch_argmax_rows(const float* logits, int m, int n, int* out, cuda
 
 cudaError_t launch_topk_rows(const float* logits, int m, int n, int k, float* vals, int* idx, cudaStream_t s) {
   size_t smem = ((size_t)n * sizeof(int) + 15) & ~(size_t)15;
-  if (smem > 227 * 1024) return cudaErrorInvalidValue;
+  if (smem > 220 * 1024) return cudaErrorInvalidValue;
   topk_rows_kernel<<<m, 1024, smem, s>>>(logits, m, n, k, vals, idx);
   return cudaGetLastError();
 }
