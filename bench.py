@@ -217,9 +217,9 @@ def run_ours(args):
     cfg = synthetic.preset(MODEL)
     weights = synthetic.random_init_weights(cfg, WEIGHT_SEED)
     model = pg.Gpt2Model(cfg, weights, pg.Gpt2CudaConfig(device=local))
-    cache = model.new_kv_cache(max_batch=SEQS_PER_GPU)
-    prompts = make_prompts(cfg, rank)
-    B, K, W = SEQS_PER_GPU, args.steps, args.warmup
+    cache = model.new_kv_cache(max_batch=args.seqs)
+    prompts = make_prompts(cfg, rank)[:args.seqs]
+    B, K, W = args.seqs, args.steps, args.warmup
     if PROMPT_LEN + W + K + 1 > cfg["n_positions"]:
         raise SystemExit("steps + warmup exceed the context window")
 
@@ -246,6 +246,14 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     sec_max = float(t.item())
     value = world * B * K / sec_max
+    if args.skip_extras:  # profiling runs: only the timed decode loop
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K,
+                              "warmup": W, "ms_per_step": sec_max / K * 1e3, "seqs_per_gpu": B,
+                              "gpu_launches": int(launches)}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- end to end through the public API: host token ids in, host argmax out, every step
     _, cur = model.prefill_batch(prompts, cache)
@@ -331,6 +339,10 @@ def main():
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--seqs", type=int, default=SEQS_PER_GPU,
+                    help="sequences per GPU (default 64, the benchmark workload; smaller for profiler captures)")
+    ap.add_argument("--skip-extras", action="store_true",
+                    help="only the device-timed decode loop (no e2e, per-op profile, CPU baseline)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
