@@ -216,7 +216,7 @@ def run_ours(args):
 
     cfg = synthetic.preset(MODEL)
     weights = synthetic.random_init_weights(cfg, WEIGHT_SEED)
-    model = pg.Gpt2Model(cfg, weights, pg.Gpt2CudaConfig(device=local))
+    model = pg.Gpt2Model(cfg, weights, pg.Gpt2CudaConfig(device=local, math_mode=args.math))
     cache = model.new_kv_cache(max_batch=args.seqs)
     prompts = make_prompts(cfg, rank)[:args.seqs]
     B, K, W = args.seqs, args.steps, args.warmup
@@ -312,6 +312,8 @@ def run_ours(args):
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"gpt2-{MODEL} fp32, {B} sequences per GPU, {PROMPT_LEN}-token prompts, "
                                    f"greedy decode; step = one batched decode step ({B} tokens per GPU)",
+                       "linears": ("fp32 weights and activations; products as 3xTF32 on tcgen05 tensor cores, "
+                                   "FP32 accumulate" if args.math == "tf32x3" else "fp32 CUDA-core FMA"),
                        "l2": "inputs larger than L2 (1.4 GB weights + KV per step)", "parallelism": f"replicas x{world}"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
             "gpu_launches": int(launches),
@@ -341,6 +343,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seqs", type=int, default=SEQS_PER_GPU,
                     help="sequences per GPU (default 64, the benchmark workload; smaller for profiler captures)")
+    ap.add_argument("--math", default="tf32x3", choices=["fp32", "tf32x3"],
+                    help="arithmetic of the batched decode linears: fp32 = CUDA-core FMA, tf32x3 = three TF32 "
+                         "tensor-core products with FP32 accumulation (FP32-grade, token-exact against the oracle)")
     ap.add_argument("--skip-extras", action="store_true",
                     help="only the device-timed decode loop (no e2e, per-op profile, CPU baseline)")
     args = ap.parse_args()

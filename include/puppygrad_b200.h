@@ -210,6 +210,16 @@ int pg_cache_time_end(pg_cache* cache, double* seconds);
 /* Kernels launched so far by decode steps on this cache. No reference counterpart. */
 uint64_t pg_cache_kernel_launches(const pg_cache* cache);
 
+/* One linear on host buffers, out[m, n] = x[m, k] . w[n, k]^T (+ bias[n]) then epilogue
+ * (0 none, 1 tanh-GELU, 2 out = resid + value): transposed_dense_projection_into,
+ * src/models/cpu.rs:58-75, with gelu_in_place / add_in_place (cpu.rs:145-171) fused. `w` is
+ * already [out, in]. math_mode selects the kernel family (pg_math_mode; tf32x3 needs m <= 64,
+ * the tensor-core modes need k % 32 == 0). With reps > 0 the kernel is launched reps more times,
+ * L2 flushed before each, and *seconds_per_launch receives the mean device time. */
+int pg_op_linear(const float* x, const float* w, const float* bias, const float* resid, int32_t m,
+                 int32_t n, int32_t k, int32_t epilogue, int32_t math_mode, int32_t device,
+                 int32_t reps, float* out, double* seconds_per_launch);
+
 /* ------------------------------------------------------------------ generation loops */
 /* non-zero return aborts generation (the closure returning Err in the reference) */
 typedef int (*pg_token_callback)(uint64_t token_id, void* user);

@@ -1,0 +1,612 @@
+// Tensor-core GEMMs for sm_100a: tcgen05.mma with accumulators in tensor memory, operands staged
+// by TMA (plain per-CTA tiled loads, 128-byte swizzle), mbarrier pipelines, warp-specialised roles.
+//
+//   tc_gemm_ss_kernel   out[m, n] = x[m, k] . w[n, k]^T, single TF32 pass, both operands from
+//                       shared memory. Prefill shapes (m = thousands of prompt rows).
+//   tc_gemm_x3_kernel   the same product to FP32 accuracy from three TF32 products
+//                       (hi*hi + hi*lo + lo*hi). The weight tile is the 128-row MMA operand: its
+//                       raw FP32 tile is split into hi/lo by the epilogue warps and placed in tensor
+//                       memory (tcgen05.st), so the MMA reads it from there; the few activation rows
+//                       arrive pre-split (x_hi, x_lo) and are the N operand. Decode shapes
+//                       (m <= 256 tokens), optional split-K with a fixed-order reduction.
+//
+// Every wait on an mbarrier is bounded: on expiry the kernel raises an error flag in global
+// memory, stops issuing work, still frees its tensor memory and returns.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <mutex>
+
+#include "kernels.cuh"
+
+namespace pg {
+namespace {
+
+constexpr int BK = 32;             // floats per k-block = one 128-byte swizzle row
+constexpr int TILE_M = 128;        // rows of the 128-lane MMA operand
+constexpr uint32_t SPIN_LIMIT = 1u << 20;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait; returns false (and records `code`) when the limit is hit or another role failed.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* failed, int* err, int code) {
+  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023) == 1023 && *failed) return false;
+  }
+  *failed = 1;
+  if (err) atomicCAS(err, 0, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+// Shared-memory operand descriptor: K-major tile whose rows are 128 bytes, 128-byte swizzle,
+// 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(const void* smem_tile) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_u32(smem_tile) & 0x3FFFF) >> 4);  // start address
+  d |= (uint64_t)1 << 16;                                  // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;                        // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                                  // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                                  // 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor for kind::tf32: FP32 accumulate, TF32 A and B, both K-major.
+__device__ __forceinline__ uint32_t umma_idesc_tf32(int m, int n) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on `bar` when every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+__device__ __forceinline__ float gelu_ref(float x) {
+  return 0.5f * x * (1.0f + tanhf(0.7978846f * (x + 0.044715f * x * x * x)));
+}
+__device__ __forceinline__ float tf32_hi(float v) { return __uint_as_float(__float_as_uint(v) & 0xFFFFE000u); }
+
+// ------------------------------------------------------------------ single-pass TF32, SS
+// grid (ceil(n / BN), ceil(m / 128)); 192 threads: warp 0 TMA producer, warp 1 MMA issuer and
+// tensor-memory owner, warps 2..5 epilogue (warp w reads TMEM lanes 32 * (w % 4) ...).
+template <int BN>
+struct SsSmem {
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int A_BYTES = TILE_M * BK * 4, B_BYTES = BN * BK * 4;
+  static constexpr size_t BYTES = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(192, 1)
+    tc_gemm_ss_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                      TcGemmArgs a) {
+  using S = SsSmem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem_a = base;
+  uint8_t* smem_b = base + (size_t)S::STAGES * S::A_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem_b + (size_t)S::STAGES * S::B_BYTES);
+  uint64_t* empty = full + S::STAGES;
+  uint64_t* d_full = empty + S::STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_full + 1);
+  volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * TILE_M;
+  const int nkb = a.k / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(d_full, 1);
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, BN);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_d = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % S::STAGES;
+        if (kb >= S::STAGES && !mbar_wait(&empty[s], ((kb / S::STAGES) - 1) & 1, failed, a.error_flag, 1)) break;
+        mbar_expect_tx(&full[s], S::A_BYTES + S::B_BYTES);
+        tma_load_2d(smem_a + (size_t)s * S::A_BYTES, &map_x, kb * BK, m0, &full[s]);
+        tma_load_2d(smem_b + (size_t)s * S::B_BYTES, &map_w, kb * BK, n0, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_tf32(TILE_M, BN);
+      bool ok = true;
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        const int s = kb % S::STAGES;
+        ok = mbar_wait(&full[s], (kb / S::STAGES) & 1, failed, a.error_flag, 2);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t da = umma_desc_sw128(smem_a + (size_t)s * S::A_BYTES);
+        const uint64_t db = umma_desc_sw128(smem_b + (size_t)s * S::B_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / 8; ++k)
+          umma_tf32_ss(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+        umma_commit(&empty[s]);
+      }
+      umma_commit(d_full);
+    }
+  } else {
+    const int q = warp & 3;
+    const int row = m0 + q * 32 + lane;
+    if (mbar_wait(d_full, 0, failed, a.error_flag, 3)) {
+      tc_fence_after();
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        float v[32];
+        tmem_ld32(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+        if (row < a.m) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = n0 + c0 + j;
+            if (col < a.n) {
+              float r = a.bias ? a.bias[col] + v[j] : v[j];
+              if (a.epilogue == EPI_GELU) r = gelu_ref(r);
+              if (a.epilogue == EPI_RESID) r = a.resid[(size_t)row * a.n + col] + r;
+              v[j] = r;
+            }
+          }
+          float* dst = a.out + (size_t)row * a.n + n0 + c0;
+          if ((a.n & 3) == 0 && n0 + c0 + 32 <= a.n) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (n0 + c0 + j < a.n) dst[j] = v[j];
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_d, BN);
+}
+
+// ------------------------------------------------------------------ 3xTF32, weights via TMEM
+// grid (ceil(n / 128), splits) with thread-block clusters of (1, splits, 1): the CTAs of one
+// cluster share a 128-row weight tile and each covers 1/splits of k. 192 threads per CTA.
+// A shared-memory stage holds the raw FP32 weight tile (128 rows x 32 k) and the pre-split
+// activation tiles x_hi, x_lo (BN rows x 32 k). The four epilogue warps turn each weight tile
+// into hi/lo in tensor memory; the MMA warp then issues, per 8-wide k step, hi*hi, hi*lo and
+// lo*hi into the same accumulator. Split-K partials are exchanged through distributed shared
+// memory and added in split order, so the result does not depend on scheduling.
+template <int BN>
+struct X3 {
+  static constexpr int STAGES = 3;   // shared-memory stages; also tensor-memory stages of the split tile
+  static constexpr int A_BYTES = TILE_M * BK * 4, B_BYTES = BN * BK * 4;
+  static constexpr int STAGE_BYTES = A_BYTES + 2 * B_BYTES;
+  static constexpr int D_BYTES = TILE_M * BN * 4;  // accumulator staging, aliases the stages after the main loop
+  static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES > D_BYTES ? STAGES * STAGE_BYTES : D_BYTES;
+  static constexpr size_t BYTES = (size_t)PIPE_BYTES + 1024 + 256;
+  static constexpr int TMEM_COLS = 256;  // BN accumulator columns, then STAGES * 64 from column 64
+  static constexpr int A_COL0 = 64;
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_dsmem(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int BN>
+__global__ void __launch_bounds__(192, 2)
+    tc_gemm_x3_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_xhi,
+                      const __grid_constant__ CUtensorMap map_xlo, TcGemmArgs a) {
+  using S = X3<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(base + (size_t)S::PIPE_BYTES);
+  uint64_t* empty = full + S::STAGES;
+  uint64_t* a_ready = empty + S::STAGES;
+  uint64_t* d_full = a_ready + S::STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_full + 1);
+  volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* dbuf = reinterpret_cast<float*>(base);  // [token][128 rows], valid after the main loop
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * TILE_M;  // first weight row (output feature) of this tile
+  const int splits = gridDim.y;
+  const int split = (int)cluster_rank();  // == blockIdx.y: the cluster spans the whole y extent
+  const int nkb_total = a.k / BK;
+  const int kb_per = (nkb_total + splits - 1) / splits;
+  const int kb0 = min(split * kb_per, nkb_total), kb1 = min(kb0 + kb_per, nkb_total);
+  const int nkb = kb1 - kb0;
+
+  pdl_launch();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+      mbar_init(&a_ready[s], 128);
+    }
+    mbar_init(d_full, 1);
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, S::TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto stage_a = [&](int s) { return base + (size_t)s * S::STAGE_BYTES; };
+  auto stage_bhi = [&](int s) { return base + (size_t)s * S::STAGE_BYTES + S::A_BYTES; };
+  auto stage_blo = [&](int s) { return base + (size_t)s * S::STAGE_BYTES + S::A_BYTES + S::B_BYTES; };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // weights do not depend on the previous kernel: start streaming them before the wait
+      const int pre = min(nkb, S::STAGES);
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(&full[i], S::STAGE_BYTES);
+        tma_load_2d(stage_a(i), &map_w, (kb0 + i) * BK, n0, &full[i]);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i) {
+        tma_load_2d(stage_bhi(i), &map_xhi, (kb0 + i) * BK, 0, &full[i]);
+        tma_load_2d(stage_blo(i), &map_xlo, (kb0 + i) * BK, 0, &full[i]);
+      }
+      for (int i = pre; i < nkb; ++i) {
+        const int s = i % S::STAGES;
+        if (!mbar_wait(&empty[s], ((i / S::STAGES) - 1) & 1, failed, a.error_flag, 11)) break;
+        mbar_expect_tx(&full[s], S::STAGE_BYTES);
+        tma_load_2d(stage_a(s), &map_w, (kb0 + i) * BK, n0, &full[s]);
+        tma_load_2d(stage_bhi(s), &map_xhi, (kb0 + i) * BK, 0, &full[s]);
+        tma_load_2d(stage_blo(s), &map_xlo, (kb0 + i) * BK, 0, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_tf32(TILE_M, BN);
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % S::STAGES;
+        if (!mbar_wait(&full[s], (i / S::STAGES) & 1, failed, a.error_flag, 12)) break;
+        if (!mbar_wait(&a_ready[s], (i / S::STAGES) & 1, failed, a.error_flag, 13)) break;
+        tc_fence_after();
+        const uint64_t dhi = umma_desc_sw128(stage_bhi(s)), dlo = umma_desc_sw128(stage_blo(s));
+        const uint32_t ahi = tmem_base + S::A_COL0 + s * 64, alo = ahi + 32;
+#pragma unroll
+        for (int k = 0; k < BK / 8; ++k) {
+          umma_tf32_ts(tmem_base, ahi + k * 8, dhi + (uint64_t)(k * 2), idesc, (i | k) != 0);
+          umma_tf32_ts(tmem_base, ahi + k * 8, dlo + (uint64_t)(k * 2), idesc, 1);
+          umma_tf32_ts(tmem_base, alo + k * 8, dhi + (uint64_t)(k * 2), idesc, 1);
+        }
+        umma_commit(&empty[s]);  // frees the shared-memory stage and its tensor-memory twin
+      }
+      umma_commit(d_full);
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;  // row of the weight tile == TMEM lane
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    bool ok = true;
+    for (int i = 0; i < nkb && ok; ++i) {
+      const int s = i % S::STAGES;
+      // the TMEM twin of stage s is free once the MMAs of its previous use completed, which is
+      // what released the stage to the producer, hence implied by `full`
+      ok = mbar_wait(&full[s], (i / S::STAGES) & 1, failed, a.error_flag, 14);
+      if (!ok) break;
+      tc_fence_after();
+      const float4* rowp = reinterpret_cast<const float4*>(stage_a(s) + (size_t)r * 128);
+      uint32_t hi[32], lo[32];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 v = rowp[j ^ (r & 7)];  // undo the 128-byte swizzle: conflict-free per quarter warp
+        const float f[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float h = tf32_hi(f[e]);
+          hi[j * 4 + e] = __float_as_uint(h);
+          lo[j * 4 + e] = __float_as_uint(f[e] - h);
+        }
+      }
+      const uint32_t col = tmem_base + S::A_COL0 + s * 64 + lane_addr;
+      tmem_st32(col, hi);
+      tmem_st32(col + 32, lo);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&a_ready[s]);
+    }
+    // accumulator -> shared memory, [token][row]: all MMAs (and so all TMA writes) are complete
+    if (ok && mbar_wait(d_full, 0, failed, a.error_flag, 16)) {
+      tc_fence_after();
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16];
+        tmem_ld16(tmem_base + lane_addr + (uint32_t)c0, v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) dbuf[(size_t)(c0 + j) * TILE_M + r] = (nkb > 0) ? v[j] : 0.f;
+      }
+    }
+  }
+  // every thread of every CTA of the cluster passes both cluster barriers exactly once
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp >= 2 && !*failed) {
+    pdl_wait();  // resid may come from the previous kernel; out must not be written before it ended
+    const int t = threadIdx.x - 64;
+    const int rows_per = TILE_M / splits;  // rows of the tile this CTA finishes
+    const int rl = t % rows_per, tg = t / rows_per;
+    const int row = split * rows_per + rl;
+    const int feat = n0 + row;
+    const uint32_t dbuf_addr = smem_u32(dbuf);
+    if (feat < a.n) {
+      const float b = a.bias ? a.bias[feat] : 0.f;
+      for (int j = tg; j < BN && j < a.m; j += splits) {
+        float acc = 0.f;
+        for (int sp = 0; sp < splits; ++sp) acc += ld_dsmem(dbuf_addr + (uint32_t)(j * TILE_M + row) * 4u, (uint32_t)sp);
+        float v = a.bias ? b + acc : acc;
+        if (a.epilogue == EPI_GELU) v = gelu_ref(v);
+        if (a.epilogue == EPI_RESID) v = a.resid[(size_t)j * a.n + feat] + v;
+        if (a.out) a.out[(size_t)j * a.n + feat] = v;
+        if (a.out_hi) {
+          const float h = tf32_hi(v);
+          a.out_hi[(size_t)j * a.n + feat] = h;
+          a.out_lo[(size_t)j * a.n + feat] = v - h;
+        }
+      }
+    }
+  }
+  cluster_sync_all();  // no CTA may leave while a peer still reads its shared memory
+  if (warp == 1) tmem_dealloc(tmem_base, S::TMEM_COLS);
+}
+
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 2-D FP32 tensor [rows, k] (k contiguous), box = 32 floats x box_rows, 128-byte swizzle,
+// out-of-range rows read as zero.
+bool make_map(CUtensorMap* map, const float* ptr, uint64_t rows, uint64_t k, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {k, rows};
+  cuuint64_t strides[1] = {k * sizeof(float)};
+  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename K>
+cudaError_t launch_ex(K kernel, dim3 grid, size_t smem, cudaStream_t s, bool pdl, void** params, int cluster_y = 1) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (pdl) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_y > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = 1;
+    attr[n].val.clusterDim.y = (unsigned)cluster_y;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(kernel), params);
+}
+
+}  // namespace
+
+bool tc_gemm_supported(int m, int n, int k) {
+  (void)m;
+  (void)n;
+  return k % BK == 0 && k >= BK && encode_fn() != nullptr;
+}
+
+cudaError_t init_tc_kernel_attributes() {
+  cudaError_t e;
+  e = cudaFuncSetAttribute(tc_gemm_ss_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SsSmem<128>::BYTES);
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(tc_gemm_ss_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SsSmem<256>::BYTES);
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(tc_gemm_x3_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)X3<64>::BYTES);
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(tc_gemm_x3_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)X3<32>::BYTES);
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(tc_gemm_x3_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)X3<16>::BYTES);
+  return e;
+}
+
+cudaError_t launch_tc_gemm_tf32(const TcGemmArgs& a, cudaStream_t s) {
+  if (!tc_gemm_supported(a.m, a.n, a.k)) return cudaErrorInvalidValue;
+  CUtensorMap mx, mw;
+  const int bn = (a.n >= 256 && a.m >= 2048) ? 256 : 128;
+  if (!make_map(&mx, a.x, a.m, a.k, TILE_M) || !make_map(&mw, a.w, a.n, a.k, bn)) return cudaErrorInvalidValue;
+  TcGemmArgs args = a;
+  void* params[3] = {&mx, &mw, &args};
+  dim3 grid((a.n + bn - 1) / bn, (a.m + TILE_M - 1) / TILE_M);
+  if (bn == 256) return launch_ex(tc_gemm_ss_kernel<256>, grid, SsSmem<256>::BYTES, s, false, params);
+  return launch_ex(tc_gemm_ss_kernel<128>, grid, SsSmem<128>::BYTES, s, false, params);
+}
+
+int tc_gemm_x3_splits(int n, int k, int num_sms) {
+  const int tiles = (n + TILE_M - 1) / TILE_M;
+  const int nkb = k / BK;
+  int splits = 1;
+  // spread small matrices over the SMs (two CTAs fit on one), but keep at least 4 k-blocks
+  // (64 KB of weights) per CTA; 8 is the portable cluster size
+  while (tiles * splits * 2 <= 2 * num_sms && nkb / (splits * 2) >= 4 && splits < 8) splits *= 2;
+  return splits;
+}
+
+cudaError_t launch_tc_gemm_x3(const TcGemmArgs& a, int splits, bool pdl, cudaStream_t s) {
+  if (!tc_gemm_supported(a.m, a.n, a.k) || a.m > 64 || !a.x || !a.x_lo) return cudaErrorInvalidValue;
+  if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return cudaErrorInvalidValue;
+  const int bn = a.m <= 16 ? 16 : a.m <= 32 ? 32 : 64;
+  CUtensorMap mw, mhi, mlo;
+  if (!make_map(&mw, a.w, a.n, a.k, TILE_M) || !make_map(&mhi, a.x, a.m, a.k, bn) ||
+      !make_map(&mlo, a.x_lo, a.m, a.k, bn))
+    return cudaErrorInvalidValue;
+  TcGemmArgs args = a;
+  void* params[4] = {&mw, &mhi, &mlo, &args};
+  dim3 grid((a.n + TILE_M - 1) / TILE_M, splits);
+  switch (bn) {
+    case 16: return launch_ex(tc_gemm_x3_kernel<16>, grid, X3<16>::BYTES, s, pdl, params, splits);
+    case 32: return launch_ex(tc_gemm_x3_kernel<32>, grid, X3<32>::BYTES, s, pdl, params, splits);
+    default: return launch_ex(tc_gemm_x3_kernel<64>, grid, X3<64>::BYTES, s, pdl, params, splits);
+  }
+}
+
+}  // namespace pg

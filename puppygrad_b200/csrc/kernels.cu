@@ -5,6 +5,7 @@
 // bias / GELU / residual (epilogue). Kernels of one decode step are chained with programmatic
 // dependent launch: each CTA issues its first weight loads *before* griddepcontrol.wait, so the
 // weight stream of kernel N+1 overlaps the tail of kernel N.
+#include <algorithm>
 #include <cfloat>
 #include <climits>
 
@@ -295,6 +296,76 @@ __global__ void layernorm_rows_kernel(const float* x, const float* __restrict__ 
   for (int i = lane; i < c; i += 32) out[(size_t)r * c + i] = (xr[i] - mean) * inv_std * g[i] + b[i];
 }
 
+__global__ void split_tf32_kernel(const float* x, float* hi, float* lo, size_t n) {
+  pdl_launch();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const float v = x[i];
+    const float h = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+    hi[i] = h;
+    lo[i] = v - h;
+  }
+}
+
+// One 128-thread CTA per row, 128-bit loads, row kept in registers (c <= 4096) between the passes.
+__global__ void __launch_bounds__(128) layernorm_rows_split_kernel(const float* x, const float* __restrict__ g,
+                                                                   const float* __restrict__ b, float eps, float* hi,
+                                                                   float* lo, int rows, int c) {
+  __shared__ float red[4];
+  pdl_launch();
+  pdl_wait();
+  const int r = blockIdx.x, tid = threadIdx.x;
+  if (r >= rows) return;
+  const int c4 = c >> 2;
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)r * c);
+  float4 v[8];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int idx = tid + i * 128;
+    v[i] = idx < c4 ? xr[idx] : make_float4(0, 0, 0, 0);
+    s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+  }
+  s = warp_sum(s);
+  if ((tid & 31) == 0) red[tid >> 5] = s;
+  __syncthreads();
+  const float mean = ((red[0] + red[1]) + (red[2] + red[3])) / (float)c;
+  __syncthreads();
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    if (tid + i * 128 < c4) {
+      const float d0 = v[i].x - mean, d1 = v[i].y - mean, d2 = v[i].z - mean, d3 = v[i].w - mean;
+      q += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+    }
+  }
+  q = warp_sum(q);
+  if ((tid & 31) == 0) red[tid >> 5] = q;
+  __syncthreads();
+  const float inv_std = 1.0f / sqrtf(((red[0] + red[1]) + (red[2] + red[3])) / (float)c + eps);
+  const float4* g4 = reinterpret_cast<const float4*>(g);
+  const float4* b4 = reinterpret_cast<const float4*>(b);
+  float4* hi4 = reinterpret_cast<float4*>(hi + (size_t)r * c);
+  float4* lo4 = reinterpret_cast<float4*>(lo + (size_t)r * c);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int idx = tid + i * 128;
+    if (idx < c4) {
+      const float4 gg = g4[idx], bb = b4[idx];
+      const float y[4] = {(v[i].x - mean) * inv_std * gg.x + bb.x, (v[i].y - mean) * inv_std * gg.y + bb.y,
+                          (v[i].z - mean) * inv_std * gg.z + bb.z, (v[i].w - mean) * inv_std * gg.w + bb.w};
+      float h[4], l[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        h[e] = __uint_as_float(__float_as_uint(y[e]) & 0xFFFFE000u);
+        l[e] = y[e] - h[e];
+      }
+      hi4[idx] = make_float4(h[0], h[1], h[2], h[3]);
+      lo4[idx] = make_float4(l[0], l[1], l[2], l[3]);
+    }
+  }
+}
+
 __global__ void transpose_kernel(const float* __restrict__ src, float* __restrict__ dst, int in_f, int out_f) {
   __shared__ float tile[32][33];
   int o0 = blockIdx.x * 32, i0 = blockIdx.y * 32;
@@ -439,7 +510,18 @@ __device__ __forceinline__ float block_sum_128(float v, float* sm) {
 }
 
 // Merges split partials (m, l, acc[D]) in split order and writes the normalised head output.
-__device__ void merge_splits(const float* part, int splits, int d_len, float* out_head) {
+// Writes one attention output value, optionally as a TF32 hi/lo pair for the tensor-core linears.
+__device__ __forceinline__ void store_split(float* out, float* out_lo, size_t idx, float v) {
+  if (out_lo) {
+    const float h = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+    out[idx] = h;
+    out_lo[idx] = v - h;
+  } else {
+    out[idx] = v;
+  }
+}
+
+__device__ void merge_splits(const float* part, int splits, int d_len, float* out, float* out_lo, size_t base) {
   for (int d = threadIdx.x; d < d_len; d += blockDim.x) {
     float mx = -INFINITY;
     for (int s = 0; s < splits; ++s) mx = fmaxf(mx, part[(size_t)s * (d_len + 2)]);
@@ -450,7 +532,7 @@ __device__ void merge_splits(const float* part, int splits, int d_len, float* ou
       l += p[1] * sc;
       o += p[2 + d] * sc;
     }
-    out_head[d] = o / l;
+    store_split(out, out_lo, base + d, o / l);
   }
 }
 
@@ -540,7 +622,7 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(DecodeAtt
   }
 
   if (a.splits == 1) {
-    if (tid < D) a.out[(size_t)b * c + h * D + tid] = o / total;
+    if (tid < D) store_split(a.out, a.out_lo, (size_t)b * c + h * D + tid, o / total);
     return;
   }
   float* mypart = a.part + ((size_t)(b * a.kv.n_head + h) * a.splits + sp) * (D + 2);
@@ -558,8 +640,8 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(DecodeAtt
   __syncthreads();
   if (is_last) {
     __threadfence();
-    merge_splits(a.part + (size_t)(b * a.kv.n_head + h) * a.splits * (D + 2), a.splits, D,
-                 a.out + (size_t)b * c + h * D);
+    merge_splits(a.part + (size_t)(b * a.kv.n_head + h) * a.splits * (D + 2), a.splits, D, a.out, a.out_lo,
+                 (size_t)b * c + h * D);
     if (tid == 0) a.counters[b * a.kv.n_head + h] = 0;
   }
 }
@@ -609,7 +691,7 @@ __global__ void decode_attention_generic_kernel(DecodeAttnArgs a) {
       const int page = table[k / a.kv.page_tokens], off = k % a.kv.page_tokens;
       o = fmaf(scores[k], a.kv_pool[kv_row_offset(a.kv, page, 1, h, off) + d], o);
     }
-    a.out[(size_t)b * c + h * D + d] = o / total;
+    store_split(a.out, a.out_lo, (size_t)b * c + h * D + d, o / total);
   }
 }
 
@@ -975,6 +1057,17 @@ cudaError_t launch_embed(const float* wte, const float* wpe, const int* ids, con
 cudaError_t launch_layernorm_rows(const float* x, const float* g, const float* b, float eps, float* out, int rows,
                                   int c, bool pdl, cudaStream_t s) {
   return launch(layernorm_rows_kernel, dim3((rows + 3) / 4), dim3(128), 0, s, pdl, x, g, b, eps, out, rows, c);
+}
+
+cudaError_t launch_split_tf32(const float* x, float* hi, float* lo, size_t n, bool pdl, cudaStream_t s) {
+  int grid = (int)std::min<size_t>((n + 255) / 256, 1184);
+  return launch(split_tf32_kernel, dim3(grid), dim3(256), 0, s, pdl, x, hi, lo, n);
+}
+
+cudaError_t launch_layernorm_rows_split(const float* x, const float* g, const float* b, float eps, float* hi,
+                                        float* lo, int rows, int c, bool pdl, cudaStream_t s) {
+  if (c % 4 != 0 || c > 4096) return cudaErrorInvalidValue;
+  return launch(layernorm_rows_split_kernel, dim3(rows), dim3(128), 0, s, pdl, x, g, b, eps, hi, lo, rows, c);
 }
 
 cudaError_t launch_gemm_f32(const LinearArgs& a, int epilogue, cudaStream_t s) {

@@ -49,6 +49,7 @@ cudaError_t launch_transpose(const float* src, float* dst, int in_f, int out_f, 
 struct DecodeAttnArgs {
   const float* qkv;       // [batch, 3c]
   float* out;             // [batch, c]
+  float* out_lo;          // optional: out receives the TF32 hi part and out_lo the remainder
   float* kv_pool;         // this layer's page pool
   const int* page_table;  // [max_batch, pages_per_seq]
   const int* pos;         // [batch]: position of the new token (= keys already cached)
@@ -92,6 +93,33 @@ struct FinalizeArgs {
 };
 // Sets the opt-in shared-memory limits of the kernels; once per device before the first launch.
 cudaError_t init_kernel_attributes();
+cudaError_t init_tc_kernel_attributes();
+
+// hi = x with the 13 low mantissa bits cleared (exactly representable in TF32), lo = x - hi
+cudaError_t launch_split_tf32(const float* x, float* hi, float* lo, size_t n, bool pdl, cudaStream_t s);
+// LayerNorm rows whose result is written as a TF32 hi/lo pair
+cudaError_t launch_layernorm_rows_split(const float* x, const float* g, const float* b, float eps, float* hi,
+                                        float* lo, int rows, int c, bool pdl, cudaStream_t s);
+
+// Tensor-core GEMM out[m, n] = x[m, k] . w[n, k]^T (+bias)(+GELU | +resid); k % 32 == 0.
+struct TcGemmArgs {
+  const float* x;     // [m, k] activations (x3: the hi part)
+  const float* x_lo;  // [m, k] lo part (x3 only)
+  const float* w;     // [n, k]
+  const float* bias;  // [n] or nullptr
+  const float* resid; // [m, n], EPI_RESID
+  float* out;         // [m, n] (may be nullptr in x3 when only the split outputs are wanted)
+  float* out_hi;      // x3: optional TF32 hi/lo pair of the result, [m, n] each
+  float* out_lo;
+  int* error_flag;    // set non-zero if a bounded wait inside the kernel expired
+  int m, n, k, epilogue;
+};
+bool tc_gemm_supported(int m, int n, int k);
+// single TF32 pass, any m (prefill)
+cudaError_t launch_tc_gemm_tf32(const TcGemmArgs& a, cudaStream_t s);
+// three TF32 passes (FP32-grade), m <= 64 (decode)
+int tc_gemm_x3_splits(int n, int k, int num_sms);
+cudaError_t launch_tc_gemm_x3(const TcGemmArgs& a, int splits, bool pdl, cudaStream_t s);
 cudaError_t launch_finalize(const FinalizeArgs& a, bool pdl, cudaStream_t s);
 // Plain argmax over rows of a [m, n] matrix (first strict maximum).
 cudaError_t launch_argmax_rows(const float* logits, int m, int n, int* out, cudaStream_t s);

@@ -75,7 +75,7 @@ namespace pg {
 static std::mutex g_init_mu;
 static std::map<int, bool> g_device_inited;
 
-static int ensure_device(int device) {
+int ensure_device(int device) {
   int count = 0;
   cudaError_t e = cudaGetDeviceCount(&count);
   if (e != cudaSuccess || count == 0) {
@@ -95,6 +95,7 @@ static int ensure_device(int device) {
                                     std::to_string(prop.major) + "." + std::to_string(prop.minor) +
                                     "; this library is built for sm_100a only");
     PG_CUDA_TRY(init_kernel_attributes());
+    PG_CUDA_TRY(init_tc_kernel_attributes());
     g_device_inited[device] = true;
   }
   return PG_OK;
@@ -113,8 +114,8 @@ static int build_model(const pg_gpt2_config& cfg, const float* const* tensors, c
     return set_error(PG_INVALID_CONFIG, "cuda page_tokens must be 16, 32 or 64");
   if (be.math_mode < PG_MATH_FP32 || be.math_mode > PG_MATH_BF16)
     return set_error(PG_INVALID_CONFIG, "cuda math_mode must be one of fp32, tf32x3, tf32, bf16");
-  if (be.math_mode != PG_MATH_FP32)
-    return set_error(PG_INVALID_CONFIG, "cuda math_mode other than fp32 is not available in this build");
+  if (be.math_mode == PG_MATH_BF16)
+    return set_error(PG_INVALID_CONFIG, "cuda math_mode bf16 is not available in this build");
   if (be.attn_splits < 0 || be.attn_splits > 16)
     return set_error(PG_INVALID_CONFIG, "cuda attn_splits must be in 0..16");
   if (cfg.vocab_size > 0x7fffffffULL || cfg.n_positions > 65536 || cfg.n_embd > 65536 || cfg.n_inner > 262144)
@@ -204,6 +205,9 @@ struct pg_cache {
   unsigned* attn_counters = nullptr;
   float* topk_vals = nullptr;
   int* topk_idx = nullptr;
+  // tensor-core decode path (9..64 sequences): TF32 hi/lo pairs of the GEMM inputs, split-K scratch
+  float *norm_lo = nullptr, *attn_lo = nullptr, *h_lo = nullptr;
+  int* d_error = nullptr;
   int *h_ids = nullptr, *h_out = nullptr;  // pinned staging
   // prefill workspace (grow-only)
   size_t pre_rows = 0;
@@ -224,7 +228,8 @@ struct pg_cache {
     for (void* p : {(void*)kv_pool, (void*)d_table, (void*)d_ids, (void*)d_pos, (void*)d_argmax, (void*)d_token_log,
                     (void*)x, (void*)norm, (void*)qkv, (void*)attn, (void*)hbuf, (void*)logits, (void*)part_val,
                     (void*)part_idx, (void*)attn_part, (void*)attn_counters, (void*)topk_vals, (void*)topk_idx,
-                    (void*)px, (void*)pnorm, (void*)pqkv, (void*)pattn, (void*)ph, (void*)prow})
+                    (void*)px, (void*)pnorm, (void*)pqkv, (void*)pattn, (void*)ph, (void*)prow, (void*)norm_lo,
+                    (void*)attn_lo, (void*)h_lo, (void*)d_error})
       if (p) cudaFree(p);
     if (t0) cudaEventDestroy(t0);
     if (t1) cudaEventDestroy(t1);
@@ -282,8 +287,16 @@ static int cache_new(const pg_model* m, int max_batch, pg_cache** out) {
   PG_CUDA_TRY(cudaMemsetAsync(c->attn_counters, 0, B * H * sizeof(unsigned), c->stream));
   PG_CUDA_TRY(cudaMalloc(&c->topk_vals, B * MAX_TOPK * sizeof(float)));
   PG_CUDA_TRY(cudaMalloc(&c->topk_idx, B * MAX_TOPK * sizeof(int)));
+  PG_CUDA_TRY(cudaMalloc(&c->d_error, sizeof(int)));
+  PG_CUDA_TRY(cudaMemsetAsync(c->d_error, 0, sizeof(int), c->stream));
+  if (max_batch > 8 && C % 32 == 0 && F % 32 == 0) {
+    const int bmax = std::min(max_batch, 64);
+    PG_CUDA_TRY(cudaMalloc(&c->norm_lo, (size_t)bmax * C * sizeof(float)));
+    PG_CUDA_TRY(cudaMalloc(&c->attn_lo, (size_t)bmax * C * sizeof(float)));
+    PG_CUDA_TRY(cudaMalloc(&c->h_lo, (size_t)bmax * F * sizeof(float)));
+  }
   PG_CUDA_TRY(cudaMallocHost(&c->h_ids, B * sizeof(int)));
-  PG_CUDA_TRY(cudaMallocHost(&c->h_out, B * (1 + 2 * MAX_TOPK) * sizeof(int)));
+  PG_CUDA_TRY(cudaMallocHost(&c->h_out, (B * (1 + 2 * MAX_TOPK) + 1) * sizeof(int)));
   PG_CUDA_TRY(cudaStreamSynchronize(c->stream));
   *out = c.release();
   return PG_OK;
@@ -375,6 +388,51 @@ static cudaError_t enqueue_decode_step(pg_cache* c, int batch, int splits, cudaS
     if (prof && (e = prof->mark(s, -1)) != cudaSuccess) return e;        \
   } while (0)
   PG_E(launch_embed(m->wte, m->wpe, c->d_ids, c->d_pos, c->x, batch, C, pdl, s));
+  if (m->backend.math_mode != PG_MATH_FP32 && batch > 8 && batch <= 64 && c->norm_lo) {
+    // tensor-core path: every linear is three TF32 products (hi*hi + hi*lo + lo*hi) accumulated
+    // in FP32; LayerNorm, attention and the GELU epilogue hand their results over as hi/lo pairs
+    auto x3 = [&](const float* w, const float* bias, const float* xhi, const float* xlo, float* out, float* ohi,
+                  float* olo, int n_out, int k, int epi, const float* resid) -> cudaError_t {
+      TcGemmArgs a{};
+      a.x = xhi; a.x_lo = xlo; a.w = w; a.bias = bias; a.resid = resid; a.out = out; a.out_hi = ohi; a.out_lo = olo;
+      a.error_flag = c->d_error;
+      a.m = batch; a.n = n_out; a.k = k; a.epilogue = epi;
+      return launch_tc_gemm_x3(a, tc_gemm_x3_splits(n_out, k, m->num_sms), pdl, s);
+    };
+    for (int l = 0; l < m->layers_n(); ++l) {
+      const LayerWeights& w = m->layers[l];
+      cur_bucket = B_LAYER_NORM;
+      PG_E(launch_layernorm_rows_split(c->x, w.ln1_g, w.ln1_b, eps, c->norm, c->norm_lo, batch, C, pdl, s));
+      cur_bucket = B_QKV;
+      PG_E(x3(w.w_qkv, w.b_qkv, c->norm, c->norm_lo, c->qkv, nullptr, nullptr, 3 * C, C, EPI_NONE, nullptr));
+      cur_bucket = B_ATTN;
+      DecodeAttnArgs at{};
+      at.qkv = c->qkv; at.out = c->attn; at.out_lo = c->attn_lo; at.kv_pool = c->layer_pool(l);
+      at.page_table = c->d_table; at.pos = c->d_pos; at.part = c->attn_part; at.counters = c->attn_counters;
+      at.kv = c->kv; at.batch = batch; at.splits = splits;
+      PG_E(launch_decode_attention(at, pdl, s));
+      cur_bucket = B_ATTN_PROJ;
+      PG_E(x3(w.w_proj, w.b_proj, c->attn, c->attn_lo, c->x, nullptr, nullptr, C, C, EPI_RESID, c->x));
+      cur_bucket = B_LAYER_NORM;
+      PG_E(launch_layernorm_rows_split(c->x, w.ln2_g, w.ln2_b, eps, c->norm, c->norm_lo, batch, C, pdl, s));
+      cur_bucket = B_MLP_FC;
+      PG_E(x3(w.w_fc, w.b_fc, c->norm, c->norm_lo, nullptr, c->hbuf, c->h_lo, F, C, EPI_GELU, nullptr));
+      cur_bucket = B_MLP_PROJ;
+      PG_E(x3(w.w_proj2, w.b_proj2, c->hbuf, c->h_lo, c->x, nullptr, nullptr, C, F, EPI_RESID, c->x));
+    }
+    cur_bucket = B_LAYER_NORM;
+    PG_E(launch_layernorm_rows_split(c->x, m->lnf_g, m->lnf_b, eps, c->norm, c->norm_lo, batch, C, pdl, s));
+    cur_bucket = B_LOGITS;
+    PG_E(x3(m->wte, nullptr, c->norm, c->norm_lo, c->logits, nullptr, nullptr, V, C, EPI_NONE, nullptr));
+    PG_E(launch_argmax_rows(c->logits, batch, V, c->d_argmax, s));
+    FinalizeArgs fx{};
+    fx.m = batch; fx.argmax_out = c->d_argmax; fx.next_ids = c->d_ids; fx.pos = c->d_pos;
+    fx.token_log = c->d_token_log; fx.n_positions = m->positions();
+    cur_bucket = B_OTHER;
+    PG_E(launch_finalize(fx, pdl, s));
+    if (launches) *launches = n;
+    return cudaSuccess;
+  }
   auto linear = [&](const float* w, const float* bias, const float* x, float* out, int n_out, int k, int epi,
                     const float* resid, const float* g, const float* b) -> cudaError_t {
     LinearArgs a{};
@@ -582,7 +640,11 @@ static int fetch_outputs(pg_cache* c, int batch, float* logits_out, int32_t* arg
     PG_CUDA_TRY(cudaMemcpyAsync(c->h_out, c->d_argmax, batch * sizeof(int), cudaMemcpyDeviceToHost, c->stream));
   if (logits_out)
     PG_CUDA_TRY(cudaMemcpyAsync(logits_out, c->logits, (size_t)batch * V * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+  int* h_err = c->h_out + (size_t)c->max_batch * (1 + 2 * MAX_TOPK);
+  PG_CUDA_TRY(cudaMemcpyAsync(h_err, c->d_error, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
   PG_CUDA_TRY(cudaStreamSynchronize(c->stream));
+  if (*h_err)
+    return set_error(PG_TIMEOUT, "a bounded wait inside a tensor-core kernel expired (role code " + std::to_string(*h_err) + ")");
   if (argmax_out) memcpy(argmax_out, c->h_out, batch * sizeof(int));
   if (k > 0 && topk_vals) memcpy(topk_vals, c->h_out + c->max_batch, (size_t)batch * k * sizeof(float));
   if (k > 0 && topk_idx) memcpy(topk_idx, c->h_out + c->max_batch + (size_t)c->max_batch * MAX_TOPK, (size_t)batch * k * sizeof(int));

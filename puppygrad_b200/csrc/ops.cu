@@ -1,0 +1,133 @@
+// Kernel-level entry points of the C ABI: one operator on host buffers, timed on the device.
+// They exist for the kernel sweeps (shapes of GPT-2 XL) and for operator-level parity tests; the
+// model path in model.cu launches the same kernels directly.
+#include <cuda_runtime.h>
+
+#include <string>
+#include <vector>
+
+#include "common.h"
+#include "kernels.cuh"
+
+namespace pg {
+int ensure_device(int device);  // model.cu
+}
+using namespace pg;
+
+#define PG_OP_TRY(expr)                                                                                     \
+  do {                                                                                                      \
+    cudaError_t _e = (expr);                                                                                \
+    if (_e != cudaSuccess) {                                                                                \
+      rc = set_error(PG_CUDA, std::string("CUDA error: ") + cudaGetErrorString(_e) + " (" #expr ")");       \
+      goto done;                                                                                            \
+    }                                                                                                       \
+  } while (0)
+
+namespace {
+struct DeviceBuf {
+  void* p = nullptr;
+  ~DeviceBuf() {
+    if (p) cudaFree(p);
+  }
+  template <typename T>
+  T* as() { return static_cast<T*>(p); }
+};
+constexpr size_t FLUSH_BYTES = 256u << 20;  // larger than the 126 MB L2
+}  // namespace
+
+extern "C" int pg_op_linear(const float* x, const float* w, const float* bias, const float* resid, int32_t m,
+                            int32_t n, int32_t k, int32_t epilogue, int32_t math_mode, int32_t device, int32_t reps,
+                            float* out, double* seconds_per_launch) {
+  if (!x || !w || !out) return set_error(PG_INVALID_INPUT, "null argument");
+  if (m <= 0 || n <= 0 || k <= 0) return set_error(PG_INVALID_INPUT, "m, n, k must be > 0");
+  if (epilogue < EPI_NONE || epilogue > EPI_RESID) return set_error(PG_INVALID_INPUT, "unknown epilogue");
+  if (epilogue == EPI_RESID && !resid) return set_error(PG_INVALID_INPUT, "residual epilogue needs resid");
+  if (math_mode < PG_MATH_FP32 || math_mode > PG_MATH_TF32) return set_error(PG_INVALID_CONFIG, "math_mode must be fp32, tf32x3 or tf32");
+  if (math_mode != PG_MATH_FP32 && !tc_gemm_supported(m, n, k))
+    return set_error(PG_INVALID_INPUT, "tensor-core modes need k to be a multiple of 32");
+  if (math_mode == PG_MATH_TF32X3 && m > 64) return set_error(PG_INVALID_INPUT, "tf32x3 is the decode path: m <= 64");
+  if (int r = ensure_device(device)) return r;
+  int rc = PG_OK;
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  const size_t xs = (size_t)m * k, ws = (size_t)n * k, os = (size_t)m * n;
+  DeviceBuf dx, dw, db, dr, dout, dhi, dlo, derr, dflush;
+  cudaStream_t s = nullptr;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  int splits = 1;
+  auto run = [&](cudaStream_t st) -> cudaError_t {
+    if (math_mode == PG_MATH_FP32) {
+      LinearArgs a{};
+      a.w = dw.as<float>(); a.bias = db.as<float>(); a.x = dx.as<float>(); a.out = dout.as<float>();
+      a.resid = dr.as<float>(); a.m = m; a.n = n; a.k = k;
+      if (m <= 64 || k % 4 != 0) return launch_linear_decode(a, epilogue, false, st, nullptr);
+      return launch_gemm_f32(a, epilogue, st);
+    }
+    TcGemmArgs a{};
+    a.w = dw.as<float>(); a.bias = db.as<float>(); a.resid = dr.as<float>(); a.out = dout.as<float>();
+    a.error_flag = derr.as<int>(); a.m = m; a.n = n; a.k = k; a.epilogue = epilogue;
+    if (math_mode == PG_MATH_TF32) {
+      a.x = dx.as<float>();
+      return launch_tc_gemm_tf32(a, st);
+    }
+    cudaError_t e = launch_split_tf32(dx.as<float>(), dhi.as<float>(), dlo.as<float>(), xs, false, st);
+    if (e != cudaSuccess) return e;
+    a.x = dhi.as<float>(); a.x_lo = dlo.as<float>();
+    return launch_tc_gemm_x3(a, splits, false, st);
+  };
+  PG_OP_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  PG_OP_TRY(cudaMalloc(&dx.p, xs * 4));
+  PG_OP_TRY(cudaMalloc(&dw.p, ws * 4));
+  PG_OP_TRY(cudaMalloc(&dout.p, os * 4));
+  PG_OP_TRY(cudaMalloc(&derr.p, 4));
+  PG_OP_TRY(cudaMemsetAsync(derr.p, 0, 4, s));
+  PG_OP_TRY(cudaMemcpyAsync(dx.p, x, xs * 4, cudaMemcpyHostToDevice, s));
+  PG_OP_TRY(cudaMemcpyAsync(dw.p, w, ws * 4, cudaMemcpyHostToDevice, s));
+  if (bias) {
+    PG_OP_TRY(cudaMalloc(&db.p, (size_t)n * 4));
+    PG_OP_TRY(cudaMemcpyAsync(db.p, bias, (size_t)n * 4, cudaMemcpyHostToDevice, s));
+  }
+  if (resid && epilogue == EPI_RESID) {
+    PG_OP_TRY(cudaMalloc(&dr.p, os * 4));
+    PG_OP_TRY(cudaMemcpyAsync(dr.p, resid, os * 4, cudaMemcpyHostToDevice, s));
+  }
+  if (math_mode == PG_MATH_TF32X3) {
+    splits = tc_gemm_x3_splits(n, k, sms);
+    PG_OP_TRY(cudaMalloc(&dhi.p, xs * 4));
+    PG_OP_TRY(cudaMalloc(&dlo.p, xs * 4));
+  }
+  PG_OP_TRY(run(s));
+  PG_OP_TRY(cudaMemcpyAsync(out, dout.p, os * 4, cudaMemcpyDeviceToHost, s));
+  PG_OP_TRY(cudaStreamSynchronize(s));
+  {
+    int flag = 0;
+    PG_OP_TRY(cudaMemcpy(&flag, derr.p, 4, cudaMemcpyDeviceToHost));
+    if (flag) {
+      rc = set_error(PG_TIMEOUT, "a bounded wait inside the tensor-core GEMM expired (role code " + std::to_string(flag) + ")");
+      goto done;
+    }
+  }
+  if (reps > 0 && seconds_per_launch) {
+    PG_OP_TRY(cudaMalloc(&dflush.p, FLUSH_BYTES));
+    PG_OP_TRY(cudaEventCreate(&e0));
+    PG_OP_TRY(cudaEventCreate(&e1));
+    double total = 0.0;
+    for (int i = 0; i < reps + 3; ++i) {
+      PG_OP_TRY(cudaMemsetAsync(dflush.p, i, FLUSH_BYTES, s));  // evict the operands from L2
+      PG_OP_TRY(cudaEventRecord(e0, s));
+      PG_OP_TRY(run(s));
+      PG_OP_TRY(cudaEventRecord(e1, s));
+      PG_OP_TRY(cudaEventSynchronize(e1));
+      float ms = 0.f;
+      PG_OP_TRY(cudaEventElapsedTime(&ms, e0, e1));
+      if (i >= 3) total += ms * 1e-3;
+    }
+    *seconds_per_launch = total / reps;
+  }
+done:
+  if (s) cudaStreamSynchronize(s);
+  if (e0) cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  if (s) cudaStreamDestroy(s);
+  return rc;
+}

@@ -1,0 +1,32 @@
+"""Single operators of the path on host arrays (kernel sweeps and operator-level parity tests)."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import numpy as np
+
+from . import _native as N
+from .errors import check
+from .gpt2 import _MATH
+
+EPILOGUES = {"none": 0, "gelu": 1, "resid": 2}
+
+
+def linear(x, w, bias=None, resid=None, epilogue: str = "none", math_mode: str = "fp32", device: int = 0,
+           reps: int = 0):
+    """out = x @ w.T (+ bias) with the epilogue fused; `w` is [out, in] like the reference keeps it
+    after transpose_dense_weights. Returns (out, seconds_per_launch or None)."""
+    x = np.ascontiguousarray(x, np.float32)
+    w = np.ascontiguousarray(w, np.float32)
+    m, k = x.shape
+    n = w.shape[0]
+    assert w.shape[1] == k
+    out = np.empty((m, n), np.float32)
+    fp = lambda a: a.ctypes.data_as(C.POINTER(C.c_float)) if a is not None else None
+    bias = None if bias is None else np.ascontiguousarray(bias, np.float32)
+    resid = None if resid is None else np.ascontiguousarray(resid, np.float32)
+    sec = C.c_double(0.0)
+    check(N.lib.pg_op_linear(fp(x), fp(w), fp(bias), fp(resid), m, n, k, EPILOGUES[epilogue], _MATH[math_mode],
+                             device, reps, fp(out), C.byref(sec)))
+    return out, (float(sec.value) if reps > 0 else None)

@@ -190,9 +190,12 @@ def test_token_by_token_prefill_equals_batched_prefill(midi):
     np.testing.assert_allclose(a.read_layer(1)[0], b.read_layer(1)[0], rtol=1e-4, atol=1e-5)
 
 
-@pytest.mark.parametrize("batch", [2, 5, 8, 12])
-def test_ragged_batches_match_single_sequences(midi, oracle, batch):
+@pytest.mark.parametrize("batch,math_mode", [(2, "fp32"), (5, "fp32"), (8, "fp32"), (12, "fp32"),
+                                             (12, "tf32x3"), (33, "tf32x3"), (64, "tf32x3")])
+def test_ragged_batches_match_single_sequences(midi, oracle, batch, math_mode):
     cfg, w, g, o = midi
+    if math_mode != "fp32":  # linears as three TF32 tensor-core products with FP32 accumulation
+        g = pg.Gpt2Model(cfg, w, pg.Gpt2CudaConfig(math_mode=math_mode))
     prompts = [synthetic.uniform_prompt(100 + i, 3 + 7 * i % 40 + i, cfg["vocab_size"]) for i in range(batch)]
     cache = g.new_kv_cache(max_batch=batch)
     logits, am = g.prefill_batch(prompts, cache, want_logits=True)
@@ -373,7 +376,8 @@ def test_gpt2_small_greedy_stream_is_token_exact_against_golden(oracle):
 
 
 # ------------------------------------------------------------------ GPT-2 medium, 64 sequences (benchmark config)
-def test_gpt2_medium_64_sequences_against_golden_streams():
+@pytest.mark.parametrize("math_mode", ["fp32", "tf32x3"])
+def test_gpt2_medium_64_sequences_against_golden_streams(math_mode):
     """64 prompts of 128 tokens, 256 greedy tokens each, against the oracle's committed streams.
     Teacher-forced: every step is fed the golden token, so all 64 x 256 arg-max decisions are
     checked even after a near-tie. A GPU arg-max may differ from the golden one only where the
@@ -387,7 +391,7 @@ def test_gpt2_medium_64_sequences_against_golden_streams():
     tokens = np.array(gold["tokens"], np.int64)  # [seq, step]
     gaps = np.array(gold["top2_gap"], np.float32)
     n_seq, n_new = tokens.shape
-    g = pg.Gpt2Model(cfg, w)
+    g = pg.Gpt2Model(cfg, w, pg.Gpt2CudaConfig(math_mode=math_mode))
     cache = g.new_kv_cache(max_batch=n_seq)
     _, am = g.prefill_batch(prompts, cache)
     near_tie = 1e-4
