@@ -324,7 +324,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-template <int BN>
+template <int BN, int SPLITS>
 __global__ void __launch_bounds__(192, 2)
     tc_gemm_x3_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_xhi,
                       const __grid_constant__ CUtensorMap map_xlo, TcGemmArgs a) {
@@ -341,7 +341,7 @@ __global__ void __launch_bounds__(192, 2)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * TILE_M;  // first weight row (output feature) of this tile
-  const int splits = gridDim.y;
+  constexpr int splits = SPLITS;          // == gridDim.y == cluster size
   const int split = (int)cluster_rank();  // == blockIdx.y: the cluster spans the whole y extent
   const int nkb_total = a.k / BK;
   const int kb_per = (nkb_total + splits - 1) / splits;
@@ -371,6 +371,9 @@ __global__ void __launch_bounds__(192, 2)
 
   if (warp == 0) {
     if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_xhi) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_xlo) : "memory");
       // weights do not depend on the previous kernel: start streaming them before the wait
       const int pre = min(nkb, S::STAGES);
       for (int i = 0; i < pre; ++i) {
@@ -458,23 +461,43 @@ __global__ void __launch_bounds__(192, 2)
   // every thread of every CTA of the cluster passes both cluster barriers exactly once
   tc_fence_before();
   __syncthreads();
+  // this CTA finishes rows [split * 128 / SPLITS, ...) of the tile: thread -> (row, token group)
+  constexpr int ROWS_PER = TILE_M / SPLITS, OUTS = BN / SPLITS;
+  const int t = (int)threadIdx.x - 64;
+  const int rl = t >= 0 ? t % ROWS_PER : 0, tg = t >= 0 ? t / ROWS_PER : 0;
+  const int row = split * ROWS_PER + rl;
+  const int feat = n0 + row;
+  const bool active = warp >= 2 && feat < a.n;
+  float bias_v = 0.f, resid_v[OUTS];
+  if (warp >= 2) pdl_wait();  // resid may come from the previous kernel; out must not be written before it ended
+  if (active) {
+    // loads that do not depend on the peers go out before the cluster barrier
+    if (a.bias) bias_v = a.bias[feat];
+#pragma unroll
+    for (int o = 0; o < OUTS; ++o) {
+      const int j = tg + o * SPLITS;
+      resid_v[o] = (a.epilogue == EPI_RESID && j < a.m) ? a.resid[(size_t)j * a.n + feat] : 0.f;
+    }
+  }
   cluster_sync_all();
-  if (warp >= 2 && !*failed) {
-    pdl_wait();  // resid may come from the previous kernel; out must not be written before it ended
-    const int t = threadIdx.x - 64;
-    const int rows_per = TILE_M / splits;  // rows of the tile this CTA finishes
-    const int rl = t % rows_per, tg = t / rows_per;
-    const int row = split * rows_per + rl;
-    const int feat = n0 + row;
+  if (active && !*failed) {
     const uint32_t dbuf_addr = smem_u32(dbuf);
-    if (feat < a.n) {
-      const float b = a.bias ? a.bias[feat] : 0.f;
-      for (int j = tg; j < BN && j < a.m; j += splits) {
-        float acc = 0.f;
-        for (int sp = 0; sp < splits; ++sp) acc += ld_dsmem(dbuf_addr + (uint32_t)(j * TILE_M + row) * 4u, (uint32_t)sp);
-        float v = a.bias ? b + acc : acc;
+    float part[OUTS][SPLITS];
+#pragma unroll
+    for (int o = 0; o < OUTS; ++o)
+#pragma unroll
+      for (int sp = 0; sp < SPLITS; ++sp)
+        part[o][sp] = ld_dsmem(dbuf_addr + (uint32_t)((tg + o * SPLITS) * TILE_M + row) * 4u, (uint32_t)sp);
+#pragma unroll
+    for (int o = 0; o < OUTS; ++o) {
+      const int j = tg + o * SPLITS;
+      float acc = 0.f;
+#pragma unroll
+      for (int sp = 0; sp < SPLITS; ++sp) acc += part[o][sp];  // split order: deterministic
+      if (j < a.m) {
+        float v = a.bias ? bias_v + acc : acc;
         if (a.epilogue == EPI_GELU) v = gelu_ref(v);
-        if (a.epilogue == EPI_RESID) v = a.resid[(size_t)j * a.n + feat] + v;
+        if (a.epilogue == EPI_RESID) v = resid_v[o] + v;
         if (a.out) a.out[(size_t)j * a.n + feat] = v;
         if (a.out_hi) {
           const float h = tf32_hi(v);
@@ -561,12 +584,15 @@ cudaError_t init_tc_kernel_attributes() {
   if (e != cudaSuccess) return e;
   e = cudaFuncSetAttribute(tc_gemm_ss_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SsSmem<256>::BYTES);
   if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(tc_gemm_x3_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)X3<64>::BYTES);
+#define PG_X3_ATTR(BN_, SP_)                                                                                  \
+  e = cudaFuncSetAttribute(tc_gemm_x3_kernel<BN_, SP_>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
+                           (int)X3<BN_>::BYTES);                                                              \
   if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(tc_gemm_x3_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)X3<32>::BYTES);
-  if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(tc_gemm_x3_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)X3<16>::BYTES);
-  return e;
+  PG_X3_ATTR(64, 1) PG_X3_ATTR(64, 2) PG_X3_ATTR(64, 4) PG_X3_ATTR(64, 8)
+  PG_X3_ATTR(32, 1) PG_X3_ATTR(32, 2) PG_X3_ATTR(32, 4) PG_X3_ATTR(32, 8)
+  PG_X3_ATTR(16, 1) PG_X3_ATTR(16, 2) PG_X3_ATTR(16, 4) PG_X3_ATTR(16, 8)
+#undef PG_X3_ATTR
+  return cudaSuccess;
 }
 
 cudaError_t launch_tc_gemm_tf32(const TcGemmArgs& a, cudaStream_t s) {
@@ -585,9 +611,10 @@ int tc_gemm_x3_splits(int n, int k, int num_sms) {
   const int tiles = (n + TILE_M - 1) / TILE_M;
   const int nkb = k / BK;
   int splits = 1;
-  // spread small matrices over the SMs (two CTAs fit on one), but keep at least 4 k-blocks
+  // spread small matrices over the SMs, one CTA per SM at most so that the next kernel of a
+  // programmatic-launch chain finds room to prefetch its weights; keep at least 4 k-blocks
   // (64 KB of weights) per CTA; 8 is the portable cluster size
-  while (tiles * splits * 2 <= 2 * num_sms && nkb / (splits * 2) >= 4 && splits < 8) splits *= 2;
+  while (tiles * splits * 2 <= num_sms && nkb / (splits * 2) >= 4 && splits < 8) splits *= 2;
   return splits;
 }
 
@@ -602,11 +629,13 @@ cudaError_t launch_tc_gemm_x3(const TcGemmArgs& a, int splits, bool pdl, cudaStr
   TcGemmArgs args = a;
   void* params[4] = {&mw, &mhi, &mlo, &args};
   dim3 grid((a.n + TILE_M - 1) / TILE_M, splits);
-  switch (bn) {
-    case 16: return launch_ex(tc_gemm_x3_kernel<16>, grid, X3<16>::BYTES, s, pdl, params, splits);
-    case 32: return launch_ex(tc_gemm_x3_kernel<32>, grid, X3<32>::BYTES, s, pdl, params, splits);
-    default: return launch_ex(tc_gemm_x3_kernel<64>, grid, X3<64>::BYTES, s, pdl, params, splits);
-  }
+#define PG_X3_CASE(BN_, SP_) \
+  if (bn == BN_ && splits == SP_) return launch_ex(tc_gemm_x3_kernel<BN_, SP_>, grid, X3<BN_>::BYTES, s, pdl, params, splits);
+  PG_X3_CASE(64, 1) PG_X3_CASE(64, 2) PG_X3_CASE(64, 4) PG_X3_CASE(64, 8)
+  PG_X3_CASE(32, 1) PG_X3_CASE(32, 2) PG_X3_CASE(32, 4) PG_X3_CASE(32, 8)
+  PG_X3_CASE(16, 1) PG_X3_CASE(16, 2) PG_X3_CASE(16, 4) PG_X3_CASE(16, 8)
+#undef PG_X3_CASE
+  return cudaErrorInvalidValue;
 }
 
 }  // namespace pg
