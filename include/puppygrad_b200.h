@@ -219,6 +219,17 @@ uint64_t pg_cache_kernel_launches(const pg_cache* cache);
 int pg_op_linear(const float* x, const float* w, const float* bias, const float* resid, int32_t m,
                  int32_t n, int32_t k, int32_t epilogue, int32_t math_mode, int32_t device,
                  int32_t reps, float* out, double* seconds_per_launch);
+/* Attention of one new token per sequence over cached keys and values, on host buffers:
+ * cached_self_attention_into, src/models/gpt2/rust.rs:1662-1741. qkv is [batch][3 * n_head *
+ * head_dim] (q, k, v of the new token); keys / values are [batch][n_head][kv_len][head_dim], the
+ * kv_len positions already cached (the reference's per-head layout, kv_index, rust.rs:1851-1855,
+ * without the unused tail). out is [batch][n_head * head_dim]. The cache is laid out in pages of
+ * `page_tokens` with a permuted page table; `splits` is the split-K factor (head_dim 64 only).
+ * Timing as in pg_op_linear. */
+int pg_op_decode_attention(const float* qkv, const float* keys, const float* values, int32_t batch,
+                           int32_t n_head, int32_t head_dim, int32_t kv_len, int32_t page_tokens,
+                           int32_t splits, int32_t device, int32_t reps, float* out,
+                           double* seconds_per_launch);
 
 /* ------------------------------------------------------------------ generation loops */
 /* non-zero return aborts generation (the closure returning Err in the reference) */

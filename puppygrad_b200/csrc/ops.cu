@@ -3,6 +3,7 @@
 // model path in model.cu launches the same kernels directly.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <string>
 #include <vector>
 
@@ -116,6 +117,99 @@ extern "C" int pg_op_linear(const float* x, const float* w, const float* bias, c
       PG_OP_TRY(cudaMemsetAsync(dflush.p, i, FLUSH_BYTES, s));  // evict the operands from L2
       PG_OP_TRY(cudaEventRecord(e0, s));
       PG_OP_TRY(run(s));
+      PG_OP_TRY(cudaEventRecord(e1, s));
+      PG_OP_TRY(cudaEventSynchronize(e1));
+      float ms = 0.f;
+      PG_OP_TRY(cudaEventElapsedTime(&ms, e0, e1));
+      if (i >= 3) total += ms * 1e-3;
+    }
+    *seconds_per_launch = total / reps;
+  }
+done:
+  if (s) cudaStreamSynchronize(s);
+  if (e0) cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  if (s) cudaStreamDestroy(s);
+  return rc;
+}
+
+// Decode attention of one new token per sequence on host buffers (cached_self_attention_into,
+// src/models/gpt2/rust.rs:1662-1741). keys/values: [batch][head][kv_len][head_dim], the positions
+// already cached; qkv: [batch][3c], the new token's q, k, v. The entry point lays the cache out in
+// pages (with a permuted page table), runs the kernel and returns out[batch][c].
+extern "C" int pg_op_decode_attention(const float* qkv, const float* keys, const float* values, int32_t batch,
+                                      int32_t n_head, int32_t head_dim, int32_t kv_len, int32_t page_tokens,
+                                      int32_t splits, int32_t device, int32_t reps, float* out,
+                                      double* seconds_per_launch) {
+  if (!qkv || !out || (kv_len > 0 && (!keys || !values))) return set_error(PG_INVALID_INPUT, "null argument");
+  if (batch <= 0 || n_head <= 0 || head_dim <= 0 || kv_len < 0) return set_error(PG_INVALID_INPUT, "bad shape");
+  if (page_tokens != 16 && page_tokens != 32 && page_tokens != 64) return set_error(PG_INVALID_CONFIG, "cuda page_tokens must be 16, 32 or 64");
+  if (splits < 1 || splits > 16) return set_error(PG_INVALID_CONFIG, "cuda attn_splits must be in 1..16");
+  if (head_dim != 64) splits = 1;
+  if (int r = ensure_device(device)) return r;
+  int rc = PG_OK;
+  const int c = n_head * head_dim;
+  KvLayout kv{n_head, head_dim, page_tokens, (kv_len + 1 + page_tokens - 1) / page_tokens};
+  const int pages = batch * kv.pages_per_seq;
+  const size_t page_floats = (size_t)2 * n_head * page_tokens * head_dim;
+  // page p of sequence b lives at physical page (b + p * batch) * 7919 % pages-ish: any bijection
+  std::vector<int> table((size_t)pages);
+  {
+    std::vector<int> perm(pages);
+    for (int i = 0; i < pages; ++i) perm[i] = i;
+    uint64_t st = 0x9e3779b97f4a7c15ULL;
+    for (int i = pages - 1; i > 0; --i) {
+      st = st * 6364136223846793005ULL + 1442695040888963407ULL;
+      std::swap(perm[i], perm[(int)((st >> 33) % (uint64_t)(i + 1))]);
+    }
+    for (int i = 0; i < pages; ++i) table[i] = perm[i];
+  }
+  std::vector<float> pool((size_t)pages * page_floats, 0.f);
+  for (int b = 0; b < batch; ++b)
+    for (int h = 0; h < n_head; ++h)
+      for (int p = 0; p < kv_len; ++p) {
+        const int page = table[(size_t)b * kv.pages_per_seq + p / page_tokens], off = p % page_tokens;
+        const size_t src = (((size_t)b * n_head + h) * kv_len + p) * head_dim;
+        const size_t kd = ((((size_t)page * 2 + 0) * n_head + h) * page_tokens + off) * head_dim;
+        const size_t vd = ((((size_t)page * 2 + 1) * n_head + h) * page_tokens + off) * head_dim;
+        for (int d = 0; d < head_dim; ++d) {
+          pool[kd + d] = keys[src + d];
+          pool[vd + d] = values[src + d];
+        }
+      }
+  std::vector<int> pos((size_t)batch, kv_len);
+  DeviceBuf dq, dout, dpool, dtab, dpos, dpart, dcnt, dflush;
+  cudaStream_t s = nullptr;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  DecodeAttnArgs a{};
+  PG_OP_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  PG_OP_TRY(cudaMalloc(&dq.p, (size_t)batch * 3 * c * 4));
+  PG_OP_TRY(cudaMalloc(&dout.p, (size_t)batch * c * 4));
+  PG_OP_TRY(cudaMalloc(&dpool.p, pool.size() * 4));
+  PG_OP_TRY(cudaMalloc(&dtab.p, table.size() * 4));
+  PG_OP_TRY(cudaMalloc(&dpos.p, pos.size() * 4));
+  PG_OP_TRY(cudaMalloc(&dpart.p, (size_t)batch * n_head * splits * (head_dim + 2) * 4));
+  PG_OP_TRY(cudaMalloc(&dcnt.p, (size_t)batch * n_head * 4));
+  PG_OP_TRY(cudaMemsetAsync(dcnt.p, 0, (size_t)batch * n_head * 4, s));
+  PG_OP_TRY(cudaMemcpyAsync(dq.p, qkv, (size_t)batch * 3 * c * 4, cudaMemcpyHostToDevice, s));
+  PG_OP_TRY(cudaMemcpyAsync(dpool.p, pool.data(), pool.size() * 4, cudaMemcpyHostToDevice, s));
+  PG_OP_TRY(cudaMemcpyAsync(dtab.p, table.data(), table.size() * 4, cudaMemcpyHostToDevice, s));
+  PG_OP_TRY(cudaMemcpyAsync(dpos.p, pos.data(), pos.size() * 4, cudaMemcpyHostToDevice, s));
+  a.qkv = dq.as<float>(); a.out = dout.as<float>(); a.kv_pool = dpool.as<float>(); a.page_table = dtab.as<int>();
+  a.pos = dpos.as<int>(); a.part = dpart.as<float>(); a.counters = dcnt.as<unsigned>(); a.kv = kv;
+  a.batch = batch; a.splits = splits;
+  PG_OP_TRY(launch_decode_attention(a, false, s));
+  PG_OP_TRY(cudaMemcpyAsync(out, dout.p, (size_t)batch * c * 4, cudaMemcpyDeviceToHost, s));
+  PG_OP_TRY(cudaStreamSynchronize(s));
+  if (reps > 0 && seconds_per_launch) {
+    PG_OP_TRY(cudaMalloc(&dflush.p, FLUSH_BYTES));
+    PG_OP_TRY(cudaEventCreate(&e0));
+    PG_OP_TRY(cudaEventCreate(&e1));
+    double total = 0.0;
+    for (int i = 0; i < reps + 3; ++i) {
+      PG_OP_TRY(cudaMemsetAsync(dflush.p, i, FLUSH_BYTES, s));
+      PG_OP_TRY(cudaEventRecord(e0, s));
+      PG_OP_TRY(launch_decode_attention(a, false, s));
       PG_OP_TRY(cudaEventRecord(e1, s));
       PG_OP_TRY(cudaEventSynchronize(e1));
       float ms = 0.f;

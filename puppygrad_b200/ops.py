@@ -30,3 +30,19 @@ def linear(x, w, bias=None, resid=None, epilogue: str = "none", math_mode: str =
     check(N.lib.pg_op_linear(fp(x), fp(w), fp(bias), fp(resid), m, n, k, EPILOGUES[epilogue], _MATH[math_mode],
                              device, reps, fp(out), C.byref(sec)))
     return out, (float(sec.value) if reps > 0 else None)
+
+
+def decode_attention(qkv, keys, values, page_tokens: int = 32, splits: int = 1, device: int = 0, reps: int = 0):
+    """One new token per sequence against `kv_len` cached positions.
+    qkv [batch, 3*c]; keys, values [batch, n_head, kv_len, head_dim]. Returns (out [batch, c], seconds)."""
+    keys = np.ascontiguousarray(keys, np.float32)
+    values = np.ascontiguousarray(values, np.float32)
+    qkv = np.ascontiguousarray(qkv, np.float32)
+    batch, n_head, kv_len, head_dim = keys.shape
+    assert qkv.shape == (batch, 3 * n_head * head_dim)
+    out = np.empty((batch, n_head * head_dim), np.float32)
+    fp = lambda a: a.ctypes.data_as(C.POINTER(C.c_float))
+    sec = C.c_double(0.0)
+    check(N.lib.pg_op_decode_attention(fp(qkv), fp(keys), fp(values), batch, n_head, head_dim, kv_len, page_tokens,
+                                       splits, device, reps, fp(out), C.byref(sec)))
+    return out, (float(sec.value) if reps > 0 else None)

@@ -1,0 +1,98 @@
+"""Operator-level GPU parity: single kernels through the C ABI against the CPU oracle's kernels
+(shapes of the GPT-2 XL kernel sweep, reduced where the oracle would take long)."""
+import numpy as np
+import pytest
+
+from puppygrad_b200 import ops
+
+pytestmark = pytest.mark.gpu
+
+
+def oracle_linear(oracle, x, w, b, epilogue, resid):
+    m, k = x.shape
+    n = w.shape[0]
+    out = oracle.transposed_dense_projection(x.reshape(-1), m, k, n, w.reshape(-1), b).reshape(m, n)
+    if epilogue == "gelu":
+        out = oracle.gelu(out).reshape(m, n)
+    if epilogue == "resid":
+        out = (resid + out).astype(np.float32)  # add_in_place: dst += src
+    return out
+
+
+# FP32 path: 1e-3 relative / 1e-4 absolute on values of magnitude sqrt(k).
+@pytest.mark.parametrize("m,n,k", [(1, 4800, 1600), (8, 1600, 1600), (64, 6400, 1600), (3, 1600, 6400),
+                                   (5, 50257, 768), (2, 7, 37), (300, 200, 96)])
+@pytest.mark.parametrize("epilogue", ["none", "gelu", "resid"])
+def test_linear_fp32_matches_oracle(oracle, m, n, k, epilogue):
+    rng = np.random.default_rng(m * 31 + n * 7 + k)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.05)
+    b = rng.standard_normal(n, dtype=np.float32)
+    r = rng.standard_normal((m, n), dtype=np.float32)
+    got, _ = ops.linear(x, w, b, r if epilogue == "resid" else None, epilogue, "fp32")
+    np.testing.assert_allclose(got, oracle_linear(oracle, x, w, b, epilogue, r), rtol=1e-3, atol=1e-4)
+
+
+@pytest.mark.parametrize("m,n,k", [(9, 4800, 1600), (16, 1600, 1600), (64, 6400, 1600), (33, 1600, 6400),
+                                   (64, 50257, 1024), (40, 1000, 256)])
+@pytest.mark.parametrize("epilogue", ["none", "gelu", "resid"])
+def test_linear_tf32x3_matches_oracle(oracle, m, n, k, epilogue):
+    """Three TF32 tensor-core products with FP32 accumulation: the same bound as the FP32 path."""
+    rng = np.random.default_rng(m * 31 + n * 7 + k + 1)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.05)
+    b = rng.standard_normal(n, dtype=np.float32)
+    r = rng.standard_normal((m, n), dtype=np.float32)
+    got, _ = ops.linear(x, w, b, r if epilogue == "resid" else None, epilogue, "tf32x3")
+    np.testing.assert_allclose(got, oracle_linear(oracle, x, w, b, epilogue, r), rtol=1e-3, atol=1e-4)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 32), (512, 4800, 1600), (1000, 770, 768), (4096, 1600, 6400)])
+def test_linear_tf32_single_pass_is_within_its_stated_bound(oracle, m, n, k):
+    """One TF32 pass (10-bit mantissas, truncated): error <= 2e-3 of the output scale
+    sqrt(k) * |x| * |w|, the looser bound of the TF32 prefill variant."""
+    rng = np.random.default_rng(m + n + k)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.05)
+    b = rng.standard_normal(n, dtype=np.float32)
+    got, _ = ops.linear(x, w, b, None, "none", "tf32")
+    rows = slice(0, min(m, 64))
+    want = oracle_linear(oracle, x[rows], w, b, "none", None)
+    scale = float(np.abs(want).max())
+    assert np.abs(got[rows] - want).max() <= 2e-3 * scale
+    full = x.astype(np.float64) @ w.astype(np.float64).T + b
+    assert np.abs(got - full).max() <= 2e-3 * np.abs(full).max()
+
+
+def oracle_attention(oracle, qkv, keys, values):
+    """cached_self_attention_into (rust.rs:1662-1741) restated with the oracle's kernels: scalar
+    sequential score sums, oracle softmax, value accumulation in key order."""
+    batch, n_head, kv_len, d = keys.shape
+    c = n_head * d
+    out = np.zeros((batch, c), np.float32)
+    scale = np.float32(1.0) / np.sqrt(np.float32(d))
+    for b in range(batch):
+        for h in range(n_head):
+            q = qkv[b, h * d:(h + 1) * d]
+            k_all = np.concatenate([keys[b, h], qkv[b, c + h * d:c + (h + 1) * d][None]], 0)
+            v_all = np.concatenate([values[b, h], qkv[b, 2 * c + h * d:2 * c + (h + 1) * d][None]], 0)
+            scores = np.array([np.float32(oracle.dot_scalar(q, k_all[i])) * scale for i in range(kv_len + 1)],
+                              np.float32)
+            p = oracle.softmax(scores)
+            acc = np.zeros(d, np.float32)
+            for i in range(kv_len + 1):
+                acc = (acc + p[i] * v_all[i]).astype(np.float32)
+            out[b, h * d:(h + 1) * d] = acc
+    return out
+
+
+@pytest.mark.parametrize("batch,n_head,d,kv_len,page,splits", [
+    (1, 25, 64, 128, 32, 1), (3, 25, 64, 255, 16, 4), (2, 12, 64, 1023, 64, 8), (32, 4, 64, 300, 32, 2),
+    (2, 3, 8, 17, 16, 1), (1, 2, 64, 0, 32, 1), (4, 16, 64, 31, 32, 16)])
+def test_decode_attention_matches_oracle(oracle, batch, n_head, d, kv_len, page, splits):
+    rng = np.random.default_rng(batch + n_head + kv_len)
+    qkv = rng.standard_normal((batch, 3 * n_head * d), dtype=np.float32)
+    keys = rng.standard_normal((batch, n_head, kv_len, d), dtype=np.float32)
+    values = rng.standard_normal((batch, n_head, kv_len, d), dtype=np.float32)
+    got, _ = ops.decode_attention(qkv, keys, values, page_tokens=page, splits=splits)
+    np.testing.assert_allclose(got, oracle_attention(oracle, qkv, keys, values), rtol=1e-3, atol=1e-4)
