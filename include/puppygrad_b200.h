@@ -230,6 +230,26 @@ int pg_op_decode_attention(const float* qkv, const float* keys, const float* val
                            int32_t n_head, int32_t head_dim, int32_t kv_len, int32_t page_tokens,
                            int32_t splits, int32_t device, int32_t reps, float* out,
                            double* seconds_per_launch);
+/* No counterpart in the reference (its CPU path owns no device memory at all). The same decode
+ * attention kernel as above for callers that must not allocate when they call it — a server
+ * whose own pool already owns all of HBM, a plugin invoked where its embedder forbids cudaMalloc,
+ * a latency-critical loop that wants no allocator call: this entry point calls no cudaMalloc,
+ * cudaFree or any allocating library routine. All pointers are DEVICE pointers owned by the
+ * caller: d_qkv [batch][3 * n_head * head_dim]; d_out [batch][n_head * head_dim]; d_kv_pool, one
+ * layer's pages laid out [page][2 (K, V)][n_head][page_tokens][head_dim]; d_page_table
+ * [batch][pages_per_seq] physical page of each logical page; d_pos [batch], the position of the
+ * new token (= positions already cached). The kernel appends the new K, V at d_pos and writes
+ * d_out; it is enqueued on `stream` (a cudaStream_t, NULL = the default stream) and not waited
+ * for. The split-K partials live in an array inside the library image (4.1 MiB per GPU that loads
+ * the library, held until exit), which bounds the sizes: batch * n_head <= 2048 and splits <= 8;
+ * larger requests fail with PG_INVALID_INPUT. The first call on a device looks up that array's
+ * address for the device and sets kernel attributes; make that first call before any stream
+ * capture begins. Every call shares the one array: two calls whose kernels overlap on the GPU
+ * (different streams, different threads) race on it, so keep calls on one device ordered. */
+int pg_decode_attention_noalloc(const float* d_qkv, float* d_out, float* d_kv_pool,
+                                const int32_t* d_page_table, const int32_t* d_pos, int32_t batch,
+                                int32_t n_head, int32_t head_dim, int32_t page_tokens,
+                                int32_t pages_per_seq, int32_t splits, int32_t device, void* stream);
 
 /* ------------------------------------------------------------------ generation loops */
 /* non-zero return aborts generation (the closure returning Err in the reference) */

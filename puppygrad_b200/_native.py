@@ -87,6 +87,8 @@ SIGNATURES = {
                                C.c_int32, C.c_int32, _fp, C.POINTER(C.c_double)]),
     "pg_op_decode_attention": (C.c_int, [_fp, _fp, _fp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                          C.c_int32, C.c_int32, C.c_int32, _fp, C.POINTER(C.c_double)]),
+    "pg_decode_attention_noalloc": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                              C.c_int32, C.c_int32, C.c_int32, _vp]),
     "pg_generate_greedy": (C.c_int, [_vp, _ip, C.c_int32, C.c_uint64, _ip, _u64p]),
     "pg_stream_greedy_tokens": (C.c_int, [_vp, _ip, C.c_int32, C.c_uint64, TOKEN_CALLBACK, _vp, _ip, _u64p]),
     "pg_generate_with_config": (C.c_int, [_vp, _ip, C.c_int32, C.POINTER(PgGenerationConfig), TOKEN_CALLBACK,

@@ -9,6 +9,9 @@
 #include <cfloat>
 #include <climits>
 
+#include <mutex>
+
+#include "common.h"
 #include "kernels.cuh"
 
 namespace pg {
@@ -1165,3 +1168,82 @@ cudaError_t launch_topk_rows(const float* logits, int m, int n, int k, float* va
 }
 
 }  // namespace pg
+
+// ================================================================== decode attention without allocation
+// Some hosts of this library may not allocate device memory at the point where they run a decode
+// step: a serving loop that has handed every byte of HBM to its own pool allocator, a plugin that
+// is called inside a region where its embedder forbids cudaMalloc (allocation synchronises the
+// device and can fail late), or a real-time path that wants no allocator call at all. For them
+// the split-K scratch of the decode attention kernel lives in the library image itself.
+namespace pg {
+int ensure_device(int device);  // model.cu
+}
+
+namespace {
+
+constexpr int NOALLOC_MAX_PAIRS = 2048;   // batch * n_head
+constexpr int NOALLOC_MAX_SPLITS = 8;
+constexpr int NOALLOC_HEAD_DIM = 64;
+constexpr size_t NOALLOC_PART_FLOATS = (size_t)NOALLOC_MAX_PAIRS * NOALLOC_MAX_SPLITS * (NOALLOC_HEAD_DIM + 2);
+// [partials: pairs x splits x (64 + 2) floats][arrival counters: one 32-bit word per pair], 4.1 MiB.
+// Every GPU that loads the library holds one copy until the process exits.
+static __device__ __align__(256) float g_attn_static_scratch[NOALLOC_PART_FLOATS + NOALLOC_MAX_PAIRS];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+std::mutex g_noalloc_mu;
+float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+
+// In host code `g_attn_static_scratch` is only a handle for the symbol, not a device address:
+// the address on the current device has to be asked for, once per device.
+int noalloc_scratch(int device, float** out) {
+  std::lock_guard<std::mutex> g(g_noalloc_mu);
+  if (!g_noalloc_ptr[device]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_attn_static_scratch);
+    if (e != cudaSuccess)
+      return pg::set_error(PG_CUDA, std::string("cudaGetSymbolAddress failed: ") + cudaGetErrorString(e));
+    g_noalloc_ptr[device] = static_cast<float*>(p);
+  }
+  *out = g_noalloc_ptr[device];
+  return PG_OK;
+}
+
+}  // namespace
+
+extern "C" int pg_decode_attention_noalloc(const float* d_qkv, float* d_out, float* d_kv_pool,
+                                           const int32_t* d_page_table, const int32_t* d_pos, int32_t batch,
+                                           int32_t n_head, int32_t head_dim, int32_t page_tokens,
+                                           int32_t pages_per_seq, int32_t splits, int32_t device, void* stream) {
+  using namespace pg;
+  if (!d_qkv || !d_out || !d_kv_pool || !d_page_table || !d_pos) return set_error(PG_INVALID_INPUT, "null argument");
+  if (batch <= 0 || n_head <= 0 || head_dim <= 0 || pages_per_seq <= 0) return set_error(PG_INVALID_INPUT, "bad shape");
+  if (page_tokens != 16 && page_tokens != 32 && page_tokens != 64)
+    return set_error(PG_INVALID_CONFIG, "cuda page_tokens must be 16, 32 or 64");
+  if (device < 0 || device >= NOALLOC_MAX_DEVICES) return set_error(PG_INVALID_INPUT, "device ordinal out of range");
+  if (head_dim != NOALLOC_HEAD_DIM) splits = 1;  // only the head_dim 64 kernel splits (and uses scratch)
+  if (splits < 1 || splits > NOALLOC_MAX_SPLITS)
+    return set_error(PG_INVALID_INPUT, "splits " + std::to_string(splits) + " exceeds the built-in scratch limit of " +
+                                           std::to_string(NOALLOC_MAX_SPLITS));
+  if ((int64_t)batch * n_head > NOALLOC_MAX_PAIRS)
+    return set_error(PG_INVALID_INPUT, "batch * n_head = " + std::to_string((int64_t)batch * n_head) +
+                                           " exceeds the built-in scratch limit of " + std::to_string(NOALLOC_MAX_PAIRS));
+  if ((int64_t)pages_per_seq * page_tokens > 16320 * (int64_t)splits)
+    return set_error(PG_INVALID_INPUT, "context too long for the kernel's score buffer");
+  if (int r = ensure_device(device)) return r;  // makes `device` current; allocates nothing
+  float* scratch = nullptr;
+  if (int r = noalloc_scratch(device, &scratch)) return r;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  unsigned* counters = reinterpret_cast<unsigned*>(scratch + NOALLOC_PART_FLOATS);
+  // the array keeps whatever the last call left: the arrival counters must start at zero
+  cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)batch * n_head * sizeof(unsigned), s);
+  if (e != cudaSuccess) return set_error(PG_CUDA, std::string("CUDA error: ") + cudaGetErrorString(e));
+  DecodeAttnArgs a{};
+  a.qkv = d_qkv; a.out = d_out; a.kv_pool = d_kv_pool; a.page_table = d_page_table; a.pos = d_pos;
+  a.part = scratch; a.counters = counters;
+  a.kv = KvLayout{n_head, head_dim, page_tokens, pages_per_seq};
+  a.batch = batch; a.splits = splits;
+  e = launch_decode_attention(a, false, s);
+  if (e != cudaSuccess) return set_error(PG_CUDA, std::string("CUDA error: ") + cudaGetErrorString(e));
+  return PG_OK;
+}
+

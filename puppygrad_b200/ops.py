@@ -46,3 +46,14 @@ def decode_attention(qkv, keys, values, page_tokens: int = 32, splits: int = 1, 
     check(N.lib.pg_op_decode_attention(fp(qkv), fp(keys), fp(values), batch, n_head, head_dim, kv_len, page_tokens,
                                        splits, device, reps, fp(out), C.byref(sec)))
     return out, (float(sec.value) if reps > 0 else None)
+
+
+def decode_attention_noalloc(d_qkv: int, d_out: int, d_kv_pool: int, d_page_table: int, d_pos: int, batch: int,
+                             n_head: int, head_dim: int, page_tokens: int, pages_per_seq: int, splits: int = 1,
+                             device: int = 0, stream: int = 0) -> None:
+    """Decode attention on device buffers the caller owns (arguments are raw device addresses),
+    for callers that may not allocate device memory when they call: the kernel's split-K scratch
+    is an array built into the library. Enqueues on `stream` and returns without waiting. Limits:
+    batch * n_head <= 2048, splits <= 8. Calls on one device must not overlap on the GPU."""
+    check(N.lib.pg_decode_attention_noalloc(d_qkv, d_out, d_kv_pool, d_page_table, d_pos, batch, n_head, head_dim,
+                                            page_tokens, pages_per_seq, splits, device, stream or None))
