@@ -203,7 +203,7 @@ def run_ours(args):
     import torch.distributed as dist
 
     import puppygrad_b200 as pg
-    from puppygrad_b200 import synthetic
+    from puppygrad_b200 import sharding, synthetic
 
     if world > 1:
         torch.cuda.set_device(local)
@@ -241,10 +241,7 @@ def run_ours(args):
     launches = cache.kernel_launches() - launches0
     lens_mid = [PROMPT_LEN + W + K // 2] * B
 
-    t = torch.tensor([sec], dtype=torch.float64, device=f"cuda:{local}")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    sec_max = float(t.item())
+    sec_max = sharding.max_over_ranks(sec, device=f"cuda:{local}")
     value = world * B * K / sec_max
     if args.skip_extras:  # profiling runs: only the timed decode loop
         if rank == 0:
@@ -265,10 +262,7 @@ def run_ours(args):
         _, cur, _, _ = model.forward_one_batch(cur, cache)
     e2e_sec = time.perf_counter() - t0
     barrier()
-    t = torch.tensor([e2e_sec], dtype=torch.float64, device=f"cuda:{local}")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_value = world * B * K / float(t.item())
+    e2e_value = world * B * K / sharding.max_over_ranks(e2e_sec, device=f"cuda:{local}")
 
     # ---- per-operation device time of one step (kernel by kernel), for the roofline line
     _, cur = model.prefill_batch(prompts, cache)

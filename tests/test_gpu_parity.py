@@ -414,3 +414,25 @@ def test_gpt2_medium_64_sequences_against_golden_streams(math_mode):
             assert gaps[i, diff[0]] < near_tie, (i, int(diff[0]), float(gaps[i, diff[0]]))
     exact = sum(int(np.array_equal(got[i], tokens[i])) for i in range(n_seq))
     assert exact >= n_seq - 4
+
+
+def test_sharding_over_two_gpus_gives_the_single_gpu_streams(midi):
+    """Sequence i on GPU i mod G: every sequence's stream is independent of G."""
+    from puppygrad_b200 import _native, sharding
+    if _native.lib.pg_device_count() < 2:
+        pytest.skip("needs two GPUs")
+    cfg, w, g0, o = midi
+    prompts = [synthetic.uniform_prompt(700 + i, 10 + i, cfg["vocab_size"]) for i in range(6)]
+
+    def run(model, idx):
+        cache = model.new_kv_cache(max_batch=len(idx))
+        _, first = model.prefill_batch([prompts[i] for i in idx], cache)
+        toks = model.decode_greedy(first, cache, 20)
+        return {i: [int(first[j])] + [int(t) for t in toks[:, j]] for j, i in enumerate(idx)}
+
+    single = run(g0, list(range(6)))
+    merged = {}
+    for rank in range(2):
+        model = pg.Gpt2Model(cfg, w, pg.Gpt2CudaConfig(device=rank))
+        merged.update(run(model, sharding.partition(6, 2, rank)))
+    assert sharding.gather_streams(merged, 6) == [single[i] for i in range(6)]
