@@ -283,15 +283,28 @@ __global__ void __launch_bounds__(192, 1)
 // memory and added in split order, so the result does not depend on scheduling.
 template <int BN>
 struct X3 {
-  static constexpr int STAGES = 3;   // shared-memory stages; also tensor-memory stages of the split tile
+  static constexpr int STAGES = (BN == 64) ? 6 : (BN == 32) ? 8 : 10;  // shared-memory stages (TMA depth)
+  static constexpr int TSTAGES = 6;  // tensor-memory stages of the split weight tile
   static constexpr int A_BYTES = TILE_M * BK * 4, B_BYTES = BN * BK * 4;
   static constexpr int STAGE_BYTES = A_BYTES + 2 * B_BYTES;
   static constexpr int D_BYTES = TILE_M * BN * 4;  // accumulator staging, aliases the stages after the main loop
   static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES > D_BYTES ? STAGES * STAGE_BYTES : D_BYTES;
   static constexpr size_t BYTES = (size_t)PIPE_BYTES + 1024 + 256;
-  static constexpr int TMEM_COLS = 256;  // BN accumulator columns, then STAGES * 64 from column 64
+  static constexpr int TMEM_COLS = 512;  // BN accumulator columns, then TSTAGES * 64 from column 64
   static constexpr int A_COL0 = 64;
 };
+
+__device__ __forceinline__ void trace_mark(const TcGemmArgs& a, int slot) {
+  if (a.trace) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    a.trace[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 16 + slot] = t;
+  }
+}
+
+__device__ __forceinline__ void trace_add(const TcGemmArgs& a, int slot, long long cycles) {
+  if (a.trace) a.trace[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 16 + slot] = (unsigned long long)cycles;
+}
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -325,7 +338,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 }
 
 template <int BN, int SPLITS>
-__global__ void __launch_bounds__(192, 2)
+__global__ void __launch_bounds__(192, 1)
     tc_gemm_x3_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_xhi,
                       const __grid_constant__ CUtensorMap map_xlo, TcGemmArgs a) {
   using S = X3<BN>;
@@ -334,7 +347,8 @@ __global__ void __launch_bounds__(192, 2)
   uint64_t* full = reinterpret_cast<uint64_t*>(base + (size_t)S::PIPE_BYTES);
   uint64_t* empty = full + S::STAGES;
   uint64_t* a_ready = empty + S::STAGES;
-  uint64_t* d_full = a_ready + S::STAGES;
+  uint64_t* a_free = a_ready + S::TSTAGES;
+  uint64_t* d_full = a_free + S::TSTAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_full + 1);
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* dbuf = reinterpret_cast<float*>(base);  // [token][128 rows], valid after the main loop
@@ -349,11 +363,15 @@ __global__ void __launch_bounds__(192, 2)
   const int nkb = kb1 - kb0;
 
   pdl_launch();
+  if (threadIdx.x == 0) trace_mark(a, 0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < S::TSTAGES; ++s) {
       mbar_init(&a_ready[s], 128);
+      mbar_init(&a_free[s], 1);
     }
     mbar_init(d_full, 1);
     *failed = 0;
@@ -364,6 +382,7 @@ __global__ void __launch_bounds__(192, 2)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) trace_mark(a, 1);
 
   auto stage_a = [&](int s) { return base + (size_t)s * S::STAGE_BYTES; };
   auto stage_bhi = [&](int s) { return base + (size_t)s * S::STAGE_BYTES + S::A_BYTES; };
@@ -378,7 +397,7 @@ __global__ void __launch_bounds__(192, 2)
       const int pre = min(nkb, S::STAGES);
       for (int i = 0; i < pre; ++i) {
         mbar_expect_tx(&full[i], S::STAGE_BYTES);
-        tma_load_2d(stage_a(i), &map_w, (kb0 + i) * BK, n0, &full[i]);
+        tma_load_2d(stage_a(i), &map_w, 0, (blockIdx.x * nkb_total + kb0 + i) * TILE_M, &full[i]);
       }
       pdl_wait();
       for (int i = 0; i < pre; ++i) {
@@ -389,7 +408,7 @@ __global__ void __launch_bounds__(192, 2)
         const int s = i % S::STAGES;
         if (!mbar_wait(&empty[s], ((i / S::STAGES) - 1) & 1, failed, a.error_flag, 11)) break;
         mbar_expect_tx(&full[s], S::STAGE_BYTES);
-        tma_load_2d(stage_a(s), &map_w, (kb0 + i) * BK, n0, &full[s]);
+        tma_load_2d(stage_a(s), &map_w, 0, (blockIdx.x * nkb_total + kb0 + i) * TILE_M, &full[s]);
         tma_load_2d(stage_bhi(s), &map_xhi, (kb0 + i) * BK, 0, &full[s]);
         tma_load_2d(stage_blo(s), &map_xlo, (kb0 + i) * BK, 0, &full[s]);
       }
@@ -397,34 +416,57 @@ __global__ void __launch_bounds__(192, 2)
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_tf32(TILE_M, BN);
+      long long m_wait = 0, m_issue = 0;
       for (int i = 0; i < nkb; ++i) {
-        const int s = i % S::STAGES;
+        const int s = i % S::STAGES, ts = i % S::TSTAGES;
+        long long c0 = clock64();
         if (!mbar_wait(&full[s], (i / S::STAGES) & 1, failed, a.error_flag, 12)) break;
-        if (!mbar_wait(&a_ready[s], (i / S::STAGES) & 1, failed, a.error_flag, 13)) break;
+        if (!mbar_wait(&a_ready[ts], (i / S::TSTAGES) & 1, failed, a.error_flag, 13)) break;
+        long long c1 = clock64();
+        m_wait += c1 - c0;
         tc_fence_after();
+        long long f1 = clock64();
         const uint64_t dhi = umma_desc_sw128(stage_bhi(s)), dlo = umma_desc_sw128(stage_blo(s));
-        const uint32_t ahi = tmem_base + S::A_COL0 + s * 64, alo = ahi + 32;
+        const uint32_t ahi = tmem_base + S::A_COL0 + ts * 64, alo = ahi + 32;
 #pragma unroll
         for (int k = 0; k < BK / 8; ++k) {
           umma_tf32_ts(tmem_base, ahi + k * 8, dhi + (uint64_t)(k * 2), idesc, (i | k) != 0);
           umma_tf32_ts(tmem_base, ahi + k * 8, dlo + (uint64_t)(k * 2), idesc, 1);
           umma_tf32_ts(tmem_base, alo + k * 8, dhi + (uint64_t)(k * 2), idesc, 1);
         }
-        umma_commit(&empty[s]);  // frees the shared-memory stage and its tensor-memory twin
+        long long f2 = clock64();
+        // one commit per block: it releases the shared-memory stage to the producer and, for the
+        // splitters, the tensor-memory stage this block used
+        umma_commit(&empty[s]);
+        if (i == 5) {
+          trace_add(a, 13, f1 - c1);
+          trace_add(a, 14, f2 - f1);
+          trace_add(a, 15, clock64() - f2);
+        }
+        m_issue += clock64() - c1;
       }
       umma_commit(d_full);
+      trace_add(a, 11, m_wait);
+      trace_add(a, 12, m_issue);
     }
   } else {
     const int q = warp & 3;
     const int r = q * 32 + lane;  // row of the weight tile == TMEM lane
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     bool ok = true;
+    long long t_wait = 0, t_ld = 0, t_st = 0;
     for (int i = 0; i < nkb && ok; ++i) {
-      const int s = i % S::STAGES;
-      // the TMEM twin of stage s is free once the MMAs of its previous use completed, which is
-      // what released the stage to the producer, hence implied by `full`
+      const int s = i % S::STAGES, ts = i % S::TSTAGES;
+      long long c0 = clock64();
       ok = mbar_wait(&full[s], (i / S::STAGES) & 1, failed, a.error_flag, 14);
+      if (ok && i >= S::TSTAGES) {  // block i - TSTAGES used this tensor-memory stage: wait for its MMAs
+        const int ip = i - S::TSTAGES;
+        ok = mbar_wait(&empty[ip % S::STAGES], (ip / S::STAGES) & 1, failed, a.error_flag, 15);
+      }
       if (!ok) break;
+      long long c1 = clock64();
+      t_wait += c1 - c0;
+      if (i == 0 && threadIdx.x == 64) trace_mark(a, 2);
       tc_fence_after();
       const float4* rowp = reinterpret_cast<const float4*>(stage_a(s) + (size_t)r * 128);
       uint32_t hi[32], lo[32];
@@ -439,16 +481,25 @@ __global__ void __launch_bounds__(192, 2)
           lo[j * 4 + e] = __float_as_uint(f[e] - h);
         }
       }
-      const uint32_t col = tmem_base + S::A_COL0 + s * 64 + lane_addr;
+      const uint32_t col = tmem_base + S::A_COL0 + ts * 64 + lane_addr;
+      long long c2 = clock64();
+      t_ld += c2 - c1;
       tmem_st32(col, hi);
       tmem_st32(col + 32, lo);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&a_ready[s]);
+      mbar_arrive(&a_ready[ts]);
+      t_st += clock64() - c2;
+    }
+    if (threadIdx.x == 64) {
+      trace_add(a, 8, t_wait);
+      trace_add(a, 9, t_ld);
+      trace_add(a, 10, t_st);
     }
     // accumulator -> shared memory, [token][row]: all MMAs (and so all TMA writes) are complete
     if (ok && mbar_wait(d_full, 0, failed, a.error_flag, 16)) {
       tc_fence_after();
+      if (threadIdx.x == 64) trace_mark(a, 3);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
         float v[16];
@@ -479,7 +530,9 @@ __global__ void __launch_bounds__(192, 2)
       resid_v[o] = (a.epilogue == EPI_RESID && j < a.m) ? a.resid[(size_t)j * a.n + feat] : 0.f;
     }
   }
+  if (threadIdx.x == 64) trace_mark(a, 4);
   cluster_sync_all();
+  if (threadIdx.x == 64) trace_mark(a, 5);
   if (active && !*failed) {
     const uint32_t dbuf_addr = smem_u32(dbuf);
     float part[OUTS][SPLITS];
@@ -507,7 +560,9 @@ __global__ void __launch_bounds__(192, 2)
       }
     }
   }
+  if (threadIdx.x == 64) trace_mark(a, 6);
   cluster_sync_all();  // no CTA may leave while a peer still reads its shared memory
+  if (threadIdx.x == 64) trace_mark(a, 7);
   if (warp == 1) tmem_dealloc(tmem_base, S::TMEM_COLS);
 }
 
@@ -572,6 +627,30 @@ cudaError_t launch_ex(K kernel, dim3 grid, size_t smem, cudaStream_t s, bool pdl
 
 }  // namespace
 
+namespace {
+// dst[((r / 128) * (k / 32) + c / 32) * 4096 + (r % 128) * 32 + c % 32] = src[r * k + c]; rows past n are zero
+__global__ void tile_weights_kernel(const float* __restrict__ src, float* __restrict__ dst, int n, int k) {
+  const int nkb = k / BK;
+  const size_t total = (size_t)((n + TILE_M - 1) / TILE_M) * nkb * TILE_M * BK;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int c_in = (int)(i % BK);
+    const int r_in = (int)((i / BK) % TILE_M);
+    const size_t tile = i / (BK * TILE_M);
+    const int kb = (int)(tile % nkb);
+    const int r = (int)(tile / nkb) * TILE_M + r_in;
+    dst[i] = r < n ? src[(size_t)r * k + kb * BK + c_in] : 0.f;
+  }
+}
+}  // namespace
+
+size_t tc_tiled_weight_floats(int n, int k) { return (size_t)((n + TILE_M - 1) / TILE_M) * TILE_M * (size_t)k; }
+
+cudaError_t launch_tile_weights(const float* src, float* dst, int n, int k, cudaStream_t s) {
+  if (k % BK != 0) return cudaErrorInvalidValue;
+  tile_weights_kernel<<<1184, 256, 0, s>>>(src, dst, n, k);
+  return cudaGetLastError();
+}
+
 bool tc_gemm_supported(int m, int n, int k) {
   (void)m;
   (void)n;
@@ -623,7 +702,9 @@ cudaError_t launch_tc_gemm_x3(const TcGemmArgs& a, int splits, bool pdl, cudaStr
   if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return cudaErrorInvalidValue;
   const int bn = a.m <= 16 ? 16 : a.m <= 32 ? 32 : 64;
   CUtensorMap mw, mhi, mlo;
-  if (!make_map(&mw, a.w, a.n, a.k, TILE_M) || !make_map(&mhi, a.x, a.m, a.k, bn) ||
+  // weights in the tiled layout: a [tiles * 128, 32] matrix whose 128-row boxes are contiguous 16 KB
+  const uint64_t tiled_rows = (uint64_t)((a.n + TILE_M - 1) / TILE_M) * (a.k / BK) * TILE_M;
+  if (!make_map(&mw, a.w, tiled_rows, BK, TILE_M) || !make_map(&mhi, a.x, a.m, a.k, bn) ||
       !make_map(&mlo, a.x_lo, a.m, a.k, bn))
     return cudaErrorInvalidValue;
   TcGemmArgs args = a;

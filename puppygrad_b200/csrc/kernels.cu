@@ -94,70 +94,106 @@ constexpr int LIN_ROWS = 4;
 template <int MT, int EPI, bool LN>
 __global__ void __launch_bounds__(LIN_THREADS) linear_decode_kernel(LinearArgs a) {
   extern __shared__ float4 dyn_smem4[];
-  float* xs = reinterpret_cast<float*>(dyn_smem4);  // [MT][k] normalised rows (LN only)
+  float4* xs4 = dyn_smem4;  // [MT][k/4] normalised rows (LN only)
   __shared__ float red[LIN_WARPS][LIN_ROWS * MT];
+  __shared__ float lnred[2][LIN_WARPS][MT];
   __shared__ float best_v[LIN_ROWS * MT];
   __shared__ int best_i[LIN_ROWS * MT];
 
+  constexpr int NV = LIN_ROWS * MT;
+  // 128-bit chunks per weight row that every thread requests before the dependency wait
+  constexpr int PRE = MT <= 2 ? 3 : 2;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int k4 = a.k >> 2;
   const int groups = (a.n + LIN_ROWS - 1) / LIN_ROWS;
   const float4* w4 = reinterpret_cast<const float4*>(a.w);
-  constexpr int NV = LIN_ROWS * MT;
 
   pdl_launch();
 
-  // First chunk of this CTA's first row group: issued before the dependency wait.
-  float4 wpre[LIN_ROWS];
+  // Weights and bias do not depend on the previous kernel: the first row group's loads go out
+  // before the dependency wait, so their HBM latency overlaps the tail of the previous kernel.
+  float4 wpre[PRE][LIN_ROWS];
   {
     const int g0 = blockIdx.x;
 #pragma unroll
-    for (int r = 0; r < LIN_ROWS; ++r) {
-      int row = min(g0 * LIN_ROWS + r, a.n - 1);
-      wpre[r] = (g0 < groups && tid < k4) ? ldg_stream(w4 + (size_t)row * k4 + tid) : make_float4(0, 0, 0, 0);
+    for (int j = 0; j < PRE; ++j) {
+      const int c = tid + j * LIN_THREADS;
+#pragma unroll
+      for (int r = 0; r < LIN_ROWS; ++r) {
+        const int row = min(g0 * LIN_ROWS + r, a.n - 1);
+        wpre[j][r] = (g0 < groups && c < k4) ? ldg_stream(w4 + (size_t)row * k4 + c) : make_float4(0, 0, 0, 0);
+      }
     }
   }
+  float bias_pre = 0.f;
+  if (tid < NV && a.bias) bias_pre = a.bias[min((int)blockIdx.x * LIN_ROWS + tid / MT, a.n - 1)];
 
   pdl_wait();
 
+  float resid_pre = 0.f;
+  if (EPI == EPI_RESID && tid < NV) {
+    const int row = blockIdx.x * LIN_ROWS + tid / MT, m = tid % MT;
+    if (row < a.n && m < a.m) resid_pre = a.resid[(size_t)m * a.n + row];
+  }
+
   if (LN) {
-    // rows of x -> LayerNorm -> shared memory; warp w handles rows w, w+4
-    for (int m = warp; m < MT; m += LIN_WARPS) {
-      float* dst = xs + (size_t)m * a.k;
-      if (m < a.m) {
-        const float4* xr = reinterpret_cast<const float4*>(a.x + (size_t)m * a.k);
-        float s = 0.f;
-        for (int c = lane; c < k4; c += 32) {
-          float4 v = xr[c];
-          reinterpret_cast<float4*>(dst)[c] = v;
-          s += (v.x + v.y) + (v.z + v.w);
-        }
-        s = warp_sum(s);
-        const float mean = s / (float)a.k;
-        float q = 0.f;
-        for (int c = lane; c < k4; c += 32) {
-          float4 v = reinterpret_cast<float4*>(dst)[c];
-          float d0 = v.x - mean, d1 = v.y - mean, d2 = v.z - mean, d3 = v.w - mean;
-          q += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
-        }
-        q = warp_sum(q);
-        const float inv_std = 1.0f / sqrtf(q / (float)a.k + a.eps);
-        const float4* g4 = reinterpret_cast<const float4*>(a.ln_g);
-        const float4* b4 = reinterpret_cast<const float4*>(a.ln_b);
-        for (int c = lane; c < k4; c += 32) {
-          float4 v = reinterpret_cast<float4*>(dst)[c];
-          float4 g = g4[c], b = b4[c];
-          v.x = (v.x - mean) * inv_std * g.x + b.x;
-          v.y = (v.y - mean) * inv_std * g.y + b.y;
-          v.z = (v.z - mean) * inv_std * g.z + b.z;
-          v.w = (v.w - mean) * inv_std * g.w + b.w;
-          reinterpret_cast<float4*>(dst)[c] = v;
-        }
-      } else {
-        for (int c = lane; c < k4; c += 32) reinterpret_cast<float4*>(dst)[c] = make_float4(0, 0, 0, 0);
+    // LayerNorm of the (at most MT) rows into shared memory; every thread owns the chunks
+    // c = tid (mod 128) of every row through all three passes
+    const float4* x4 = reinterpret_cast<const float4*>(a.x);
+    float s[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) s[m] = 0.f;
+    for (int c = tid; c < k4; c += LIN_THREADS) {
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        const float4 v = m < a.m ? x4[(size_t)m * k4 + c] : make_float4(0, 0, 0, 0);
+        xs4[(size_t)m * k4 + c] = v;
+        s[m] += (v.x + v.y) + (v.z + v.w);
       }
     }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      s[m] = warp_sum(s[m]);
+      if (lane == 0) lnred[0][warp][m] = s[m];
+    }
     __syncthreads();
+    float mean[MT], q[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      mean[m] = ((lnred[0][0][m] + lnred[0][1][m]) + (lnred[0][2][m] + lnred[0][3][m])) / (float)a.k;
+      q[m] = 0.f;
+    }
+    for (int c = tid; c < k4; c += LIN_THREADS) {
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        const float4 v = xs4[(size_t)m * k4 + c];
+        const float d0 = v.x - mean[m], d1 = v.y - mean[m], d2 = v.z - mean[m], d3 = v.w - mean[m];
+        q[m] += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      q[m] = warp_sum(q[m]);
+      if (lane == 0) lnred[1][warp][m] = q[m];
+    }
+    __syncthreads();
+    const float4* g4 = reinterpret_cast<const float4*>(a.ln_g);
+    const float4* b4 = reinterpret_cast<const float4*>(a.ln_b);
+    for (int c = tid; c < k4; c += LIN_THREADS) {
+      const float4 g = g4[c], b = b4[c];
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        const float var = ((lnred[1][0][m] + lnred[1][1][m]) + (lnred[1][2][m] + lnred[1][3][m])) / (float)a.k;
+        const float inv_std = 1.0f / sqrtf(var + a.eps);
+        float4 v = xs4[(size_t)m * k4 + c];
+        v.x = (v.x - mean[m]) * inv_std * g.x + b.x;
+        v.y = (v.y - mean[m]) * inv_std * g.y + b.y;
+        v.z = (v.z - mean[m]) * inv_std * g.z + b.z;
+        v.w = (v.w - mean[m]) * inv_std * g.w + b.w;
+        xs4[(size_t)m * k4 + c] = m < a.m ? v : make_float4(0, 0, 0, 0);
+      }
+    }
+    // no barrier needed: the main loop below reads only the chunks this thread wrote
   }
 
   float run_best = -INFINITY;  // lm_head argmax partial of this thread's (row-in-group, m) pair
@@ -165,6 +201,7 @@ __global__ void __launch_bounds__(LIN_THREADS) linear_decode_kernel(LinearArgs a
 
   for (int g = blockIdx.x; g < groups; g += gridDim.x) {
     const int row0 = g * LIN_ROWS;
+    const bool first_group = g == (int)blockIdx.x;
     const float4* wrow[LIN_ROWS];
 #pragma unroll
     for (int r = 0; r < LIN_ROWS; ++r) wrow[r] = w4 + (size_t)min(row0 + r, a.n - 1) * k4;
@@ -173,31 +210,34 @@ __global__ void __launch_bounds__(LIN_THREADS) linear_decode_kernel(LinearArgs a
       float acc[NV];
 #pragma unroll
       for (int i = 0; i < NV; ++i) acc[i] = 0.f;
-      const float* xbase = LN ? xs : a.x + (size_t)m0 * a.k;
+      const float4* xbase = LN ? xs4 : reinterpret_cast<const float4*>(a.x) + (size_t)m0 * k4;
 
-      bool first = (g == (int)blockIdx.x) && (m0 == 0);
-#pragma unroll 2
-      for (int c = tid; c < k4; c += LIN_THREADS) {
-        float4 w[LIN_ROWS];
-        if (first && c == tid) {
-#pragma unroll
-          for (int r = 0; r < LIN_ROWS; ++r) w[r] = wpre[r];
-        } else {
-#pragma unroll
-          for (int r = 0; r < LIN_ROWS; ++r) w[r] = ldg_stream(wrow[r] + c);
-        }
+      auto accumulate = [&](const float4 (&w)[LIN_ROWS], int c) {
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
           float4 xv;
-          if (LN) {
-            xv = reinterpret_cast<const float4*>(xbase + (size_t)m * a.k)[c];
-          } else {
-            xv = (m0 + m < a.m) ? reinterpret_cast<const float4*>(xbase + (size_t)m * a.k)[c]
-                                : make_float4(0, 0, 0, 0);
-          }
+          if (LN) xv = xbase[(size_t)m * k4 + c];
+          else xv = (m0 + m < a.m) ? xbase[(size_t)m * k4 + c] : make_float4(0, 0, 0, 0);
 #pragma unroll
           for (int r = 0; r < LIN_ROWS; ++r) acc[r * MT + m] = dot4(w[r], xv, acc[r * MT + m]);
         }
+      };
+
+      int cstart = tid;
+      if (first_group && m0 == 0) {
+#pragma unroll
+        for (int j = 0; j < PRE; ++j) {
+          const int c = tid + j * LIN_THREADS;
+          if (c < k4) accumulate(wpre[j], c);
+        }
+        cstart = tid + PRE * LIN_THREADS;
+      }
+#pragma unroll 2
+      for (int c = cstart; c < k4; c += LIN_THREADS) {
+        float4 w[LIN_ROWS];
+#pragma unroll
+        for (int r = 0; r < LIN_ROWS; ++r) w[r] = ldg_stream(wrow[r] + c);
+        accumulate(w, c);
       }
 
       WarpMultiReduce<NV, 16>::run(acc, lane);
@@ -207,10 +247,11 @@ __global__ void __launch_bounds__(LIN_THREADS) linear_decode_kernel(LinearArgs a
       if (tid < NV) {
         const int r = tid / MT, m = m0 + tid % MT, row = row0 + r;
         if (row < a.n && m < a.m) {
-          float dotv = ((red[0][tid] + red[1][tid]) + red[2][tid]) + red[3][tid];
-          float v = a.bias ? a.bias[row] + dotv : dotv;
+          const float dotv = ((red[0][tid] + red[1][tid]) + red[2][tid]) + red[3][tid];
+          const float b = (first_group || !a.bias) ? bias_pre : a.bias[row];
+          float v = a.bias ? b + dotv : dotv;
           if (EPI == EPI_GELU) v = gelu_ref(v);
-          if (EPI == EPI_RESID) v = a.resid[(size_t)m * a.n + row] + v;
+          if (EPI == EPI_RESID) v = ((first_group && m0 == 0) ? resid_pre : a.resid[(size_t)m * a.n + row]) + v;
           a.out[(size_t)m * a.n + row] = v;
           if (a.part_val && v > run_best) {
             run_best = v;
@@ -245,6 +286,7 @@ __global__ void __launch_bounds__(LIN_THREADS) linear_decode_kernel(LinearArgs a
     }
   }
 }
+
 
 // Any k (no alignment requirement): one thread per output element. Only shapes whose inner
 // dimension is not a multiple of 4 take this path.

@@ -105,16 +105,22 @@ cudaError_t launch_layernorm_rows_split(const float* x, const float* g, const fl
 struct TcGemmArgs {
   const float* x;     // [m, k] activations (x3: the hi part)
   const float* x_lo;  // [m, k] lo part (x3 only)
-  const float* w;     // [n, k]
+  const float* w;     // [n, k] row-major; for the x3 kernel the tiled copy made by launch_tile_weights
   const float* bias;  // [n] or nullptr
   const float* resid; // [m, n], EPI_RESID
   float* out;         // [m, n] (may be nullptr in x3 when only the split outputs are wanted)
   float* out_hi;      // x3: optional TF32 hi/lo pair of the result, [m, n] each
   float* out_lo;
   int* error_flag;    // set non-zero if a bounded wait inside the kernel expired
+  unsigned long long* trace;  // optional tuning aid (x3 kernel): 16 words per CTA, phase timestamps and cycle counts
   int m, n, k, epilogue;
 };
 bool tc_gemm_supported(int m, int n, int k);
+// Tiled weight layout of the x3 kernel: [n / 128][k / 32][128 rows][32 floats], every TMA tile one
+// contiguous 16 KB run in HBM (row-major tiles would be 128 scattered 128-byte pieces, which costs
+// most of the DRAM bandwidth). Rows are padded with zeros to a multiple of 128.
+size_t tc_tiled_weight_floats(int n, int k);
+cudaError_t launch_tile_weights(const float* src, float* dst, int n, int k, cudaStream_t s);
 // single TF32 pass, any m (prefill)
 cudaError_t launch_tc_gemm_tf32(const TcGemmArgs& a, cudaStream_t s);
 // three TF32 passes (FP32-grade), m <= 64 (decode)

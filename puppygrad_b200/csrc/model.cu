@@ -30,6 +30,8 @@ namespace pg {
 
 struct LayerWeights {
   float *ln1_g, *ln1_b, *w_qkv, *b_qkv, *w_proj, *b_proj, *ln2_g, *ln2_b, *w_fc, *b_fc, *w_proj2, *b_proj2;
+  // copies in the tiled layout of the tensor-core decode kernel (nullptr in fp32 mode)
+  float *t_qkv = nullptr, *t_proj = nullptr, *t_fc = nullptr, *t_proj2 = nullptr;
 };
 
 static bool env_flag(const char* name) {
@@ -48,6 +50,8 @@ struct pg_model {
   int device = 0;
   int num_sms = 148;
   float* arena = nullptr;  // every weight tensor lives in this one allocation
+  float* tiled_arena = nullptr;  // second copy of the dense matrices, tiled for TMA (tensor-core modes)
+  float* t_wte = nullptr;
   size_t arena_floats = 0;
   float *wte = nullptr, *wpe = nullptr, *lnf_g = nullptr, *lnf_b = nullptr;
   std::vector<LayerWeights> layers;
@@ -66,6 +70,7 @@ struct pg_model {
     if (arena) {
       cudaSetDevice(device);
       cudaFree(arena);
+      if (tiled_arena) cudaFree(tiled_arena);
     }
   }
 };
@@ -176,6 +181,28 @@ static int build_model(const pg_gpt2_config& cfg, const float* const* tensors, c
   }
   cudaFree(staging);
   if (rc != PG_OK) return rc;
+  if (be.math_mode != PG_MATH_FP32 && C % 32 == 0 && F % 32 == 0) {
+    const int V = (int)cfg.vocab_size;
+    const size_t per_layer = tc_tiled_weight_floats(3 * C, C) + tc_tiled_weight_floats(C, C) +
+                             tc_tiled_weight_floats(F, C) + tc_tiled_weight_floats(C, F);
+    const size_t total_t = per_layer * cfg.n_layer + tc_tiled_weight_floats(V, C);
+    PG_CUDA_TRY(cudaMalloc(&m->tiled_arena, total_t * sizeof(float)));
+    float* p = m->tiled_arena;
+    auto tile = [&](const float* src, int n_rows, int k_cols, float** dst) -> int {
+      *dst = p;
+      PG_CUDA_TRY(launch_tile_weights(src, p, n_rows, k_cols, 0));
+      p += tc_tiled_weight_floats(n_rows, k_cols);
+      return PG_OK;
+    };
+    for (auto& w : m->layers) {
+      if (int r = tile(w.w_qkv, 3 * C, C, &w.t_qkv)) return r;
+      if (int r = tile(w.w_proj, C, C, &w.t_proj)) return r;
+      if (int r = tile(w.w_fc, F, C, &w.t_fc)) return r;
+      if (int r = tile(w.w_proj2, C, F, &w.t_proj2)) return r;
+    }
+    if (int r = tile(m->wte, V, C, &m->t_wte)) return r;
+    PG_CUDA_TRY(cudaDeviceSynchronize());
+  }
   *out = m.release();
   return PG_OK;
 }
@@ -388,7 +415,7 @@ static cudaError_t enqueue_decode_step(pg_cache* c, int batch, int splits, cudaS
     if (prof && (e = prof->mark(s, -1)) != cudaSuccess) return e;        \
   } while (0)
   PG_E(launch_embed(m->wte, m->wpe, c->d_ids, c->d_pos, c->x, batch, C, pdl, s));
-  if (m->backend.math_mode != PG_MATH_FP32 && batch > 8 && batch <= 64 && c->norm_lo) {
+  if (m->t_wte && batch > 8 && batch <= 64 && c->norm_lo) {
     // tensor-core path: every linear is three TF32 products (hi*hi + hi*lo + lo*hi) accumulated
     // in FP32; LayerNorm, attention and the GELU epilogue hand their results over as hi/lo pairs
     auto x3 = [&](const float* w, const float* bias, const float* xhi, const float* xlo, float* out, float* ohi,
@@ -404,7 +431,7 @@ static cudaError_t enqueue_decode_step(pg_cache* c, int batch, int splits, cudaS
       cur_bucket = B_LAYER_NORM;
       PG_E(launch_layernorm_rows_split(c->x, w.ln1_g, w.ln1_b, eps, c->norm, c->norm_lo, batch, C, pdl, s));
       cur_bucket = B_QKV;
-      PG_E(x3(w.w_qkv, w.b_qkv, c->norm, c->norm_lo, c->qkv, nullptr, nullptr, 3 * C, C, EPI_NONE, nullptr));
+      PG_E(x3(w.t_qkv, w.b_qkv, c->norm, c->norm_lo, c->qkv, nullptr, nullptr, 3 * C, C, EPI_NONE, nullptr));
       cur_bucket = B_ATTN;
       DecodeAttnArgs at{};
       at.qkv = c->qkv; at.out = c->attn; at.out_lo = c->attn_lo; at.kv_pool = c->layer_pool(l);
@@ -412,18 +439,18 @@ static cudaError_t enqueue_decode_step(pg_cache* c, int batch, int splits, cudaS
       at.kv = c->kv; at.batch = batch; at.splits = splits;
       PG_E(launch_decode_attention(at, pdl, s));
       cur_bucket = B_ATTN_PROJ;
-      PG_E(x3(w.w_proj, w.b_proj, c->attn, c->attn_lo, c->x, nullptr, nullptr, C, C, EPI_RESID, c->x));
+      PG_E(x3(w.t_proj, w.b_proj, c->attn, c->attn_lo, c->x, nullptr, nullptr, C, C, EPI_RESID, c->x));
       cur_bucket = B_LAYER_NORM;
       PG_E(launch_layernorm_rows_split(c->x, w.ln2_g, w.ln2_b, eps, c->norm, c->norm_lo, batch, C, pdl, s));
       cur_bucket = B_MLP_FC;
-      PG_E(x3(w.w_fc, w.b_fc, c->norm, c->norm_lo, nullptr, c->hbuf, c->h_lo, F, C, EPI_GELU, nullptr));
+      PG_E(x3(w.t_fc, w.b_fc, c->norm, c->norm_lo, nullptr, c->hbuf, c->h_lo, F, C, EPI_GELU, nullptr));
       cur_bucket = B_MLP_PROJ;
-      PG_E(x3(w.w_proj2, w.b_proj2, c->hbuf, c->h_lo, c->x, nullptr, nullptr, C, F, EPI_RESID, c->x));
+      PG_E(x3(w.t_proj2, w.b_proj2, c->hbuf, c->h_lo, c->x, nullptr, nullptr, C, F, EPI_RESID, c->x));
     }
     cur_bucket = B_LAYER_NORM;
     PG_E(launch_layernorm_rows_split(c->x, m->lnf_g, m->lnf_b, eps, c->norm, c->norm_lo, batch, C, pdl, s));
     cur_bucket = B_LOGITS;
-    PG_E(x3(m->wte, nullptr, c->norm, c->norm_lo, c->logits, nullptr, nullptr, V, C, EPI_NONE, nullptr));
+    PG_E(x3(m->t_wte, nullptr, c->norm, c->norm_lo, c->logits, nullptr, nullptr, V, C, EPI_NONE, nullptr));
     PG_E(launch_argmax_rows(c->logits, batch, V, c->d_argmax, s));
     FinalizeArgs fx{};
     fx.m = batch; fx.argmax_out = c->d_argmax; fx.next_ids = c->d_ids; fx.pos = c->d_pos;

@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <string>
 #include <vector>
 
@@ -52,7 +54,8 @@ extern "C" int pg_op_linear(const float* x, const float* w, const float* bias, c
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   const size_t xs = (size_t)m * k, ws = (size_t)n * k, os = (size_t)m * n;
-  DeviceBuf dx, dw, db, dr, dout, dhi, dlo, derr, dflush;
+  DeviceBuf dx, dw, dwt, db, dr, dout, dhi, dlo, derr, dflush, dtrace;
+  const bool want_trace = getenv("PG_TRACE") != nullptr;
   cudaStream_t s = nullptr;
   cudaEvent_t e0 = nullptr, e1 = nullptr;
   int splits = 1;
@@ -73,7 +76,8 @@ extern "C" int pg_op_linear(const float* x, const float* w, const float* bias, c
     }
     cudaError_t e = launch_split_tf32(dx.as<float>(), dhi.as<float>(), dlo.as<float>(), xs, false, st);
     if (e != cudaSuccess) return e;
-    a.x = dhi.as<float>(); a.x_lo = dlo.as<float>();
+    a.x = dhi.as<float>(); a.x_lo = dlo.as<float>(); a.w = dwt.as<float>();
+    a.trace = dtrace.as<unsigned long long>();
     return launch_tc_gemm_x3(a, splits, false, st);
   };
   PG_OP_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
@@ -96,6 +100,12 @@ extern "C" int pg_op_linear(const float* x, const float* w, const float* bias, c
     splits = tc_gemm_x3_splits(n, k, sms);
     PG_OP_TRY(cudaMalloc(&dhi.p, xs * 4));
     PG_OP_TRY(cudaMalloc(&dlo.p, xs * 4));
+    PG_OP_TRY(cudaMalloc(&dwt.p, tc_tiled_weight_floats(n, k) * 4));
+    PG_OP_TRY(launch_tile_weights(dw.as<float>(), dwt.as<float>(), n, k, s));
+    if (want_trace) {
+      PG_OP_TRY(cudaMalloc(&dtrace.p, (size_t)((n + 127) / 128) * splits * 128));
+      PG_OP_TRY(cudaMemset(dtrace.p, 0, (size_t)((n + 127) / 128) * splits * 128));
+    }
   }
   PG_OP_TRY(run(s));
   PG_OP_TRY(cudaMemcpyAsync(out, dout.p, os * 4, cudaMemcpyDeviceToHost, s));
@@ -124,6 +134,30 @@ extern "C" int pg_op_linear(const float* x, const float* w, const float* bias, c
       if (i >= 3) total += ms * 1e-3;
     }
     *seconds_per_launch = total / reps;
+  }
+  if (want_trace && dtrace.p) {
+    // tuning aid: phase timestamps of the last launch, relative to the earliest CTA start
+    const size_t ctas = (size_t)((n + 127) / 128) * splits;
+    std::vector<unsigned long long> t(ctas * 16);
+    PG_OP_TRY(cudaMemcpy(t.data(), dtrace.p, t.size() * 8, cudaMemcpyDeviceToHost));
+    unsigned long long t0 = ~0ULL;
+    for (size_t i = 0; i < ctas; ++i) t0 = std::min(t0, t[i * 16]);
+    const char* names[8] = {"start", "setup", "first_full", "d_full", "pre_cluster", "post_cluster", "epi_done", "end"};
+    for (int sl = 0; sl < 8; ++sl) {
+      unsigned long long lo = ~0ULL, hi = 0;
+      double mean = 0;
+      for (size_t i = 0; i < ctas; ++i) {
+        unsigned long long v = t[i * 16 + sl] - t0;
+        lo = std::min(lo, v); hi = std::max(hi, v); mean += (double)v;
+      }
+      fprintf(stderr, "trace %-13s min %6llu ns  mean %8.0f ns  max %6llu ns\n", names[sl], lo, mean / ctas, hi);
+    }
+    const char* cn[8] = {"split_wait", "split_ld_alu", "split_st", "mma_wait", "mma_issue", "blk5_fence", "blk5_mmas", "blk5_commit"};
+    for (int sl = 0; sl < 8; ++sl) {
+      double mean = 0;
+      for (size_t i = 0; i < ctas; ++i) mean += (double)t[i * 16 + 8 + sl];
+      fprintf(stderr, "trace %-13s mean %8.0f cycles per CTA\n", cn[sl], mean / ctas);
+    }
   }
 done:
   if (s) cudaStreamSynchronize(s);
