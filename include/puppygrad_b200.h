@@ -53,10 +53,13 @@ typedef struct {
 /* Arithmetic of the linears. The reference is FP32 only (src/models/safetensors.rs:126-130);
  * the other modes are extensions with their own stated error bounds. */
 typedef enum {
-  PG_MATH_FP32 = 0,   /* FP32 FMA everywhere: the parity path */
-  PG_MATH_TF32X3 = 1, /* prefill GEMMs on tensor cores, 3-term TF32 split (near-FP32) */
-  PG_MATH_TF32 = 2,   /* prefill GEMMs on tensor cores, single TF32 pass */
-  PG_MATH_BF16 = 3    /* weights rounded to BF16 at load; BF16 tensor-core prefill GEMMs */
+  PG_MATH_FP32 = 0,   /* FP32 FMA everywhere */
+  PG_MATH_TF32X3 = 1, /* decode linears of 9..64 sequences on tensor cores as three TF32 products
+                         (hi*hi + hi*lo + lo*hi) with FP32 accumulation: FP32-grade, passes the same
+                         token-exact tests; everything else as PG_MATH_FP32 */
+  PG_MATH_TF32 = 2,   /* as TF32X3 for decode; single-pass TF32 is available per operator
+                         (pg_op_linear) with its looser bound */
+  PG_MATH_BF16 = 3    /* reserved: rejected by this build */
 } pg_math_mode;
 
 /* Stands where Gpt2BackendConfig::Rust(Gpt2RustConfig) stands in the reference
@@ -67,7 +70,11 @@ typedef struct {
   int32_t page_tokens;  /* KV page size in tokens: 16, 32 or 64 (default 32) */
   int32_t use_graphs;   /* 0 = default (on), 1 = on, 2 = off: one CUDA graph per decode step */
   int32_t attn_splits;  /* split-K factor of decode attention, 0 = choose from the batch */
-  int32_t reserved[3];
+  int32_t persistent_step; /* 1 = run a decode step of at most 8 sequences as one persistent
+                              cooperative kernel (grid barriers between phases) instead of a graph
+                              of kernels; off by default (on B200 it measured 336 us against
+                              290 us per GPT-2 small token for the kernel graph) */
+  int32_t reserved[2];
 } pg_backend_config;
 
 /* TextGenerationConfig, src/models/generation.rs:60-85. None is encoded as a negative value. */

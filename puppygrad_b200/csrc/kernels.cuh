@@ -127,6 +127,36 @@ cudaError_t launch_tc_gemm_tf32(const TcGemmArgs& a, cudaStream_t s);
 int tc_gemm_x3_splits(int n, int k, int num_sms);
 cudaError_t launch_tc_gemm_x3(const TcGemmArgs& a, int splits, bool pdl, cudaStream_t s);
 cudaError_t launch_finalize(const FinalizeArgs& a, bool pdl, cudaStream_t s);
+
+// Whole decode step in one persistent cooperative kernel (decode_mega.cu), for at most 8 sequences
+// and head_dim 64: every CTA stays resident, phases are separated by a bounded grid barrier, and
+// each warp requests the weights of its next phase before it enters the barrier.
+struct MegaLayer {
+  const float *ln1_g, *ln1_b, *w_qkv, *b_qkv, *w_proj, *b_proj, *ln2_g, *ln2_b, *w_fc, *b_fc, *w_proj2, *b_proj2;
+  float* kv_pool;  // this layer's page pool
+};
+struct MegaArgs {
+  const MegaLayer* layers;  // device array [n_layer]
+  const float *wte, *wpe, *lnf_g, *lnf_b;
+  int n_layer, c, f, v, n_positions;
+  float eps;
+  int *ids, *pos, *argmax, *token_log;     // [m] / [m][n_positions]
+  float *x, *qkv, *attn, *h, *logits;      // [m, .] activations in global memory
+  const int* page_table;
+  KvLayout kv;
+  float* attn_part;       // split-K partials of the attention phase
+  unsigned* attn_counters;
+  float* part_val;        // lm_head argmax partials [m][grid]
+  int* part_idx;
+  unsigned* barrier;      // two words: arrival count, generation; zero before the first launch
+  int* error_flag;
+  unsigned long long* trace;  // optional tuning aid: cycle counts of CTA 0 (total, barriers, attention, staging, lm_head)
+  int m, attn_splits;
+};
+// Largest cooperative grid of the step kernel on this device (0 if it cannot be launched).
+int decode_mega_grid(int num_sms);
+bool decode_mega_supported(int m, int c, int f, int head_dim);
+cudaError_t launch_decode_mega(const MegaArgs& a, int grid, cudaStream_t s);
 // Plain argmax over rows of a [m, n] matrix (first strict maximum).
 cudaError_t launch_argmax_rows(const float* logits, int m, int n, int* out, cudaStream_t s);
 // k largest per row, descending, ties by lower index; k <= 64.

@@ -8,6 +8,7 @@
 
 #include <algorithm>
 #include <chrono>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <map>
@@ -235,6 +236,11 @@ struct pg_cache {
   // tensor-core decode path (9..64 sequences): TF32 hi/lo pairs of the GEMM inputs, split-K scratch
   float *norm_lo = nullptr, *attn_lo = nullptr, *h_lo = nullptr;
   int* d_error = nullptr;
+  // single-kernel decode step (at most 8 sequences)
+  MegaLayer* d_mega_layers = nullptr;
+  unsigned* d_barrier = nullptr;
+  unsigned long long* d_mega_trace = nullptr;  // PG_MEGA_TRACE=1: cycle accounting printed when the cache is freed
+  int mega_grid = 0;
   int *h_ids = nullptr, *h_out = nullptr;  // pinned staging
   // prefill workspace (grow-only)
   size_t pre_rows = 0;
@@ -251,12 +257,19 @@ struct pg_cache {
     if (!model) return;
     cudaSetDevice(model->device);
     if (stream) cudaStreamSynchronize(stream);
+    if (d_mega_trace) {
+      unsigned long long t[8] = {0};
+      if (cudaMemcpy(t, d_mega_trace, sizeof(t), cudaMemcpyDeviceToHost) == cudaSuccess && t[5])
+        fprintf(stderr, "mega trace (CTA 0, cycles per step over %llu steps): total %llu barriers %llu attention %llu "
+                        "staging %llu lm_head %llu qkv-linear %llu\n", t[5], t[0] / t[5], t[1] / t[5], t[2] / t[5], t[3] / t[5], t[4] / t[5], t[6] / t[5]);
+      cudaFree(d_mega_trace);
+    }
     for (auto& g : graphs) cudaGraphExecDestroy(g.second);
     for (void* p : {(void*)kv_pool, (void*)d_table, (void*)d_ids, (void*)d_pos, (void*)d_argmax, (void*)d_token_log,
                     (void*)x, (void*)norm, (void*)qkv, (void*)attn, (void*)hbuf, (void*)logits, (void*)part_val,
                     (void*)part_idx, (void*)attn_part, (void*)attn_counters, (void*)topk_vals, (void*)topk_idx,
                     (void*)px, (void*)pnorm, (void*)pqkv, (void*)pattn, (void*)ph, (void*)prow, (void*)norm_lo,
-                    (void*)attn_lo, (void*)h_lo, (void*)d_error})
+                    (void*)attn_lo, (void*)h_lo, (void*)d_error, (void*)d_mega_layers, (void*)d_barrier})
       if (p) cudaFree(p);
     if (t0) cudaEventDestroy(t0);
     if (t1) cudaEventDestroy(t1);
@@ -321,6 +334,26 @@ static int cache_new(const pg_model* m, int max_batch, pg_cache** out) {
     PG_CUDA_TRY(cudaMalloc(&c->norm_lo, (size_t)bmax * C * sizeof(float)));
     PG_CUDA_TRY(cudaMalloc(&c->attn_lo, (size_t)bmax * C * sizeof(float)));
     PG_CUDA_TRY(cudaMalloc(&c->h_lo, (size_t)bmax * F * sizeof(float)));
+  }
+  if (decode_mega_supported(1, C, F, D) && (m->backend.persistent_step == 1 || env_flag("PG_MEGA"))) {
+    c->mega_grid = decode_mega_grid(m->num_sms);
+    if (c->mega_grid > 0) {
+      std::vector<MegaLayer> ml(m->layers_n());
+      for (int l = 0; l < m->layers_n(); ++l) {
+        const LayerWeights& w = m->layers[l];
+        ml[l] = MegaLayer{w.ln1_g, w.ln1_b, w.w_qkv, w.b_qkv, w.w_proj, w.b_proj, w.ln2_g, w.ln2_b,
+                          w.w_fc, w.b_fc, w.w_proj2, w.b_proj2, c->layer_pool(l)};
+      }
+      PG_CUDA_TRY(cudaMalloc(&c->d_mega_layers, ml.size() * sizeof(MegaLayer)));
+      PG_CUDA_TRY(cudaMemcpyAsync(c->d_mega_layers, ml.data(), ml.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice, c->stream));
+      PG_CUDA_TRY(cudaMalloc(&c->d_barrier, 2 * sizeof(unsigned)));
+      PG_CUDA_TRY(cudaMemsetAsync(c->d_barrier, 0, 2 * sizeof(unsigned), c->stream));
+      if (env_flag("PG_MEGA_TRACE")) {
+        PG_CUDA_TRY(cudaMalloc(&c->d_mega_trace, 8 * sizeof(unsigned long long)));
+        PG_CUDA_TRY(cudaMemsetAsync(c->d_mega_trace, 0, 8 * sizeof(unsigned long long), c->stream));
+      }
+      PG_CUDA_TRY(cudaStreamSynchronize(c->stream));  // `ml` is a pageable temporary
+    }
   }
   PG_CUDA_TRY(cudaMallocHost(&c->h_ids, B * sizeof(int)));
   PG_CUDA_TRY(cudaMallocHost(&c->h_out, (B * (1 + 2 * MAX_TOPK) + 1) * sizeof(int)));
@@ -398,6 +431,23 @@ struct StepProfiler {
 // forward_one_profiled_with_scratch + block_forward_one_profiled (rust.rs:943-1006, 1136-1250).
 static cudaError_t enqueue_decode_step(pg_cache* c, int batch, int splits, cudaStream_t s, uint64_t* launches,
                                        StepProfiler* prof = nullptr) {
+  if (!prof && c->mega_grid > 0 && decode_mega_supported(batch, c->model->c(), c->model->f(), c->model->head_dim()) &&
+      c->mega_grid <= c->part_stride) {
+    // the whole step in one persistent cooperative kernel
+    const pg_model* m = c->model;
+    MegaArgs a{};
+    a.layers = c->d_mega_layers; a.wte = m->wte; a.wpe = m->wpe; a.lnf_g = m->lnf_g; a.lnf_b = m->lnf_b;
+    a.n_layer = m->layers_n(); a.c = m->c(); a.f = m->f(); a.v = m->v(); a.n_positions = m->positions();
+    a.eps = m->cfg.layer_norm_epsilon;
+    a.ids = c->d_ids; a.pos = c->d_pos; a.argmax = c->d_argmax; a.token_log = c->d_token_log;
+    a.x = c->x; a.qkv = c->qkv; a.attn = c->attn; a.h = c->hbuf; a.logits = c->logits;
+    a.page_table = c->d_table; a.kv = c->kv; a.attn_part = c->attn_part; a.attn_counters = c->attn_counters;
+    a.part_val = c->part_val; a.part_idx = c->part_idx; a.barrier = c->d_barrier; a.error_flag = c->d_error;
+    a.trace = c->d_mega_trace;
+    a.m = batch; a.attn_splits = splits;
+    if (launches) *launches = 1;
+    return launch_decode_mega(a, c->mega_grid, s);
+  }
   const pg_model* m = c->model;
   const int C = m->c(), F = m->f(), V = m->v();
   const bool pdl = m->use_pdl;
@@ -671,7 +721,7 @@ static int fetch_outputs(pg_cache* c, int batch, float* logits_out, int32_t* arg
   PG_CUDA_TRY(cudaMemcpyAsync(h_err, c->d_error, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
   PG_CUDA_TRY(cudaStreamSynchronize(c->stream));
   if (*h_err)
-    return set_error(PG_TIMEOUT, "a bounded wait inside a tensor-core kernel expired (role code " + std::to_string(*h_err) + ")");
+    return set_error(PG_TIMEOUT, "a bounded wait inside a device kernel expired (code " + std::to_string(*h_err) + ")");
   if (argmax_out) memcpy(argmax_out, c->h_out, batch * sizeof(int));
   if (k > 0 && topk_vals) memcpy(topk_vals, c->h_out + c->max_batch, (size_t)batch * k * sizeof(float));
   if (k > 0 && topk_idx) memcpy(topk_idx, c->h_out + c->max_batch + (size_t)c->max_batch * MAX_TOPK, (size_t)batch * k * sizeof(int));

@@ -71,6 +71,7 @@ class Gpt2CudaConfig:
     page_tokens: int = 32
     use_graphs: bool = True
     attn_splits: int = 0
+    persistent_step: bool = False  # one cooperative kernel per decode step (<= 8 sequences)
 
     def to_native(self) -> N.PgBackendConfig:
         if self.math_mode not in _MATH:
@@ -78,6 +79,7 @@ class Gpt2CudaConfig:
         b = N.PgBackendConfig()
         b.device, b.math_mode, b.page_tokens = self.device, _MATH[self.math_mode], self.page_tokens
         b.use_graphs, b.attn_splits = (1 if self.use_graphs else 2), self.attn_splits
+        b.persistent_step = 1 if self.persistent_step else 0
         return b
 
 

@@ -267,6 +267,28 @@ def test_graphs_and_plain_launches_agree_bitwise(oracle):
     assert np.array_equal(outs[0], outs[1])
 
 
+@pytest.mark.parametrize("batch", [1, 3, 8])
+def test_persistent_step_kernel_matches_oracle(midi, oracle, batch):
+    """The whole decode step as one cooperative kernel with grid barriers (opt-in)."""
+    cfg, w, _, o = midi
+    g = pg.Gpt2Model(cfg, w, pg.Gpt2CudaConfig(persistent_step=True, attn_splits=2 if batch == 3 else 0))
+    prompts = [synthetic.uniform_prompt(800 + i, 40 + 9 * i, cfg["vocab_size"]) for i in range(batch)]
+    cache = g.new_kv_cache(max_batch=batch)
+    _, cur = g.prefill_batch(prompts, cache)
+    ocaches = []
+    for p in prompts:
+        c = o.new_kv_cache()
+        o.prefill(p, c)
+        ocaches.append(c)
+    for step in range(5):
+        logits, am, _, _ = g.forward_one_batch(cur, cache, want_logits=True)
+        ol = np.stack([o.forward_one(int(cur[i]), ocaches[i]) for i in range(batch)])
+        assert_logits_close(logits, ol)
+        assert list(am) == [oracle.argmax_logits(l) for l in ol]
+        cur = am.copy()
+    np.testing.assert_allclose(cache.read_layer(1, batch - 1)[0], ocaches[-1].read_layer(1)[0], rtol=1e-4, atol=1e-5)
+
+
 def test_odd_inner_dimension_takes_the_generic_path(oracle):
     """n_embd = 6 is not a multiple of 4: no vector loads, no fusion; head_dim 3."""
     cfg = dict(vocab_size=11, n_positions=9, n_embd=6, n_layer=2, n_head=2, n_inner=10, layer_norm_epsilon=1e-5)
