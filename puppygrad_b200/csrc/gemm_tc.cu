@@ -171,7 +171,8 @@ template <int BN>
 struct SsSmem {
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
   static constexpr int A_BYTES = TILE_M * BK * 4, B_BYTES = BN * BK * 4;
-  static constexpr size_t BYTES = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int EPI_BYTES = 4 * 32 * 33 * 4;  // one padded 32x32 transpose tile per epilogue warp
+  static constexpr size_t BYTES = (size_t)STAGES * (A_BYTES + B_BYTES) + EPI_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 template <int BN>
@@ -183,7 +184,8 @@ __global__ void __launch_bounds__(192, 1)
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* smem_a = base;
   uint8_t* smem_b = base + (size_t)S::STAGES * S::A_BYTES;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem_b + (size_t)S::STAGES * S::B_BYTES);
+  float* epi_tiles = reinterpret_cast<float*>(smem_b + (size_t)S::STAGES * S::B_BYTES);
+  uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(epi_tiles) + S::EPI_BYTES);
   uint64_t* empty = full + S::STAGES;
   uint64_t* d_full = empty + S::STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_full + 1);
@@ -237,34 +239,36 @@ __global__ void __launch_bounds__(192, 1)
       umma_commit(d_full);
     }
   } else {
+    // TMEM lane = output row, but a row-per-thread store touches 32 cache lines per instruction:
+    // every 32x32 block goes through a padded shared-memory tile and leaves column-per-lane, so
+    // that residual loads and output stores are 128-byte coalesced.
     const int q = warp & 3;
-    const int row = m0 + q * 32 + lane;
+    float* tile = epi_tiles + q * (32 * 33);
     if (mbar_wait(d_full, 0, failed, a.error_flag, 3)) {
       tc_fence_after();
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         float v[32];
         tmem_ld32(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
-        if (row < a.m) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int col = n0 + c0 + j;
-            if (col < a.n) {
-              float r = a.bias ? a.bias[col] + v[j] : v[j];
+        for (int j = 0; j < 32; ++j) tile[lane * 33 + j] = v[j];
+        __syncwarp();
+        const int col = n0 + c0 + lane;
+        const float bias = (a.bias && col < a.n) ? a.bias[col] : 0.f;
+        if (col < a.n) {
+#pragma unroll 4
+          for (int rr = 0; rr < 32; ++rr) {
+            const int row = m0 + q * 32 + rr;
+            if (row < a.m) {
+              float r = tile[rr * 33 + lane];
+              if (a.bias) r = bias + r;
               if (a.epilogue == EPI_GELU) r = gelu_ref(r);
               if (a.epilogue == EPI_RESID) r = a.resid[(size_t)row * a.n + col] + r;
-              v[j] = r;
+              a.out[(size_t)row * a.n + col] = r;
             }
           }
-          float* dst = a.out + (size_t)row * a.n + n0 + c0;
-          if ((a.n & 3) == 0 && n0 + c0 + 32 <= a.n) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-          } else {
-            for (int j = 0; j < 32; ++j)
-              if (n0 + c0 + j < a.n) dst[j] = v[j];
-          }
         }
+        __syncwarp();
       }
     }
   }

@@ -635,6 +635,7 @@ static int grow_prefill_workspace(pg_cache* c, size_t rows) {
 struct BlockWorkspace {
   float *x, *norm, *qkv, *attn, *h;
   const int *d_slot, *d_pos, *d_seq_start;
+  int* d_error;  // error word of the tensor-core kernels (may be nullptr: then they are not used)
 };
 
 static int run_blocks(const pg_model* m, const BlockWorkspace& ws, const PrefillPlan& plan, pg_cache* cache,
@@ -647,6 +648,13 @@ static int run_blocks(const pg_model* m, const BlockWorkspace& ws, const Prefill
     a.w = w; a.bias = bias; a.x = x; a.out = out; a.resid = resid; a.eps = eps;
     a.m = rows; a.n = n_out; a.k = k;
     if (rows <= 16 && k % 4 == 0) return launch_linear_decode(a, epi, false, s, nullptr);
+    if (m->backend.math_mode == PG_MATH_TF32 && ws.d_error && rows >= 128 && tc_gemm_supported(rows, n_out, k)) {
+      // single TF32 pass on the tensor cores: the fast prefill variant with its own looser bound
+      TcGemmArgs t{};
+      t.x = x; t.w = w; t.bias = bias; t.resid = resid; t.out = out; t.error_flag = ws.d_error;
+      t.m = rows; t.n = n_out; t.k = k; t.epilogue = epi;
+      return launch_tc_gemm_tf32(t, s);
+    }
     return launch_gemm_f32(a, epi, s);
   };
   for (int l = 0; l < m->layers_n(); ++l) {
@@ -777,7 +785,7 @@ static int do_prefill(const pg_model* m, pg_cache* c, const int32_t* ids, const 
   PG_CUDA_TRY(cudaMemcpyAsync(d_start, plan.seq_start.data(), (batch + 1) * sizeof(int), cudaMemcpyHostToDevice, s));
   PG_CUDA_TRY(cudaMemcpyAsync(d_last, plan.last_rows.data(), batch * sizeof(int), cudaMemcpyHostToDevice, s));
   PG_CUDA_TRY(launch_embed(m->wte, m->wpe, d_ids, d_pos, c->px, plan.rows, m->c(), false, s));
-  BlockWorkspace ws{c->px, c->pnorm, c->pqkv, c->pattn, c->ph, d_slot, d_pos, d_start};
+  BlockWorkspace ws{c->px, c->pnorm, c->pqkv, c->pattn, c->ph, d_slot, d_pos, d_start, c->d_error};
   if (int r = run_blocks(m, ws, plan, c, s)) return r;
   // last position of each prompt -> ln_f -> lm_head (the reference computes logits for every
   // prompt token and keeps the last, rust.rs:920-926; only the last is observable)
@@ -859,7 +867,7 @@ static int do_forward(const pg_model* m, const int32_t* ids, int t, float* logit
     hm[2 * R + 1] = t;
     PG_CUDA_TRY(cudaMemcpyAsync(meta, hm.data(), hm.size() * sizeof(int), cudaMemcpyHostToDevice, s));
     PG_CUDA_TRY(launch_embed(m->wte, m->wpe, meta, meta + R, x, t, (int)C, false, s));
-    BlockWorkspace ws{x, norm, qkv, attn, h, nullptr, meta + R, meta + 2 * R};
+    BlockWorkspace ws{x, norm, qkv, attn, h, nullptr, meta + R, meta + 2 * R, nullptr};
     if (int r = run_blocks(m, ws, plan, nullptr, s)) return r;
     const float* hidden = last_only ? x + (R - 1) * C : x;
     PG_CUDA_TRY(launch_layernorm_rows(hidden, m->lnf_g, m->lnf_b, m->cfg.layer_norm_epsilon, norm, (int)out_rows, (int)C, false, s));

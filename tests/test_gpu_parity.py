@@ -458,3 +458,20 @@ def test_sharding_over_two_gpus_gives_the_single_gpu_streams(midi):
         model = pg.Gpt2Model(cfg, w, pg.Gpt2CudaConfig(device=rank))
         merged.update(run(model, sharding.partition(6, 2, rank)))
     assert sharding.gather_streams(merged, 6) == [single[i] for i in range(6)]
+
+
+def test_tf32_prefill_is_within_its_stated_bound(oracle):
+    """math_mode tf32: prefill GEMMs as one TF32 tensor-core pass. Stated bound for the final-position
+    logits against the FP32 oracle: 5e-3 of the logit range (the FP32 path holds 1e-3 / 1e-4)."""
+    cfg = synthetic.preset("midi")
+    cfg["n_positions"] = 512
+    w = synthetic.random_init_weights(cfg, 5)
+    prompts = [synthetic.uniform_prompt(900 + i, 300, cfg["vocab_size"]) for i in range(2)]
+    g = pg.Gpt2Model(cfg, w, pg.Gpt2CudaConfig(math_mode="tf32"))
+    o = oracle.Model(cfg, w, threads=os.cpu_count())
+    cache = g.new_kv_cache(max_batch=2)
+    logits, _ = g.prefill_batch(prompts, cache, want_logits=True)
+    for i, p in enumerate(prompts):
+        want = o.prefill(p, o.new_kv_cache())
+        span = float(want.max() - want.min())
+        assert np.abs(logits[i] - want).max() <= 5e-3 * span
