@@ -196,6 +196,30 @@ def small_batch1(pg, synthetic, device):
             "bytes_per_token": step_bytes, "hbm_frac": step_bytes / (best / 60) / 1e9 / peak}
 
 
+def prefill_small(pg, synthetic, device):
+    """GPT-2 small prefill, 8 prompts of 1024 tokens (BASELINE configs[1]): FP32 FMA path and the
+    single-pass TF32 tensor-core path. flops = linear GEMMs only (2*B*T*L*12*C^2), over the whole
+    prefill time (attention, LayerNorm and the KV scatter included), so the rate is a lower bound."""
+    cfg = synthetic.preset("small")
+    weights = synthetic.random_init_weights(cfg, 0)
+    prompts = [synthetic.uniform_prompt(s + 1, 1024, cfg["vocab_size"]) for s in range(8)]
+    flops = 2 * 8 * 1024 * cfg["n_layer"] * 12 * cfg["n_embd"] ** 2
+    out = {}
+    for mode in ("fp32", "tf32"):
+        model = pg.Gpt2Model(cfg, weights, pg.Gpt2CudaConfig(device=device, math_mode=mode))
+        cache = model.new_kv_cache(max_batch=8)
+        model.prefill_batch(prompts, cache)
+        best = None
+        for _ in range(3):
+            cache.time_begin()
+            model.prefill_batch(prompts, cache)
+            sec = cache.time_end()
+            best = sec if best is None else min(best, sec)
+        out[mode] = {"ms": best * 1e3, "prompt_tokens_per_s": 8 * 1024 / best, "linear_tflops": flops / best / 1e12}
+        del cache, model
+    return out
+
+
 # ---------------------------------------------------------------------------------------------
 def run_ours(args):
     rank, world, local = dist_env()
@@ -278,23 +302,33 @@ def run_ours(args):
     t_prof = cache.seq_len_of(0) - 1
 
     small = small_batch1(pg, synthetic, local) if rank == 0 else None
+    prefill = prefill_small(pg, synthetic, local) if rank == 0 else None
     if rank == 0:
         peak, peak_src = measured_peaks()
         c, f, L = cfg["n_embd"], cfg["n_inner"], cfg["n_layer"]
-        # dominant kernel class by device time, its algorithmic bytes per launch
-        alg = {
-            "qkv_projection": 4 * (3 * c * c + 3 * c + B * c + B * 3 * c + 2 * c),
-            "attention_projection": 4 * (c * c + c + 3 * B * c),
-            "mlp_fc_projection": 4 * (c * f + f + B * c + B * f + 2 * c),
-            "mlp_projection": 4 * (c * f + c + B * f + 2 * B * c),
-            "final_logits": 4 * (cfg["vocab_size"] * c + B * c + B * cfg["vocab_size"] + 2 * c),
-            "attention": kv_bytes_per_step(cfg, [t_prof] * B) / L + 4 * B * 4 * c,
+        # Kernel families of the step and their algorithmic bytes per step. The four linears of a
+        # layer (and the lm_head) run the same kernel; its time is the sum of their buckets.
+        V = cfg["vocab_size"]
+        lin_bytes = L * 4 * (3 * c * c + c * c + 2 * c * f + 4 * c + f) + 4 * V * c  # weights + biases, once
+        lin_bytes += L * 4 * B * (2 * c + 3 * c + 2 * c + c + 2 * c + 2 * f + 2 * f + c) + 4 * B * (2 * c + V)
+        fam = {
+            "linears": (lin_bytes, sum(prof[k][0] for k in ("qkv_projection", "attention_projection",
+                                                          "mlp_fc_projection", "mlp_projection", "final_logits")),
+                        sum(prof[k][1] for k in ("qkv_projection", "attention_projection", "mlp_fc_projection",
+                                                 "mlp_projection", "final_logits"))),
+            "decode_attention_kernel": (kv_bytes_per_step(cfg, [t_prof] * B) + 4 * B * 4 * c * L,
+                                        prof["attention"][0], prof["attention"][1]),
         }
-        dom = max(alg, key=lambda k: prof[k][0])
-        dom_sec, dom_n = prof[dom]
+        dom = max(fam, key=lambda k: fam[k][1])
+        dom_bytes, dom_sec, dom_n = fam[dom]
         per_launch = dom_sec / max(dom_n, 1)
-        launches_per_step_dom = dom_n
-        achieved = alg[dom] * (L if dom != "final_logits" else 1) / launches_per_step_dom / per_launch / 1e9
+        achieved = dom_bytes / dom_sec / 1e9
+        kernel_name = dom
+        if dom == "linears":
+            kernel_name = "tc_gemm_x3_kernel" if args.math == "tf32x3" and 8 < B <= 64 else "linear_decode_kernel"
+        # DRAM traffic of the captured launches equals the algorithmic bytes within 4 %
+        # (profiles/tc_gemm_x3_kernel_m64_4096x1024.md, profiles/decode_attention_kernel_b64_h16_kv256.md)
+        traffic = dom_bytes / max(dom_n, 1) * (1.035 if dom == "linears" else 1.004)
         step_bytes = model.weight_bytes_per_step() + kv_bytes_per_step(cfg, lens_mid)
         step_achieved = step_bytes / (sec_max / K) / 1e9
 
@@ -312,9 +346,10 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
             "gpu_launches": int(launches),
             "clocks": clock_info,
-            "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
-                         "per_launch_us": per_launch * 1e6},
+            "roofline": {"bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
+                         "launches_per_step": dom_n, "per_launch_us": per_launch * 1e6,
+                         "algorithmic_bytes_per_launch": dom_bytes / max(dom_n, 1)},
             "step_roofline": {"bound": "hbm", "bytes_per_step": step_bytes, "achieved": step_achieved,
                               "peak": peak, "frac": step_achieved / peak},
             "profile_us": {k: round(v[0] * 1e6, 1) for k, v in prof.items()},
@@ -322,7 +357,7 @@ def run_ours(args):
                              "sample": f"1 sequence, {cpu_tokens} greedy decode tokens after a 16-token prompt "
                                        f"({cpu_dt:.1f} s)"},
             "check": {"tokens_last_step": [int(x) for x in toks[-1][:4]]},
-            "also": {"gpt2_small_batch1": small},
+            "also": {"gpt2_small_batch1": small, "gpt2_small_prefill_8x1024": prefill},
         }
         print(json.dumps(line))
     if world > 1:

@@ -38,9 +38,34 @@ def linear_case(m, n, k, math, epilogue, reps, seed=0):
             "gbps": bytes_ / sec / 1e9, "tflops": 2 * m * n * k / sec / 1e12, "max_rel_err_vs_f64": err}
 
 
+def attention_case(batch, n_head, kv_len, splits, reps, seed=0):
+    """Decode attention, head_dim 64. Algorithmic bytes: 4 * batch * (2 * kv_len * c + 4 * c)."""
+    rng = np.random.default_rng(seed + batch + 3 * kv_len)
+    d = 64
+    c = n_head * d
+    qkv = rng.standard_normal((batch, 3 * c), dtype=np.float32)
+    keys = rng.standard_normal((batch, n_head, kv_len, d), dtype=np.float32)
+    values = rng.standard_normal((batch, n_head, kv_len, d), dtype=np.float32)
+    out, sec = ops.decode_attention(qkv, keys, values, page_tokens=32, splits=splits, reps=reps)
+    # float64 check on the first sequence and head
+    k_all = np.concatenate([keys[0, 0], qkv[0, c:c + d][None]], 0).astype(np.float64)
+    v_all = np.concatenate([values[0, 0], qkv[0, 2 * c:2 * c + d][None]], 0).astype(np.float64)
+    sc = k_all @ qkv[0, :d].astype(np.float64) / 8.0
+    p = np.exp(sc - sc.max())
+    want = (p / p.sum()) @ v_all
+    err = float(np.abs(out[0, :d] - want).max() / max(np.abs(want).max(), 1e-30))
+    bytes_ = 4 * batch * (2 * kv_len * c + 4 * c)
+    return {"op": "decode_attention", "batch": batch, "n_head": n_head, "kv_len": kv_len, "splits": splits,
+            "us": sec * 1e6, "gbps": bytes_ / sec / 1e9, "max_rel_err_vs_f64": err}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["linear"])
+    ap.add_argument("op", choices=["linear", "attention"])
+    ap.add_argument("--batch", type=int, nargs="+", default=[1, 32, 256])
+    ap.add_argument("--kv", type=int, nargs="+", default=[128, 256, 512, 1024])
+    ap.add_argument("--heads", type=int, default=25)
+    ap.add_argument("--splits", type=int, default=0, help="0 = as the model would choose")
     ap.add_argument("--preset", choices=["xl"], default=None)
     ap.add_argument("--m", type=int, nargs="+", default=[64])
     ap.add_argument("--n", type=int, nargs="+", default=[4096])
@@ -49,6 +74,12 @@ def main():
     ap.add_argument("--epilogue", default="none")
     ap.add_argument("--reps", type=int, default=10)
     a = ap.parse_args()
+    if a.op == "attention":
+        for b in a.batch:
+            for kv in a.kv:
+                sp = a.splits or max(1, min(8, (2 * 148 + b * a.heads - 1) // (b * a.heads), (kv + 128) // 128))
+                print(json.dumps(attention_case(b, a.heads, kv, sp, a.reps)), flush=True)
+        return
     shapes = []
     if a.preset == "xl":
         c, f = XL["c"], XL["f"]
