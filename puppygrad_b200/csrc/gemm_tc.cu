@@ -295,7 +295,7 @@ struct X3 {
   static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES > D_BYTES ? STAGES * STAGE_BYTES : D_BYTES;
   static constexpr size_t BYTES = (size_t)PIPE_BYTES + 1024 + 256;
   static constexpr int TMEM_COLS = 512;  // BN accumulator columns, then TSTAGES * 64 from column 64
-  static constexpr int A_COL0 = 64;
+  static constexpr int A_COL0 = 128;     // accumulator: columns [0, BN) hi*hi + lo*hi, [BN, 2 BN) hi*lo
 };
 
 __device__ __forceinline__ void trace_mark(const TcGemmArgs& a, int slot) {
@@ -419,7 +419,10 @@ __global__ void __launch_bounds__(192, 1)
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc_tf32(TILE_M, BN);
+      // x_hi and x_lo tiles are adjacent in a stage: one MMA over both (N = 2 BN) yields hi*hi and
+      // hi*lo side by side, a second one (N = BN) adds lo*hi onto the first half. Two MMAs per k step
+      // instead of three: the issue cost of these small MMAs does not depend on N.
+      const uint32_t idesc = umma_idesc_tf32(TILE_M, BN), idesc2 = umma_idesc_tf32(TILE_M, 2 * BN);
       long long m_wait = 0, m_issue = 0;
       for (int i = 0; i < nkb; ++i) {
         const int s = i % S::STAGES, ts = i % S::TSTAGES;
@@ -430,12 +433,11 @@ __global__ void __launch_bounds__(192, 1)
         m_wait += c1 - c0;
         tc_fence_after();
         long long f1 = clock64();
-        const uint64_t dhi = umma_desc_sw128(stage_bhi(s)), dlo = umma_desc_sw128(stage_blo(s));
+        const uint64_t dhi = umma_desc_sw128(stage_bhi(s));  // spans x_hi then x_lo
         const uint32_t ahi = tmem_base + S::A_COL0 + ts * 64, alo = ahi + 32;
 #pragma unroll
         for (int k = 0; k < BK / 8; ++k) {
-          umma_tf32_ts(tmem_base, ahi + k * 8, dhi + (uint64_t)(k * 2), idesc, (i | k) != 0);
-          umma_tf32_ts(tmem_base, ahi + k * 8, dlo + (uint64_t)(k * 2), idesc, 1);
+          umma_tf32_ts(tmem_base, ahi + k * 8, dhi + (uint64_t)(k * 2), idesc2, (i | k) != 0);
           umma_tf32_ts(tmem_base, alo + k * 8, dhi + (uint64_t)(k * 2), idesc, 1);
         }
         long long f2 = clock64();
@@ -506,10 +508,11 @@ __global__ void __launch_bounds__(192, 1)
       if (threadIdx.x == 64) trace_mark(a, 3);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
-        float v[16];
+        float v[16], v2[16];
         tmem_ld16(tmem_base + lane_addr + (uint32_t)c0, v);
+        tmem_ld16(tmem_base + lane_addr + (uint32_t)(BN + c0), v2);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) dbuf[(size_t)(c0 + j) * TILE_M + r] = (nkb > 0) ? v[j] : 0.f;
+        for (int j = 0; j < 16; ++j) dbuf[(size_t)(c0 + j) * TILE_M + r] = (nkb > 0) ? v[j] + v2[j] : 0.f;
       }
     }
   }
