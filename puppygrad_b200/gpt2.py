@@ -321,6 +321,75 @@ class Gpt2Model:
                  "mlp_projection", "final_logits", "other")
         return {n: (getattr(p, n), int(p.launches[i])) for i, n in enumerate(names)}
 
+    def generate_batch(self, prompts: Sequence[Sequence[int]], config: TextGenerationConfig,
+                       seeds: Optional[Sequence[int]] = None, cache: Optional[Gpt2KvCache] = None) -> List[List[int]]:
+        """The token-id loop of Gpt2Runtime::stream_token_ids_with_stats (rust.rs:577-617) for a
+        batch of independent sequences, each with its own LogitsSampler seeded `seeds[i]`
+        (default config.seed + i). Greedy without repeat penalty uses the device arg-max;
+        temperature with top_k <= 64 and no repeat penalty uses the device top-k and the host
+        draw of sample_logits; anything else brings the logits rows back to the host sampler.
+        A sequence that emits EOS stops; the others continue. Returns the generated ids."""
+        from .generation import LogitsSampler
+        config.validate()
+        n = len(prompts)
+        seeds = list(seeds) if seeds is not None else [config.seed + i for i in range(n)]
+        samplers = [LogitsSampler(s) for s in seeds]
+        cache = cache or self.new_kv_cache(max_batch=n)
+        penalty = not (config.repeat_penalty == 1.0 or config.repeat_last_n == 0)
+        greedy = config.temperature <= 0.0
+        use_argmax = greedy and not penalty
+        use_topk = (not greedy) and (not penalty) and config.top_k is not None and 0 < config.top_k <= 64
+        k = config.top_k if use_topk else 0
+        history = [[int(t) for t in p] for p in prompts]
+        out: List[List[int]] = [[] for _ in range(n)]
+        done = [False] * n
+        logits, am = self.prefill_batch(prompts, cache, want_logits=not use_argmax)
+        tv = ti = None
+        if use_topk:  # prefill returns whole rows: order them on the host like the device top-k does
+            tv = np.empty((n, k), np.float32)
+            ti = np.empty((n, k), np.int32)
+            idx = np.arange(logits.shape[1])
+            for i in range(n):
+                order = np.lexsort((idx, -logits[i]))[:k]  # descending value, ties by lower index
+                tv[i], ti[i] = logits[i, order], order
+        for step in range(config.max_new_tokens):
+            nxt = np.zeros(n, np.int32)
+            for i in range(n):
+                if done[i]:
+                    nxt[i] = history[i][-1]
+                    continue
+                if len(history[i]) >= self.config.n_positions:
+                    done[i] = True
+                    nxt[i] = history[i][-1]
+                    continue
+                if use_argmax:
+                    tok = int(am[i])
+                elif use_topk:
+                    tok = samplers[i].select_from_topk(tv[i], ti[i], config)
+                else:
+                    tok = samplers[i].select_next_token(logits[i], history[i], config)
+                if config.eos_token_id is not None and tok == config.eos_token_id:
+                    done[i] = True
+                    nxt[i] = history[i][-1]
+                    continue
+                history[i].append(tok)
+                out[i].append(tok)
+                nxt[i] = tok
+            if all(done) or step + 1 == config.max_new_tokens:
+                break
+            if any(len(h) >= self.config.n_positions for h, d in zip(history, done) if not d):
+                for i in range(n):
+                    if len(history[i]) >= self.config.n_positions:
+                        done[i] = True
+                if all(done):
+                    break
+            # finished sequences keep stepping on their last token: their slots are independent
+            # and their outputs are ignored; a full slot would raise, so stop feeding those
+            if any(cache.seq_len_of(i) >= self.config.n_positions for i in range(n)):
+                break
+            logits, am, tv, ti = self.forward_one_batch(nxt, cache, want_logits=not (use_argmax or use_topk), top_k=k)
+        return out
+
     def decode_greedy(self, first_ids: Sequence[int], cache: Gpt2KvCache, steps: int) -> np.ndarray:
         """`steps` greedy steps with the token fed back on the device; returns [steps, batch]."""
         ids = _i32(first_ids)

@@ -475,3 +475,28 @@ def test_tf32_prefill_is_within_its_stated_bound(oracle):
         want = o.prefill(p, o.new_kv_cache())
         span = float(want.max() - want.min())
         assert np.abs(logits[i] - want).max() <= 5e-3 * span
+
+
+@pytest.mark.parametrize("kw", [dict(temperature=0.8, top_k=40), dict(temperature=0.0),
+                                dict(temperature=0.7, top_p=0.9, repeat_penalty=1.2)])
+def test_batched_sampling_with_per_sequence_seeds_matches_oracle(midi, oracle, kw):
+    """Temperature / top-k sampling for a batch, one RNG per sequence (seed base + i): every
+    sequence must reproduce the oracle's single-sequence sampler loop draw for draw."""
+    cfg, w, g, o = midi
+    n, new = 6, 20
+    prompts = [synthetic.uniform_prompt(1000 + i, 12 + 3 * i, cfg["vocab_size"]) for i in range(n)]
+    conf = pg.TextGenerationConfig(new, seed=500, **kw)
+    got = g.generate_batch(prompts, conf)
+    for i, p in enumerate(prompts):
+        og = oracle.generation_config(new, seed=500 + i, **kw)
+        sampler = oracle.LogitsSampler(og.seed)
+        cache = o.new_kv_cache()
+        logits = o.prefill(p, cache)
+        hist, want = [int(t) for t in p], []
+        for s in range(new):
+            nxt = sampler.select_next_token(logits, hist, og)
+            hist.append(nxt)
+            want.append(nxt)
+            if s + 1 < new:
+                logits = o.forward_one(nxt, cache)
+        assert got[i] == want, i
