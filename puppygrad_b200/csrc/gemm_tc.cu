@@ -291,9 +291,10 @@ struct X3 {
   static constexpr int TSTAGES = 6;  // tensor-memory stages of the split weight tile
   static constexpr int A_BYTES = TILE_M * BK * 4, B_BYTES = BN * BK * 4;
   static constexpr int STAGE_BYTES = A_BYTES + 2 * B_BYTES;
-  static constexpr int D_BYTES = TILE_M * BN * 4;  // accumulator staging, aliases the stages after the main loop
-  static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES > D_BYTES ? STAGES * STAGE_BYTES : D_BYTES;
-  static constexpr size_t BYTES = (size_t)PIPE_BYTES + 1024 + 256;
+  static constexpr int D_BYTES = TILE_M * BN * 4;  // receive buffer of the split-K exchange (never aliased:
+                                                   // peers write it while this CTA may still be in its main loop)
+  static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES;
+  static constexpr size_t BYTES = (size_t)PIPE_BYTES + D_BYTES + 1024 + 256;
   static constexpr int TMEM_COLS = 512;  // BN accumulator columns, then TSTAGES * 64 from column 64
   static constexpr int A_COL0 = 128;     // accumulator: columns [0, BN) hi*hi + lo*hi, [BN, 2 BN) hi*lo
 };
@@ -319,12 +320,14 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float ld_dsmem(uint32_t local_addr, uint32_t rank) {
+// Address of `local_addr` (a shared::cta address of this kernel's layout) inside CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t rank) {
   uint32_t remote;
-  float v;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-  return v;
+  return remote;
+}
+__device__ __forceinline__ void st_dsmem(uint32_t remote_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote_addr), "f"(v) : "memory");
 }
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
@@ -348,14 +351,14 @@ __global__ void __launch_bounds__(192, 1)
   using S = X3<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* full = reinterpret_cast<uint64_t*>(base + (size_t)S::PIPE_BYTES);
+  float* recv = reinterpret_cast<float*>(base + (size_t)S::PIPE_BYTES);  // [split][token][row of my slice]
+  uint64_t* full = reinterpret_cast<uint64_t*>(base + (size_t)S::PIPE_BYTES + S::D_BYTES);
   uint64_t* empty = full + S::STAGES;
   uint64_t* a_ready = empty + S::STAGES;
   uint64_t* a_free = a_ready + S::TSTAGES;
   uint64_t* d_full = a_free + S::TSTAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_full + 1);
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* dbuf = reinterpret_cast<float*>(base);  // [token][128 rows], valid after the main loop
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * TILE_M;  // first weight row (output feature) of this tile
@@ -502,21 +505,26 @@ __global__ void __launch_bounds__(192, 1)
       trace_add(a, 9, t_ld);
       trace_add(a, 10, t_st);
     }
-    // accumulator -> shared memory, [token][row]: all MMAs (and so all TMA writes) are complete
+    // Split-K exchange, push model: row r of the tile is finished by CTA r / ROWS_PER of the
+    // cluster, so this thread sends its partial sums of row r straight from registers into that
+    // CTA's receive buffer (distributed shared memory).
     if (ok && mbar_wait(d_full, 0, failed, a.error_flag, 16)) {
       tc_fence_after();
       if (threadIdx.x == 64) trace_mark(a, 3);
+      constexpr int RP = TILE_M / SPLITS;
+      const uint32_t dst = dsmem_addr(smem_u32(recv), (uint32_t)(r / RP)) +
+                           (uint32_t)((split * BN) * RP + (r % RP)) * 4u;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
         float v[16], v2[16];
         tmem_ld16(tmem_base + lane_addr + (uint32_t)c0, v);
         tmem_ld16(tmem_base + lane_addr + (uint32_t)(BN + c0), v2);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) dbuf[(size_t)(c0 + j) * TILE_M + r] = (nkb > 0) ? v[j] + v2[j] : 0.f;
+        for (int j = 0; j < 16; ++j) st_dsmem(dst + (uint32_t)((c0 + j) * RP) * 4u, (nkb > 0) ? v[j] + v2[j] : 0.f);
       }
     }
   }
-  // every thread of every CTA of the cluster passes both cluster barriers exactly once
+  // every thread of every CTA of the cluster passes the cluster barrier exactly once
   tc_fence_before();
   __syncthreads();
   // this CTA finishes rows [split * 128 / SPLITS, ...) of the tile: thread -> (row, token group)
@@ -538,22 +546,17 @@ __global__ void __launch_bounds__(192, 1)
     }
   }
   if (threadIdx.x == 64) trace_mark(a, 4);
+  // release / acquire: every peer's pushes into this CTA's buffer are complete and visible after
+  // the barrier, and no peer touches this CTA's shared memory after it, so the CTA may then exit
   cluster_sync_all();
   if (threadIdx.x == 64) trace_mark(a, 5);
   if (active && !*failed) {
-    const uint32_t dbuf_addr = smem_u32(dbuf);
-    float part[OUTS][SPLITS];
-#pragma unroll
-    for (int o = 0; o < OUTS; ++o)
-#pragma unroll
-      for (int sp = 0; sp < SPLITS; ++sp)
-        part[o][sp] = ld_dsmem(dbuf_addr + (uint32_t)((tg + o * SPLITS) * TILE_M + row) * 4u, (uint32_t)sp);
 #pragma unroll
     for (int o = 0; o < OUTS; ++o) {
       const int j = tg + o * SPLITS;
       float acc = 0.f;
 #pragma unroll
-      for (int sp = 0; sp < SPLITS; ++sp) acc += part[o][sp];  // split order: deterministic
+      for (int sp = 0; sp < SPLITS; ++sp) acc += recv[(size_t)(sp * BN + j) * ROWS_PER + rl];  // split order
       if (j < a.m) {
         float v = a.bias ? bias_v + acc : acc;
         if (a.epilogue == EPI_GELU) v = gelu_ref(v);
@@ -567,12 +570,14 @@ __global__ void __launch_bounds__(192, 1)
       }
     }
   }
-  if (threadIdx.x == 64) trace_mark(a, 6);
-  cluster_sync_all();  // no CTA may leave while a peer still reads its shared memory
-  if (threadIdx.x == 64) trace_mark(a, 7);
+  if (threadIdx.x == 64) {
+    trace_mark(a, 6);
+    trace_mark(a, 7);
+  }
+  tc_fence_before();
+  __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, S::TMEM_COLS);
 }
-
 
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -658,6 +663,8 @@ cudaError_t launch_tile_weights(const float* src, float* dst, int n, int k, cuda
   return cudaGetLastError();
 }
 
+static bool g_cluster16_ok = false;  // set by init_tc_kernel_attributes
+
 bool tc_gemm_supported(int m, int n, int k) {
   (void)m;
   (void)n;
@@ -674,7 +681,26 @@ cudaError_t init_tc_kernel_attributes() {
   e = cudaFuncSetAttribute(tc_gemm_x3_kernel<BN_, SP_>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
                            (int)X3<BN_>::BYTES);                                                              \
   if (e != cudaSuccess) return e;
-  PG_X3_ATTR(64, 1) PG_X3_ATTR(64, 2) PG_X3_ATTR(64, 4) PG_X3_ATTR(64, 8)
+  PG_X3_ATTR(64, 1) PG_X3_ATTR(64, 2) PG_X3_ATTR(64, 4) PG_X3_ATTR(64, 8) PG_X3_ATTR(64, 16)
+  // clusters of 16 CTAs are beyond the portable size of 8: opt in, and use them only if the device
+  // can actually place one (a GPC with 16 free SMs)
+  if (cudaFuncSetAttribute(tc_gemm_x3_kernel<64, 16>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, 16);
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = X3<64>::BYTES;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 1;
+    at[0].val.clusterDim.y = 16;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, tc_gemm_x3_kernel<64, 16>, &cfg) == cudaSuccess && clusters >= 8)
+      g_cluster16_ok = true;
+    cudaGetLastError();
+  }
   PG_X3_ATTR(32, 1) PG_X3_ATTR(32, 2) PG_X3_ATTR(32, 4) PG_X3_ATTR(32, 8)
   PG_X3_ATTR(16, 1) PG_X3_ATTR(16, 2) PG_X3_ATTR(16, 4) PG_X3_ATTR(16, 8)
 #undef PG_X3_ATTR
@@ -699,14 +725,15 @@ int tc_gemm_x3_splits(int n, int k, int num_sms) {
   int splits = 1;
   // spread small matrices over the SMs, one CTA per SM at most so that the next kernel of a
   // programmatic-launch chain finds room to prefetch its weights; keep at least 4 k-blocks
-  // (64 KB of weights) per CTA; 8 is the portable cluster size
-  while (tiles * splits * 2 <= num_sms && nkb / (splits * 2) >= 4 && splits < 8) splits *= 2;
+  // (64 KB of weights) per CTA; 8 is the portable cluster size, 16 is used where the device allows
+  const int max_splits = g_cluster16_ok ? 16 : 8;
+  while (tiles * splits * 2 <= num_sms && nkb / (splits * 2) >= 4 && splits < max_splits) splits *= 2;
   return splits;
 }
 
 cudaError_t launch_tc_gemm_x3(const TcGemmArgs& a, int splits, bool pdl, cudaStream_t s) {
   if (!tc_gemm_supported(a.m, a.n, a.k) || a.m > 64 || !a.x || !a.x_lo) return cudaErrorInvalidValue;
-  if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return cudaErrorInvalidValue;
+  if (splits != 1 && splits != 2 && splits != 4 && splits != 8 && splits != 16) return cudaErrorInvalidValue;
   const int bn = a.m <= 16 ? 16 : a.m <= 32 ? 32 : 64;
   CUtensorMap mw, mhi, mlo;
   // weights in the tiled layout: a [tiles * 128, 32] matrix whose 128-row boxes are contiguous 16 KB
@@ -719,7 +746,7 @@ cudaError_t launch_tc_gemm_x3(const TcGemmArgs& a, int splits, bool pdl, cudaStr
   dim3 grid((a.n + TILE_M - 1) / TILE_M, splits);
 #define PG_X3_CASE(BN_, SP_) \
   if (bn == BN_ && splits == SP_) return launch_ex(tc_gemm_x3_kernel<BN_, SP_>, grid, X3<BN_>::BYTES, s, pdl, params, splits);
-  PG_X3_CASE(64, 1) PG_X3_CASE(64, 2) PG_X3_CASE(64, 4) PG_X3_CASE(64, 8)
+  PG_X3_CASE(64, 1) PG_X3_CASE(64, 2) PG_X3_CASE(64, 4) PG_X3_CASE(64, 8) PG_X3_CASE(64, 16)
   PG_X3_CASE(32, 1) PG_X3_CASE(32, 2) PG_X3_CASE(32, 4) PG_X3_CASE(32, 8)
   PG_X3_CASE(16, 1) PG_X3_CASE(16, 2) PG_X3_CASE(16, 4) PG_X3_CASE(16, 8)
 #undef PG_X3_CASE

@@ -1194,6 +1194,19 @@ cudaError_t init_kernel_attributes() {
   PG_SET(decode_attention_generic_kernel, 64 * 1024)
   PG_SET(topk_rows_kernel, 220 * 1024)
 #undef PG_SET
+  // The tensor-core GEMMs of a batched decode step need the largest shared-memory carve-out. If
+  // the small kernels between them asked for the default (L1-heavy) split, every switch would
+  // drain and reconfigure the SMs; they do not depend on L1, so they all request the same split.
+#define PG_CARVE(kern)                                                                                      \
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared); \
+  if (e != cudaSuccess) return e;
+  PG_CARVE(layernorm_rows_split_kernel)
+  PG_CARVE(decode_attention_kernel<64>)
+  PG_CARVE(argmax_rows_kernel)
+  PG_CARVE(finalize_kernel)
+  PG_CARVE(embed_kernel)
+  PG_CARVE(split_tf32_kernel)
+#undef PG_CARVE
   return cudaSuccess;
 }
 
