@@ -1,0 +1,679 @@
+// A chain of dependent decode linears as one persistent cooperative kernel for sm_100a.
+//
+// The decode step of a transformer block is four small GEMMs (m <= 64 tokens) that depend on each
+// other through row-wise operations (bias, residual, LayerNorm, GELU). Launched one by one, each
+// pays its launch, its pipeline fill and its epilogue, which together cost several times the
+// streaming time of its weights. Here one CTA per SM stays resident for the whole chain:
+//
+//   warp 0      weight producer: TMA loads of 16 KB weight blocks into a ring of shared-memory
+//               stages. Weights do not depend on activations, so this warp never waits for a phase
+//               to begin: while the other warps reduce, normalise or wait at the grid barrier it
+//               already fetches the next GEMM's blocks.
+//   warps 4-7   splitters: FP32 weight tile -> TF32 hi/lo pair in tensor memory (tcgen05.st); they
+//               run ahead as far as tensor memory stages are free.
+//   warp 2      activation producer: after the phase's inputs exist (grid barrier), TMA loads of
+//               the 64-token x 32 hi and lo tiles.
+//   warp 1      MMA issuer: per 8-wide k slice one tcgen05.mma of N = 128 (w_hi . [x_hi | x_lo])
+//               and one of N = 64 (w_lo . x_hi), accumulators in tensor memory, two accumulator
+//               buffers so that a finished row tile drains while the next one accumulates.
+//   warps 8-15  workers: drain accumulators into per-CTA partial tiles (global memory, L2
+//               resident), take part in the grid barrier, and run the reduce phases.
+//
+// Every GEMM's blocks (row tile major, k block minor) are cut into equal contiguous shares, one
+// per CTA, so all SMs stream the same number of bytes whatever the matrix shape. Partials are
+// added in k order by the following phase: results do not depend on scheduling.
+//
+// Every wait is bounded. On expiry the CTA raises the error word; every role then falls through
+// its remaining loops without touching memory, tensor memory is freed and the kernel ends.
+#include "kernels.cuh"
+#include "tc_common.cuh"
+
+namespace pg {
+namespace {
+
+constexpr int CH_THREADS = 512;
+// The pipelines move units of CH_UB consecutive k blocks (128 weight rows x 32 floats each): a wait
+// on an mbarrier or a tcgen05.commit costs the single MMA-issuing thread as much as several MMAs,
+// so fewer, larger hand-overs keep the tensor pipe busier.
+constexpr int CH_UB = 2;
+constexpr int CH_W_STAGES = 5;    // weight units in flight per SM (32 KB each)
+constexpr int CH_X_STAGES = 2;    // units whose activation tiles (shared memory) and split weights (tensor memory) are staged
+constexpr int CH_BN = 64;
+constexpr int CH_W_BYTES = CH_UB * TILE_M * BK * 4;
+constexpr int CH_ACT_BYTES = CH_UB * 2 * CH_BN * BK * 4;  // per block: x_hi tile then x_lo tile
+constexpr int CH_MAX_SEG = 4;     // row tiles one CTA's share may touch
+constexpr int CH_WORKERS = 256;
+constexpr uint32_t CH_D_COLS = 128, CH_A_COL0 = 256, CH_TMEM_COLS = 512;
+constexpr size_t CH_SMEM = (size_t)CH_W_STAGES * CH_W_BYTES + (size_t)CH_X_STAGES * CH_ACT_BYTES + 1024 + 1024;
+constexpr size_t CH_PART_TILE = (size_t)CH_BN * TILE_M;  // floats of one partial tile: [token][row]
+
+// Share of one CTA in units: [g0, g1) of the phase's tiles * nkb units (row tile major); per = units per CTA.
+struct ChRange {
+  int g0, g1, nkb, per;
+};
+__device__ __host__ inline ChRange chain_range(int n, int k, int cta, int grid) {
+  const int tiles = (n + TILE_M - 1) / TILE_M, nkb = k / (BK * CH_UB);  // units per row tile
+  const int total = tiles * nkb;
+  int per = (total + grid - 1) / grid;
+  // one block more per CTA when that makes shares line up with row tiles: fewer partial tiles to
+  // write and to add, at the price of a few idle SMs
+  if (nkb % per != 0 && nkb % (per + 1) == 0) per += 1;
+  ChRange r;
+  r.nkb = nkb;
+  r.per = per;
+  r.g0 = cta * per < total ? cta * per : total;
+  r.g1 = r.g0 + per < total ? r.g0 + per : total;
+  return r;
+}
+
+__device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+// All lanes wait; the verdict is made warp-uniform because aligned tcgen05 instructions follow.
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* failed, int* err, int code) {
+  const bool ok = mbar_wait(bar, parity, failed, err, code);
+  return __all_sync(0xffffffffu, ok);
+}
+
+// Grid barrier of the worker warps: arrival count only grows during a launch, barrier b (1-based)
+// is passed when it reaches grid * b. Returns the same verdict to every worker thread.
+__device__ __forceinline__ bool chain_grid_barrier(unsigned* counter, unsigned target, volatile int* failed, int* err,
+                                                   int wt, volatile int* verdict) {
+  workers_sync();
+  if (wt == 0) {
+    if (!*failed) {
+      __threadfence();
+      asm volatile("fence.proxy.async;" ::: "memory");  // results written here are read by other CTAs' TMA loads
+      asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
+      uint32_t spins = 0;
+      for (;;) {
+        unsigned v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+        if (v >= target) break;
+        if (++spins > (1u << 22) || *failed) {
+          *failed = 1;
+          atomicCAS(err, 0, 30);
+          break;
+        }
+      }
+    }
+    *verdict = *failed;  // one read, so that all workers agree
+  }
+  workers_sync();
+  return *verdict == 0;
+}
+
+__device__ __forceinline__ float4 ldcg4(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
+
+__device__ __forceinline__ void chain_trace(const ChainArgs& a, int slot) {
+  if (a.trace) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    a.trace[(size_t)blockIdx.x * 32 + slot] = t;
+  }
+}
+
+// Sum of the partial tiles covering features [f, f + 4) of token j, in k order. Loads go out in
+// batches of NB before the first add, so that their L2 latencies overlap.
+template <int NB>
+__device__ __forceinline__ float4 sum_partials(const float* partials, int f, int j, int nkb, int per) {
+  const int tile = f >> 7, row = f & 127;
+  const int c_lo = (tile * nkb) / per, c_hi = ((tile + 1) * nkb - 1) / per;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int c0 = c_lo; c0 <= c_hi; c0 += NB) {
+    float4 v[NB];
+#pragma unroll
+    for (int i = 0; i < NB; ++i) {
+      const int c = c0 + i;
+      v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (c <= c_hi) {
+        const int seg = tile - (c * per) / nkb;
+        v[i] = ldcg4(partials + ((size_t)(c * CH_MAX_SEG + seg) * CH_BN + j) * TILE_M + row);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NB; ++i) {
+      if (c0 + i <= c_hi) {
+        acc.x += v[i].x;
+        acc.y += v[i].y;
+        acc.z += v[i].z;
+        acc.w += v[i].w;
+      }
+    }
+  }
+  return acc;
+}
+
+// The same sum when every share lies inside one row tile (nkb % per == 0): the tile's `cnt` = nkb / per
+// partial tiles belong to consecutive CTAs and are each CTA's first segment, so the addresses are an
+// arithmetic sequence and need no division.
+template <int NB>
+__device__ __forceinline__ float4 sum_partials_aligned(const float* partials, int f, int j, int cnt) {
+  const int tile = f >> 7, row = f & 127;
+  const float* p0 = partials + ((size_t)(tile * cnt) * CH_MAX_SEG * CH_BN + j) * TILE_M + row;
+  constexpr size_t STRIDE = (size_t)CH_MAX_SEG * CH_BN * TILE_M;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int c0 = 0; c0 < cnt; c0 += NB) {
+    float4 v[NB];
+#pragma unroll
+    for (int i = 0; i < NB; ++i) {
+      v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (c0 + i < cnt) v[i] = ldcg4(p0 + (size_t)(c0 + i) * STRIDE);
+    }
+#pragma unroll
+    for (int i = 0; i < NB; ++i) {
+      if (c0 + i < cnt) {
+        acc.x += v[i].x;
+        acc.y += v[i].y;
+        acc.z += v[i].z;
+        acc.w += v[i].w;
+      }
+    }
+  }
+  return acc;
+}
+
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ROWS phase: x[j, :] += bias + sum of partials, then optional LayerNorm of the updated row written
+// as a TF32 hi/lo pair. One CTA per token; wt = worker thread 0..255; n % 4 == 0, n <= 4096.
+__device__ __forceinline__ void chain_rows_phase(const ChainArgs& a, const ChainPhase& ph, int j, int wt, float* red, int pidx) {
+  const int n = ph.n, n4 = n >> 2;
+  const ChRange r = chain_range(ph.n, ph.k, 0, (int)gridDim.x);
+  const bool aligned = r.nkb % r.per == 0;
+  const int cnt = r.nkb / r.per;
+  float4 v[4];
+  float s = 0.f;
+  const bool tr = a.trace && blockIdx.x == 0 && wt == 0;
+  unsigned long long* tq = a.trace + (size_t)gridDim.x * 32 + 256 + pidx * 8;
+  if (tr) tq[0] = clock64();
+  float4* xrow = reinterpret_cast<float4*>(ph.x + (size_t)j * n);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int u = wt + i * CH_WORKERS;
+    v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (u < n4) {
+      const float4 xv = __ldcg(xrow + u);
+      float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (ph.bias) b = __ldg(reinterpret_cast<const float4*>(ph.bias) + u);
+      const float4 acc = aligned ? sum_partials_aligned<16>(a.partials, u * 4, j, cnt)
+                                 : sum_partials<16>(a.partials, u * 4, j, r.nkb, r.per);
+      v[i].x = xv.x + (b.x + acc.x);
+      v[i].y = xv.y + (b.y + acc.y);
+      v[i].z = xv.z + (b.z + acc.z);
+      v[i].w = xv.w + (b.w + acc.w);
+      xrow[u] = v[i];
+      s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+  }
+  if (tr) tq[1] = clock64();
+  if (!ph.ln_g) return;
+  const int warp = wt >> 5, lane = wt & 31;
+  s = warp_sum_f(s);
+  if (lane == 0) red[warp] = s;
+  workers_sync();
+  const float mean = (((red[0] + red[1]) + (red[2] + red[3])) + ((red[4] + red[5]) + (red[6] + red[7]))) / (float)n;
+  workers_sync();
+  if (tr) tq[2] = clock64();
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (wt + i * CH_WORKERS < n4) {
+      const float d0 = v[i].x - mean, d1 = v[i].y - mean, d2 = v[i].z - mean, d3 = v[i].w - mean;
+      q += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+    }
+  }
+  q = warp_sum_f(q);
+  if (lane == 0) red[warp] = q;
+  workers_sync();
+  const float var = (((red[0] + red[1]) + (red[2] + red[3])) + ((red[4] + red[5]) + (red[6] + red[7]))) / (float)n;
+  const float inv_std = 1.0f / sqrtf(var + a.eps);
+  if (tr) tq[3] = clock64();
+  float4* hi4 = reinterpret_cast<float4*>(ph.out_hi + (size_t)j * n);
+  float4* lo4 = reinterpret_cast<float4*>(ph.out_lo + (size_t)j * n);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int u = wt + i * CH_WORKERS;
+    if (u < n4) {
+      const float4 g = __ldg(reinterpret_cast<const float4*>(ph.ln_g) + u);
+      const float4 b = __ldg(reinterpret_cast<const float4*>(ph.ln_b) + u);
+      const float y[4] = {(v[i].x - mean) * inv_std * g.x + b.x, (v[i].y - mean) * inv_std * g.y + b.y,
+                          (v[i].z - mean) * inv_std * g.z + b.z, (v[i].w - mean) * inv_std * g.w + b.w};
+      float h[4], l[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        h[e] = tf32_hi(y[e]);
+        l[e] = y[e] - h[e];
+      }
+      hi4[u] = make_float4(h[0], h[1], h[2], h[3]);
+      lo4[u] = make_float4(l[0], l[1], l[2], l[3]);
+    }
+  }
+  if (tr) tq[4] = clock64();
+  workers_sync();  // `red` is reused by the next phase
+}
+
+// ELEM phase: out[j, f] = act(bias[f] + sum of partials), all CTAs, four features per thread.
+__device__ __forceinline__ void chain_elem_phase(const ChainArgs& a, const ChainPhase& ph, int wt) {
+  const int n = ph.n, n4 = (n + 3) >> 2;
+  const ChRange r = chain_range(ph.n, ph.k, 0, (int)gridDim.x);
+  const int total = a.m * n4;
+  const bool vec = (n & 3) == 0;
+  const bool aligned = r.nkb % r.per == 0;
+  const int cnt = r.nkb / r.per;
+  const int stride = (int)gridDim.x * CH_WORKERS;
+  for (int id0 = (int)blockIdx.x * CH_WORKERS + wt; id0 < total; id0 += 2 * stride) {
+    // two units per pass: the second one's loads are in flight while the first is finished
+    const int id1 = id0 + stride;
+    const int j0 = id0 / n4, f0 = (id0 - j0 * n4) * 4;
+    const int j1 = id1 < total ? id1 / n4 : j0, f1 = id1 < total ? (id1 - j1 * n4) * 4 : f0;
+    const float4 acc0 = aligned ? sum_partials_aligned<8>(a.partials, f0, j0, cnt) : sum_partials<8>(a.partials, f0, j0, r.nkb, r.per);
+    const float4 acc1 = aligned ? sum_partials_aligned<8>(a.partials, f1, j1, cnt) : sum_partials<8>(a.partials, f1, j1, r.nkb, r.per);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+    if (half == 1 && id1 >= total) break;
+    const int j = half ? j1 : j0, f = half ? f1 : f0;
+    const float4 acc = half ? acc1 : acc0;
+    float y[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (f + e < n) {
+        if (ph.bias) y[e] = __ldg(ph.bias + f + e) + y[e];
+        if (ph.gelu) y[e] = gelu_ref(y[e]);
+      }
+    }
+    const size_t o = (size_t)j * n + f;
+    if (vec) {
+      if (ph.out) *reinterpret_cast<float4*>(ph.out + o) = make_float4(y[0], y[1], y[2], y[3]);
+      if (ph.out_hi) {
+        float h[4], l[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          h[e] = tf32_hi(y[e]);
+          l[e] = y[e] - h[e];
+        }
+        *reinterpret_cast<float4*>(ph.out_hi + o) = make_float4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<float4*>(ph.out_lo + o) = make_float4(l[0], l[1], l[2], l[3]);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (f + e < n) {
+          if (ph.out) ph.out[o + e] = y[e];
+          if (ph.out_hi) {
+            const float h = tf32_hi(y[e]);
+            ph.out_hi[o + e] = h;
+            ph.out_lo[o + e] = y[e] - h;
+          }
+        }
+      }
+    }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(CH_THREADS, 1)
+    chain_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_hi0,
+                 const __grid_constant__ CUtensorMap map_lo0, const __grid_constant__ CUtensorMap map_hi1,
+                 const __grid_constant__ CUtensorMap map_lo1, const __grid_constant__ CUtensorMap map_hi2,
+                 const __grid_constant__ CUtensorMap map_lo2, const __grid_constant__ ChainArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* w_ring = base;
+  uint8_t* act_ring = base + (size_t)CH_W_STAGES * CH_W_BYTES;
+  uint64_t* w_full = reinterpret_cast<uint64_t*>(act_ring + (size_t)CH_X_STAGES * CH_ACT_BYTES);
+  uint64_t* w_empty = w_full + CH_W_STAGES;
+  uint64_t* ready = w_empty + CH_W_STAGES;  // split weights in tensor memory AND activation tiles in shared memory
+  uint64_t* done = ready + CH_X_STAGES;     // the MMAs that read them have completed
+  uint64_t* d_full = done + CH_X_STAGES;
+  uint64_t* d_empty = d_full + 2;
+  uint64_t* go = d_empty + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(go + 1);
+  volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* verdict = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  float* red = reinterpret_cast<float*>(tmem_slot + 4);  // 8 floats
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cta = (int)blockIdx.x, grid = (int)gridDim.x;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < CH_W_STAGES; ++s) {
+      mbar_init(&w_full[s], 1);
+      mbar_init(&w_empty[s], 4);
+    }
+    for (int s = 0; s < CH_X_STAGES; ++s) {
+      mbar_init(&ready[s], 5);  // four splitter warps + the activation producer's expect_tx arrival
+      mbar_init(&done[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&d_full[s], 1);
+      mbar_init(&d_empty[s], 8);
+    }
+    mbar_init(go, 1);
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, CH_TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- weight producer
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      uint32_t wi = 0;
+      bool ok = true;
+      for (int p = 0; p < a.n_phases && ok; ++p) {
+        if (a.ph[p].kind != CH_GEMM) continue;
+        const ChRange r = chain_range(a.ph[p].n, a.ph[p].k, cta, grid);
+        const uint32_t b0 = a.ph[p].w_block0;
+        for (int g = r.g0; g < r.g1 && ok; ++g, ++wi) {
+          const uint32_t s = wi % CH_W_STAGES;
+          if (wi >= CH_W_STAGES) ok = mbar_wait(&w_empty[s], ((wi / CH_W_STAGES) - 1) & 1, failed, a.error_flag, 21);
+          if (!ok) break;
+          // one unit = CH_UB consecutive 16 KB blocks of the tiled arena = one box of CH_UB * 128 rows
+          mbar_expect_tx(&w_full[s], CH_W_BYTES);
+          tma_load_2d(w_ring + (size_t)s * CH_W_BYTES, &map_w, 0, (int)((b0 + (uint32_t)g * CH_UB) * TILE_M), &w_full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc1 = umma_idesc_tf32(TILE_M, CH_BN), idesc2 = umma_idesc_tf32(TILE_M, 2 * CH_BN);
+      uint32_t wi = 0, si = 0;
+      bool ok = true;
+      long long t_wait = 0, t_issue = 0, t_dempty = 0;
+      for (int p = 0; p < a.n_phases && ok; ++p) {
+        if (a.ph[p].kind != CH_GEMM) continue;
+        const ChRange r = chain_range(a.ph[p].n, a.ph[p].k, cta, grid);
+        for (int g = r.g0; g < r.g1 && ok;) {
+          const int tile = g / r.nkb;
+          const int gend = min(r.g1, (tile + 1) * r.nkb);
+          const uint32_t buf = si & 1;
+          long long c0 = clock64();
+          if (si >= 2) ok = mbar_wait(&d_empty[buf], ((si >> 1) - 1) & 1, failed, a.error_flag, 22);
+          if (!ok) break;
+          t_dempty += clock64() - c0;
+          tc_fence_after();
+          const uint32_t dcol = tmem_base + buf * CH_D_COLS;
+          for (int gb = g; gb < gend && ok; ++gb, ++wi) {
+            const uint32_t xs = wi % CH_X_STAGES;
+            c0 = clock64();
+            ok = mbar_wait(&ready[xs], (wi / CH_X_STAGES) & 1, failed, a.error_flag, 23);
+            if (!ok) break;
+            const long long c1 = clock64();
+            t_wait += c1 - c0;
+            tc_fence_after();
+#pragma unroll
+            for (int b = 0; b < CH_UB; ++b) {
+              // block b of the unit: x_hi rows then x_lo rows in shared memory, w_hi | w_lo columns in tensor memory
+              const uint64_t dx = umma_desc_sw128(act_ring + (size_t)xs * CH_ACT_BYTES + (size_t)b * (CH_ACT_BYTES / CH_UB));
+              const uint32_t ahi = tmem_base + CH_A_COL0 + xs * (64 * CH_UB) + b * 64, alo = ahi + 32;
+#pragma unroll
+              for (int k = 0; k < BK / 8; ++k) {
+                umma_tf32_ts(dcol, ahi + k * 8, dx + (uint64_t)(k * 2), idesc2, (gb != g || b != 0 || k != 0) ? 1u : 0u);
+                umma_tf32_ts(dcol, alo + k * 8, dx + (uint64_t)(k * 2), idesc1, 1u);
+              }
+            }
+            umma_commit(&done[xs]);
+            t_issue += clock64() - c1;
+          }
+          if (ok) umma_commit(&d_full[buf]);
+          ++si;
+          g = gend;
+        }
+      }
+      if (a.trace) {
+        unsigned long long* t = a.trace + (size_t)blockIdx.x * 32;
+        t[22] = (unsigned long long)t_wait;
+        t[24] = (unsigned long long)t_issue;
+        t[25] = (unsigned long long)t_dempty;
+      }
+    }
+  } else if (warp == 2) {
+    // ---------------------------------------------------------------- activation producer
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_hi0) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_lo0) : "memory");
+      uint32_t wi = 0, gp = 0;
+      bool ok = true;
+      for (int p = 0; p < a.n_phases && ok; ++p) {
+        if (a.ph[p].kind != CH_GEMM) continue;
+        const ChRange r = chain_range(a.ph[p].n, a.ph[p].k, cta, grid);
+        const int act = a.ph[p].act;
+        const CUtensorMap* mh = act == 0 ? &map_hi0 : act == 1 ? &map_hi1 : &map_hi2;
+        const CUtensorMap* ml = act == 0 ? &map_lo0 : act == 1 ? &map_lo1 : &map_lo2;
+        ok = mbar_wait(go, gp & 1, failed, a.error_flag, 25);
+        ++gp;
+        if (!ok) break;
+        asm volatile("fence.proxy.async;" ::: "memory");
+        for (int g = r.g0; g < r.g1 && ok; ++g, ++wi) {
+          const uint32_t s = wi % CH_X_STAGES;
+          if (wi >= CH_X_STAGES) ok = mbar_wait(&done[s], ((wi / CH_X_STAGES) - 1) & 1, failed, a.error_flag, 26);
+          if (!ok) break;
+          const int kb = (g % r.nkb) * CH_UB;
+          uint8_t* dst = act_ring + (size_t)s * CH_ACT_BYTES;
+          mbar_expect_tx(&ready[s], CH_ACT_BYTES);
+#pragma unroll
+          for (int b = 0; b < CH_UB; ++b) {
+            tma_load_2d(dst + (size_t)b * (CH_ACT_BYTES / CH_UB), mh, (kb + b) * BK, 0, &ready[s]);
+            tma_load_2d(dst + (size_t)b * (CH_ACT_BYTES / CH_UB) + CH_BN * BK * 4, ml, (kb + b) * BK, 0, &ready[s]);
+          }
+        }
+      }
+    }
+  } else if (warp >= 4 && warp < 8) {
+    // ---------------------------------------------------------------- splitters
+    const int q = warp & 3;
+    const int row = q * 32 + lane;  // row of the weight tile == tensor-memory lane
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    uint32_t wi = 0;
+    bool ok = true;
+    long long t_wfull = 0, t_afree = 0;
+    for (int p = 0; p < a.n_phases && ok; ++p) {
+      if (a.ph[p].kind != CH_GEMM) continue;
+      const ChRange r = chain_range(a.ph[p].n, a.ph[p].k, cta, grid);
+      for (int g = r.g0; g < r.g1 && ok; ++g, ++wi) {
+        const uint32_t s = wi % CH_W_STAGES, xs = wi % CH_X_STAGES;
+        long long c0 = clock64();
+        ok = warp_wait(&w_full[s], (wi / CH_W_STAGES) & 1, failed, a.error_flag, 27);
+        if (!ok) break;
+        long long c1 = clock64();
+        t_wfull += c1 - c0;
+        // the tensor-memory stage is free once the MMAs of the unit that used it last have completed
+        if (wi >= CH_X_STAGES) ok = warp_wait(&done[xs], ((wi / CH_X_STAGES) - 1) & 1, failed, a.error_flag, 28);
+        if (!ok) break;
+        t_afree += clock64() - c1;
+        tc_fence_after();
+#pragma unroll
+        for (int b = 0; b < CH_UB; ++b) {
+          const float4* rowp = reinterpret_cast<const float4*>(w_ring + (size_t)s * CH_W_BYTES + (size_t)b * (TILE_M * BK * 4) +
+                                                               (size_t)row * 128);
+          uint32_t hi[32], lo[32];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 v = rowp[j ^ (row & 7)];  // undo the 128-byte swizzle: conflict-free per quarter warp
+            const float f[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float h = tf32_hi(f[e]);
+              hi[j * 4 + e] = __float_as_uint(h);
+              lo[j * 4 + e] = __float_as_uint(f[e] - h);
+            }
+          }
+          const uint32_t col = tmem_base + CH_A_COL0 + xs * (64 * CH_UB) + b * 64 + lane_addr;
+          tmem_st32(col, hi);
+          tmem_st32(col + 32, lo);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&w_empty[s]);  // the unit is in registers / tensor memory: the stage may be refilled
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ready[xs]);
+      }
+    }
+    if (a.trace && threadIdx.x == 128) {
+      a.trace[(size_t)blockIdx.x * 32 + 20] = (unsigned long long)t_wfull;
+      a.trace[(size_t)blockIdx.x * 32 + 21] = (unsigned long long)t_afree;
+    }
+  } else if (warp >= 8) {
+    // ---------------------------------------------------------------- workers
+    const int wt = (int)threadIdx.x - 256;
+    const int ww = wt >> 5;
+    const int q = ww & 3, half = ww >> 2;
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    const int row = q * 32 + lane;
+    uint32_t si = 0, barriers = 0;
+    bool ok = true;     // this warp's drains
+    bool live = true;   // same for all workers of the CTA: decided at the grid barriers
+    if (wt == 0) chain_trace(a, 31);
+    // bias and LayerNorm vectors were last read a whole step ago: pull them into L2 now (CTA p for phase p)
+    if (cta < a.n_phases && a.ph[cta].kind != CH_GEMM) {
+      const ChainPhase& pp = a.ph[cta];
+      for (int i = wt * 32; i < pp.n; i += CH_WORKERS * 32) {
+        if (pp.bias) asm volatile("prefetch.global.L2 [%0];" ::"l"(pp.bias + i));
+        if (pp.kind == CH_ROWS && pp.ln_g) {
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(pp.ln_g + i));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(pp.ln_b + i));
+        }
+      }
+    }
+    for (int p = 0; p < a.n_phases; ++p) {
+      const int kind = a.ph[p].kind;
+      if (kind == CH_GEMM) {
+        if (wt == 0) mbar_arrive(go);  // inputs of this phase exist (previous kernel, or the barrier just passed)
+        const ChRange r = chain_range(a.ph[p].n, a.ph[p].k, cta, grid);
+        int seg = 0;
+        for (int g = r.g0; g < r.g1; ++seg) {
+          const int tile = g / r.nkb;
+          const int gend = min(r.g1, (tile + 1) * r.nkb);
+          const uint32_t buf = si & 1;
+          if (ok) ok = warp_wait(&d_full[buf], (si >> 1) & 1, failed, a.error_flag, 29);
+          if (ok) {
+            tc_fence_after();
+            float* dst = a.partials + ((size_t)(cta * CH_MAX_SEG + seg) * CH_BN) * TILE_M + row;
+#pragma unroll
+            for (int cc = 0; cc < 32; cc += 16) {
+              const int c0 = half * 32 + cc;
+              float v[16], v2[16];
+              tmem_ld16(tmem_base + buf * CH_D_COLS + lane_addr + (uint32_t)c0, v);
+              tmem_ld16(tmem_base + buf * CH_D_COLS + lane_addr + (uint32_t)(CH_BN + c0), v2);
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (c0 + j < a.m) dst[(size_t)(c0 + j) * TILE_M] = v[j] + v2[j];
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&d_empty[buf]);
+          }
+          ++si;
+          g = gend;
+        }
+      } else if (kind == CH_ROWS) {
+        if (live && cta < a.m) chain_rows_phase(a, a.ph[p], cta, wt, red, p);
+      } else {
+        if (live) chain_elem_phase(a, a.ph[p], wt);
+      }
+      if (wt == 0) chain_trace(a, 10 + p);
+      if (p + 1 < a.n_phases) {
+        ++barriers;
+        live = chain_grid_barrier(a.barrier, (unsigned)grid * barriers, failed, a.error_flag, wt, verdict);
+        ok = ok && live;
+      }
+      if (wt == 0) chain_trace(a, p);
+    }
+    // leave the barrier word zero for the next launch: the last CTA to get here resets it
+    if (wt == 0 && !*failed) {
+      const unsigned old = atomicAdd(a.barrier, 1u);
+      if (old == (unsigned)grid * (barriers + 1) - 1) atomicExch(a.barrier, 0u);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, CH_TMEM_COLS);
+}
+
+}  // namespace
+
+int chain_grid(int num_sms) {
+  static int cached = -1;
+  if (cached >= 0) return cached;
+  cached = 0;
+  if (!encode_fn()) return 0;
+  if (cudaFuncSetAttribute(chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CH_SMEM) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, chain_kernel, CH_THREADS, CH_SMEM) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  int coop = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+  if (per_sm >= 1 && coop) cached = num_sms;
+  return cached;
+}
+
+size_t chain_partial_floats(int grid) { return (size_t)grid * CH_MAX_SEG * CH_PART_TILE; }
+
+bool chain_supported(const ChainArgs& a, int grid) {
+  if (grid <= 0 || a.m < 1 || a.m > CH_BN || a.n_phases < 1 || a.n_phases > CHAIN_MAX_PHASES) return false;
+  for (int p = 0; p < a.n_phases; ++p) {
+    const ChainPhase& ph = a.ph[p];
+    if (ph.k < BK * CH_UB || ph.k % (BK * CH_UB) != 0 || ph.n < 1) return false;
+    const ChRange r = chain_range(ph.n, ph.k, 0, grid);
+    if ((r.per + r.nkb - 2) / r.nkb + 1 > CH_MAX_SEG) return false;
+    if (ph.kind == CH_GEMM) {
+      if (ph.act < 0 || ph.act > 2 || !a.act_hi[ph.act] || !a.act_lo[ph.act] || a.act_k[ph.act] != ph.k) return false;
+      const unsigned long long rows = ((unsigned long long)ph.w_block0 + (unsigned long long)((ph.n + TILE_M - 1) / TILE_M) * r.nkb * CH_UB) * TILE_M;
+      if (rows > 0x7fffffffull || rows * BK > a.arena_floats) return false;
+    } else if (ph.kind == CH_ROWS) {
+      if (ph.n % 4 != 0 || ph.n > 4 * 4 * CH_WORKERS || !ph.x) return false;
+      if (ph.ln_g && (!ph.ln_b || !ph.out_hi || !ph.out_lo)) return false;
+      if (p == 0 || a.ph[p - 1].kind != CH_GEMM || a.ph[p - 1].n != ph.n || a.ph[p - 1].k != ph.k) return false;
+    } else if (ph.kind == CH_ELEM) {
+      if (ph.out_hi && !ph.out_lo) return false;
+      if (p == 0 || a.ph[p - 1].kind != CH_GEMM || a.ph[p - 1].n != ph.n || a.ph[p - 1].k != ph.k) return false;
+    } else {
+      return false;
+    }
+  }
+  return true;
+}
+
+cudaError_t launch_chain(const ChainArgs& a, int grid, cudaStream_t s) {
+  if (!chain_supported(a, grid)) return cudaErrorInvalidValue;
+  CUtensorMap maps[7];
+  memset(maps, 0, sizeof(maps));
+  if (!make_map(&maps[0], a.arena, a.arena_floats / BK, BK, CH_UB * TILE_M)) return cudaErrorInvalidValue;
+  for (int i = 0; i < 3; ++i) {
+    if (!a.act_hi[i]) continue;
+    if (!make_map(&maps[1 + 2 * i], a.act_hi[i], (uint64_t)a.m, (uint64_t)a.act_k[i], CH_BN) ||
+        !make_map(&maps[2 + 2 * i], a.act_lo[i], (uint64_t)a.m, (uint64_t)a.act_k[i], CH_BN))
+      return cudaErrorInvalidValue;
+  }
+  ChainArgs args = a;
+  void* params[8] = {&maps[0], &maps[1], &maps[2], &maps[3], &maps[4], &maps[5], &maps[6], &args};
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(CH_THREADS);
+  cfg.dynamicSmemBytes = CH_SMEM;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;  // the runtime checks that the whole grid is co-resident
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(chain_kernel), params);
+}
+
+}  // namespace pg

@@ -128,6 +128,54 @@ int tc_gemm_x3_splits(int n, int k, int num_sms);
 cudaError_t launch_tc_gemm_x3(const TcGemmArgs& a, int splits, bool pdl, cudaStream_t s);
 cudaError_t launch_finalize(const FinalizeArgs& a, bool pdl, cudaStream_t s);
 
+// A chain of dependent decode linears (m <= 64 tokens, three TF32 products each) as ONE persistent
+// cooperative kernel (gemm_chain.cu), one CTA per SM. The weights of every GEMM phase are one
+// contiguous run of 16 KB blocks of the tiled arena, cut into equal shares per CTA whatever the
+// matrix shape; a CTA's share may cross row tiles, and it writes one partial accumulator per tile
+// it touched. The phase after a GEMM adds the partials in k order and applies the bias with either
+// a residual update (+ LayerNorm, written as a TF32 hi/lo pair) or an element-wise epilogue (GELU,
+// hi/lo pair and/or plain FP32). Phases are separated by a bounded grid barrier that only the
+// worker warps take part in: the weight stream of later phases keeps running through it.
+enum ChainKind { CH_GEMM = 0, CH_ROWS = 1, CH_ELEM = 2 };
+enum ChainAct { CH_ACT_NORM = 0, CH_ACT_ATTN = 1, CH_ACT_H = 2 };
+struct ChainPhase {
+  int kind;
+  int n, k;           // GEMM: output features and reduction length; ROWS / ELEM: those of the GEMM being reduced
+  int act;            // GEMM: which hi/lo activation pair is the input (ChainAct)
+  unsigned w_block0;  // GEMM: index of the first 16 KB block of this matrix inside the tiled arena
+  int gelu;           // ELEM: tanh-GELU after the bias
+  const float* bias;  // ROWS / ELEM: [n] or nullptr
+  float* x;           // ROWS: residual stream [m, n], updated in place
+  const float* ln_g;  // ROWS: LayerNorm over the updated row (nullptr: none) ...
+  const float* ln_b;
+  float* out;         // ELEM: plain FP32 result [m, n] or nullptr
+  float* out_hi;      // ROWS: LayerNorm result, ELEM: result, as a TF32 hi/lo pair (or nullptr)
+  float* out_lo;
+};
+constexpr int CHAIN_MAX_PHASES = 10;
+struct ChainArgs {
+  ChainPhase ph[CHAIN_MAX_PHASES];
+  int n_phases;
+  int m;               // tokens (rows of every activation matrix), <= 64
+  float eps;
+  const float* arena;  // tiled weight arena (all matrices of the model)
+  size_t arena_floats;
+  const float* act_hi[3];  // activation pairs by ChainAct: [m, k] each
+  const float* act_lo[3];
+  int act_k[3];
+  float* partials;     // chain_partial_floats(grid) floats
+  unsigned* barrier;   // one word, zero before the first launch (the kernel leaves it zero)
+  int* error_flag;     // set non-zero when a bounded wait expired
+  unsigned long long* trace;  // optional tuning aid, 32 words per CTA: [p] when worker thread 0 left phase p, [10 + p]
+                              // when its work of phase p was done, [20..25] wait / issue cycle counts, [31] start
+};
+// Cooperative grid of the chain kernel on this device (0: not launchable) and the scratch it needs.
+int chain_grid(int num_sms);
+size_t chain_partial_floats(int grid);
+// True when every GEMM phase of `a` fits the kernel's limits for a grid of `grid` CTAs.
+bool chain_supported(const ChainArgs& a, int grid);
+cudaError_t launch_chain(const ChainArgs& a, int grid, cudaStream_t s);
+
 // Whole decode step in one persistent cooperative kernel (decode_mega.cu), for at most 8 sequences
 // and head_dim 64: every CTA stays resident, phases are separated by a bounded grid barrier, and
 // each warp requests the weights of its next phase before it enters the barrier.

@@ -52,6 +52,7 @@ struct pg_model {
   int num_sms = 148;
   float* arena = nullptr;  // every weight tensor lives in this one allocation
   float* tiled_arena = nullptr;  // second copy of the dense matrices, tiled for TMA (tensor-core modes)
+  size_t tiled_floats = 0;
   float* t_wte = nullptr;
   size_t arena_floats = 0;
   float *wte = nullptr, *wpe = nullptr, *lnf_g = nullptr, *lnf_b = nullptr;
@@ -188,6 +189,7 @@ static int build_model(const pg_gpt2_config& cfg, const float* const* tensors, c
                              tc_tiled_weight_floats(F, C) + tc_tiled_weight_floats(C, F);
     const size_t total_t = per_layer * cfg.n_layer + tc_tiled_weight_floats(V, C);
     PG_CUDA_TRY(cudaMalloc(&m->tiled_arena, total_t * sizeof(float)));
+    m->tiled_floats = total_t;
     float* p = m->tiled_arena;
     auto tile = [&](const float* src, int n_rows, int k_cols, float** dst) -> int {
       *dst = p;
@@ -236,6 +238,11 @@ struct pg_cache {
   // tensor-core decode path (9..64 sequences): TF32 hi/lo pairs of the GEMM inputs, split-K scratch
   float *norm_lo = nullptr, *attn_lo = nullptr, *h_lo = nullptr;
   int* d_error = nullptr;
+  // persistent chain kernel of the tensor-core decode path: partial tiles, grid-barrier word
+  float* chain_partials = nullptr;
+  unsigned* d_chain_barrier = nullptr;
+  unsigned long long* d_chain_trace = nullptr;  // PG_CHAIN_TRACE=1
+  int chain_ctas = 0;
   // single-kernel decode step (at most 8 sequences)
   MegaLayer* d_mega_layers = nullptr;
   unsigned* d_barrier = nullptr;
@@ -264,12 +271,32 @@ struct pg_cache {
                         "staging %llu lm_head %llu qkv-linear %llu\n", t[5], t[0] / t[5], t[1] / t[5], t[2] / t[5], t[3] / t[5], t[4] / t[5], t[6] / t[5]);
       cudaFree(d_mega_trace);
     }
+    if (d_chain_trace) {
+      std::vector<unsigned long long> t((size_t)chain_ctas * 32 + 512);
+      if (cudaMemcpy(t.data(), d_chain_trace, t.size() * 8, cudaMemcpyDeviceToHost) == cudaSuccess) {
+        for (int pp = 0; pp < 8; ++pp) {
+          const unsigned long long* tq = &t[(size_t)chain_ctas * 32 + 256 + pp * 8];
+          if (tq[0]) fprintf(stderr, "rows phase %d (CTA 0) cycles: partial sums %llu, mean %llu, var %llu, write %llu\n", pp, tq[1] - tq[0], tq[2] - tq[1], tq[3] - tq[2], tq[4] - tq[3]);
+        }
+        unsigned long long t0 = ~0ULL;
+        for (int i = 0; i < chain_ctas; ++i) t0 = std::min(t0, t[(size_t)i * 32 + 31]);
+        for (int sl = 0; sl < 8; ++sl) {
+          unsigned long long lo = ~0ULL, hi = 0, wlo = ~0ULL, whi = 0;
+          for (int i = 0; i < chain_ctas; ++i) {
+            const unsigned long long v = t[(size_t)i * 32 + sl] - t0, w = t[(size_t)i * 32 + 10 + sl] - t0;
+            lo = std::min(lo, v); hi = std::max(hi, v); wlo = std::min(wlo, w); whi = std::max(whi, w);
+          }
+          fprintf(stderr, "chain trace (layer 1) phase %d: work done %6llu..%6llu ns, barrier passed %6llu..%6llu ns\n", sl, wlo, whi, lo, hi);
+        }
+      }
+    }
     for (auto& g : graphs) cudaGraphExecDestroy(g.second);
     for (void* p : {(void*)kv_pool, (void*)d_table, (void*)d_ids, (void*)d_pos, (void*)d_argmax, (void*)d_token_log,
                     (void*)x, (void*)norm, (void*)qkv, (void*)attn, (void*)hbuf, (void*)logits, (void*)part_val,
                     (void*)part_idx, (void*)attn_part, (void*)attn_counters, (void*)topk_vals, (void*)topk_idx,
                     (void*)px, (void*)pnorm, (void*)pqkv, (void*)pattn, (void*)ph, (void*)prow, (void*)norm_lo,
-                    (void*)attn_lo, (void*)h_lo, (void*)d_error, (void*)d_mega_layers, (void*)d_barrier})
+                    (void*)attn_lo, (void*)h_lo, (void*)d_error, (void*)d_mega_layers, (void*)d_barrier,
+                    (void*)chain_partials, (void*)d_chain_barrier, (void*)d_chain_trace})
       if (p) cudaFree(p);
     if (t0) cudaEventDestroy(t0);
     if (t1) cudaEventDestroy(t1);
@@ -334,6 +361,16 @@ static int cache_new(const pg_model* m, int max_batch, pg_cache** out) {
     PG_CUDA_TRY(cudaMalloc(&c->norm_lo, (size_t)bmax * C * sizeof(float)));
     PG_CUDA_TRY(cudaMalloc(&c->attn_lo, (size_t)bmax * C * sizeof(float)));
     PG_CUDA_TRY(cudaMalloc(&c->h_lo, (size_t)bmax * F * sizeof(float)));
+    if (m->t_wte && !env_flag("PG_NO_CHAIN") && chain_grid(m->num_sms) > 0) {
+      c->chain_ctas = chain_grid(m->num_sms);
+      PG_CUDA_TRY(cudaMalloc(&c->chain_partials, chain_partial_floats(c->chain_ctas) * sizeof(float)));
+      PG_CUDA_TRY(cudaMalloc(&c->d_chain_barrier, sizeof(unsigned)));
+      PG_CUDA_TRY(cudaMemsetAsync(c->d_chain_barrier, 0, sizeof(unsigned), c->stream));
+      if (env_flag("PG_CHAIN_TRACE")) {
+        PG_CUDA_TRY(cudaMalloc(&c->d_chain_trace, ((size_t)c->chain_ctas * 32 + 512) * sizeof(unsigned long long)));
+        PG_CUDA_TRY(cudaMemsetAsync(c->d_chain_trace, 0, ((size_t)c->chain_ctas * 32 + 512) * sizeof(unsigned long long), c->stream));
+      }
+    }
   }
   if (decode_mega_supported(1, C, F, D) && (m->backend.persistent_step == 1 || env_flag("PG_MEGA"))) {
     c->mega_grid = decode_mega_grid(m->num_sms);
@@ -468,6 +505,83 @@ static cudaError_t enqueue_decode_step(pg_cache* c, int batch, int splits, cudaS
   if (m->t_wte && batch > 8 && batch <= 64 && c->norm_lo) {
     // tensor-core path: every linear is three TF32 products (hi*hi + hi*lo + lo*hi) accumulated
     // in FP32; LayerNorm, attention and the GELU epilogue hand their results over as hi/lo pairs
+    if (c->chain_ctas > 0 && !prof) {
+      // persistent chain kernel: per layer one launch runs attention-output projection, MLP and the
+      // next layer's QKV projection (or the lm_head) with their bias / residual / LayerNorm / GELU
+      // phases; attention stays a launch of its own between two chains
+      ChainArgs base{};
+      base.m = batch; base.eps = eps; base.arena = m->tiled_arena; base.arena_floats = m->tiled_floats;
+      base.act_hi[CH_ACT_NORM] = c->norm; base.act_lo[CH_ACT_NORM] = c->norm_lo; base.act_k[CH_ACT_NORM] = C;
+      base.act_hi[CH_ACT_ATTN] = c->attn; base.act_lo[CH_ACT_ATTN] = c->attn_lo; base.act_k[CH_ACT_ATTN] = C;
+      base.act_hi[CH_ACT_H] = c->hbuf; base.act_lo[CH_ACT_H] = c->h_lo; base.act_k[CH_ACT_H] = F;
+      base.partials = c->chain_partials; base.barrier = c->d_chain_barrier; base.error_flag = c->d_error;
+      auto block0 = [&](const float* t) { return (unsigned)((size_t)(t - m->tiled_arena) / 4096); };
+      auto gemm = [&](ChainArgs& a, const float* t, int n_out, int k, int act) {
+        ChainPhase& ph = a.ph[a.n_phases++];
+        ph = ChainPhase{};
+        ph.kind = CH_GEMM; ph.n = n_out; ph.k = k; ph.act = act; ph.w_block0 = block0(t);
+      };
+      auto rows = [&](ChainArgs& a, int n_out, int k, const float* bias, const float* g, const float* b) {
+        ChainPhase& ph = a.ph[a.n_phases++];
+        ph = ChainPhase{};
+        ph.kind = CH_ROWS; ph.n = n_out; ph.k = k; ph.bias = bias; ph.x = c->x; ph.ln_g = g; ph.ln_b = b;
+        ph.out_hi = c->norm; ph.out_lo = c->norm_lo;
+      };
+      auto elem = [&](ChainArgs& a, int n_out, int k, const float* bias, int gelu, float* out, float* ohi, float* olo) {
+        ChainPhase& ph = a.ph[a.n_phases++];
+        ph = ChainPhase{};
+        ph.kind = CH_ELEM; ph.n = n_out; ph.k = k; ph.bias = bias; ph.gelu = gelu; ph.out = out; ph.out_hi = ohi; ph.out_lo = olo;
+      };
+      const int L = m->layers_n();
+      bool ok_chain = true;
+      std::vector<ChainArgs> chains((size_t)L + 1, base);
+      {
+        ChainArgs& a = chains[0];
+        gemm(a, m->layers[0].t_qkv, 3 * C, C, CH_ACT_NORM);
+        elem(a, 3 * C, C, m->layers[0].b_qkv, 0, c->qkv, nullptr, nullptr);
+        ok_chain = ok_chain && chain_supported(a, c->chain_ctas);
+      }
+      for (int l = 0; l < L; ++l) {
+        const LayerWeights& w = m->layers[l];
+        ChainArgs& a = chains[(size_t)l + 1];
+        gemm(a, w.t_proj, C, C, CH_ACT_ATTN);
+        rows(a, C, C, w.b_proj, w.ln2_g, w.ln2_b);
+        gemm(a, w.t_fc, F, C, CH_ACT_NORM);
+        elem(a, F, C, w.b_fc, 1, nullptr, c->hbuf, c->h_lo);
+        gemm(a, w.t_proj2, C, F, CH_ACT_H);
+        if (l + 1 < L) {
+          rows(a, C, F, w.b_proj2, m->layers[l + 1].ln1_g, m->layers[l + 1].ln1_b);
+          gemm(a, m->layers[l + 1].t_qkv, 3 * C, C, CH_ACT_NORM);
+          elem(a, 3 * C, C, m->layers[l + 1].b_qkv, 0, c->qkv, nullptr, nullptr);
+        } else {
+          rows(a, C, F, w.b_proj2, m->lnf_g, m->lnf_b);
+          gemm(a, m->t_wte, V, C, CH_ACT_NORM);
+          elem(a, V, C, nullptr, 0, c->logits, nullptr, nullptr);
+        }
+        ok_chain = ok_chain && chain_supported(a, c->chain_ctas);
+      }
+      if (L > 1) chains[2].trace = c->d_chain_trace;  // tuning aid: phase times of layer 1's chain
+      if (ok_chain) {
+        cur_bucket = B_LAYER_NORM;
+        PG_E(launch_layernorm_rows_split(c->x, m->layers[0].ln1_g, m->layers[0].ln1_b, eps, c->norm, c->norm_lo, batch, C, pdl, s));
+        PG_E(launch_chain(chains[0], c->chain_ctas, s));
+        for (int l = 0; l < L; ++l) {
+          DecodeAttnArgs at{};
+          at.qkv = c->qkv; at.out = c->attn; at.out_lo = c->attn_lo; at.kv_pool = c->layer_pool(l);
+          at.page_table = c->d_table; at.pos = c->d_pos; at.part = c->attn_part; at.counters = c->attn_counters;
+          at.kv = c->kv; at.batch = batch; at.splits = splits;
+          PG_E(launch_decode_attention(at, false, s));
+          PG_E(launch_chain(chains[(size_t)l + 1], c->chain_ctas, s));
+        }
+        PG_E(launch_argmax_rows(c->logits, batch, V, c->d_argmax, s));
+        FinalizeArgs fx{};
+        fx.m = batch; fx.argmax_out = c->d_argmax; fx.next_ids = c->d_ids; fx.pos = c->d_pos;
+        fx.token_log = c->d_token_log; fx.n_positions = m->positions();
+        PG_E(launch_finalize(fx, false, s));
+        if (launches) *launches = n;
+        return cudaSuccess;
+      }
+    }
     auto x3 = [&](const float* w, const float* bias, const float* xhi, const float* xlo, float* out, float* ohi,
                   float* olo, int n_out, int k, int epi, const float* resid) -> cudaError_t {
       TcGemmArgs a{};

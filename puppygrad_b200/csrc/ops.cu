@@ -54,8 +54,11 @@ extern "C" int pg_op_linear(const float* x, const float* w, const float* bias, c
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   const size_t xs = (size_t)m * k, ws = (size_t)n * k, os = (size_t)m * n;
-  DeviceBuf dx, dw, dwt, db, dr, dout, dhi, dlo, derr, dflush, dtrace;
+  DeviceBuf dx, dw, dwt, db, dr, dout, dhi, dlo, derr, dflush, dtrace, dpart, dbar;
   const bool want_trace = getenv("PG_TRACE") != nullptr;
+  // tf32x3 runs on the persistent chain kernel (one GEMM phase + its reduce phase) unless PG_NO_CHAIN is set
+  int chain_ctas = 0;
+  ChainArgs chain{};
   cudaStream_t s = nullptr;
   cudaEvent_t e0 = nullptr, e1 = nullptr;
   int splits = 1;
@@ -76,6 +79,13 @@ extern "C" int pg_op_linear(const float* x, const float* w, const float* bias, c
     }
     cudaError_t e = launch_split_tf32(dx.as<float>(), dhi.as<float>(), dlo.as<float>(), xs, false, st);
     if (e != cudaSuccess) return e;
+    if (chain_ctas > 0) {
+      if (epilogue == EPI_RESID) {
+        e = cudaMemcpyAsync(dout.p, dr.p, os * 4, cudaMemcpyDeviceToDevice, st);
+        if (e != cudaSuccess) return e;
+      }
+      return launch_chain(chain, chain_ctas, st);
+    }
     a.x = dhi.as<float>(); a.x_lo = dlo.as<float>(); a.w = dwt.as<float>();
     a.trace = dtrace.as<unsigned long long>();
     return launch_tc_gemm_x3(a, splits, false, st);
@@ -102,7 +112,29 @@ extern "C" int pg_op_linear(const float* x, const float* w, const float* bias, c
     PG_OP_TRY(cudaMalloc(&dlo.p, xs * 4));
     PG_OP_TRY(cudaMalloc(&dwt.p, tc_tiled_weight_floats(n, k) * 4));
     PG_OP_TRY(launch_tile_weights(dw.as<float>(), dwt.as<float>(), n, k, s));
-    if (want_trace) {
+    if (!getenv("PG_NO_CHAIN") && chain_grid(sms) > 0) {
+      const int g = chain_grid(sms);
+      chain.n_phases = 2;
+      chain.ph[0].kind = CH_GEMM; chain.ph[0].n = n; chain.ph[0].k = k; chain.ph[0].act = CH_ACT_NORM;
+      chain.ph[0].w_block0 = 0;
+      chain.ph[1].kind = epilogue == EPI_RESID ? CH_ROWS : CH_ELEM;
+      chain.ph[1].n = n; chain.ph[1].k = k; chain.ph[1].bias = db.as<float>();
+      chain.ph[1].gelu = epilogue == EPI_GELU; chain.ph[1].x = dout.as<float>(); chain.ph[1].out = dout.as<float>();
+      chain.m = m; chain.eps = 1e-5f; chain.arena = dwt.as<float>(); chain.arena_floats = tc_tiled_weight_floats(n, k);
+      chain.act_hi[0] = dhi.as<float>(); chain.act_lo[0] = dlo.as<float>(); chain.act_k[0] = k;
+      chain.error_flag = derr.as<int>();
+      PG_OP_TRY(cudaMalloc(&dpart.p, chain_partial_floats(g) * 4));
+      PG_OP_TRY(cudaMalloc(&dbar.p, 4));
+      PG_OP_TRY(cudaMemsetAsync(dbar.p, 0, 4, s));
+      chain.partials = dpart.as<float>(); chain.barrier = dbar.as<unsigned>();
+      if (want_trace) {
+        PG_OP_TRY(cudaMalloc(&dtrace.p, (size_t)g * 256 + 4096));
+        PG_OP_TRY(cudaMemset(dtrace.p, 0, (size_t)g * 256 + 4096));
+        chain.trace = dtrace.as<unsigned long long>();
+      }
+      if (chain_supported(chain, g)) chain_ctas = g;
+    }
+    if (want_trace && chain_ctas == 0) {
       PG_OP_TRY(cudaMalloc(&dtrace.p, (size_t)((n + 127) / 128) * splits * 128));
       PG_OP_TRY(cudaMemset(dtrace.p, 0, (size_t)((n + 127) / 128) * splits * 128));
     }
@@ -135,7 +167,46 @@ extern "C" int pg_op_linear(const float* x, const float* w, const float* bias, c
     }
     *seconds_per_launch = total / reps;
   }
-  if (want_trace && dtrace.p) {
+  if (want_trace && dtrace.p && chain_ctas > 0) {
+    // tuning aid: when worker thread 0 of each CTA left each phase, relative to the earliest start
+    std::vector<unsigned long long> t((size_t)chain_ctas * 32 + 512);
+    PG_OP_TRY(cudaMemcpy(t.data(), dtrace.p, t.size() * 8, cudaMemcpyDeviceToHost));
+    unsigned long long t0 = ~0ULL;
+    for (int i = 0; i < chain_ctas; ++i) t0 = std::min(t0, t[(size_t)i * 32 + 31]);
+    for (int sl = 0; sl < chain.n_phases; ++sl) {
+      unsigned long long lo = ~0ULL, hi = 0, wlo = ~0ULL, whi = 0;
+      for (int i = 0; i < chain_ctas; ++i) {
+        const unsigned long long v = t[(size_t)i * 32 + sl] - t0, w = t[(size_t)i * 32 + 10 + sl] - t0;
+        lo = std::min(lo, v); hi = std::max(hi, v); wlo = std::min(wlo, w); whi = std::max(whi, w);
+      }
+      fprintf(stderr, "chain trace phase %d: work done %6llu..%6llu ns, barrier passed %6llu..%6llu ns\n", sl, wlo, whi, lo, hi);
+    }
+    const char* cn[6] = {"split wait w_full", "split wait a_free", "mma wait a_ready", "mma wait act_full", "mma issue", "mma wait d_empty"};
+    for (int sl = 0; sl < 6; ++sl) {
+      double mean = 0;
+      for (int i = 0; i < chain_ctas; ++i) mean += (double)t[(size_t)i * 32 + 20 + sl];
+      fprintf(stderr, "chain trace %-18s mean %8.0f cycles per CTA\n", cn[sl], mean / chain_ctas);
+    }
+    {
+      const unsigned long long* q = &t[(size_t)chain_ctas * 32 + 400];
+      fprintf(stderr, "blk 40 fine: wait_ready %llu wait_act %llu fence %llu | mma", q[0], q[1], q[2]);
+      for (int z = 3; z <= 10; ++z) fprintf(stderr, " %llu", q[z]);
+      fprintf(stderr, " | commit %llu %llu\n", q[11], q[12]);
+    }
+    for (int b = 0; b < 0; ++b) {
+      const unsigned long long* q = &t[(size_t)chain_ctas * 32 + b * 4];
+      if (q[2]) fprintf(stderr, "blk %2d start %7llu wait_ready %5llu wait_act %5llu issue %5llu\n", b, q[2] - t[(size_t)chain_ctas * 32 + 2], q[0], q[1], q[3]);
+    }
+    {
+      double d1 = 0, d2 = 0, d3 = 0;
+      for (int i = 0; i < chain_ctas; ++i) {
+        const unsigned long long* q = &t[(size_t)i * 32];
+        d1 += (double)(long long)(q[27] - q[26]); d2 += (double)(long long)(q[29] - q[27]); d3 += (double)(long long)(q[28] - q[29]);
+      }
+      fprintf(stderr, "chain trace block 40 commit -> splitter saw a_free %.0f clk; -> a_ready arrive %.0f clk; -> mma saw a_ready %.0f clk\n",
+              d1 / chain_ctas, d2 / chain_ctas, d3 / chain_ctas);
+    }
+  } else if (want_trace && dtrace.p) {
     // tuning aid: phase timestamps of the last launch, relative to the earliest CTA start
     const size_t ctas = (size_t)((n + 127) / 128) * splits;
     std::vector<unsigned long long> t(ctas * 16);

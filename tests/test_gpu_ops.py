@@ -47,6 +47,21 @@ def test_linear_tf32x3_matches_oracle(oracle, m, n, k, epilogue):
     np.testing.assert_allclose(got, oracle_linear(oracle, x, w, b, epilogue, r), rtol=1e-3, atol=1e-4)
 
 
+@pytest.mark.parametrize("m,n,k", [(16, 1600, 1600), (64, 6400, 1600), (33, 1600, 6400), (40, 1000, 256)])
+@pytest.mark.parametrize("epilogue", ["none", "gelu", "resid"])
+def test_linear_tf32x3_one_launch_per_gemm_kernel_matches_oracle(oracle, monkeypatch, m, n, k, epilogue):
+    """The same product on the kernel that is launched once per GEMM (split-K over a thread-block
+    cluster), which the model keeps for shapes the persistent chain kernel does not take."""
+    monkeypatch.setenv("PG_NO_CHAIN", "1")
+    rng = np.random.default_rng(m * 31 + n * 7 + k + 2)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.05)
+    b = rng.standard_normal(n, dtype=np.float32)
+    r = rng.standard_normal((m, n), dtype=np.float32)
+    got, _ = ops.linear(x, w, b, r if epilogue == "resid" else None, epilogue, "tf32x3")
+    np.testing.assert_allclose(got, oracle_linear(oracle, x, w, b, epilogue, r), rtol=1e-3, atol=1e-4)
+
+
 @pytest.mark.parametrize("m,n,k", [(128, 128, 32), (512, 4800, 1600), (1000, 770, 768), (4096, 1600, 6400)])
 def test_linear_tf32_single_pass_is_within_its_stated_bound(oracle, m, n, k):
     """One TF32 pass (10-bit mantissas, truncated): error <= 2e-3 of the output scale
