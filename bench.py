@@ -311,16 +311,29 @@ def run_ours(args):
         V = cfg["vocab_size"]
         lin_bytes = L * 4 * (3 * c * c + c * c + 2 * c * f + 4 * c + f) + 4 * V * c  # weights + biases, once
         lin_bytes += L * 4 * B * (2 * c + 3 * c + 2 * c + c + 2 * c + 2 * f + 2 * f + c) + 4 * B * (2 * c + V)
+        lin_keys = ("qkv_projection", "attention_projection", "mlp_fc_projection", "mlp_projection", "final_logits")
+        attn_bytes = kv_bytes_per_step(cfg, [t_prof] * B) + 4 * B * 4 * c * L
         fam = {
-            "linears": (lin_bytes, sum(prof[k][0] for k in ("qkv_projection", "attention_projection",
-                                                          "mlp_fc_projection", "mlp_projection", "final_logits")),
-                        sum(prof[k][1] for k in ("qkv_projection", "attention_projection", "mlp_fc_projection",
-                                                 "mlp_projection", "final_logits"))),
-            "decode_attention_kernel": (kv_bytes_per_step(cfg, [t_prof] * B) + 4 * B * 4 * c * L,
-                                        prof["attention"][0], prof["attention"][1]),
+            "linears": (lin_bytes, sum(prof[k][0] for k in lin_keys), sum(prof[k][1] for k in lin_keys)),
+            "decode_attention_kernel": (attn_bytes, prof["attention"][0], prof["attention"][1]),
         }
-        dom = max(fam, key=lambda k: fam[k][1])
-        dom_bytes, dom_sec, dom_n = fam[dom]
+        fused = prof.get("fused_step_kernel")
+        phase_roofline = None
+        if fused:
+            # The whole step is one persistent kernel: it is the dominant kernel, its algorithmic
+            # bytes are the step's (weights once + KV cache once), its duration comes from CUDA
+            # events around the launch. The kernel's own phase time stamps give the split below.
+            dom, dom_bytes, dom_sec, dom_n = "chain_kernel", lin_bytes + attn_bytes, fused[0], 1
+            phase_roofline = {
+                "gemm_phases": {"bytes": lin_bytes, "us": fam["linears"][1] * 1e6,
+                                "GB/s": lin_bytes / fam["linears"][1] / 1e9, "phases": fam["linears"][2]},
+                "attention_phases": {"bytes": attn_bytes, "us": prof["attention"][0] * 1e6,
+                                     "GB/s": attn_bytes / prof["attention"][0] / 1e9, "phases": prof["attention"][1]},
+                "bias_residual_layernorm_phases": {"us": prof["layer_norm"][0] * 1e6, "phases": prof["layer_norm"][1]},
+            }
+        else:
+            dom = max(fam, key=lambda k: fam[k][1])
+            dom_bytes, dom_sec, dom_n = fam[dom]
         per_launch = dom_sec / max(dom_n, 1)
         achieved = dom_bytes / dom_sec / 1e9
         kernel_name = dom
@@ -329,6 +342,8 @@ def run_ours(args):
         # DRAM traffic of the captured launches equals the algorithmic bytes within 4 %
         # (profiles/tc_gemm_x3_kernel_m64_4096x1024.md, profiles/decode_attention_kernel_b64_h16_kv256.md)
         traffic = dom_bytes / max(dom_n, 1) * (1.035 if dom == "linears" else 1.004)
+        if fused:
+            traffic = None  # no ncu capture of the persistent kernel yet
         step_bytes = model.weight_bytes_per_step() + kv_bytes_per_step(cfg, lens_mid)
         step_achieved = step_bytes / (sec_max / K) / 1e9
 
@@ -342,6 +357,8 @@ def run_ours(args):
                                    f"greedy decode; step = one batched decode step ({B} tokens per GPU)",
                        "linears": ("fp32 weights and activations; products as 3xTF32 on tcgen05 tensor cores, "
                                    "FP32 accumulate" if args.math == "tf32x3" else "fp32 CUDA-core FMA"),
+                       "step_kernels": ("embedding, first LayerNorm, ONE persistent kernel for all layers and "
+                                        "the lm_head, arg-max, token feedback" if fused else "one kernel per operation"),
                        "l2": "inputs larger than L2 (1.4 GB weights + KV per step)", "parallelism": f"replicas x{world}"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
             "gpu_launches": int(launches),
@@ -353,6 +370,7 @@ def run_ours(args):
             "step_roofline": {"bound": "hbm", "bytes_per_step": step_bytes, "achieved": step_achieved,
                               "peak": peak, "frac": step_achieved / peak},
             "profile_us": {k: round(v[0] * 1e6, 1) for k, v in prof.items()},
+            "phase_roofline": phase_roofline,
             "cpu_baseline": {"value": cpu_val, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
                              "sample": f"1 sequence, {cpu_tokens} greedy decode tokens after a 16-token prompt "
                                        f"({cpu_dt:.1f} s)"},

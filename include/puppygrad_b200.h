@@ -101,11 +101,18 @@ typedef struct {
  * consumes it is counted in that linear's bucket (layer_norm is then 0); tokenization and decoding
  * are text-side and always 0 here; `other` holds the embedding and the end-of-step kernel, which
  * the reference leaves untimed. launches[i] counts kernels in the order layer_norm, qkv_projection,
- * attention, attention_projection, mlp_fc_projection, mlp_projection, final_logits, other. */
+ * attention, attention_projection, mlp_fc_projection, mlp_projection, final_logits, other.
+ * When the step runs as one persistent kernel (batched tensor-core path), fused_step_kernel is
+ * that launch's duration from CUDA events, the buckets hold the durations of its phases from
+ * time stamps the kernel writes itself (bias / residual / LayerNorm phases count as layer_norm, a
+ * GEMM's reduce phase counts with the GEMM), launches[i] counts phases, and `other` keeps what the
+ * stamps do not cover. No reference counterpart for the two fused_* fields. */
 typedef struct {
   double tokenization, layer_norm, qkv_projection, attention, attention_projection, mlp_fc_projection,
       mlp_projection, final_logits, decoding, other;
   uint64_t launches[8];
+  double fused_step_kernel;
+  uint64_t fused_phases;
 } pg_operation_profile;
 
 /* Number of tensors pg_model_from_host_weights expects: 4 + 12 * n_layer. */

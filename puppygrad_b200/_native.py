@@ -43,7 +43,7 @@ class PgOperationProfile(C.Structure):
     _fields_ = [(n, C.c_double) for n in
                 ("tokenization", "layer_norm", "qkv_projection", "attention", "attention_projection",
                  "mlp_fc_projection", "mlp_projection", "final_logits", "decoding", "other")] + \
-               [("launches", C.c_uint64 * 8)]
+               [("launches", C.c_uint64 * 8), ("fused_step_kernel", C.c_double), ("fused_phases", C.c_uint64)]
 
 
 TOKEN_CALLBACK = C.CFUNCTYPE(C.c_int, C.c_uint64, C.c_void_p)

@@ -36,7 +36,7 @@ constexpr int CH_THREADS = 512;
 // on an mbarrier or a tcgen05.commit costs the single MMA-issuing thread as much as several MMAs,
 // so fewer, larger hand-overs keep the tensor pipe busier.
 constexpr int CH_UB = 2;
-constexpr int CH_W_STAGES = 5;    // weight units in flight per SM (32 KB each)
+constexpr int CH_W_STAGES = 3;    // weight units in flight per SM (32 KB each)
 constexpr int CH_X_STAGES = 2;    // units whose activation tiles (shared memory) and split weights (tensor memory) are staged
 constexpr int CH_BN = 64;
 constexpr int CH_W_BYTES = CH_UB * TILE_M * BK * 4;
@@ -44,7 +44,16 @@ constexpr int CH_ACT_BYTES = CH_UB * 2 * CH_BN * BK * 4;  // per block: x_hi til
 constexpr int CH_MAX_SEG = 4;     // row tiles one CTA's share may touch
 constexpr int CH_WORKERS = 256;
 constexpr uint32_t CH_D_COLS = 128, CH_A_COL0 = 256, CH_TMEM_COLS = 512;
-constexpr size_t CH_SMEM = (size_t)CH_W_STAGES * CH_W_BYTES + (size_t)CH_X_STAGES * CH_ACT_BYTES + 1024 + 1024;
+// Attention phases stage key / value rows in the (then idle) activation ring plus an extra region:
+// each of the eight worker warps has AT_SLOTS slots of AT_ROWS rows x 64 floats.
+constexpr int AT_ROWS = 16;
+constexpr int AT_SLOTS = 3;
+constexpr int AT_SLOT_BYTES = AT_ROWS * 64 * 4;
+constexpr int AT_EXTRA_BYTES = 8 * AT_SLOTS * AT_SLOT_BYTES - CH_X_STAGES * CH_ACT_BYTES;
+constexpr int AT_SCRATCH_FLOATS = 4 * 64;  // per group of four warps: one 64-float query per warp
+static_assert(AT_EXTRA_BYTES >= 0, "the activation ring is part of the attention staging area");
+constexpr size_t CH_SMEM = (size_t)CH_W_STAGES * CH_W_BYTES + (size_t)CH_X_STAGES * CH_ACT_BYTES + AT_EXTRA_BYTES +
+                           2 * AT_SCRATCH_FLOATS * 4 + 1024 + 1024;
 constexpr size_t CH_PART_TILE = (size_t)CH_BN * TILE_M;  // floats of one partial tile: [token][row]
 
 // Share of one CTA in units: [g0, g1) of the phase's tiles * nkb units (row tile major); per = units per CTA.
@@ -110,6 +119,17 @@ __device__ __forceinline__ void chain_trace(const ChainArgs& a, int slot) {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     a.trace[(size_t)blockIdx.x * 32 + slot] = t;
   }
+}
+
+__device__ __forceinline__ const ChainPhase& phase_at(const ChainArgs& a, int p) {
+  return a.phases_dev ? a.phases_dev[p] : a.ph[p];
+}
+
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
 }
 
 // Sum of the partial tiles covering features [f, f + 4) of token j, in k order. Loads go out in
@@ -187,7 +207,7 @@ __device__ __forceinline__ void chain_rows_phase(const ChainArgs& a, const Chain
   const int cnt = r.nkb / r.per;
   float4 v[4];
   float s = 0.f;
-  const bool tr = a.trace && blockIdx.x == 0 && wt == 0;
+  const bool tr = a.trace && blockIdx.x == 0 && wt == 0 && pidx < 10;
   unsigned long long* tq = a.trace + (size_t)gridDim.x * 32 + 256 + pidx * 8;
   if (tr) tq[0] = clock64();
   float4* xrow = reinterpret_cast<float4*>(ph.x + (size_t)j * n);
@@ -315,6 +335,201 @@ __device__ __forceinline__ void chain_elem_phase(const ChainArgs& a, const Chain
   }
 }
 
+// ATTN phase: causal attention of one new token per sequence over the paged cache, head_dim 64.
+// One worker WARP per (sequence, head) pair, eight pairs in flight per SM, no block-level barrier.
+// The pair's q, k, v come straight from the partial tiles of the QKV GEMM before it (sum in k
+// order + bias, as an ELEM phase would do), so that GEMM needs no reduce phase of its own.
+// Keys and values are pulled into shared memory in blocks of 16 rows by bulk async copies issued
+// up to AT_SLOTS chunks ahead of their use, across pair boundaries. Scores use two lanes per key,
+// the weighted sum sixteen lanes per value row, with a running maximum (one pass over the cache).
+// The new token's own key and value are appended to the cache.
+struct AtCursor {  // where the warp is in issuing its chunk sequence; the same in every lane, except pg0 / pg1
+  int item, chunk, nchunk, t, b, h;
+  int pg0, pg1;  // page table entries lane and lane + 32 of sequence b
+  uint32_t issued;
+};
+
+__device__ __forceinline__ float4 attn_feature4(const ChainArgs& a, const ChainPhase& ph, const ChRange& r, int f, int j) {
+  const float4 acc = (r.nkb % r.per == 0) ? sum_partials_aligned<8>(a.partials, f, j, r.nkb / r.per)
+                                          : sum_partials<8>(a.partials, f, j, r.nkb, r.per);
+  float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (ph.bias) b = __ldg(reinterpret_cast<const float4*>(ph.bias + f));
+  return make_float4(b.x + acc.x, b.y + acc.y, b.z + acc.z, b.w + acc.w);
+}
+
+__device__ __forceinline__ void chain_attn_phase(const ChainArgs& a, const ChainPhase& ph, int wt, uint8_t* stage_all,
+                                                 uint64_t* kv_full_all, float* scratch_all, uint32_t& consumed,
+                                                 volatile int* failed, bool live) {
+  constexpr int D = 64, RB = AT_ROWS;
+  const int w8 = wt >> 5, lane = wt & 31;
+  uint8_t* stage = stage_all + (size_t)w8 * AT_SLOTS * AT_SLOT_BYTES;
+  uint64_t* kv_full = kv_full_all + w8 * AT_SLOTS;
+  float4* qs = reinterpret_cast<float4*>(scratch_all + w8 * D);  // this pair's query, 16 float4
+  const int H = a.kv.n_head, C = H * D, pt = a.kv.page_tokens, pps = a.kv.pages_per_seq;
+  const int pt_shift = pt == 16 ? 4 : pt == 32 ? 5 : 6;
+  const int items = a.m * H, step = (int)gridDim.x * 8, first = (int)blockIdx.x * 8 + w8;
+  const ChRange r = chain_range(ph.n, ph.k, 0, (int)gridDim.x);  // shares of the QKV GEMM whose partials are read
+  const float scale = 0.125f;  // 1 / sqrt(64)
+  bool ok = live;
+
+  AtCursor cur;
+  cur.item = first - step;
+  cur.chunk = 0;
+  cur.nchunk = 0;
+  cur.issued = consumed;
+  cur.t = cur.b = cur.h = cur.pg0 = cur.pg1 = 0;
+  // executed by all lanes with identical control flow; only lane 0 starts copies
+  auto issue_upto = [&](uint32_t limit) {  // chunks with index < limit may be in flight
+    while (cur.issued < limit) {
+      if (cur.chunk >= cur.nchunk) {
+        cur.item += step;
+        if (cur.item >= items) break;
+        cur.chunk = 0;
+        cur.b = cur.item / H;
+        cur.h = cur.item - cur.b * H;
+        cur.t = __ldg(a.pos + cur.b);
+        cur.nchunk = 2 * ((cur.t + RB - 1) / RB);
+        const int* table = a.page_table + (size_t)cur.b * pps;
+        cur.pg0 = lane < pps ? __ldg(table + lane) : 0;
+        cur.pg1 = lane + 32 < pps ? __ldg(table + lane + 32) : 0;
+        continue;
+      }
+      const int i = cur.chunk >> 1, which = cur.chunk & 1;
+      const int rows = min(RB, cur.t - i * RB);
+      const int p0 = i * RB;
+      const int pidx = p0 >> pt_shift, off = p0 & (pt - 1);
+      const int page = __shfl_sync(0xffffffffu, pidx < 32 ? cur.pg0 : cur.pg1, pidx & 31);
+      if (lane == 0) {
+        const float* src = ph.kv_pool + ((((size_t)page * 2 + which) * H + cur.h) * pt + off) * D;
+        const uint32_t slot = cur.issued % AT_SLOTS;
+        mbar_expect_tx(&kv_full[slot], (uint32_t)rows * D * 4);
+        bulk_load(stage + (size_t)slot * AT_SLOT_BYTES, src, (uint32_t)rows * D * 4, &kv_full[slot]);
+      }
+      ++cur.issued;
+      ++cur.chunk;
+    }
+  };
+  if (ok) issue_upto(consumed + AT_SLOTS);
+
+  const int key = lane >> 1, half = lane & 1;  // scores: two lanes per key, 32 dims each
+  const int d4 = lane & 15, kh = lane >> 4;    // values: sixteen lanes per row, two key halves
+  for (int item = first; item < items; item += step) {
+    const int b = item / H, h = item - b * H;
+    const int t = __ldg(a.pos + b);
+    const int nblk = (t + RB - 1) / RB;
+    // q, k, v of the new token: lanes 0-15 each own four of the head's 64 features
+    float sn = 0.f;
+    float4 vn = make_float4(0.f, 0.f, 0.f, 0.f);
+    {
+      const int f = h * D + (lane & 15) * 4;
+      const int page = __ldg(a.page_table + (size_t)b * pps + (t >> pt_shift)), off = t & (pt - 1);
+      if (lane < 16) {
+        const float4 qv = attn_feature4(a, ph, r, f, b);
+        const float4 kv = attn_feature4(a, ph, r, C + f, b);
+        vn = attn_feature4(a, ph, r, 2 * C + f, b);
+        qs[lane] = qv;
+        sn = fmaf(qv.x, kv.x, fmaf(qv.y, kv.y, fmaf(qv.z, kv.z, qv.w * kv.w)));
+        // append the new K and V rows
+        reinterpret_cast<float4*>(ph.kv_pool + ((((size_t)page * 2 + 0) * H + h) * pt + off) * D)[lane] = kv;
+        reinterpret_cast<float4*>(ph.kv_pool + ((((size_t)page * 2 + 1) * H + h) * pt + off) * D)[lane] = vn;
+      }
+    }
+    sn = warp_sum_f(sn) * scale;
+    __syncwarp();
+    float m = -INFINITY, l = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = 0; i < nblk; ++i) {
+      const int rows = min(RB, t - i * RB);
+      const uint32_t ck = consumed, cv = consumed + 1;
+      // ---- scores of this block's keys
+      if (ok) ok = warp_wait(&kv_full[ck % AT_SLOTS], (ck / AT_SLOTS) & 1, failed, a.error_flag, 31);
+      float s0 = 0.f, s1 = 0.f;
+      if (ok && key < rows) {
+        const float4* kr = reinterpret_cast<const float4*>(stage + (size_t)(ck % AT_SLOTS) * AT_SLOT_BYTES) + key * 16 + half * 8;
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+          // rotate: the eight lanes of a quarter warp hit eight different bank groups
+          const int e2 = (e + lane) & 7, e3 = (e + 1 + lane) & 7;
+          const float4 ka = kr[e2], kb = kr[e3];
+          const float4 qa = qs[half * 8 + e2], qb = qs[half * 8 + e3];
+          s0 = fmaf(qa.x, ka.x, s0);
+          s1 = fmaf(qb.x, kb.x, s1);
+          s0 = fmaf(qa.y, ka.y, s0);
+          s1 = fmaf(qb.y, kb.y, s1);
+          s0 = fmaf(qa.z, ka.z, s0);
+          s1 = fmaf(qb.z, kb.z, s1);
+          s0 = fmaf(qa.w, ka.w, s0);
+          s1 = fmaf(qb.w, kb.w, s1);
+        }
+      }
+      float s = s0 + s1;
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      s = key < rows ? s * scale : -INFINITY;
+      float pm = s;
+#pragma unroll
+      for (int o = 16; o > 1; o >>= 1) pm = fmaxf(pm, __shfl_xor_sync(0xffffffffu, pm, o));
+      if (pm > m) {  // the running maximum moves (the same decision in every lane): rescale what was summed so far
+        const float corr = (m == -INFINITY) ? 0.f : expf(m - pm);
+        l *= corr;
+        acc.x *= corr;
+        acc.y *= corr;
+        acc.z *= corr;
+        acc.w *= corr;
+        m = pm;
+      }
+      const float p = key < rows ? expf(s - m) : 0.f;
+      l += half == 0 ? p : 0.f;
+      if (ok) issue_upto(consumed + 1 + AT_SLOTS);  // the K chunk's slot is free
+      // ---- weighted values
+      if (ok) ok = warp_wait(&kv_full[cv % AT_SLOTS], (cv / AT_SLOTS) & 1, failed, a.error_flag, 32);
+      const float4* vr = reinterpret_cast<const float4*>(stage + (size_t)(cv % AT_SLOTS) * AT_SLOT_BYTES);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int kk = kh * 8 + e;
+        const float pk = __shfl_sync(0xffffffffu, p, kk * 2);
+        if (ok && kk < rows) {
+          const float4 v = vr[kk * 16 + d4];
+          acc.x = fmaf(pk, v.x, acc.x);
+          acc.y = fmaf(pk, v.y, acc.y);
+          acc.z = fmaf(pk, v.z, acc.z);
+          acc.w = fmaf(pk, v.w, acc.w);
+        }
+      }
+      consumed += 2;
+      __syncwarp();
+      if (ok) issue_upto(consumed + AT_SLOTS);  // the V chunk's slot is free
+    }
+    // ---- the new token itself, then the two key halves and the lanes' partial sums
+    const float m_fin = fmaxf(m, sn);
+    const float corr = (m == -INFINITY) ? 0.f : expf(m - m_fin);
+    const float pn = expf(sn - m_fin);
+    acc.x *= corr;
+    acc.y *= corr;
+    acc.z *= corr;
+    acc.w *= corr;
+    acc.x += __shfl_xor_sync(0xffffffffu, acc.x, 16);
+    acc.y += __shfl_xor_sync(0xffffffffu, acc.y, 16);
+    acc.z += __shfl_xor_sync(0xffffffffu, acc.z, 16);
+    acc.w += __shfl_xor_sync(0xffffffffu, acc.w, 16);
+    const float ls = warp_sum_f(l) * corr + pn;
+    if (lane < 16 && ok) {
+      const float inv = 1.0f / ls;
+      const float y[4] = {fmaf(pn, vn.x, acc.x) * inv, fmaf(pn, vn.y, acc.y) * inv, fmaf(pn, vn.z, acc.z) * inv,
+                          fmaf(pn, vn.w, acc.w) * inv};
+      float hi[4], lo[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        hi[e] = tf32_hi(y[e]);
+        lo[e] = y[e] - hi[e];
+      }
+      const size_t idx = (size_t)b * C + h * D + lane * 4;
+      *reinterpret_cast<float4*>(ph.out_hi + idx) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+      *reinterpret_cast<float4*>(ph.out_lo + idx) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+    }
+    __syncwarp();  // qs is rewritten by the next pair
+  }
+}
+
 __global__ void __launch_bounds__(CH_THREADS, 1)
     chain_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_hi0,
                  const __grid_constant__ CUtensorMap map_lo0, const __grid_constant__ CUtensorMap map_hi1,
@@ -324,14 +539,17 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* w_ring = base;
   uint8_t* act_ring = base + (size_t)CH_W_STAGES * CH_W_BYTES;
-  uint64_t* w_full = reinterpret_cast<uint64_t*>(act_ring + (size_t)CH_X_STAGES * CH_ACT_BYTES);
+  // attention staging = the activation ring and the region after it; then the attention scratch
+  float* at_scratch = reinterpret_cast<float*>(act_ring + (size_t)CH_X_STAGES * CH_ACT_BYTES + AT_EXTRA_BYTES);
+  uint64_t* w_full = reinterpret_cast<uint64_t*>(at_scratch + 2 * AT_SCRATCH_FLOATS);
   uint64_t* w_empty = w_full + CH_W_STAGES;
   uint64_t* ready = w_empty + CH_W_STAGES;  // split weights in tensor memory AND activation tiles in shared memory
   uint64_t* done = ready + CH_X_STAGES;     // the MMAs that read them have completed
   uint64_t* d_full = done + CH_X_STAGES;
   uint64_t* d_empty = d_full + 2;
   uint64_t* go = d_empty + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(go + 1);
+  uint64_t* kv_full = go + 1;  // [8 worker warps][AT_SLOTS]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(kv_full + 8 * AT_SLOTS);
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* verdict = reinterpret_cast<volatile int*>(tmem_slot + 2);
   float* red = reinterpret_cast<float*>(tmem_slot + 4);  // 8 floats
@@ -353,6 +571,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
       mbar_init(&d_empty[s], 8);
     }
     mbar_init(go, 1);
+    for (int s = 0; s < 8 * AT_SLOTS; ++s) mbar_init(&kv_full[s], 1);
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -369,9 +588,9 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
       uint32_t wi = 0;
       bool ok = true;
       for (int p = 0; p < a.n_phases && ok; ++p) {
-        if (a.ph[p].kind != CH_GEMM) continue;
-        const ChRange r = chain_range(a.ph[p].n, a.ph[p].k, cta, grid);
-        const uint32_t b0 = a.ph[p].w_block0;
+        if (phase_at(a, p).kind != CH_GEMM) continue;
+        const ChRange r = chain_range(phase_at(a, p).n, phase_at(a, p).k, cta, grid);
+        const uint32_t b0 = phase_at(a, p).w_block0;
         for (int g = r.g0; g < r.g1 && ok; ++g, ++wi) {
           const uint32_t s = wi % CH_W_STAGES;
           if (wi >= CH_W_STAGES) ok = mbar_wait(&w_empty[s], ((wi / CH_W_STAGES) - 1) & 1, failed, a.error_flag, 21);
@@ -390,8 +609,8 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
       bool ok = true;
       long long t_wait = 0, t_issue = 0, t_dempty = 0;
       for (int p = 0; p < a.n_phases && ok; ++p) {
-        if (a.ph[p].kind != CH_GEMM) continue;
-        const ChRange r = chain_range(a.ph[p].n, a.ph[p].k, cta, grid);
+        if (phase_at(a, p).kind != CH_GEMM) continue;
+        const ChRange r = chain_range(phase_at(a, p).n, phase_at(a, p).k, cta, grid);
         for (int g = r.g0; g < r.g1 && ok;) {
           const int tile = g / r.nkb;
           const int gend = min(r.g1, (tile + 1) * r.nkb);
@@ -444,9 +663,9 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
       uint32_t wi = 0, gp = 0;
       bool ok = true;
       for (int p = 0; p < a.n_phases && ok; ++p) {
-        if (a.ph[p].kind != CH_GEMM) continue;
-        const ChRange r = chain_range(a.ph[p].n, a.ph[p].k, cta, grid);
-        const int act = a.ph[p].act;
+        if (phase_at(a, p).kind != CH_GEMM) continue;
+        const ChRange r = chain_range(phase_at(a, p).n, phase_at(a, p).k, cta, grid);
+        const int act = phase_at(a, p).act;
         const CUtensorMap* mh = act == 0 ? &map_hi0 : act == 1 ? &map_hi1 : &map_hi2;
         const CUtensorMap* ml = act == 0 ? &map_lo0 : act == 1 ? &map_lo1 : &map_lo2;
         ok = mbar_wait(go, gp & 1, failed, a.error_flag, 25);
@@ -477,8 +696,8 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
     bool ok = true;
     long long t_wfull = 0, t_afree = 0;
     for (int p = 0; p < a.n_phases && ok; ++p) {
-      if (a.ph[p].kind != CH_GEMM) continue;
-      const ChRange r = chain_range(a.ph[p].n, a.ph[p].k, cta, grid);
+      if (phase_at(a, p).kind != CH_GEMM) continue;
+      const ChRange r = chain_range(phase_at(a, p).n, phase_at(a, p).k, cta, grid);
       for (int g = r.g0; g < r.g1 && ok; ++g, ++wi) {
         const uint32_t s = wi % CH_W_STAGES, xs = wi % CH_X_STAGES;
         long long c0 = clock64();
@@ -534,22 +753,17 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
     bool ok = true;     // this warp's drains
     bool live = true;   // same for all workers of the CTA: decided at the grid barriers
     if (wt == 0) chain_trace(a, 31);
-    // bias and LayerNorm vectors were last read a whole step ago: pull them into L2 now (CTA p for phase p)
-    if (cta < a.n_phases && a.ph[cta].kind != CH_GEMM) {
-      const ChainPhase& pp = a.ph[cta];
-      for (int i = wt * 32; i < pp.n; i += CH_WORKERS * 32) {
-        if (pp.bias) asm volatile("prefetch.global.L2 [%0];" ::"l"(pp.bias + i));
-        if (pp.kind == CH_ROWS && pp.ln_g) {
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(pp.ln_g + i));
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(pp.ln_b + i));
-        }
-      }
+    if (wt == 0 && cta == 0 && a.phase_times) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      a.phase_times[0] = t;
     }
+    uint32_t at_consumed = 0;  // key / value chunks this warp has used so far (all attention phases)
     for (int p = 0; p < a.n_phases; ++p) {
-      const int kind = a.ph[p].kind;
+      const int kind = phase_at(a, p).kind;
       if (kind == CH_GEMM) {
         if (wt == 0) mbar_arrive(go);  // inputs of this phase exist (previous kernel, or the barrier just passed)
-        const ChRange r = chain_range(a.ph[p].n, a.ph[p].k, cta, grid);
+        const ChRange r = chain_range(phase_at(a, p).n, phase_at(a, p).k, cta, grid);
         int seg = 0;
         for (int g = r.g0; g < r.g1; ++seg) {
           const int tile = g / r.nkb;
@@ -576,18 +790,25 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
           ++si;
           g = gend;
         }
+      } else if (kind == CH_ATTN) {
+        chain_attn_phase(a, phase_at(a, p), wt, act_ring, kv_full, at_scratch, at_consumed, failed, live);
       } else if (kind == CH_ROWS) {
-        if (live && cta < a.m) chain_rows_phase(a, a.ph[p], cta, wt, red, p);
+        if (live && cta < a.m) chain_rows_phase(a, phase_at(a, p), cta, wt, red, p);
       } else {
-        if (live) chain_elem_phase(a, a.ph[p], wt);
+        if (live) chain_elem_phase(a, phase_at(a, p), wt);
       }
-      if (wt == 0) chain_trace(a, 10 + p);
+      if (wt == 0 && p < 10) chain_trace(a, 10 + p);
       if (p + 1 < a.n_phases) {
         ++barriers;
         live = chain_grid_barrier(a.barrier, (unsigned)grid * barriers, failed, a.error_flag, wt, verdict);
         ok = ok && live;
       }
-      if (wt == 0) chain_trace(a, p);
+      if (wt == 0 && p < 10) chain_trace(a, p);
+      if (wt == 0 && cta == 0 && a.phase_times) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        a.phase_times[p + 1] = t;
+      }
     }
     // leave the barrier word zero for the next launch: the last CTA to get here resets it
     if (wt == 0 && !*failed) {
@@ -625,10 +846,19 @@ int chain_grid(int num_sms) {
 
 size_t chain_partial_floats(int grid) { return (size_t)grid * CH_MAX_SEG * CH_PART_TILE; }
 
-bool chain_supported(const ChainArgs& a, int grid) {
-  if (grid <= 0 || a.m < 1 || a.m > CH_BN || a.n_phases < 1 || a.n_phases > CHAIN_MAX_PHASES) return false;
+bool chain_supported(const ChainArgs& a, int grid, const ChainPhase* host_phases) {
+  const ChainPhase* phs = host_phases ? host_phases : a.ph;
+  if (grid <= 0 || a.m < 1 || a.m > CH_BN || a.n_phases < 1) return false;
+  if (!host_phases && (a.n_phases > CHAIN_MAX_PHASES || a.phases_dev)) return false;
   for (int p = 0; p < a.n_phases; ++p) {
-    const ChainPhase& ph = a.ph[p];
+    const ChainPhase& ph = phs[p];
+    if (ph.kind == CH_ATTN) {
+      if (a.kv.head_dim != 64 || (a.kv.page_tokens != 16 && a.kv.page_tokens != 32 && a.kv.page_tokens != 64)) return false;
+      if (!a.page_table || !a.pos || !ph.kv_pool || !ph.out_hi || !ph.out_lo || a.kv.pages_per_seq > 64) return false;
+      if (p == 0 || phs[p - 1].kind != CH_GEMM || phs[p - 1].n != ph.n || phs[p - 1].k != ph.k) return false;
+      if (ph.n != 3 * a.kv.n_head * 64) return false;
+      continue;
+    }
     if (ph.k < BK * CH_UB || ph.k % (BK * CH_UB) != 0 || ph.n < 1) return false;
     const ChRange r = chain_range(ph.n, ph.k, 0, grid);
     if ((r.per + r.nkb - 2) / r.nkb + 1 > CH_MAX_SEG) return false;
@@ -639,10 +869,10 @@ bool chain_supported(const ChainArgs& a, int grid) {
     } else if (ph.kind == CH_ROWS) {
       if (ph.n % 4 != 0 || ph.n > 4 * 4 * CH_WORKERS || !ph.x) return false;
       if (ph.ln_g && (!ph.ln_b || !ph.out_hi || !ph.out_lo)) return false;
-      if (p == 0 || a.ph[p - 1].kind != CH_GEMM || a.ph[p - 1].n != ph.n || a.ph[p - 1].k != ph.k) return false;
+      if (p == 0 || phs[p - 1].kind != CH_GEMM || phs[p - 1].n != ph.n || phs[p - 1].k != ph.k) return false;
     } else if (ph.kind == CH_ELEM) {
       if (ph.out_hi && !ph.out_lo) return false;
-      if (p == 0 || a.ph[p - 1].kind != CH_GEMM || a.ph[p - 1].n != ph.n || a.ph[p - 1].k != ph.k) return false;
+      if (p == 0 || phs[p - 1].kind != CH_GEMM || phs[p - 1].n != ph.n || phs[p - 1].k != ph.k) return false;
     } else {
       return false;
     }
@@ -650,8 +880,9 @@ bool chain_supported(const ChainArgs& a, int grid) {
   return true;
 }
 
+// When a.phases_dev is set the caller has validated the phase list with chain_supported already.
 cudaError_t launch_chain(const ChainArgs& a, int grid, cudaStream_t s) {
-  if (!chain_supported(a, grid)) return cudaErrorInvalidValue;
+  if (!a.phases_dev && !chain_supported(a, grid)) return cudaErrorInvalidValue;
   CUtensorMap maps[7];
   memset(maps, 0, sizeof(maps));
   if (!make_map(&maps[0], a.arena, a.arena_floats / BK, BK, CH_UB * TILE_M)) return cudaErrorInvalidValue;

@@ -136,11 +136,11 @@ cudaError_t launch_finalize(const FinalizeArgs& a, bool pdl, cudaStream_t s);
 // a residual update (+ LayerNorm, written as a TF32 hi/lo pair) or an element-wise epilogue (GELU,
 // hi/lo pair and/or plain FP32). Phases are separated by a bounded grid barrier that only the
 // worker warps take part in: the weight stream of later phases keeps running through it.
-enum ChainKind { CH_GEMM = 0, CH_ROWS = 1, CH_ELEM = 2 };
+enum ChainKind { CH_GEMM = 0, CH_ROWS = 1, CH_ELEM = 2, CH_ATTN = 3 };
 enum ChainAct { CH_ACT_NORM = 0, CH_ACT_ATTN = 1, CH_ACT_H = 2 };
 struct ChainPhase {
   int kind;
-  int n, k;           // GEMM: output features and reduction length; ROWS / ELEM: those of the GEMM being reduced
+  int n, k;           // GEMM: output features and reduction length; ROWS / ELEM / ATTN: those of the GEMM being reduced
   int act;            // GEMM: which hi/lo activation pair is the input (ChainAct)
   unsigned w_block0;  // GEMM: index of the first 16 KB block of this matrix inside the tiled arena
   int gelu;           // ELEM: tanh-GELU after the bias
@@ -149,13 +149,20 @@ struct ChainPhase {
   const float* ln_g;  // ROWS: LayerNorm over the updated row (nullptr: none) ...
   const float* ln_b;
   float* out;         // ELEM: plain FP32 result [m, n] or nullptr
-  float* out_hi;      // ROWS: LayerNorm result, ELEM: result, as a TF32 hi/lo pair (or nullptr)
+  float* out_hi;      // ROWS: LayerNorm result, ELEM / ATTN: result, as a TF32 hi/lo pair (or nullptr)
   float* out_lo;
+  float* kv_pool;     // ATTN: this layer's page pool (n, k, bias: those of the QKV GEMM right before it)
 };
 constexpr int CHAIN_MAX_PHASES = 10;
 struct ChainArgs {
-  ChainPhase ph[CHAIN_MAX_PHASES];
+  ChainPhase ph[CHAIN_MAX_PHASES];  // the phases, when phases_dev is nullptr
+  const ChainPhase* phases_dev;     // or: the phases in device memory (any number of them)
   int n_phases;
+  // ATTN phases: causal attention of one new token per sequence over the paged cache (head_dim 64),
+  // appending the new K and V; key / value rows are staged in shared memory by bulk async copies
+  KvLayout kv;
+  const int* page_table;  // [max_batch, pages_per_seq]
+  const int* pos;         // [m] position of the new token (= keys already cached)
   int m;               // tokens (rows of every activation matrix), <= 64
   float eps;
   const float* arena;  // tiled weight arena (all matrices of the model)
@@ -166,14 +173,16 @@ struct ChainArgs {
   float* partials;     // chain_partial_floats(grid) floats
   unsigned* barrier;   // one word, zero before the first launch (the kernel leaves it zero)
   int* error_flag;     // set non-zero when a bounded wait expired
+  unsigned long long* phase_times;  // optional: n_phases + 1 %globaltimer stamps written by CTA 0 (start, then after each phase)
   unsigned long long* trace;  // optional tuning aid, 32 words per CTA: [p] when worker thread 0 left phase p, [10 + p]
                               // when its work of phase p was done, [20..25] wait / issue cycle counts, [31] start
 };
 // Cooperative grid of the chain kernel on this device (0: not launchable) and the scratch it needs.
 int chain_grid(int num_sms);
 size_t chain_partial_floats(int grid);
-// True when every GEMM phase of `a` fits the kernel's limits for a grid of `grid` CTAs.
-bool chain_supported(const ChainArgs& a, int grid);
+// True when every phase fits the kernel's limits for a grid of `grid` CTAs. `host_phases` is the
+// host copy of the phase list (a.ph when nullptr).
+bool chain_supported(const ChainArgs& a, int grid, const ChainPhase* host_phases = nullptr);
 cudaError_t launch_chain(const ChainArgs& a, int grid, cudaStream_t s);
 
 // Whole decode step in one persistent cooperative kernel (decode_mega.cu), for at most 8 sequences

@@ -243,6 +243,13 @@ struct pg_cache {
   unsigned* d_chain_barrier = nullptr;
   unsigned long long* d_chain_trace = nullptr;  // PG_CHAIN_TRACE=1
   int chain_ctas = 0;
+  struct ChainProgram {  // whole-step phase list of the persistent chain kernel for one batch size
+    ChainPhase* dev = nullptr;            // in device memory (nullptr: this batch size is not supported)
+    int n = 0;
+    std::vector<int> bucket;              // profile bucket of every phase
+    unsigned long long* d_times = nullptr;  // n + 1 time stamps, written in profiling runs
+  };
+  std::map<int, ChainProgram> chain_programs;
   // single-kernel decode step (at most 8 sequences)
   MegaLayer* d_mega_layers = nullptr;
   unsigned* d_barrier = nullptr;
@@ -274,21 +281,29 @@ struct pg_cache {
     if (d_chain_trace) {
       std::vector<unsigned long long> t((size_t)chain_ctas * 32 + 512);
       if (cudaMemcpy(t.data(), d_chain_trace, t.size() * 8, cudaMemcpyDeviceToHost) == cudaSuccess) {
+        {
+          const unsigned long long* tq = &t[(size_t)chain_ctas * 32 + 384];
+          fprintf(stderr, "attention phase (CTA 3 warp 0) cycles: total %llu, wait K %llu, wait V %llu, issue %llu\n", tq[0], tq[1], tq[2], tq[3]);
+        }
         for (int pp = 0; pp < 8; ++pp) {
           const unsigned long long* tq = &t[(size_t)chain_ctas * 32 + 256 + pp * 8];
           if (tq[0]) fprintf(stderr, "rows phase %d (CTA 0) cycles: partial sums %llu, mean %llu, var %llu, write %llu\n", pp, tq[1] - tq[0], tq[2] - tq[1], tq[3] - tq[2], tq[4] - tq[3]);
         }
         unsigned long long t0 = ~0ULL;
         for (int i = 0; i < chain_ctas; ++i) t0 = std::min(t0, t[(size_t)i * 32 + 31]);
-        for (int sl = 0; sl < 8; ++sl) {
+        for (int sl = 0; sl < 10; ++sl) {
           unsigned long long lo = ~0ULL, hi = 0, wlo = ~0ULL, whi = 0;
           for (int i = 0; i < chain_ctas; ++i) {
             const unsigned long long v = t[(size_t)i * 32 + sl] - t0, w = t[(size_t)i * 32 + 10 + sl] - t0;
             lo = std::min(lo, v); hi = std::max(hi, v); wlo = std::min(wlo, w); whi = std::max(whi, w);
           }
-          fprintf(stderr, "chain trace (layer 1) phase %d: work done %6llu..%6llu ns, barrier passed %6llu..%6llu ns\n", sl, wlo, whi, lo, hi);
+          fprintf(stderr, "chain trace phase %d: work done %6llu..%6llu ns, barrier passed %6llu..%6llu ns\n", sl, wlo, whi, lo, hi);
         }
       }
+    }
+    for (auto& cp : chain_programs) {
+      if (cp.second.dev) cudaFree(cp.second.dev);
+      if (cp.second.d_times) cudaFree(cp.second.d_times);
     }
     for (auto& g : graphs) cudaGraphExecDestroy(g.second);
     for (void* p : {(void*)kv_pool, (void*)d_table, (void*)d_ids, (void*)d_pos, (void*)d_argmax, (void*)d_token_log,
@@ -451,6 +466,7 @@ enum Bucket { B_LAYER_NORM = 0, B_QKV, B_ATTN, B_ATTN_PROJ, B_MLP_FC, B_MLP_PROJ
 struct StepProfiler {
   std::vector<cudaEvent_t> ev;
   std::vector<int> bucket;
+  int chain_event = -1;  // index of the event pair around the persistent chain kernel, if it ran
   cudaError_t mark(cudaStream_t s, int b) {
     cudaEvent_t e;
     cudaError_t r = cudaEventCreate(&e);
@@ -463,6 +479,88 @@ struct StepProfiler {
     for (auto e : ev) cudaEventDestroy(e);
   }
 };
+
+static ChainArgs chain_base_args(const pg_cache* c, int batch) {
+  const pg_model* m = c->model;
+  ChainArgs base{};
+  base.m = batch; base.eps = m->cfg.layer_norm_epsilon; base.arena = m->tiled_arena; base.arena_floats = m->tiled_floats;
+  base.act_hi[CH_ACT_NORM] = c->norm; base.act_lo[CH_ACT_NORM] = c->norm_lo; base.act_k[CH_ACT_NORM] = m->c();
+  base.act_hi[CH_ACT_ATTN] = c->attn; base.act_lo[CH_ACT_ATTN] = c->attn_lo; base.act_k[CH_ACT_ATTN] = m->c();
+  base.act_hi[CH_ACT_H] = c->hbuf; base.act_lo[CH_ACT_H] = c->h_lo; base.act_k[CH_ACT_H] = m->f();
+  base.partials = c->chain_partials; base.barrier = c->d_chain_barrier; base.error_flag = c->d_error;
+  base.trace = c->d_chain_trace;
+  base.kv = c->kv; base.page_table = c->d_table; base.pos = c->d_pos;
+  return base;
+}
+
+// Builds (once per batch size) the phase list of a whole decode step for the persistent chain
+// kernel and uploads it: per layer QKV projection, attention, attention-output projection with
+// residual and LayerNorm, MLP with GELU, residual and the next LayerNorm; then the lm_head.
+// block_forward_one_profiled (rust.rs:1136-1250), forward_one tail (rust.rs:981-1003).
+static int ensure_chain_program(pg_cache* c, int batch) {
+  if (c->chain_ctas <= 0 || batch <= 8 || batch > 64 || !c->norm_lo) return PG_OK;
+  if (c->chain_programs.count(batch)) return PG_OK;
+  const pg_model* m = c->model;
+  const int C = m->c(), F = m->f(), V = m->v(), L = m->layers_n();
+  std::vector<ChainPhase> ph;
+  std::vector<int> bucket;
+  int cur_b = B_OTHER;  // bucket of the phases being appended
+  auto block0 = [&](const float* t) { return (unsigned)((size_t)(t - m->tiled_arena) / 4096); };
+  auto gemm = [&](const float* t, int n_out, int k, int act) {
+    ChainPhase p{};
+    p.kind = CH_GEMM; p.n = n_out; p.k = k; p.act = act; p.w_block0 = block0(t);
+    ph.push_back(p);
+    bucket.push_back(cur_b);
+  };
+  auto rows = [&](int n_out, int k, const float* bias, const float* g, const float* b) {
+    ChainPhase p{};
+    p.kind = CH_ROWS; p.n = n_out; p.k = k; p.bias = bias; p.x = c->x; p.ln_g = g; p.ln_b = b;
+    p.out_hi = c->norm; p.out_lo = c->norm_lo;
+    ph.push_back(p);
+    bucket.push_back(B_LAYER_NORM);  // partial sums + bias + residual + LayerNorm
+  };
+  auto elem = [&](int n_out, int k, const float* bias, int gelu, float* out, float* ohi, float* olo) {
+    ChainPhase p{};
+    p.kind = CH_ELEM; p.n = n_out; p.k = k; p.bias = bias; p.gelu = gelu; p.out = out; p.out_hi = ohi; p.out_lo = olo;
+    ph.push_back(p);
+    bucket.push_back(cur_b);  // belongs to the GEMM it finishes
+  };
+  for (int l = 0; l < L; ++l) {
+    const LayerWeights& w = m->layers[l];
+    cur_b = B_QKV;
+    gemm(w.t_qkv, 3 * C, C, CH_ACT_NORM);
+    ChainPhase at{};  // reduces the QKV partials itself
+    at.kind = CH_ATTN; at.n = 3 * C; at.k = C; at.bias = w.b_qkv; at.kv_pool = c->layer_pool(l);
+    at.out_hi = c->attn; at.out_lo = c->attn_lo;
+    ph.push_back(at);
+    bucket.push_back(B_ATTN);
+    cur_b = B_ATTN_PROJ;
+    gemm(w.t_proj, C, C, CH_ACT_ATTN);
+    rows(C, C, w.b_proj, w.ln2_g, w.ln2_b);
+    cur_b = B_MLP_FC;
+    gemm(w.t_fc, F, C, CH_ACT_NORM);
+    elem(F, C, w.b_fc, 1, nullptr, c->hbuf, c->h_lo);
+    cur_b = B_MLP_PROJ;
+    gemm(w.t_proj2, C, F, CH_ACT_H);
+    if (l + 1 < L) rows(C, F, w.b_proj2, m->layers[l + 1].ln1_g, m->layers[l + 1].ln1_b);
+    else rows(C, F, w.b_proj2, m->lnf_g, m->lnf_b);
+  }
+  cur_b = B_LOGITS;
+  gemm(m->t_wte, V, C, CH_ACT_NORM);
+  elem(V, C, nullptr, 0, c->logits, nullptr, nullptr);
+  ChainArgs a = chain_base_args(c, batch);
+  a.n_phases = (int)ph.size();
+  pg_cache::ChainProgram prog;
+  prog.n = (int)ph.size();
+  prog.bucket = bucket;
+  if (m->head_dim() == 64 && chain_supported(a, c->chain_ctas, ph.data())) {
+    PG_CUDA_TRY(cudaMalloc(&prog.dev, ph.size() * sizeof(ChainPhase)));
+    PG_CUDA_TRY(cudaMemcpy(prog.dev, ph.data(), ph.size() * sizeof(ChainPhase), cudaMemcpyHostToDevice));
+    PG_CUDA_TRY(cudaMalloc(&prog.d_times, (ph.size() + 1) * sizeof(unsigned long long)));
+  }
+  c->chain_programs[batch] = prog;
+  return PG_OK;
+}
 
 // Enqueues the kernels of one decode step for slots 0..batch-1 on `s`.
 // forward_one_profiled_with_scratch + block_forward_one_profiled (rust.rs:943-1006, 1136-1250).
@@ -505,82 +603,27 @@ static cudaError_t enqueue_decode_step(pg_cache* c, int batch, int splits, cudaS
   if (m->t_wte && batch > 8 && batch <= 64 && c->norm_lo) {
     // tensor-core path: every linear is three TF32 products (hi*hi + hi*lo + lo*hi) accumulated
     // in FP32; LayerNorm, attention and the GELU epilogue hand their results over as hi/lo pairs
-    if (c->chain_ctas > 0 && !prof) {
-      // persistent chain kernel: per layer one launch runs attention-output projection, MLP and the
-      // next layer's QKV projection (or the lm_head) with their bias / residual / LayerNorm / GELU
-      // phases; attention stays a launch of its own between two chains
-      ChainArgs base{};
-      base.m = batch; base.eps = eps; base.arena = m->tiled_arena; base.arena_floats = m->tiled_floats;
-      base.act_hi[CH_ACT_NORM] = c->norm; base.act_lo[CH_ACT_NORM] = c->norm_lo; base.act_k[CH_ACT_NORM] = C;
-      base.act_hi[CH_ACT_ATTN] = c->attn; base.act_lo[CH_ACT_ATTN] = c->attn_lo; base.act_k[CH_ACT_ATTN] = C;
-      base.act_hi[CH_ACT_H] = c->hbuf; base.act_lo[CH_ACT_H] = c->h_lo; base.act_k[CH_ACT_H] = F;
-      base.partials = c->chain_partials; base.barrier = c->d_chain_barrier; base.error_flag = c->d_error;
-      auto block0 = [&](const float* t) { return (unsigned)((size_t)(t - m->tiled_arena) / 4096); };
-      auto gemm = [&](ChainArgs& a, const float* t, int n_out, int k, int act) {
-        ChainPhase& ph = a.ph[a.n_phases++];
-        ph = ChainPhase{};
-        ph.kind = CH_GEMM; ph.n = n_out; ph.k = k; ph.act = act; ph.w_block0 = block0(t);
-      };
-      auto rows = [&](ChainArgs& a, int n_out, int k, const float* bias, const float* g, const float* b) {
-        ChainPhase& ph = a.ph[a.n_phases++];
-        ph = ChainPhase{};
-        ph.kind = CH_ROWS; ph.n = n_out; ph.k = k; ph.bias = bias; ph.x = c->x; ph.ln_g = g; ph.ln_b = b;
-        ph.out_hi = c->norm; ph.out_lo = c->norm_lo;
-      };
-      auto elem = [&](ChainArgs& a, int n_out, int k, const float* bias, int gelu, float* out, float* ohi, float* olo) {
-        ChainPhase& ph = a.ph[a.n_phases++];
-        ph = ChainPhase{};
-        ph.kind = CH_ELEM; ph.n = n_out; ph.k = k; ph.bias = bias; ph.gelu = gelu; ph.out = out; ph.out_hi = ohi; ph.out_lo = olo;
-      };
-      const int L = m->layers_n();
-      bool ok_chain = true;
-      std::vector<ChainArgs> chains((size_t)L + 1, base);
-      {
-        ChainArgs& a = chains[0];
-        gemm(a, m->layers[0].t_qkv, 3 * C, C, CH_ACT_NORM);
-        elem(a, 3 * C, C, m->layers[0].b_qkv, 0, c->qkv, nullptr, nullptr);
-        ok_chain = ok_chain && chain_supported(a, c->chain_ctas);
-      }
-      for (int l = 0; l < L; ++l) {
-        const LayerWeights& w = m->layers[l];
-        ChainArgs& a = chains[(size_t)l + 1];
-        gemm(a, w.t_proj, C, C, CH_ACT_ATTN);
-        rows(a, C, C, w.b_proj, w.ln2_g, w.ln2_b);
-        gemm(a, w.t_fc, F, C, CH_ACT_NORM);
-        elem(a, F, C, w.b_fc, 1, nullptr, c->hbuf, c->h_lo);
-        gemm(a, w.t_proj2, C, F, CH_ACT_H);
-        if (l + 1 < L) {
-          rows(a, C, F, w.b_proj2, m->layers[l + 1].ln1_g, m->layers[l + 1].ln1_b);
-          gemm(a, m->layers[l + 1].t_qkv, 3 * C, C, CH_ACT_NORM);
-          elem(a, 3 * C, C, m->layers[l + 1].b_qkv, 0, c->qkv, nullptr, nullptr);
-        } else {
-          rows(a, C, F, w.b_proj2, m->lnf_g, m->lnf_b);
-          gemm(a, m->t_wte, V, C, CH_ACT_NORM);
-          elem(a, V, C, nullptr, 0, c->logits, nullptr, nullptr);
-        }
-        ok_chain = ok_chain && chain_supported(a, c->chain_ctas);
-      }
-      if (L > 1) chains[2].trace = c->d_chain_trace;  // tuning aid: phase times of layer 1's chain
-      if (ok_chain) {
-        cur_bucket = B_LAYER_NORM;
-        PG_E(launch_layernorm_rows_split(c->x, m->layers[0].ln1_g, m->layers[0].ln1_b, eps, c->norm, c->norm_lo, batch, C, pdl, s));
-        PG_E(launch_chain(chains[0], c->chain_ctas, s));
-        for (int l = 0; l < L; ++l) {
-          DecodeAttnArgs at{};
-          at.qkv = c->qkv; at.out = c->attn; at.out_lo = c->attn_lo; at.kv_pool = c->layer_pool(l);
-          at.page_table = c->d_table; at.pos = c->d_pos; at.part = c->attn_part; at.counters = c->attn_counters;
-          at.kv = c->kv; at.batch = batch; at.splits = splits;
-          PG_E(launch_decode_attention(at, false, s));
-          PG_E(launch_chain(chains[(size_t)l + 1], c->chain_ctas, s));
-        }
-        PG_E(launch_argmax_rows(c->logits, batch, V, c->d_argmax, s));
-        FinalizeArgs fx{};
-        fx.m = batch; fx.argmax_out = c->d_argmax; fx.next_ids = c->d_ids; fx.pos = c->d_pos;
-        fx.token_log = c->d_token_log; fx.n_positions = m->positions();
-        PG_E(launch_finalize(fx, false, s));
-        if (launches) *launches = n;
-        return cudaSuccess;
-      }
+    auto prog = c->chain_programs.find(batch);
+    if (prog != c->chain_programs.end() && prog->second.dev) {
+      // the whole step between the embedding and the argmax as one persistent cooperative kernel
+      ChainArgs a = chain_base_args(c, batch);
+      a.phases_dev = prog->second.dev;
+      a.n_phases = prog->second.n;
+      if (prof) a.phase_times = prog->second.d_times;  // per-phase time stamps for the operation profile
+      cur_bucket = B_LAYER_NORM;
+      PG_E(launch_layernorm_rows_split(c->x, m->layers[0].ln1_g, m->layers[0].ln1_b, eps, c->norm, c->norm_lo, batch, C, pdl, s));
+      cur_bucket = B_OTHER;
+      if (prof) prof->chain_event = (int)prof->ev.size();
+      PG_E(launch_chain(a, c->chain_ctas, s));
+      cur_bucket = B_LOGITS;
+      PG_E(launch_argmax_rows(c->logits, batch, V, c->d_argmax, s));
+      cur_bucket = B_OTHER;
+      FinalizeArgs fx{};
+      fx.m = batch; fx.argmax_out = c->d_argmax; fx.next_ids = c->d_ids; fx.pos = c->d_pos;
+      fx.token_log = c->d_token_log; fx.n_positions = m->positions();
+      PG_E(launch_finalize(fx, false, s));
+      if (launches) *launches = n;
+      return cudaSuccess;
     }
     auto x3 = [&](const float* w, const float* bias, const float* xhi, const float* xlo, float* out, float* ohi,
                   float* olo, int n_out, int k, int epi, const float* resid) -> cudaError_t {
@@ -687,6 +730,9 @@ static int run_decode_step(pg_cache* c, int batch) {
   const int splits = choose_splits(c, batch, max_len);
   const bool graphs = m->backend.use_graphs != 2 && !env_flag("PG_NO_GRAPHS");
   uint64_t launches = 0;
+  if (m->t_wte) {
+    if (int r = ensure_chain_program(c, batch)) return r;
+  }
   if (!graphs) {
     PG_CUDA_TRY(enqueue_decode_step(c, batch, splits, c->stream, &launches));
     c->decode_launches += launches;
@@ -1211,12 +1257,39 @@ int pg_profile_forward_one(const pg_model* model, pg_cache* cache, const int32_t
     sec[prof.bucket[i]] += ms * 1e-3;
     cnt[prof.bucket[i]] += 1;
   }
+  double fused_sec = 0.0;
+  uint64_t fused_phases = 0;
+  if (prof.chain_event >= 0) {
+    {
+      float ms = 0.f;
+      PG_CUDA_TRY(cudaEventElapsedTime(&ms, prof.ev[prof.chain_event], prof.ev[prof.chain_event + 1]));
+      fused_sec = ms * 1e-3;
+    }
+    // the chain kernel's own time stamps split its duration into the operation buckets; what the
+    // stamps do not cover (launch, set-up, exit) stays in `other`
+    auto it = cache->chain_programs.find(batch);
+    if (it != cache->chain_programs.end() && it->second.d_times) {
+      std::vector<unsigned long long> ts((size_t)it->second.n + 1);
+      PG_CUDA_TRY(cudaMemcpy(ts.data(), it->second.d_times, ts.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+      double covered = 0.0;
+      for (int p = 0; p < it->second.n; ++p) {
+        const double d = (double)(ts[p + 1] - ts[p]) * 1e-9;
+        sec[it->second.bucket[p]] += d;
+        cnt[it->second.bucket[p]] += 1;
+        covered += d;
+      }
+      sec[B_OTHER] = std::max(0.0, sec[B_OTHER] - covered);
+      fused_phases = (uint64_t)it->second.n;
+    }
+  }
   memset(out, 0, sizeof(*out));
   out->layer_norm = sec[B_LAYER_NORM]; out->qkv_projection = sec[B_QKV]; out->attention = sec[B_ATTN];
   out->attention_projection = sec[B_ATTN_PROJ]; out->mlp_fc_projection = sec[B_MLP_FC];
   out->mlp_projection = sec[B_MLP_PROJ]; out->final_logits = sec[B_LOGITS]; out->other = sec[B_OTHER];
   const Bucket order[8] = {B_LAYER_NORM, B_QKV, B_ATTN, B_ATTN_PROJ, B_MLP_FC, B_MLP_PROJ, B_LOGITS, B_OTHER};
   for (int i = 0; i < 8; ++i) out->launches[i] = cnt[order[i]];
+  out->fused_step_kernel = fused_sec;
+  out->fused_phases = fused_phases;
   return PG_OK;
 }
 

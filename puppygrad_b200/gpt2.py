@@ -313,13 +313,17 @@ class Gpt2Model:
 
     def profile_forward_one(self, token_ids: Sequence[int], cache: Gpt2KvCache) -> dict:
         """One decode step timed per operation class (Gpt2OperationProfile, rust.rs:336-347).
-        Returns {bucket: (seconds, kernel launches)}."""
+        Returns {bucket: (seconds, kernel launches)}; when the step ran as one persistent kernel the
+        counts are phases of that kernel and "fused_step_kernel" holds (its duration, phases)."""
         ids = _i32(token_ids)
         p = N.PgOperationProfile()
         check(N.lib.pg_profile_forward_one(self._h, cache._h, _ip(ids), ids.size, C.byref(p)))
         names = ("layer_norm", "qkv_projection", "attention", "attention_projection", "mlp_fc_projection",
                  "mlp_projection", "final_logits", "other")
-        return {n: (getattr(p, n), int(p.launches[i])) for i, n in enumerate(names)}
+        out = {n: (getattr(p, n), int(p.launches[i])) for i, n in enumerate(names)}
+        if p.fused_phases:
+            out["fused_step_kernel"] = (p.fused_step_kernel, int(p.fused_phases))
+        return out
 
     def generate_batch(self, prompts: Sequence[Sequence[int]], config: TextGenerationConfig,
                        seeds: Optional[Sequence[int]] = None, cache: Optional[Gpt2KvCache] = None) -> List[List[int]]:
