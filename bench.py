@@ -343,7 +343,9 @@ def run_ours(args):
         # (profiles/tc_gemm_x3_kernel_m64_4096x1024.md, profiles/decode_attention_kernel_b64_h16_kv256.md)
         traffic = dom_bytes / max(dom_n, 1) * (1.035 if dom == "linears" else 1.004)
         if fused:
-            traffic = None  # no ncu capture of the persistent kernel yet
+            # ncu capture at 16 sequences: 1.823 GB read vs 1.825 GB algorithmic, writes 0.8 %
+            # (profiles/chain_kernel_medium_seqs16.md); both terms scale with the sequences
+            traffic = dom_bytes * 1.008
         step_bytes = model.weight_bytes_per_step() + kv_bytes_per_step(cfg, lens_mid)
         step_achieved = step_bytes / (sec_max / K) / 1e9
 

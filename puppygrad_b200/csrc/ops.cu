@@ -181,30 +181,11 @@ extern "C" int pg_op_linear(const float* x, const float* w, const float* bias, c
       }
       fprintf(stderr, "chain trace phase %d: work done %6llu..%6llu ns, barrier passed %6llu..%6llu ns\n", sl, wlo, whi, lo, hi);
     }
-    const char* cn[6] = {"split wait w_full", "split wait a_free", "mma wait a_ready", "mma wait act_full", "mma issue", "mma wait d_empty"};
+    const char* cn[6] = {"split wait w_full", "split wait tmem", "mma wait ready", "(unused)", "mma issue", "mma wait d_empty"};
     for (int sl = 0; sl < 6; ++sl) {
       double mean = 0;
       for (int i = 0; i < chain_ctas; ++i) mean += (double)t[(size_t)i * 32 + 20 + sl];
       fprintf(stderr, "chain trace %-18s mean %8.0f cycles per CTA\n", cn[sl], mean / chain_ctas);
-    }
-    {
-      const unsigned long long* q = &t[(size_t)chain_ctas * 32 + 400];
-      fprintf(stderr, "blk 40 fine: wait_ready %llu wait_act %llu fence %llu | mma", q[0], q[1], q[2]);
-      for (int z = 3; z <= 10; ++z) fprintf(stderr, " %llu", q[z]);
-      fprintf(stderr, " | commit %llu %llu\n", q[11], q[12]);
-    }
-    for (int b = 0; b < 0; ++b) {
-      const unsigned long long* q = &t[(size_t)chain_ctas * 32 + b * 4];
-      if (q[2]) fprintf(stderr, "blk %2d start %7llu wait_ready %5llu wait_act %5llu issue %5llu\n", b, q[2] - t[(size_t)chain_ctas * 32 + 2], q[0], q[1], q[3]);
-    }
-    {
-      double d1 = 0, d2 = 0, d3 = 0;
-      for (int i = 0; i < chain_ctas; ++i) {
-        const unsigned long long* q = &t[(size_t)i * 32];
-        d1 += (double)(long long)(q[27] - q[26]); d2 += (double)(long long)(q[29] - q[27]); d3 += (double)(long long)(q[28] - q[29]);
-      }
-      fprintf(stderr, "chain trace block 40 commit -> splitter saw a_free %.0f clk; -> a_ready arrive %.0f clk; -> mma saw a_ready %.0f clk\n",
-              d1 / chain_ctas, d2 / chain_ctas, d3 / chain_ctas);
     }
   } else if (want_trace && dtrace.p) {
     // tuning aid: phase timestamps of the last launch, relative to the earliest CTA start

@@ -254,6 +254,54 @@ def test_page_sizes_and_attention_splits(oracle, page_tokens, splits):
         assert_logits_close(g.forward_one(int(t), gc), o.forward_one(int(t), oc))
 
 
+@pytest.mark.parametrize("page_tokens", [16, 32, 64])
+def test_batched_tensor_core_step_is_one_persistent_kernel(oracle, monkeypatch, page_tokens):
+    """9..64 sequences in the tensor-core modes: the layers and the lm_head of a decode step run as
+    ONE persistent kernel (embedding, first LayerNorm, that kernel, arg-max, token feedback = five
+    launches). Checked against the oracle for every page size, for sequences of very different
+    lengths up to the last position of the context, and against the kernel-per-operation path."""
+    cfg = synthetic.preset("midi")
+    w = synthetic.perturbed_weights(cfg, 21)
+    o = oracle.Model(cfg, w, threads=4)
+    batch = 12
+    lens = [1, 2, 15, 16, 17, 31, 33, 64, 100, 200, cfg["n_positions"] - 4, cfg["n_positions"] - 3]
+    prompts = [synthetic.uniform_prompt(500 + i, n, cfg["vocab_size"]) for i, n in enumerate(lens)]
+
+    def run(no_chain):
+        if no_chain:
+            monkeypatch.setenv("PG_NO_CHAIN", "1")
+        else:
+            monkeypatch.delenv("PG_NO_CHAIN", raising=False)
+        g = pg.Gpt2Model(cfg, w, pg.Gpt2CudaConfig(math_mode="tf32x3", page_tokens=page_tokens))
+        cache = g.new_kv_cache(max_batch=batch)
+        _, cur = g.prefill_batch(prompts, cache)
+        out, launches = [], []
+        for _ in range(3):
+            n0 = cache.kernel_launches()
+            logits, am, _, _ = g.forward_one_batch(cur, cache, want_logits=True)
+            launches.append(cache.kernel_launches() - n0)
+            out.append(logits)
+            cur = am.copy()
+        return out, launches, cache, g
+
+    fused, fused_launches, cache, g = run(False)
+    assert fused_launches == [5, 5, 5]
+    split, split_launches, _, _ = run(True)
+    assert min(split_launches) > 5 * cfg["n_layer"]
+    ocaches = [o.new_kv_cache() for _ in prompts]
+    cur = [oracle.argmax_logits(o.prefill(p, c)) for p, c in zip(prompts, ocaches)]
+    for step in range(3):
+        ol = np.stack([o.forward_one(int(cur[i]), ocaches[i]) for i in range(batch)])
+        assert_logits_close(fused[step], ol)
+        assert_logits_close(split[step], ol)
+        cur = [oracle.argmax_logits(l) for l in ol]
+    # the keys and values the persistent kernel appended are the oracle's
+    k, v = cache.read_layer(cfg["n_layer"] - 1, slot=3)
+    ok_, ov_ = ocaches[3].read_layer(cfg["n_layer"] - 1)
+    np.testing.assert_allclose(k, ok_, rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(v, ov_, rtol=1e-4, atol=1e-5)
+
+
 def test_graphs_and_plain_launches_agree_bitwise(oracle):
     cfg = synthetic.preset("mini")
     w = synthetic.perturbed_weights(cfg, 13)
