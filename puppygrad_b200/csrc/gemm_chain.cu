@@ -45,15 +45,18 @@ constexpr int CH_MAX_SEG = 4;     // row tiles one CTA's share may touch
 constexpr int CH_WORKERS = 256;
 constexpr uint32_t CH_D_COLS = 128, CH_A_COL0 = 256, CH_TMEM_COLS = 512;
 // Attention phases stage key / value rows in the (then idle) activation ring plus an extra region:
-// each of the eight worker warps has AT_SLOTS slots of AT_ROWS rows x 64 floats.
+// each of the eight worker warps has AT_SLOTS slots, each holding AT_ROWS key rows and the AT_ROWS
+// value rows of the same positions (one mbarrier per slot: one wait per block of keys).
 constexpr int AT_ROWS = 16;
-constexpr int AT_SLOTS = 3;
-constexpr int AT_SLOT_BYTES = AT_ROWS * 64 * 4;
+constexpr int AT_SLOTS = 2;
+constexpr int AT_SLOT_BYTES = 2 * AT_ROWS * 64 * 4;
 constexpr int AT_EXTRA_BYTES = 8 * AT_SLOTS * AT_SLOT_BYTES - CH_X_STAGES * CH_ACT_BYTES;
 constexpr int AT_SCRATCH_FLOATS = 4 * 64;  // per group of four warps: one 64-float query per warp
 static_assert(AT_EXTRA_BYTES >= 0, "the activation ring is part of the attention staging area");
+// 227 KB, the most a CTA can have: the dynamic shared memory must start 1024-byte aligned (checked at run time)
 constexpr size_t CH_SMEM = (size_t)CH_W_STAGES * CH_W_BYTES + (size_t)CH_X_STAGES * CH_ACT_BYTES + AT_EXTRA_BYTES +
-                           2 * AT_SCRATCH_FLOATS * 4 + 1024 + 1024;
+                           2 * AT_SCRATCH_FLOATS * 4 + 1024;
+static_assert(CH_SMEM <= 232448, "shared memory of one CTA");
 constexpr size_t CH_PART_TILE = (size_t)CH_BN * TILE_M;  // floats of one partial tile: [token][row]
 
 // Share of one CTA in units: [g0, g1) of the phase's tiles * nkb units (row tile major); per = units per CTA.
@@ -200,16 +203,13 @@ __device__ __forceinline__ float warp_sum_f(float v) {
 
 // ROWS phase: x[j, :] += bias + sum of partials, then optional LayerNorm of the updated row written
 // as a TF32 hi/lo pair. One CTA per token; wt = worker thread 0..255; n % 4 == 0, n <= 4096.
-__device__ __forceinline__ void chain_rows_phase(const ChainArgs& a, const ChainPhase& ph, int j, int wt, float* red, int pidx) {
+__device__ __forceinline__ void chain_rows_phase(const ChainArgs& a, const ChainPhase& ph, int j, int wt, float* red) {
   const int n = ph.n, n4 = n >> 2;
   const ChRange r = chain_range(ph.n, ph.k, 0, (int)gridDim.x);
   const bool aligned = r.nkb % r.per == 0;
   const int cnt = r.nkb / r.per;
   float4 v[4];
   float s = 0.f;
-  const bool tr = a.trace && blockIdx.x == 0 && wt == 0 && pidx < 10;
-  unsigned long long* tq = a.trace + (size_t)gridDim.x * 32 + 256 + pidx * 8;
-  if (tr) tq[0] = clock64();
   float4* xrow = reinterpret_cast<float4*>(ph.x + (size_t)j * n);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -229,7 +229,6 @@ __device__ __forceinline__ void chain_rows_phase(const ChainArgs& a, const Chain
       s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
     }
   }
-  if (tr) tq[1] = clock64();
   if (!ph.ln_g) return;
   const int warp = wt >> 5, lane = wt & 31;
   s = warp_sum_f(s);
@@ -237,7 +236,6 @@ __device__ __forceinline__ void chain_rows_phase(const ChainArgs& a, const Chain
   workers_sync();
   const float mean = (((red[0] + red[1]) + (red[2] + red[3])) + ((red[4] + red[5]) + (red[6] + red[7]))) / (float)n;
   workers_sync();
-  if (tr) tq[2] = clock64();
   float q = 0.f;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -251,7 +249,6 @@ __device__ __forceinline__ void chain_rows_phase(const ChainArgs& a, const Chain
   workers_sync();
   const float var = (((red[0] + red[1]) + (red[2] + red[3])) + ((red[4] + red[5]) + (red[6] + red[7]))) / (float)n;
   const float inv_std = 1.0f / sqrtf(var + a.eps);
-  if (tr) tq[3] = clock64();
   float4* hi4 = reinterpret_cast<float4*>(ph.out_hi + (size_t)j * n);
   float4* lo4 = reinterpret_cast<float4*>(ph.out_lo + (size_t)j * n);
 #pragma unroll
@@ -272,7 +269,6 @@ __device__ __forceinline__ void chain_rows_phase(const ChainArgs& a, const Chain
       lo4[u] = make_float4(l[0], l[1], l[2], l[3]);
     }
   }
-  if (tr) tq[4] = clock64();
   workers_sync();  // `red` is reused by the next phase
 }
 
@@ -343,8 +339,8 @@ __device__ __forceinline__ void chain_elem_phase(const ChainArgs& a, const Chain
 // up to AT_SLOTS chunks ahead of their use, across pair boundaries. Scores use two lanes per key,
 // the weighted sum sixteen lanes per value row, with a running maximum (one pass over the cache).
 // The new token's own key and value are appended to the cache.
-struct AtCursor {  // where the warp is in issuing its chunk sequence; the same in every lane, except pg0 / pg1
-  int item, chunk, nchunk, t, b, h;
+struct AtCursor {  // where the warp is in issuing its block sequence; the same in every lane, except pg0 / pg1
+  int item, blk, nblk, t, b, h;
   int pg0, pg1;  // page table entries lane and lane + 32 of sequence b
   uint32_t issued;
 };
@@ -374,39 +370,42 @@ __device__ __forceinline__ void chain_attn_phase(const ChainArgs& a, const Chain
 
   AtCursor cur;
   cur.item = first - step;
-  cur.chunk = 0;
-  cur.nchunk = 0;
+  cur.blk = 0;
+  cur.nblk = 0;
   cur.issued = consumed;
   cur.t = cur.b = cur.h = cur.pg0 = cur.pg1 = 0;
   // executed by all lanes with identical control flow; only lane 0 starts copies
-  auto issue_upto = [&](uint32_t limit) {  // chunks with index < limit may be in flight
+  auto issue_upto = [&](uint32_t limit) {  // blocks with index < limit may be in flight
     while (cur.issued < limit) {
-      if (cur.chunk >= cur.nchunk) {
+      if (cur.blk >= cur.nblk) {
         cur.item += step;
         if (cur.item >= items) break;
-        cur.chunk = 0;
+        cur.blk = 0;
         cur.b = cur.item / H;
         cur.h = cur.item - cur.b * H;
         cur.t = __ldg(a.pos + cur.b);
-        cur.nchunk = 2 * ((cur.t + RB - 1) / RB);
+        cur.nblk = (cur.t + RB - 1) / RB;
         const int* table = a.page_table + (size_t)cur.b * pps;
         cur.pg0 = lane < pps ? __ldg(table + lane) : 0;
         cur.pg1 = lane + 32 < pps ? __ldg(table + lane + 32) : 0;
         continue;
       }
-      const int i = cur.chunk >> 1, which = cur.chunk & 1;
-      const int rows = min(RB, cur.t - i * RB);
-      const int p0 = i * RB;
+      const int rows = min(RB, cur.t - cur.blk * RB);
+      const int p0 = cur.blk * RB;
       const int pidx = p0 >> pt_shift, off = p0 & (pt - 1);
       const int page = __shfl_sync(0xffffffffu, pidx < 32 ? cur.pg0 : cur.pg1, pidx & 31);
       if (lane == 0) {
-        const float* src = ph.kv_pool + ((((size_t)page * 2 + which) * H + cur.h) * pt + off) * D;
+        const float* ksrc = ph.kv_pool + ((((size_t)page * 2 + 0) * H + cur.h) * pt + off) * D;
+        const float* vsrc = ksrc + (size_t)H * pt * D;
         const uint32_t slot = cur.issued % AT_SLOTS;
-        mbar_expect_tx(&kv_full[slot], (uint32_t)rows * D * 4);
-        bulk_load(stage + (size_t)slot * AT_SLOT_BYTES, src, (uint32_t)rows * D * 4, &kv_full[slot]);
+        const uint32_t bytes = (uint32_t)rows * D * 4;
+        uint8_t* dst = stage + (size_t)slot * AT_SLOT_BYTES;
+        mbar_expect_tx(&kv_full[slot], 2 * bytes);
+        bulk_load(dst, ksrc, bytes, &kv_full[slot]);
+        bulk_load(dst + AT_SLOT_BYTES / 2, vsrc, bytes, &kv_full[slot]);
       }
       ++cur.issued;
-      ++cur.chunk;
+      ++cur.blk;
     }
   };
   if (ok) issue_upto(consumed + AT_SLOTS);
@@ -440,12 +439,13 @@ __device__ __forceinline__ void chain_attn_phase(const ChainArgs& a, const Chain
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int i = 0; i < nblk; ++i) {
       const int rows = min(RB, t - i * RB);
-      const uint32_t ck = consumed, cv = consumed + 1;
+      const uint32_t slot = consumed % AT_SLOTS;
+      const uint8_t* blk = stage + (size_t)slot * AT_SLOT_BYTES;  // key rows, then value rows
       // ---- scores of this block's keys
-      if (ok) ok = warp_wait(&kv_full[ck % AT_SLOTS], (ck / AT_SLOTS) & 1, failed, a.error_flag, 31);
+      if (ok) ok = warp_wait(&kv_full[slot], (consumed / AT_SLOTS) & 1, failed, a.error_flag, 31);
       float s0 = 0.f, s1 = 0.f;
       if (ok && key < rows) {
-        const float4* kr = reinterpret_cast<const float4*>(stage + (size_t)(ck % AT_SLOTS) * AT_SLOT_BYTES) + key * 16 + half * 8;
+        const float4* kr = reinterpret_cast<const float4*>(blk) + key * 16 + half * 8;
 #pragma unroll
         for (int e = 0; e < 8; e += 2) {
           // rotate: the eight lanes of a quarter warp hit eight different bank groups
@@ -479,10 +479,8 @@ __device__ __forceinline__ void chain_attn_phase(const ChainArgs& a, const Chain
       }
       const float p = key < rows ? expf(s - m) : 0.f;
       l += half == 0 ? p : 0.f;
-      if (ok) issue_upto(consumed + 1 + AT_SLOTS);  // the K chunk's slot is free
       // ---- weighted values
-      if (ok) ok = warp_wait(&kv_full[cv % AT_SLOTS], (cv / AT_SLOTS) & 1, failed, a.error_flag, 32);
-      const float4* vr = reinterpret_cast<const float4*>(stage + (size_t)(cv % AT_SLOTS) * AT_SLOT_BYTES);
+      const float4* vr = reinterpret_cast<const float4*>(blk + AT_SLOT_BYTES / 2);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const int kk = kh * 8 + e;
@@ -495,9 +493,9 @@ __device__ __forceinline__ void chain_attn_phase(const ChainArgs& a, const Chain
           acc.w = fmaf(pk, v.w, acc.w);
         }
       }
-      consumed += 2;
+      consumed += 1;
       __syncwarp();
-      if (ok) issue_upto(consumed + AT_SLOTS);  // the V chunk's slot is free
+      if (ok) issue_upto(consumed + AT_SLOTS);  // this block's slot is free
     }
     // ---- the new token itself, then the two key halves and the lanes' partial sums
     const float m_fin = fmaxf(m, sn);
@@ -535,8 +533,12 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
                  const __grid_constant__ CUtensorMap map_lo0, const __grid_constant__ CUtensorMap map_hi1,
                  const __grid_constant__ CUtensorMap map_lo1, const __grid_constant__ CUtensorMap map_hi2,
                  const __grid_constant__ CUtensorMap map_lo2, const __grid_constant__ ChainArgs a) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* base = smem_raw;
+  if ((smem_u32(base) & 1023u) != 0) {  // swizzled TMA tiles need it; every thread takes the same way out
+    if (threadIdx.x == 0) atomicCAS(a.error_flag, 0, 35);
+    return;
+  }
   uint8_t* w_ring = base;
   uint8_t* act_ring = base + (size_t)CH_W_STAGES * CH_W_BYTES;
   // attention staging = the activation ring and the region after it; then the attention scratch
@@ -793,7 +795,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
       } else if (kind == CH_ATTN) {
         chain_attn_phase(a, phase_at(a, p), wt, act_ring, kv_full, at_scratch, at_consumed, failed, live);
       } else if (kind == CH_ROWS) {
-        if (live && cta < a.m) chain_rows_phase(a, phase_at(a, p), cta, wt, red, p);
+        if (live && cta < a.m) chain_rows_phase(a, phase_at(a, p), cta, wt, red);
       } else {
         if (live) chain_elem_phase(a, phase_at(a, p), wt);
       }

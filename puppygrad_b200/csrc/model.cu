@@ -281,14 +281,6 @@ struct pg_cache {
     if (d_chain_trace) {
       std::vector<unsigned long long> t((size_t)chain_ctas * 32 + 512);
       if (cudaMemcpy(t.data(), d_chain_trace, t.size() * 8, cudaMemcpyDeviceToHost) == cudaSuccess) {
-        {
-          const unsigned long long* tq = &t[(size_t)chain_ctas * 32 + 384];
-          fprintf(stderr, "attention phase (CTA 3 warp 0) cycles: total %llu, wait K %llu, wait V %llu, issue %llu\n", tq[0], tq[1], tq[2], tq[3]);
-        }
-        for (int pp = 0; pp < 8; ++pp) {
-          const unsigned long long* tq = &t[(size_t)chain_ctas * 32 + 256 + pp * 8];
-          if (tq[0]) fprintf(stderr, "rows phase %d (CTA 0) cycles: partial sums %llu, mean %llu, var %llu, write %llu\n", pp, tq[1] - tq[0], tq[2] - tq[1], tq[3] - tq[2], tq[4] - tq[3]);
-        }
         unsigned long long t0 = ~0ULL;
         for (int i = 0; i < chain_ctas; ++i) t0 = std::min(t0, t[(size_t)i * 32 + 31]);
         for (int sl = 0; sl < 10; ++sl) {
