@@ -359,8 +359,8 @@ def run_ours(args):
                                    f"greedy decode; step = one batched decode step ({B} tokens per GPU)",
                        "linears": ("fp32 weights and activations; products as 3xTF32 on tcgen05 tensor cores, "
                                    "FP32 accumulate" if args.math == "tf32x3" else "fp32 CUDA-core FMA"),
-                       "step_kernels": ("embedding, first LayerNorm, ONE persistent kernel for all layers and "
-                                        "the lm_head, arg-max, token feedback" if fused else "one kernel per operation"),
+                       "step_kernels": ("ONE persistent kernel per step: embedding, all layers, lm_head, arg-max, "
+                                        "token feedback" if fused else "one kernel per operation"),
                        "l2": "inputs larger than L2 (1.4 GB weights + KV per step)", "parallelism": f"replicas x{world}"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
             "gpu_launches": int(launches),

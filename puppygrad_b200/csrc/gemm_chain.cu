@@ -116,6 +116,14 @@ __device__ __forceinline__ bool chain_grid_barrier(unsigned* counter, unsigned t
 
 __device__ __forceinline__ float4 ldcg4(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
 
+// Row arg-max as one 64-bit maximum: high word = the float mapped to an unsigned that orders like the
+// float, low word = ~index, so the larger key is the larger value and, among equal values, the lower
+// index; the maximum over any order of updates is the first strict maximum of a sequential scan.
+__device__ __host__ inline unsigned long long argmax_key(unsigned int float_bits, unsigned int index) {
+  const unsigned int ord = (float_bits & 0x80000000u) ? ~float_bits : (float_bits | 0x80000000u);
+  return ((unsigned long long)ord << 32) | (unsigned long long)(0xffffffffu - index);
+}
+
 __device__ __forceinline__ void chain_trace(const ChainArgs& a, int slot) {
   if (a.trace) {
     unsigned long long t;
@@ -203,7 +211,7 @@ __device__ __forceinline__ float warp_sum_f(float v) {
 
 // ROWS phase: x[j, :] += bias + sum of partials, then optional LayerNorm of the updated row written
 // as a TF32 hi/lo pair. One CTA per token; wt = worker thread 0..255; n % 4 == 0, n <= 4096.
-__device__ __forceinline__ void chain_rows_phase(const ChainArgs& a, const ChainPhase& ph, int j, int wt, float* red) {
+__device__ __forceinline__ void chain_rows_phase(const ChainArgs& a, const ChainPhase& ph, int j, int wt, float* red, bool embed) {
   const int n = ph.n, n4 = n >> 2;
   const ChRange r = chain_range(ph.n, ph.k, 0, (int)gridDim.x);
   const bool aligned = r.nkb % r.per == 0;
@@ -215,7 +223,13 @@ __device__ __forceinline__ void chain_rows_phase(const ChainArgs& a, const Chain
   for (int i = 0; i < 4; ++i) {
     const int u = wt + i * CH_WORKERS;
     v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (u < n4) {
+    if (u < n4 && embed) {  // x = token embedding + position embedding
+      const float4 te = __ldg(reinterpret_cast<const float4*>(a.wte + (size_t)__ldg(a.ids + j) * n) + u);
+      const float4 pe = __ldg(reinterpret_cast<const float4*>(a.wpe + (size_t)__ldg(a.pos + j) * n) + u);
+      v[i] = make_float4(te.x + pe.x, te.y + pe.y, te.z + pe.z, te.w + pe.w);
+      xrow[u] = v[i];
+      s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    } else if (u < n4) {
       const float4 xv = __ldcg(xrow + u);
       float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
       if (ph.bias) b = __ldg(reinterpret_cast<const float4*>(ph.bias) + u);
@@ -273,7 +287,7 @@ __device__ __forceinline__ void chain_rows_phase(const ChainArgs& a, const Chain
 }
 
 // ELEM phase: out[j, f] = act(bias[f] + sum of partials), all CTAs, four features per thread.
-__device__ __forceinline__ void chain_elem_phase(const ChainArgs& a, const ChainPhase& ph, int wt) {
+__device__ __forceinline__ void chain_elem_phase(const ChainArgs& a, const ChainPhase& ph, int wt, unsigned long long* best_s) {
   const int n = ph.n, n4 = (n + 3) >> 2;
   const ChRange r = chain_range(ph.n, ph.k, 0, (int)gridDim.x);
   const int total = a.m * n4;
@@ -281,6 +295,12 @@ __device__ __forceinline__ void chain_elem_phase(const ChainArgs& a, const Chain
   const bool aligned = r.nkb % r.per == 0;
   const int cnt = r.nkb / r.per;
   const int stride = (int)gridDim.x * CH_WORKERS;
+  // row arg-max: shared-memory maxima per CTA first (a thread's consecutive units lie in different
+  // rows, so per-thread running maxima would mean one global atomic per unit)
+  if (ph.best) {
+    if (wt < CH_BN) best_s[wt] = 0ull;
+    workers_sync();
+  }
   for (int id0 = (int)blockIdx.x * CH_WORKERS + wt; id0 < total; id0 += 2 * stride) {
     // two units per pass: the second one's loads are in flight while the first is finished
     const int id1 = id0 + stride;
@@ -300,6 +320,14 @@ __device__ __forceinline__ void chain_elem_phase(const ChainArgs& a, const Chain
         if (ph.bias) y[e] = __ldg(ph.bias + f + e) + y[e];
         if (ph.gelu) y[e] = gelu_ref(y[e]);
       }
+    }
+    if (ph.best) {
+      unsigned long long key = 0ull;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (f + e < n && y[e] == y[e])  // NaN never wins; -0 counts as +0 (neither is greater than the other)
+          key = max(key, argmax_key(y[e] == 0.f ? 0u : __float_as_uint(y[e]), (unsigned)(f + e)));
+      if (key) atomicMax(best_s + j, key);
     }
     const size_t o = (size_t)j * n + f;
     if (vec) {
@@ -329,6 +357,23 @@ __device__ __forceinline__ void chain_elem_phase(const ChainArgs& a, const Chain
     }
     }
   }
+  if (ph.best) {
+    workers_sync();
+    if (wt < a.m && best_s[wt]) atomicMax(ph.best + wt, best_s[wt]);
+  }
+}
+
+// FINAL phase: end of a decode step for token j (finalize_kernel's work): the row arg-max the lm_head's
+// ELEM phase accumulated becomes the next input id, the position advances, the token is logged.
+__device__ __forceinline__ void chain_final_phase(const ChainArgs& a, int j) {
+  const unsigned long long key = __ldcg(a.best + j);
+  const int tok = (int)(0xffffffffu - (unsigned)(key & 0xffffffffull));
+  a.argmax_out[j] = tok;
+  a.ids[j] = tok;
+  const int np = a.pos_rw[j] + 1;
+  a.pos_rw[j] = np;
+  if (np < a.n_positions) a.token_log[(size_t)j * a.n_positions + np] = tok;
+  a.best[j] = argmax_key(0xff800000u, 0u);  // (-inf, index 0) for the next step
 }
 
 // ATTN phase: causal attention of one new token per sequence over the paged cache, head_dim 64.
@@ -394,15 +439,15 @@ __device__ __forceinline__ void chain_attn_phase(const ChainArgs& a, const Chain
       const int p0 = cur.blk * RB;
       const int pidx = p0 >> pt_shift, off = p0 & (pt - 1);
       const int page = __shfl_sync(0xffffffffu, pidx < 32 ? cur.pg0 : cur.pg1, pidx & 31);
-      if (lane == 0) {
-        const float* ksrc = ph.kv_pool + ((((size_t)page * 2 + 0) * H + cur.h) * pt + off) * D;
-        const float* vsrc = ksrc + (size_t)H * pt * D;
+      {
+        // lane 0 copies the key rows, lane 1 the value rows: both copies leave in one instruction
         const uint32_t slot = cur.issued % AT_SLOTS;
         const uint32_t bytes = (uint32_t)rows * D * 4;
-        uint8_t* dst = stage + (size_t)slot * AT_SLOT_BYTES;
-        mbar_expect_tx(&kv_full[slot], 2 * bytes);
-        bulk_load(dst, ksrc, bytes, &kv_full[slot]);
-        bulk_load(dst + AT_SLOT_BYTES / 2, vsrc, bytes, &kv_full[slot]);
+        const float* src = ph.kv_pool + ((((size_t)page * 2 + lane) * H + cur.h) * pt + off) * D;  // lane = 0: K, 1: V
+        uint8_t* dst = stage + (size_t)slot * AT_SLOT_BYTES + (size_t)lane * (AT_SLOT_BYTES / 2);
+        if (lane == 0) mbar_expect_tx(&kv_full[slot], 2 * bytes);
+        __syncwarp();
+        if (lane < 2) bulk_load(dst, src, bytes, &kv_full[slot]);
       }
       ++cur.issued;
       ++cur.blk;
@@ -794,10 +839,12 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
         }
       } else if (kind == CH_ATTN) {
         chain_attn_phase(a, phase_at(a, p), wt, act_ring, kv_full, at_scratch, at_consumed, failed, live);
-      } else if (kind == CH_ROWS) {
-        if (live && cta < a.m) chain_rows_phase(a, phase_at(a, p), cta, wt, red);
+      } else if (kind == CH_ROWS || kind == CH_EMBED) {
+        if (live && cta < a.m) chain_rows_phase(a, phase_at(a, p), cta, wt, red, kind == CH_EMBED);
+      } else if (kind == CH_FINAL) {
+        if (live && cta == 0 && wt < a.m) chain_final_phase(a, wt);
       } else {
-        if (live) chain_elem_phase(a, phase_at(a, p), wt);
+        if (live) chain_elem_phase(a, phase_at(a, p), wt, reinterpret_cast<unsigned long long*>(at_scratch));
       }
       if (wt == 0 && p < 10) chain_trace(a, 10 + p);
       if (p + 1 < a.n_phases) {
@@ -848,6 +895,8 @@ int chain_grid(int num_sms) {
 
 size_t chain_partial_floats(int grid) { return (size_t)grid * CH_MAX_SEG * CH_PART_TILE; }
 
+unsigned long long chain_argmax_init() { return argmax_key(0xff800000u, 0u); }
+
 bool chain_supported(const ChainArgs& a, int grid, const ChainPhase* host_phases) {
   const ChainPhase* phs = host_phases ? host_phases : a.ph;
   if (grid <= 0 || a.m < 1 || a.m > CH_BN || a.n_phases < 1) return false;
@@ -861,7 +910,17 @@ bool chain_supported(const ChainArgs& a, int grid, const ChainPhase* host_phases
       if (ph.n != 3 * a.kv.n_head * 64) return false;
       continue;
     }
+    if (ph.kind == CH_FINAL) {
+      if (!a.best || !a.argmax_out || !a.ids || !a.pos_rw || !a.token_log || a.n_positions < 1) return false;
+      if (p == 0 || phs[p - 1].kind != CH_ELEM || phs[p - 1].best != a.best) return false;
+      continue;
+    }
     if (ph.k < BK * CH_UB || ph.k % (BK * CH_UB) != 0 || ph.n < 1) return false;
+    if (ph.kind == CH_EMBED) {
+      if (ph.n % 4 != 0 || ph.n > 4 * 4 * CH_WORKERS || !ph.x || !ph.ln_g || !ph.ln_b || !ph.out_hi || !ph.out_lo) return false;
+      if (!a.wte || !a.wpe || !a.ids || !a.pos) return false;
+      continue;
+    }
     const ChRange r = chain_range(ph.n, ph.k, 0, grid);
     if ((r.per + r.nkb - 2) / r.nkb + 1 > CH_MAX_SEG) return false;
     if (ph.kind == CH_GEMM) {

@@ -136,7 +136,7 @@ cudaError_t launch_finalize(const FinalizeArgs& a, bool pdl, cudaStream_t s);
 // a residual update (+ LayerNorm, written as a TF32 hi/lo pair) or an element-wise epilogue (GELU,
 // hi/lo pair and/or plain FP32). Phases are separated by a bounded grid barrier that only the
 // worker warps take part in: the weight stream of later phases keeps running through it.
-enum ChainKind { CH_GEMM = 0, CH_ROWS = 1, CH_ELEM = 2, CH_ATTN = 3 };
+enum ChainKind { CH_GEMM = 0, CH_ROWS = 1, CH_ELEM = 2, CH_ATTN = 3, CH_EMBED = 4, CH_FINAL = 5 };
 enum ChainAct { CH_ACT_NORM = 0, CH_ACT_ATTN = 1, CH_ACT_H = 2 };
 struct ChainPhase {
   int kind;
@@ -152,6 +152,7 @@ struct ChainPhase {
   float* out_hi;      // ROWS: LayerNorm result, ELEM / ATTN: result, as a TF32 hi/lo pair (or nullptr)
   float* out_lo;
   float* kv_pool;     // ATTN: this layer's page pool (n, k, bias: those of the QKV GEMM right before it)
+  unsigned long long* best;  // ELEM: optional row arg-max accumulator [m] (packed value | index, see CH_FINAL)
 };
 constexpr int CHAIN_MAX_PHASES = 10;
 struct ChainArgs {
@@ -163,6 +164,17 @@ struct ChainArgs {
   KvLayout kv;
   const int* page_table;  // [max_batch, pages_per_seq]
   const int* pos;         // [m] position of the new token (= keys already cached)
+  // EMBED phase (x[j] = wte[ids[j]] + wpe[pos[j]], then the first LayerNorm as in a ROWS phase) and FINAL phase
+  // (end of a decode step, as FinalizeArgs: row arg-max from the accumulator the lm_head's ELEM phase filled,
+  // token fed back as the next id, position advanced, token logged; the accumulator is reset)
+  const float* wte;
+  const float* wpe;
+  int* ids;          // [m]
+  int* pos_rw;       // the same array as `pos`
+  int* argmax_out;   // [m]
+  int* token_log;    // [m][n_positions]
+  int n_positions;
+  unsigned long long* best;  // [m], holds chain_argmax_init() between launches
   int m;               // tokens (rows of every activation matrix), <= 64
   float eps;
   const float* arena;  // tiled weight arena (all matrices of the model)
@@ -180,6 +192,8 @@ struct ChainArgs {
 // Cooperative grid of the chain kernel on this device (0: not launchable) and the scratch it needs.
 int chain_grid(int num_sms);
 size_t chain_partial_floats(int grid);
+// Value of an empty row arg-max accumulator: (-inf, index 0), the start of argmax_logits (generation.rs:269-279).
+unsigned long long chain_argmax_init();
 // True when every phase fits the kernel's limits for a grid of `grid` CTAs. `host_phases` is the
 // host copy of the phase list (a.ph when nullptr).
 bool chain_supported(const ChainArgs& a, int grid, const ChainPhase* host_phases = nullptr);

@@ -241,6 +241,7 @@ struct pg_cache {
   // persistent chain kernel of the tensor-core decode path: partial tiles, grid-barrier word
   float* chain_partials = nullptr;
   unsigned* d_chain_barrier = nullptr;
+  unsigned long long* d_chain_best = nullptr;  // row arg-max accumulators of the lm_head phase
   unsigned long long* d_chain_trace = nullptr;  // PG_CHAIN_TRACE=1
   int chain_ctas = 0;
   struct ChainProgram {  // whole-step phase list of the persistent chain kernel for one batch size
@@ -303,7 +304,7 @@ struct pg_cache {
                     (void*)part_idx, (void*)attn_part, (void*)attn_counters, (void*)topk_vals, (void*)topk_idx,
                     (void*)px, (void*)pnorm, (void*)pqkv, (void*)pattn, (void*)ph, (void*)prow, (void*)norm_lo,
                     (void*)attn_lo, (void*)h_lo, (void*)d_error, (void*)d_mega_layers, (void*)d_barrier,
-                    (void*)chain_partials, (void*)d_chain_barrier, (void*)d_chain_trace})
+                    (void*)chain_partials, (void*)d_chain_barrier, (void*)d_chain_trace, (void*)d_chain_best})
       if (p) cudaFree(p);
     if (t0) cudaEventDestroy(t0);
     if (t1) cudaEventDestroy(t1);
@@ -373,6 +374,11 @@ static int cache_new(const pg_model* m, int max_batch, pg_cache** out) {
       PG_CUDA_TRY(cudaMalloc(&c->chain_partials, chain_partial_floats(c->chain_ctas) * sizeof(float)));
       PG_CUDA_TRY(cudaMalloc(&c->d_chain_barrier, sizeof(unsigned)));
       PG_CUDA_TRY(cudaMemsetAsync(c->d_chain_barrier, 0, sizeof(unsigned), c->stream));
+      {
+        const std::vector<unsigned long long> init(64, chain_argmax_init());
+        PG_CUDA_TRY(cudaMalloc(&c->d_chain_best, init.size() * sizeof(unsigned long long)));
+        PG_CUDA_TRY(cudaMemcpy(c->d_chain_best, init.data(), init.size() * sizeof(unsigned long long), cudaMemcpyHostToDevice));
+      }
       if (env_flag("PG_CHAIN_TRACE")) {
         PG_CUDA_TRY(cudaMalloc(&c->d_chain_trace, ((size_t)c->chain_ctas * 32 + 512) * sizeof(unsigned long long)));
         PG_CUDA_TRY(cudaMemsetAsync(c->d_chain_trace, 0, ((size_t)c->chain_ctas * 32 + 512) * sizeof(unsigned long long), c->stream));
@@ -482,6 +488,8 @@ static ChainArgs chain_base_args(const pg_cache* c, int batch) {
   base.partials = c->chain_partials; base.barrier = c->d_chain_barrier; base.error_flag = c->d_error;
   base.trace = c->d_chain_trace;
   base.kv = c->kv; base.page_table = c->d_table; base.pos = c->d_pos;
+  base.wte = m->wte; base.wpe = m->wpe; base.ids = c->d_ids; base.pos_rw = c->d_pos; base.argmax_out = c->d_argmax;
+  base.token_log = c->d_token_log; base.n_positions = m->positions(); base.best = c->d_chain_best;
   return base;
 }
 
@@ -517,6 +525,13 @@ static int ensure_chain_program(pg_cache* c, int batch) {
     ph.push_back(p);
     bucket.push_back(cur_b);  // belongs to the GEMM it finishes
   };
+  {
+    ChainPhase p{};  // token + position embedding and the first LayerNorm
+    p.kind = CH_EMBED; p.n = C; p.k = C; p.x = c->x; p.ln_g = m->layers[0].ln1_g; p.ln_b = m->layers[0].ln1_b;
+    p.out_hi = c->norm; p.out_lo = c->norm_lo;
+    ph.push_back(p);
+    bucket.push_back(B_LAYER_NORM);
+  }
   for (int l = 0; l < L; ++l) {
     const LayerWeights& w = m->layers[l];
     cur_b = B_QKV;
@@ -540,6 +555,13 @@ static int ensure_chain_program(pg_cache* c, int batch) {
   cur_b = B_LOGITS;
   gemm(m->t_wte, V, C, CH_ACT_NORM);
   elem(V, C, nullptr, 0, c->logits, nullptr, nullptr);
+  ph.back().best = c->d_chain_best;  // the reduce phase of the lm_head also finds the row arg-max
+  {
+    ChainPhase p{};
+    p.kind = CH_FINAL;
+    ph.push_back(p);
+    bucket.push_back(B_OTHER);
+  }
   ChainArgs a = chain_base_args(c, batch);
   a.n_phases = (int)ph.size();
   pg_cache::ChainProgram prog;
@@ -591,32 +613,25 @@ static cudaError_t enqueue_decode_step(pg_cache* c, int batch, int splits, cudaS
     if (e != cudaSuccess) return e;                                      \
     if (prof && (e = prof->mark(s, -1)) != cudaSuccess) return e;        \
   } while (0)
-  PG_E(launch_embed(m->wte, m->wpe, c->d_ids, c->d_pos, c->x, batch, C, pdl, s));
-  if (m->t_wte && batch > 8 && batch <= 64 && c->norm_lo) {
-    // tensor-core path: every linear is three TF32 products (hi*hi + hi*lo + lo*hi) accumulated
-    // in FP32; LayerNorm, attention and the GELU epilogue hand their results over as hi/lo pairs
+  {
     auto prog = c->chain_programs.find(batch);
-    if (prog != c->chain_programs.end() && prog->second.dev) {
-      // the whole step between the embedding and the argmax as one persistent cooperative kernel
+    if (m->t_wte && prog != c->chain_programs.end() && prog->second.dev) {
+      // the whole step, from the embedding to the token fed back, as one persistent cooperative kernel
       ChainArgs a = chain_base_args(c, batch);
       a.phases_dev = prog->second.dev;
       a.n_phases = prog->second.n;
       if (prof) a.phase_times = prog->second.d_times;  // per-phase time stamps for the operation profile
-      cur_bucket = B_LAYER_NORM;
-      PG_E(launch_layernorm_rows_split(c->x, m->layers[0].ln1_g, m->layers[0].ln1_b, eps, c->norm, c->norm_lo, batch, C, pdl, s));
       cur_bucket = B_OTHER;
       if (prof) prof->chain_event = (int)prof->ev.size();
       PG_E(launch_chain(a, c->chain_ctas, s));
-      cur_bucket = B_LOGITS;
-      PG_E(launch_argmax_rows(c->logits, batch, V, c->d_argmax, s));
-      cur_bucket = B_OTHER;
-      FinalizeArgs fx{};
-      fx.m = batch; fx.argmax_out = c->d_argmax; fx.next_ids = c->d_ids; fx.pos = c->d_pos;
-      fx.token_log = c->d_token_log; fx.n_positions = m->positions();
-      PG_E(launch_finalize(fx, false, s));
       if (launches) *launches = n;
       return cudaSuccess;
     }
+  }
+  PG_E(launch_embed(m->wte, m->wpe, c->d_ids, c->d_pos, c->x, batch, C, pdl, s));
+  if (m->t_wte && batch > 8 && batch <= 64 && c->norm_lo) {
+    // tensor-core path: every linear is three TF32 products (hi*hi + hi*lo + lo*hi) accumulated
+    // in FP32; LayerNorm, attention and the GELU epilogue hand their results over as hi/lo pairs
     auto x3 = [&](const float* w, const float* bias, const float* xhi, const float* xlo, float* out, float* ohi,
                   float* olo, int n_out, int k, int epi, const float* resid) -> cudaError_t {
       TcGemmArgs a{};

@@ -257,8 +257,7 @@ def test_page_sizes_and_attention_splits(oracle, page_tokens, splits):
 @pytest.mark.parametrize("page_tokens", [16, 32, 64])
 def test_batched_tensor_core_step_is_one_persistent_kernel(oracle, monkeypatch, page_tokens):
     """9..64 sequences in the tensor-core modes: the layers and the lm_head of a decode step run as
-    ONE persistent kernel (embedding, first LayerNorm, that kernel, arg-max, token feedback = five
-    launches). Checked against the oracle for every page size, for sequences of very different
+    ONE persistent kernel, from the embedding to the token fed back: one launch per step. Checked against the oracle for every page size, for sequences of very different
     lengths up to the last position of the context, and against the kernel-per-operation path."""
     cfg = synthetic.preset("midi")
     w = synthetic.perturbed_weights(cfg, 21)
@@ -285,7 +284,7 @@ def test_batched_tensor_core_step_is_one_persistent_kernel(oracle, monkeypatch, 
         return out, launches, cache, g
 
     fused, fused_launches, cache, g = run(False)
-    assert fused_launches == [5, 5, 5]
+    assert fused_launches == [1, 1, 1]
     split, split_launches, _, _ = run(True)
     assert min(split_launches) > 5 * cfg["n_layer"]
     ocaches = [o.new_kv_cache() for _ in prompts]
