@@ -57,6 +57,7 @@ static_assert(AT_EXTRA_BYTES >= 0, "the activation ring is part of the attention
 constexpr size_t CH_SMEM = (size_t)CH_W_STAGES * CH_W_BYTES + (size_t)CH_X_STAGES * CH_ACT_BYTES + AT_EXTRA_BYTES +
                            2 * AT_SCRATCH_FLOATS * 4 + 1024;
 static_assert(CH_SMEM <= 232448, "shared memory of one CTA");
+static_assert(CH_UB == 2, "one MMA issuer per k block of a unit");
 constexpr size_t CH_PART_TILE = (size_t)CH_BN * TILE_M;  // floats of one partial tile: [token][row]
 
 // Share of one CTA in units: [g0, g1) of the phase's tiles * nkb units (row tile major); per = units per CTA.
@@ -611,10 +612,10 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
     }
     for (int s = 0; s < CH_X_STAGES; ++s) {
       mbar_init(&ready[s], 5);  // four splitter warps + the activation producer's expect_tx arrival
-      mbar_init(&done[s], 1);
+      mbar_init(&done[s], 2);  // both MMA issuers commit
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&d_full[s], 1);
+      mbar_init(&d_full[s], 2);  // both MMA issuers commit ([0] is used; accumulators are not double-buffered)
       mbar_init(&d_empty[s], 8);
     }
     mbar_init(go, 1);
@@ -648,10 +649,15 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
         }
       }
     }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer
+  } else if (warp == 1 || warp == 3) {
+    // ---------------------------------------------------------------- MMA issuers
+    // Issuing one tcgen05.mma costs its thread ~60 clocks whatever the tile, so two threads share the
+    // work: the issuer of warp 1 takes k block 0 of every unit, the one of warp 3 k block 1, each
+    // into an accumulator of its own; the drain adds the two.
     if (lane == 0) {
+      const int b = warp == 1 ? 0 : 1;
       const uint32_t idesc1 = umma_idesc_tf32(TILE_M, CH_BN), idesc2 = umma_idesc_tf32(TILE_M, 2 * CH_BN);
+      const uint32_t dcol = tmem_base + (uint32_t)b * CH_D_COLS;
       uint32_t wi = 0, si = 0;
       bool ok = true;
       long long t_wait = 0, t_issue = 0, t_dempty = 0;
@@ -661,13 +667,11 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
         for (int g = r.g0; g < r.g1 && ok;) {
           const int tile = g / r.nkb;
           const int gend = min(r.g1, (tile + 1) * r.nkb);
-          const uint32_t buf = si & 1;
           long long c0 = clock64();
-          if (si >= 2) ok = mbar_wait(&d_empty[buf], ((si >> 1) - 1) & 1, failed, a.error_flag, 22);
+          if (si >= 1) ok = mbar_wait(d_empty, (si - 1) & 1, failed, a.error_flag, 22);  // the previous row tile is drained
           if (!ok) break;
           t_dempty += clock64() - c0;
           tc_fence_after();
-          const uint32_t dcol = tmem_base + buf * CH_D_COLS;
           for (int gb = g; gb < gend && ok; ++gb, ++wi) {
             const uint32_t xs = wi % CH_X_STAGES;
             c0 = clock64();
@@ -676,26 +680,23 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
             const long long c1 = clock64();
             t_wait += c1 - c0;
             tc_fence_after();
+            // block b of the unit: x_hi rows then x_lo rows in shared memory, w_hi | w_lo columns in tensor memory
+            const uint64_t dx = umma_desc_sw128(act_ring + (size_t)xs * CH_ACT_BYTES + (size_t)b * (CH_ACT_BYTES / CH_UB));
+            const uint32_t ahi = tmem_base + CH_A_COL0 + xs * (64 * CH_UB) + b * 64, alo = ahi + 32;
 #pragma unroll
-            for (int b = 0; b < CH_UB; ++b) {
-              // block b of the unit: x_hi rows then x_lo rows in shared memory, w_hi | w_lo columns in tensor memory
-              const uint64_t dx = umma_desc_sw128(act_ring + (size_t)xs * CH_ACT_BYTES + (size_t)b * (CH_ACT_BYTES / CH_UB));
-              const uint32_t ahi = tmem_base + CH_A_COL0 + xs * (64 * CH_UB) + b * 64, alo = ahi + 32;
-#pragma unroll
-              for (int k = 0; k < BK / 8; ++k) {
-                umma_tf32_ts(dcol, ahi + k * 8, dx + (uint64_t)(k * 2), idesc2, (gb != g || b != 0 || k != 0) ? 1u : 0u);
-                umma_tf32_ts(dcol, alo + k * 8, dx + (uint64_t)(k * 2), idesc1, 1u);
-              }
+            for (int k = 0; k < BK / 8; ++k) {
+              umma_tf32_ts(dcol, ahi + k * 8, dx + (uint64_t)(k * 2), idesc2, (gb != g || k != 0) ? 1u : 0u);
+              umma_tf32_ts(dcol, alo + k * 8, dx + (uint64_t)(k * 2), idesc1, 1u);
             }
             umma_commit(&done[xs]);
             t_issue += clock64() - c1;
           }
-          if (ok) umma_commit(&d_full[buf]);
+          if (ok) umma_commit(d_full);
           ++si;
           g = gend;
         }
       }
-      if (a.trace) {
+      if (a.trace && b == 0) {
         unsigned long long* t = a.trace + (size_t)blockIdx.x * 32;
         t[22] = (unsigned long long)t_wait;
         t[24] = (unsigned long long)t_issue;
@@ -815,24 +816,26 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
         for (int g = r.g0; g < r.g1; ++seg) {
           const int tile = g / r.nkb;
           const int gend = min(r.g1, (tile + 1) * r.nkb);
-          const uint32_t buf = si & 1;
-          if (ok) ok = warp_wait(&d_full[buf], (si >> 1) & 1, failed, a.error_flag, 29);
+          if (ok) ok = warp_wait(d_full, si & 1, failed, a.error_flag, 29);
           if (ok) {
             tc_fence_after();
             float* dst = a.partials + ((size_t)(cta * CH_MAX_SEG + seg) * CH_BN) * TILE_M + row;
 #pragma unroll
             for (int cc = 0; cc < 32; cc += 16) {
               const int c0 = half * 32 + cc;
-              float v[16], v2[16];
-              tmem_ld16(tmem_base + buf * CH_D_COLS + lane_addr + (uint32_t)c0, v);
-              tmem_ld16(tmem_base + buf * CH_D_COLS + lane_addr + (uint32_t)(CH_BN + c0), v2);
+              // two accumulators (k block 0 and 1 of every unit), each with hi*hi + lo*hi and hi*lo columns
+              float v[16], v2[16], u[16], u2[16];
+              tmem_ld16(tmem_base + lane_addr + (uint32_t)c0, v);
+              tmem_ld16(tmem_base + lane_addr + (uint32_t)(CH_BN + c0), v2);
+              tmem_ld16(tmem_base + CH_D_COLS + lane_addr + (uint32_t)c0, u);
+              tmem_ld16(tmem_base + CH_D_COLS + lane_addr + (uint32_t)(CH_BN + c0), u2);
 #pragma unroll
               for (int j = 0; j < 16; ++j)
-                if (c0 + j < a.m) dst[(size_t)(c0 + j) * TILE_M] = v[j] + v2[j];
+                if (c0 + j < a.m) dst[(size_t)(c0 + j) * TILE_M] = (v[j] + v2[j]) + (u[j] + u2[j]);
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&d_empty[buf]);
+            if (lane == 0) mbar_arrive(d_empty);
           }
           ++si;
           g = gend;
