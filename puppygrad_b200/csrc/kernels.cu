@@ -742,32 +742,40 @@ __global__ void decode_attention_generic_kernel(DecodeAttnArgs a) {
 
 // ------------------------------------------------------------------ prefill attention
 // causal_self_attention (src/models/gpt2/rust.rs:1580-1659) over concatenated sequences.
-// CTA = 32 queries of one (head, sequence); four threads per query, each owning 16 of 64 dims;
-// keys/values staged through shared memory in tiles of 32; online softmax per tile.
-constexpr int PA_Q = 32, PA_K = 32;
+// CTA = 128 queries of one (head, sequence). Four threads share a query's 64 dims (16 each) and
+// every such quad serves FOUR queries, so a key or value float4 read from shared memory feeds four
+// dot products: the kernel is bound by FMA issue, not by shared-memory bandwidth. Keys / values are
+// staged in tiles of 32 rows; softmax runs online in steps of 8 keys.
+constexpr int PA_Q = 128, PA_K = 32, PA_R = 4, PA_S = 8;
 template <int D>
-__global__ void __launch_bounds__(128) prefill_attention_kernel(PrefillAttnArgs a) {
+__global__ void __launch_bounds__(128, 2) prefill_attention_kernel(PrefillAttnArgs a) {
   static_assert(D == 64, "fast path is written for head_dim 64");
   __shared__ float4 Ks[PA_K][D / 4];
   __shared__ float4 Vs[PA_K][D / 4];
   const int h = blockIdx.x, qb = blockIdx.y, b = blockIdx.z;
-  const int tid = threadIdx.x, part = tid & 3, qi = tid >> 2;
+  const int tid = threadIdx.x, part = tid & 3, qd = tid >> 2;
   const int c = a.n_head * D;
   const int r0 = a.seq_start[b], len = a.seq_start[b + 1] - r0;
   const int q0 = qb * PA_Q;
   if (q0 >= len) return;
-  const int qpos = q0 + qi;
-  const bool qok = qpos < len;
-  float4 q[4];
+  int qpos[PA_R];
+  float4 q[PA_R][4], acc[PA_R][4];
+  float m[PA_R], l[PA_R];
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
-    q[i] = qok ? reinterpret_cast<const float4*>(a.qkv + (size_t)(r0 + qpos) * 3 * c + h * D)[i * 4 + part]
-               : make_float4(0, 0, 0, 0);
+  for (int r = 0; r < PA_R; ++r) {
+    qpos[r] = q0 + qd + 32 * r;  // the quad's queries are 32 apart: every warp sees a similar causal limit
+    const bool qok = qpos[r] < len;
+    if (!qok) qpos[r] = -1;  // no key position is <= -1: everything stays masked
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      q[r][i] = qok ? reinterpret_cast<const float4*>(a.qkv + (size_t)(r0 + qpos[r]) * 3 * c + h * D)[i * 4 + part]
+                    : make_float4(0, 0, 0, 0);
+      acc[r][i] = make_float4(0, 0, 0, 0);
+    }
+    m[r] = -INFINITY;
+    l[r] = 0.f;
+  }
   const float scale = 1.0f / sqrtf((float)D);
-  float m = -INFINITY, l = 0.f;
-  float4 acc[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) acc[i] = make_float4(0, 0, 0, 0);
 
   const int kend = min(len, q0 + PA_Q);  // keys needed by the last query of this CTA
   for (int kt = 0; kt < kend; kt += PA_K) {
@@ -785,49 +793,75 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(PrefillAttnArgs 
       Vs[j][d4] = vv;
     }
     __syncthreads();
-    float s[PA_K];
-    float tmax = -INFINITY;
+#pragma unroll 1
+    for (int sub = 0; sub < PA_K; sub += PA_S) {
+      if (kt + sub >= kend) break;
+      float s[PA_R][PA_S];
 #pragma unroll
-    for (int j = 0; j < PA_K; ++j) {
-      float d = 0.f;
+      for (int jj = 0; jj < PA_S; ++jj) {
+        const float4 k0 = Ks[sub + jj][part], k1 = Ks[sub + jj][4 + part], k2 = Ks[sub + jj][8 + part],
+                     k3 = Ks[sub + jj][12 + part];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) d = dot4(q[i], Ks[j][i * 4 + part], d);
-      d += __shfl_xor_sync(FULL, d, 1);
-      d += __shfl_xor_sync(FULL, d, 2);
-      d *= scale;
-      const bool ok = qok && (kt + j <= qpos);
-      s[j] = ok ? d : -INFINITY;
-      tmax = fmaxf(tmax, s[j]);
-    }
-    if (tmax == -INFINITY) continue;  // whole tile masked for this query (uniform within the quad)
-    const float mn = fmaxf(m, tmax);
-    const float corr = expf(m - mn);  // m = -inf on the first tile: expf(-inf) = 0
-    l *= corr;
+        for (int r = 0; r < PA_R; ++r) {
+          float d = dot4(q[r][0], k0, 0.f);
+          d = dot4(q[r][1], k1, d);
+          d = dot4(q[r][2], k2, d);
+          d = dot4(q[r][3], k3, d);
+          d += __shfl_xor_sync(FULL, d, 1);
+          d += __shfl_xor_sync(FULL, d, 2);
+          s[r][jj] = (kt + sub + jj <= qpos[r]) ? d * scale : -INFINITY;
+        }
+      }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      acc[i].x *= corr; acc[i].y *= corr; acc[i].z *= corr; acc[i].w *= corr;
-    }
+      for (int r = 0; r < PA_R; ++r) {
+        float tmax = s[r][0];
 #pragma unroll
-    for (int j = 0; j < PA_K; ++j) {
-      const float p = (s[j] == -INFINITY) ? 0.f : expf(s[j] - mn);
-      l += p;
+        for (int jj = 1; jj < PA_S; ++jj) tmax = fmaxf(tmax, s[r][jj]);
+        const float mn = fmaxf(m[r], tmax);
+        const float mref = (mn == -INFINITY) ? 0.f : mn;  // nothing unmasked yet: every term below is 0
+        const float corr = expf(m[r] - mref);             // m = -inf before the first unmasked key: 0
+        float ls = l[r] * corr;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float4 v = Vs[j][i * 4 + part];
-        acc[i].x = fmaf(p, v.x, acc[i].x);
-        acc[i].y = fmaf(p, v.y, acc[i].y);
-        acc[i].z = fmaf(p, v.z, acc[i].z);
-        acc[i].w = fmaf(p, v.w, acc[i].w);
+        for (int i = 0; i < 4; ++i) {
+          acc[r][i].x *= corr; acc[r][i].y *= corr; acc[r][i].z *= corr; acc[r][i].w *= corr;
+        }
+#pragma unroll
+        for (int jj = 0; jj < PA_S; ++jj) {
+          const float p = expf(s[r][jj] - mref);  // masked: expf(-inf) = 0
+          ls += p;
+          s[r][jj] = p;
+        }
+        l[r] = ls;
+        m[r] = mn;
+      }
+#pragma unroll
+      for (int jj = 0; jj < PA_S; ++jj) {
+        const float4 v0 = Vs[sub + jj][part], v1 = Vs[sub + jj][4 + part], v2 = Vs[sub + jj][8 + part],
+                     v3 = Vs[sub + jj][12 + part];
+#pragma unroll
+        for (int r = 0; r < PA_R; ++r) {
+          const float p = s[r][jj];
+          acc[r][0].x = fmaf(p, v0.x, acc[r][0].x); acc[r][0].y = fmaf(p, v0.y, acc[r][0].y);
+          acc[r][0].z = fmaf(p, v0.z, acc[r][0].z); acc[r][0].w = fmaf(p, v0.w, acc[r][0].w);
+          acc[r][1].x = fmaf(p, v1.x, acc[r][1].x); acc[r][1].y = fmaf(p, v1.y, acc[r][1].y);
+          acc[r][1].z = fmaf(p, v1.z, acc[r][1].z); acc[r][1].w = fmaf(p, v1.w, acc[r][1].w);
+          acc[r][2].x = fmaf(p, v2.x, acc[r][2].x); acc[r][2].y = fmaf(p, v2.y, acc[r][2].y);
+          acc[r][2].z = fmaf(p, v2.z, acc[r][2].z); acc[r][2].w = fmaf(p, v2.w, acc[r][2].w);
+          acc[r][3].x = fmaf(p, v3.x, acc[r][3].x); acc[r][3].y = fmaf(p, v3.y, acc[r][3].y);
+          acc[r][3].z = fmaf(p, v3.z, acc[r][3].z); acc[r][3].w = fmaf(p, v3.w, acc[r][3].w);
+        }
       }
     }
-    m = mn;
   }
-  if (qok) {
-    const float inv = 1.0f / l;
-    float4* o = reinterpret_cast<float4*>(a.out + (size_t)(r0 + qpos) * c + h * D);
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-      o[i * 4 + part] = make_float4(acc[i].x * inv, acc[i].y * inv, acc[i].z * inv, acc[i].w * inv);
+  for (int r = 0; r < PA_R; ++r) {
+    if (qpos[r] >= 0) {
+      const float inv = 1.0f / l[r];
+      float4* o = reinterpret_cast<float4*>(a.out + (size_t)(r0 + qpos[r]) * c + h * D);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        o[i * 4 + part] = make_float4(acc[r][i].x * inv, acc[r][i].y * inv, acc[r][i].z * inv, acc[r][i].w * inv);
+    }
   }
 }
 

@@ -547,3 +547,33 @@ def test_batched_sampling_with_per_sequence_seeds_matches_oracle(midi, oracle, k
             if s + 1 < new:
                 logits = o.forward_one(nxt, cache)
         assert got[i] == want, i
+
+
+def test_batched_sampling_on_the_persistent_step_kernel(oracle):
+    """configs of the XL run in small: temperature 0.8 / top-k 40 with a fixed seed per sequence, 12
+    sequences on the tensor-core path (device top-k after the persistent step kernel, host draw).
+    A draw that falls within rounding distance of a cumulative-probability boundary may legitimately
+    go the other way and changes the rest of that sequence, so one of the 12 may differ."""
+    cfg = synthetic.preset("midi")
+    w = synthetic.perturbed_weights(cfg, 31)
+    g = pg.Gpt2Model(cfg, w, pg.Gpt2CudaConfig(math_mode="tf32x3"))
+    o = oracle.Model(cfg, w, threads=4)
+    n, new = 12, 24
+    kw = dict(temperature=0.8, top_k=40)
+    prompts = [synthetic.uniform_prompt(2000 + i, 10 + 5 * i, cfg["vocab_size"]) for i in range(n)]
+    got = g.generate_batch(prompts, pg.TextGenerationConfig(new, seed=900, **kw))
+    differing = 0
+    for i, p in enumerate(prompts):
+        og = oracle.generation_config(new, seed=900 + i, **kw)
+        sampler = oracle.LogitsSampler(og.seed)
+        cache = o.new_kv_cache()
+        logits = o.prefill(p, cache)
+        hist, want = [int(t) for t in p], []
+        for s in range(new):
+            nxt = sampler.select_next_token(logits, hist, og)
+            hist.append(nxt)
+            want.append(nxt)
+            if s + 1 < new:
+                logits = o.forward_one(nxt, cache)
+        differing += got[i] != want
+    assert differing <= 1
