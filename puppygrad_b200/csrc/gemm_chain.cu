@@ -385,6 +385,7 @@ __device__ __forceinline__ void chain_final_phase(const ChainArgs& a, int j) {
 // up to AT_SLOTS chunks ahead of their use, across pair boundaries. Scores use two lanes per key,
 // the weighted sum sixteen lanes per value row, with a running maximum (one pass over the cache).
 // The new token's own key and value are appended to the cache.
+
 struct AtCursor {  // where the warp is in issuing its block sequence; the same in every lane, except pg0 / pg1
   int item, blk, nblk, t, b, h;
   int pg0, pg1;  // page table entries lane and lane + 32 of sequence b
@@ -399,9 +400,81 @@ __device__ __forceinline__ float4 attn_feature4(const ChainArgs& a, const ChainP
   return make_float4(b.x + acc.x, b.y + acc.y, b.z + acc.z, b.w + acc.w);
 }
 
+// q, k and v features [f, f + 4), [c + f, ...), [2c + f, ...) of token j. With at most four partial
+// tiles per feature (shares aligned to row tiles) all twelve loads and the three bias loads go out
+// before the first add: one L2 round trip instead of three.
+__device__ __forceinline__ void attn_qkv4(const ChainArgs& a, const ChainPhase& ph, const ChRange& r, int f, int c, int j,
+                                          float4& q, float4& k, float4& v) {
+  const int cnt = r.nkb / r.per;
+  if (r.nkb % r.per != 0 || cnt > 4) {
+    q = attn_feature4(a, ph, r, f, j);
+    k = attn_feature4(a, ph, r, c + f, j);
+    v = attn_feature4(a, ph, r, 2 * c + f, j);
+    return;
+  }
+  constexpr size_t STRIDE = (size_t)CH_MAX_SEG * CH_BN * TILE_M;
+  const float* base[3];
+  float4 part[3][4], bias[3];
+#pragma unroll
+  for (int w = 0; w < 3; ++w) {
+    const int ff = w * c + f;
+    const int tile = ff >> 7, row = ff & 127;
+    base[w] = a.partials + ((size_t)(tile * cnt) * CH_MAX_SEG * CH_BN + j) * TILE_M + row;
+    bias[w] = ph.bias ? __ldg(reinterpret_cast<const float4*>(ph.bias + ff)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int w = 0; w < 3; ++w)
+      part[w][i] = i < cnt ? ldcg4(base[w] + (size_t)i * STRIDE) : make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 out[3];
+#pragma unroll
+  for (int w = 0; w < 3; ++w) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (i < cnt) {
+        acc.x += part[w][i].x;
+        acc.y += part[w][i].y;
+        acc.z += part[w][i].z;
+        acc.w += part[w][i].w;
+      }
+    }
+    out[w] = make_float4(bias[w].x + acc.x, bias[w].y + acc.y, bias[w].z + acc.z, bias[w].w + acc.w);
+  }
+  q = out[0];
+  k = out[1];
+  v = out[2];
+}
+
+// Moves the issuing cursor of an attention warp to pair `item` (all lanes, identical control flow).
+__device__ __forceinline__ void at_cursor_load(const ChainArgs& a, AtCursor& cur, int item, int items, int lane) {
+  const int H = a.kv.n_head, pps = a.kv.pages_per_seq;
+  cur.item = item;
+  cur.blk = 0;
+  cur.nblk = 0;
+  if (item >= items) return;
+  cur.b = item / H;
+  cur.h = item - cur.b * H;
+  cur.t = __ldg(a.pos + cur.b);
+  cur.nblk = (cur.t + AT_ROWS - 1) / AT_ROWS;
+  const int* table = a.page_table + (size_t)cur.b * pps;
+  cur.pg0 = lane < pps ? __ldg(table + lane) : 0;
+  cur.pg1 = lane + 32 < pps ? __ldg(table + lane + 32) : 0;
+}
+
+// Called by the attention warps while they have nothing to do in the GEMM phase before an attention
+// phase: position and page table entries of the warp's first pair come in (two dependent global
+// loads), so that the attention phase starts with its first copies. (Asking L2 for the pair's first
+// key / value blocks here with cp.async.bulk.prefetch.L2 measured slower, twice, and is not done.)
+__device__ __forceinline__ void chain_attn_prepare(const ChainArgs& a, int w8, int lane, AtCursor& cur, uint32_t consumed) {
+  at_cursor_load(a, cur, (int)blockIdx.x * 8 + w8, a.m * a.kv.n_head, lane);
+  cur.issued = consumed;
+}
+
 __device__ __forceinline__ void chain_attn_phase(const ChainArgs& a, const ChainPhase& ph, int wt, uint8_t* stage_all,
-                                                 uint64_t* kv_full_all, float* scratch_all, uint32_t& consumed,
-                                                 volatile int* failed, bool live) {
+                                                 uint64_t* kv_full_all, float* scratch_all, uint32_t& consumed, AtCursor& cur,
+                                                 bool prepared, volatile int* failed, bool live) {
   constexpr int D = 64, RB = AT_ROWS;
   const int w8 = wt >> 5, lane = wt & 31;
   uint8_t* stage = stage_all + (size_t)w8 * AT_SLOTS * AT_SLOT_BYTES;
@@ -414,26 +487,17 @@ __device__ __forceinline__ void chain_attn_phase(const ChainArgs& a, const Chain
   const float scale = 0.125f;  // 1 / sqrt(64)
   bool ok = live;
 
-  AtCursor cur;
-  cur.item = first - step;
-  cur.blk = 0;
-  cur.nblk = 0;
-  cur.issued = consumed;
-  cur.t = cur.b = cur.h = cur.pg0 = cur.pg1 = 0;
+  if (!prepared) {
+    at_cursor_load(a, cur, first, items, lane);
+    cur.issued = consumed;
+  }
   // executed by all lanes with identical control flow; only lane 0 starts copies
   auto issue_upto = [&](uint32_t limit) {  // blocks with index < limit may be in flight
     while (cur.issued < limit) {
       if (cur.blk >= cur.nblk) {
-        cur.item += step;
         if (cur.item >= items) break;
-        cur.blk = 0;
-        cur.b = cur.item / H;
-        cur.h = cur.item - cur.b * H;
-        cur.t = __ldg(a.pos + cur.b);
-        cur.nblk = (cur.t + RB - 1) / RB;
-        const int* table = a.page_table + (size_t)cur.b * pps;
-        cur.pg0 = lane < pps ? __ldg(table + lane) : 0;
-        cur.pg1 = lane + 32 < pps ? __ldg(table + lane + 32) : 0;
+        at_cursor_load(a, cur, cur.item + step, items, lane);
+        if (cur.item >= items) break;
         continue;
       }
       const int rows = min(RB, cur.t - cur.blk * RB);
@@ -464,20 +528,13 @@ __device__ __forceinline__ void chain_attn_phase(const ChainArgs& a, const Chain
     const int nblk = (t + RB - 1) / RB;
     // q, k, v of the new token: lanes 0-15 each own four of the head's 64 features
     float sn = 0.f;
-    float4 vn = make_float4(0.f, 0.f, 0.f, 0.f);
-    {
-      const int f = h * D + (lane & 15) * 4;
-      const int page = __ldg(a.page_table + (size_t)b * pps + (t >> pt_shift)), off = t & (pt - 1);
-      if (lane < 16) {
-        const float4 qv = attn_feature4(a, ph, r, f, b);
-        const float4 kv = attn_feature4(a, ph, r, C + f, b);
-        vn = attn_feature4(a, ph, r, 2 * C + f, b);
-        qs[lane] = qv;
-        sn = fmaf(qv.x, kv.x, fmaf(qv.y, kv.y, fmaf(qv.z, kv.z, qv.w * kv.w)));
-        // append the new K and V rows
-        reinterpret_cast<float4*>(ph.kv_pool + ((((size_t)page * 2 + 0) * H + h) * pt + off) * D)[lane] = kv;
-        reinterpret_cast<float4*>(ph.kv_pool + ((((size_t)page * 2 + 1) * H + h) * pt + off) * D)[lane] = vn;
-      }
+    float4 vn = make_float4(0.f, 0.f, 0.f, 0.f), kn = vn;
+    const int app_page = __ldg(a.page_table + (size_t)b * pps + (t >> pt_shift));  // used after the walk
+    if (lane < 16) {
+      float4 qv;
+      attn_qkv4(a, ph, r, h * D + lane * 4, C, b, qv, kn, vn);
+      qs[lane] = qv;
+      sn = fmaf(qv.x, kn.x, fmaf(qv.y, kn.y, fmaf(qv.z, kn.z, qv.w * kn.w)));
     }
     sn = warp_sum_f(sn) * scale;
     __syncwarp();
@@ -569,6 +626,11 @@ __device__ __forceinline__ void chain_attn_phase(const ChainArgs& a, const Chain
       const size_t idx = (size_t)b * C + h * D + lane * 4;
       *reinterpret_cast<float4*>(ph.out_hi + idx) = make_float4(hi[0], hi[1], hi[2], hi[3]);
       *reinterpret_cast<float4*>(ph.out_lo + idx) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+    }
+    if (lane < 16) {  // append the new K and V rows
+      const int off = t & (pt - 1);
+      reinterpret_cast<float4*>(ph.kv_pool + ((((size_t)app_page * 2 + 0) * H + h) * pt + off) * D)[lane] = kn;
+      reinterpret_cast<float4*>(ph.kv_pool + ((((size_t)app_page * 2 + 1) * H + h) * pt + off) * D)[lane] = vn;
     }
     __syncwarp();  // qs is rewritten by the next pair
   }
@@ -806,11 +868,19 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
       a.phase_times[0] = t;
     }
-    uint32_t at_consumed = 0;  // key / value chunks this warp has used so far (all attention phases)
+    uint32_t at_consumed = 0;  // key / value blocks this warp has used so far (all attention phases)
+    AtCursor at_cur;
+    bool at_prepared = false;
+    at_cur.item = at_cur.blk = at_cur.nblk = at_cur.t = at_cur.b = at_cur.h = at_cur.pg0 = at_cur.pg1 = 0;
+    at_cur.issued = 0;
     for (int p = 0; p < a.n_phases; ++p) {
       const int kind = phase_at(a, p).kind;
       if (kind == CH_GEMM) {
         if (wt == 0) mbar_arrive(go);  // inputs of this phase exist (previous kernel, or the barrier just passed)
+        if (live && p + 1 < a.n_phases && phase_at(a, p + 1).kind == CH_ATTN) {
+          chain_attn_prepare(a, ww, lane, at_cur, at_consumed);
+          at_prepared = true;
+        }
         const ChRange r = chain_range(phase_at(a, p).n, phase_at(a, p).k, cta, grid);
         int seg = 0;
         for (int g = r.g0; g < r.g1; ++seg) {
@@ -841,7 +911,8 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
           g = gend;
         }
       } else if (kind == CH_ATTN) {
-        chain_attn_phase(a, phase_at(a, p), wt, act_ring, kv_full, at_scratch, at_consumed, failed, live);
+        chain_attn_phase(a, phase_at(a, p), wt, act_ring, kv_full, at_scratch, at_consumed, at_cur, at_prepared, failed, live);
+        at_prepared = false;
       } else if (kind == CH_ROWS || kind == CH_EMBED) {
         if (live && cta < a.m) chain_rows_phase(a, phase_at(a, p), cta, wt, red, kind == CH_EMBED);
       } else if (kind == CH_FINAL) {
