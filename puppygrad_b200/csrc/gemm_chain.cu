@@ -146,10 +146,23 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* src, uint3
 
 // Sum of the partial tiles covering features [f, f + 4) of token j, in k order. Loads go out in
 // batches of NB before the first add, so that their L2 latencies overlap.
+// x / d for the small non-negative operands of the share arithmetic (x * d < 2^32): one multiply-high.
+struct FastDiv {
+  unsigned magic, d;
+};
+__device__ __forceinline__ FastDiv fast_div(int d) {
+  FastDiv f;
+  f.d = (unsigned)d;
+  f.magic = d > 1 ? (unsigned)((0x100000000ull + (unsigned)d - 1) / (unsigned)d) : 0u;
+  return f;
+}
+__device__ __forceinline__ int div_by(int x, FastDiv f) { return f.d > 1 ? (int)__umulhi((unsigned)x, f.magic) : x; }
+
 template <int NB>
-__device__ __forceinline__ float4 sum_partials(const float* partials, int f, int j, int nkb, int per) {
+__device__ __forceinline__ float4 sum_partials(const float* partials, int f, int j, int nkb, FastDiv by_per, FastDiv by_nkb) {
+  const int per = (int)by_per.d;
   const int tile = f >> 7, row = f & 127;
-  const int c_lo = (tile * nkb) / per, c_hi = ((tile + 1) * nkb - 1) / per;
+  const int c_lo = div_by(tile * nkb, by_per), c_hi = div_by((tile + 1) * nkb - 1, by_per);
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int c0 = c_lo; c0 <= c_hi; c0 += NB) {
     float4 v[NB];
@@ -158,7 +171,7 @@ __device__ __forceinline__ float4 sum_partials(const float* partials, int f, int
       const int c = c0 + i;
       v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (c <= c_hi) {
-        const int seg = tile - (c * per) / nkb;
+        const int seg = tile - div_by(c * per, by_nkb);
         v[i] = ldcg4(partials + ((size_t)(c * CH_MAX_SEG + seg) * CH_BN + j) * TILE_M + row);
       }
     }
@@ -235,7 +248,7 @@ __device__ __forceinline__ void chain_rows_phase(const ChainArgs& a, const Chain
       float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
       if (ph.bias) b = __ldg(reinterpret_cast<const float4*>(ph.bias) + u);
       const float4 acc = aligned ? sum_partials_aligned<16>(a.partials, u * 4, j, cnt)
-                                 : sum_partials<16>(a.partials, u * 4, j, r.nkb, r.per);
+                                 : sum_partials<16>(a.partials, u * 4, j, r.nkb, fast_div(r.per), fast_div(r.nkb));
       v[i].x = xv.x + (b.x + acc.x);
       v[i].y = xv.y + (b.y + acc.y);
       v[i].z = xv.z + (b.z + acc.z);
@@ -295,23 +308,39 @@ __device__ __forceinline__ void chain_elem_phase(const ChainArgs& a, const Chain
   const bool vec = (n & 3) == 0;
   const bool aligned = r.nkb % r.per == 0;
   const int cnt = r.nkb / r.per;
-  const int stride = (int)gridDim.x * CH_WORKERS;
-  // row arg-max: shared-memory maxima per CTA first (a thread's consecutive units lie in different
-  // rows, so per-thread running maxima would mean one global atomic per unit)
+  const FastDiv by_per = fast_div(r.per), by_nkb = fast_div(r.nkb);
+  // Every CTA takes one contiguous run of (token, four features) units, its threads interleaved over
+  // it: a thread's units then lie in one row, rarely two, so the row arg-max is a running maximum
+  // per thread that goes to shared memory only when the row changes.
+  const int chunk = (total + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int begin = (int)blockIdx.x * chunk, end = min(begin + chunk, total);
+  int best_row = -1;
+  unsigned long long best_key = 0ull;
   if (ph.best) {
     if (wt < CH_BN) best_s[wt] = 0ull;
     workers_sync();
   }
-  for (int id0 = (int)blockIdx.x * CH_WORKERS + wt; id0 < total; id0 += 2 * stride) {
+  // (row, unit in row) of this thread's next unit, advanced without divisions
+  int j0 = begin / n4, u0 = begin - j0 * n4 + wt;
+  while (u0 >= n4) {
+    u0 -= n4;
+    ++j0;
+  }
+  for (int id0 = begin + wt; id0 < end; id0 += 2 * CH_WORKERS) {
     // two units per pass: the second one's loads are in flight while the first is finished
-    const int id1 = id0 + stride;
-    const int j0 = id0 / n4, f0 = (id0 - j0 * n4) * 4;
-    const int j1 = id1 < total ? id1 / n4 : j0, f1 = id1 < total ? (id1 - j1 * n4) * 4 : f0;
-    const float4 acc0 = aligned ? sum_partials_aligned<8>(a.partials, f0, j0, cnt) : sum_partials<8>(a.partials, f0, j0, r.nkb, r.per);
-    const float4 acc1 = aligned ? sum_partials_aligned<8>(a.partials, f1, j1, cnt) : sum_partials<8>(a.partials, f1, j1, r.nkb, r.per);
+    const int id1 = id0 + CH_WORKERS;
+    int j1 = j0, u1 = u0 + CH_WORKERS;
+    while (u1 >= n4) {
+      u1 -= n4;
+      ++j1;
+    }
+    const int f0 = u0 * 4, f1 = id1 < end ? u1 * 4 : f0;
+    if (id1 >= end) j1 = j0;
+    const float4 acc0 = aligned ? sum_partials_aligned<8>(a.partials, f0, j0, cnt) : sum_partials<8>(a.partials, f0, j0, r.nkb, by_per, by_nkb);
+    const float4 acc1 = aligned ? sum_partials_aligned<8>(a.partials, f1, j1, cnt) : sum_partials<8>(a.partials, f1, j1, r.nkb, by_per, by_nkb);
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-    if (half == 1 && id1 >= total) break;
+    if (half == 1 && id1 >= end) break;
     const int j = half ? j1 : j0, f = half ? f1 : f0;
     const float4 acc = half ? acc1 : acc0;
     float y[4] = {acc.x, acc.y, acc.z, acc.w};
@@ -323,12 +352,15 @@ __device__ __forceinline__ void chain_elem_phase(const ChainArgs& a, const Chain
       }
     }
     if (ph.best) {
-      unsigned long long key = 0ull;
+      if (j != best_row) {
+        if (best_row >= 0 && best_key) atomicMax(best_s + best_row, best_key);
+        best_row = j;
+        best_key = 0ull;
+      }
 #pragma unroll
       for (int e = 0; e < 4; ++e)
         if (f + e < n && y[e] == y[e])  // NaN never wins; -0 counts as +0 (neither is greater than the other)
-          key = max(key, argmax_key(y[e] == 0.f ? 0u : __float_as_uint(y[e]), (unsigned)(f + e)));
-      if (key) atomicMax(best_s + j, key);
+          best_key = max(best_key, argmax_key(y[e] == 0.f ? 0u : __float_as_uint(y[e]), (unsigned)(f + e)));
     }
     const size_t o = (size_t)j * n + f;
     if (vec) {
@@ -357,8 +389,14 @@ __device__ __forceinline__ void chain_elem_phase(const ChainArgs& a, const Chain
       }
     }
     }
+    u0 += 2 * CH_WORKERS;
+    while (u0 >= n4) {
+      u0 -= n4;
+      ++j0;
+    }
   }
   if (ph.best) {
+    if (best_row >= 0 && best_key) atomicMax(best_s + best_row, best_key);
     workers_sync();
     if (wt < a.m && best_s[wt]) atomicMax(ph.best + wt, best_s[wt]);
   }
@@ -394,7 +432,7 @@ struct AtCursor {  // where the warp is in issuing its block sequence; the same 
 
 __device__ __forceinline__ float4 attn_feature4(const ChainArgs& a, const ChainPhase& ph, const ChRange& r, int f, int j) {
   const float4 acc = (r.nkb % r.per == 0) ? sum_partials_aligned<8>(a.partials, f, j, r.nkb / r.per)
-                                          : sum_partials<8>(a.partials, f, j, r.nkb, r.per);
+                                          : sum_partials<8>(a.partials, f, j, r.nkb, fast_div(r.per), fast_div(r.nkb));
   float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
   if (ph.bias) b = __ldg(reinterpret_cast<const float4*>(ph.bias + f));
   return make_float4(b.x + acc.x, b.y + acc.y, b.z + acc.z, b.w + acc.w);

@@ -1279,8 +1279,10 @@ int pg_profile_forward_one(const pg_model* model, pg_cache* cache, const int32_t
       std::vector<unsigned long long> ts((size_t)it->second.n + 1);
       PG_CUDA_TRY(cudaMemcpy(ts.data(), it->second.d_times, ts.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
       double covered = 0.0;
+      const bool dump = env_flag("PG_PHASE_DUMP");  // tuning aid: every phase's duration
       for (int p = 0; p < it->second.n; ++p) {
         const double d = (double)(ts[p + 1] - ts[p]) * 1e-9;
+        if (dump) fprintf(stderr, "phase %3d bucket %d %8.2f us\n", p, it->second.bucket[p], d * 1e6);
         sec[it->second.bucket[p]] += d;
         cnt[it->second.bucket[p]] += 1;
         covered += d;
