@@ -1,27 +1,30 @@
-// A chain of dependent decode linears as one persistent cooperative kernel for sm_100a.
+// The batched decode step as one persistent cooperative kernel for sm_100a.
 //
-// The decode step of a transformer block is four small GEMMs (m <= 64 tokens) that depend on each
-// other through row-wise operations (bias, residual, LayerNorm, GELU). Launched one by one, each
-// pays its launch, its pipeline fill and its epilogue, which together cost several times the
-// streaming time of its weights. Here one CTA per SM stays resident for the whole chain:
+// One decode step of a transformer for m <= 64 tokens is a chain of small operations that depend
+// on each other through row-wise work (bias, residual, LayerNorm, GELU, attention). Launched one
+// by one, each pays its launch, its pipeline fill and its epilogue, which together cost several
+// times the streaming time of its weights. Here one CTA per SM stays resident for a whole list of
+// phases (GEMM, ROWS, ELEM, ATTN, EMBED, FINAL; see kernels.cuh), separated by grid barriers:
 //
-//   warp 0      weight producer: TMA loads of 16 KB weight blocks into a ring of shared-memory
-//               stages. Weights do not depend on activations, so this warp never waits for a phase
-//               to begin: while the other warps reduce, normalise or wait at the grid barrier it
-//               already fetches the next GEMM's blocks.
+//   warp 0      weight producer: TMA loads of 32 KB weight units (two 128 x 32 blocks of the tiled
+//               weight copy) into a ring of shared-memory stages. Weights do not depend on
+//               activations, so this warp never waits for a phase to begin: while the other warps
+//               reduce, normalise, attend or wait at the grid barrier it already fetches the next
+//               GEMM's units.
 //   warps 4-7   splitters: FP32 weight tile -> TF32 hi/lo pair in tensor memory (tcgen05.st); they
 //               run ahead as far as tensor memory stages are free.
 //   warp 2      activation producer: after the phase's inputs exist (grid barrier), TMA loads of
 //               the 64-token x 32 hi and lo tiles.
-//   warp 1      MMA issuer: per 8-wide k slice one tcgen05.mma of N = 128 (w_hi . [x_hi | x_lo])
-//               and one of N = 64 (w_lo . x_hi), accumulators in tensor memory, two accumulator
-//               buffers so that a finished row tile drains while the next one accumulates.
-//   warps 8-15  workers: drain accumulators into per-CTA partial tiles (global memory, L2
-//               resident), take part in the grid barrier, and run the reduce phases.
+//   warps 1, 3  MMA issuers, one per k block of a unit, an accumulator in tensor memory each: per
+//               8-wide k slice one tcgen05.mma of N = 128 (w_hi . [x_hi | x_lo]) and one of N = 64
+//               (w_lo . x_hi).
+//   warps 8-15  workers: drain the accumulators into per-CTA partial tiles (global memory, L2
+//               resident), take part in the grid barrier, run the reduce phases, the attention
+//               phases (one warp per sequence-head pair), the embedding and the end-of-step phase.
 //
-// Every GEMM's blocks (row tile major, k block minor) are cut into equal contiguous shares, one
-// per CTA, so all SMs stream the same number of bytes whatever the matrix shape. Partials are
-// added in k order by the following phase: results do not depend on scheduling.
+// Every GEMM's units (row tile major, k minor) are cut into equal contiguous shares, one per CTA,
+// so all SMs stream the same number of bytes whatever the matrix shape. Partials are added in k
+// order by the following phase: results do not depend on scheduling.
 //
 // Every wait is bounded. On expiry the CTA raises the error word; every role then falls through
 // its remaining loops without touching memory, tensor memory is freed and the kernel ends.
