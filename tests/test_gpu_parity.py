@@ -577,3 +577,30 @@ def test_batched_sampling_on_the_persistent_step_kernel(oracle):
                 logits = o.forward_one(nxt, cache)
         differing += got[i] != want
     assert differing <= 1
+
+
+def test_persistent_step_when_shares_straddle_row_tiles(oracle):
+    """A width whose GEMMs do not divide evenly over the SMs (17 units of 64 per 1088-wide row, as
+    25 for GPT-2 XL's 1600): every CTA's share of the QKV, both projections, the MLP and the lm_head
+    then crosses row-tile boundaries, the reduce and attention phases add a varying number of
+    partial tiles per output, and rows need two float4 per worker thread."""
+    cfg = dict(vocab_size=2003, n_positions=96, n_embd=1088, n_layer=2, n_head=17, n_inner=4352,
+               layer_norm_epsilon=1e-5)
+    w = synthetic.perturbed_weights(cfg, 41)
+    g = pg.Gpt2Model(cfg, w, pg.Gpt2CudaConfig(math_mode="tf32x3"))
+    o = oracle.Model(cfg, w, threads=8)
+    batch = 10
+    prompts = [synthetic.uniform_prompt(700 + i, 1 + 9 * i, cfg["vocab_size"]) for i in range(batch)]
+    cache = g.new_kv_cache(max_batch=batch)
+    _, cur = g.prefill_batch(prompts, cache)
+    ocaches = [o.new_kv_cache() for _ in prompts]
+    ocur = [oracle.argmax_logits(o.prefill(p, c)) for p, c in zip(prompts, ocaches)]
+    assert list(cur) == ocur
+    for _ in range(3):
+        n0 = cache.kernel_launches()
+        logits, am, _, _ = g.forward_one_batch(cur, cache, want_logits=True)
+        assert cache.kernel_launches() - n0 == 1
+        ol = np.stack([o.forward_one(int(cur[i]), ocaches[i]) for i in range(batch)])
+        assert_logits_close(logits, ol)
+        assert list(am) == [oracle.argmax_logits(l) for l in ol]
+        cur = am.copy()
