@@ -196,6 +196,33 @@ def small_batch1(pg, synthetic, device):
             "bytes_per_token": step_bytes, "hbm_frac": step_bytes / (best / 60) / 1e9 / peak}
 
 
+def xl_sampling(pg, synthetic, device, seqs=32, prompt_len=512, steps=48):
+    """GPT-2 XL with temperature 0.8 / top-k 40 sampling and one RNG seed per sequence (BASELINE
+    configs[3], one GPU's share of it: 256 sequences over 8 GPUs = 32 per GPU, 512-token prompts).
+    Every step runs the persistent step kernel, the device top-k, and the host draw of the reference
+    sampler; timed on the host clock through the public API (token ids in, top-k rows out)."""
+    from puppygrad_b200.generation import LogitsSampler
+    cfg = synthetic.preset("xl")
+    model = pg.Gpt2Model(cfg, synthetic.random_init_weights(cfg, 0), pg.Gpt2CudaConfig(device=device, math_mode="tf32x3"))
+    cache = model.new_kv_cache(max_batch=seqs)
+    prompts = [synthetic.uniform_prompt(5000 + i, prompt_len, cfg["vocab_size"]) for i in range(seqs)]
+    conf = pg.TextGenerationConfig(steps, temperature=0.8, top_k=40, seed=1234)
+    samplers = [LogitsSampler(conf.seed + i) for i in range(seqs)]
+    t0 = time.perf_counter()
+    _, cur = model.prefill_batch(prompts, cache)
+    prefill_s = time.perf_counter() - t0
+    _, _, tv, ti = model.forward_one_batch(cur, cache, top_k=40)  # warm-up step: graph capture
+    launches0 = cache.kernel_launches()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        nxt = [samplers[i].select_from_topk(tv[i], ti[i], conf) for i in range(seqs)]
+        _, _, tv, ti = model.forward_one_batch(nxt, cache, top_k=40)
+    sec = time.perf_counter() - t0
+    return {"tokens_per_s": seqs * steps / sec, "ms_per_step": sec / steps * 1e3, "seqs": seqs, "prompt_len": prompt_len,
+            "steps": steps, "prefill_s": prefill_s, "kernel_launches_per_step": (cache.kernel_launches() - launches0) / steps,
+            "bytes_per_step": model.weight_bytes_per_step() + kv_bytes_per_step(cfg, [prompt_len + steps // 2] * seqs)}
+
+
 def prefill_small(pg, synthetic, device):
     """GPT-2 small prefill, 8 prompts of 1024 tokens (BASELINE configs[1]): FP32 FMA path and the
     single-pass TF32 tensor-core path. flops = linear GEMMs only (2*B*T*L*12*C^2), over the whole
@@ -301,8 +328,16 @@ def run_ours(args):
         _, cur, _, _ = model.forward_one_batch(cur, cache)
     t_prof = cache.seq_len_of(0) - 1
 
+    weight_bytes_step = model.weight_bytes_per_step()
     small = small_batch1(pg, synthetic, local) if rank == 0 else None
     prefill = prefill_small(pg, synthetic, local) if rank == 0 else None
+    xl = None
+    if rank == 0 and not args.no_xl:
+        del model, cache  # free the medium model before the 6 GB one comes in
+        try:
+            xl = xl_sampling(pg, synthetic, local)
+        except Exception as exc:  # reported, not fatal: the headline numbers above stand
+            xl = {"error": f"{type(exc).__name__}: {exc}"[:300]}
     if rank == 0:
         peak, peak_src = measured_peaks()
         c, f, L = cfg["n_embd"], cfg["n_inner"], cfg["n_layer"]
@@ -346,7 +381,7 @@ def run_ours(args):
             # ncu capture at 16 sequences: 1.823 GB read vs 1.825 GB algorithmic, writes 0.8 %
             # (profiles/chain_kernel_medium_seqs16.md); both terms scale with the sequences
             traffic = dom_bytes * 1.008
-        step_bytes = model.weight_bytes_per_step() + kv_bytes_per_step(cfg, lens_mid)
+        step_bytes = weight_bytes_step + kv_bytes_per_step(cfg, lens_mid)
         step_achieved = step_bytes / (sec_max / K) / 1e9
 
         cpu_tokens = 24
@@ -377,7 +412,8 @@ def run_ours(args):
                              "sample": f"1 sequence, {cpu_tokens} greedy decode tokens after a 16-token prompt "
                                        f"({cpu_dt:.1f} s)"},
             "check": {"tokens_last_step": [int(x) for x in toks[-1][:4]]},
-            "also": {"gpt2_small_batch1": small, "gpt2_small_prefill_8x1024": prefill},
+            "also": {"gpt2_small_batch1": small, "gpt2_small_prefill_8x1024": prefill,
+                     "gpt2_xl_sampling_32x512_per_gpu": xl},
         }
         print(json.dumps(line))
     if world > 1:
@@ -395,6 +431,7 @@ def main():
     ap.add_argument("--math", default="tf32x3", choices=["fp32", "tf32x3"],
                     help="arithmetic of the batched decode linears: fp32 = CUDA-core FMA, tf32x3 = three TF32 "
                          "tensor-core products with FP32 accumulation (FP32-grade, token-exact against the oracle)")
+    ap.add_argument("--no-xl", action="store_true", help="skip the GPT-2 XL sampling line under `also`")
     ap.add_argument("--skip-extras", action="store_true",
                     help="only the device-timed decode loop (no e2e, per-op profile, CPU baseline)")
     args = ap.parse_args()
