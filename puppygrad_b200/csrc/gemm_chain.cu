@@ -732,6 +732,12 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Registers follow the work: the producer / issuer warps (one busy lane each) and the splitters
+  // give registers back, the worker warps, whose reduce and attention code wants many loads in
+  // flight, take them (per warp group of four warps; 128 * (40 + 128) + 256 * 168 = 64 K).
+
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
   if (warp == 0) {
     // ---------------------------------------------------------------- weight producer
     if (lane == 0) {
@@ -763,25 +769,19 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
       const uint32_t dcol = tmem_base + (uint32_t)b * CH_D_COLS;
       uint32_t wi = 0, si = 0;
       bool ok = true;
-      long long t_wait = 0, t_issue = 0, t_dempty = 0;
       for (int p = 0; p < a.n_phases && ok; ++p) {
         if (phase_at(a, p).kind != CH_GEMM) continue;
         const ChRange r = chain_range(phase_at(a, p).n, phase_at(a, p).k, cta, grid);
         for (int g = r.g0; g < r.g1 && ok;) {
           const int tile = g / r.nkb;
           const int gend = min(r.g1, (tile + 1) * r.nkb);
-          long long c0 = clock64();
           if (si >= 1) ok = mbar_wait(d_empty, (si - 1) & 1, failed, a.error_flag, 22);  // the previous row tile is drained
           if (!ok) break;
-          t_dempty += clock64() - c0;
           tc_fence_after();
           for (int gb = g; gb < gend && ok; ++gb, ++wi) {
             const uint32_t xs = wi % CH_X_STAGES;
-            c0 = clock64();
             ok = mbar_wait(&ready[xs], (wi / CH_X_STAGES) & 1, failed, a.error_flag, 23);
             if (!ok) break;
-            const long long c1 = clock64();
-            t_wait += c1 - c0;
             tc_fence_after();
             // block b of the unit: x_hi rows then x_lo rows in shared memory, w_hi | w_lo columns in tensor memory
             const uint64_t dx = umma_desc_sw128(act_ring + (size_t)xs * CH_ACT_BYTES + (size_t)b * (CH_ACT_BYTES / CH_UB));
@@ -792,18 +792,11 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
               umma_tf32_ts(dcol, alo + k * 8, dx + (uint64_t)(k * 2), idesc1, 1u);
             }
             umma_commit(&done[xs]);
-            t_issue += clock64() - c1;
           }
           if (ok) umma_commit(d_full);
           ++si;
           g = gend;
         }
-      }
-      if (a.trace && b == 0) {
-        unsigned long long* t = a.trace + (size_t)blockIdx.x * 32;
-        t[22] = (unsigned long long)t_wait;
-        t[24] = (unsigned long long)t_issue;
-        t[25] = (unsigned long long)t_dempty;
       }
     }
   } else if (warp == 2) {
@@ -838,28 +831,24 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
         }
       }
     }
-  } else if (warp >= 4 && warp < 8) {
+  }
+  } else if (warp < 8) {
     // ---------------------------------------------------------------- splitters
     const int q = warp & 3;
     const int row = q * 32 + lane;  // row of the weight tile == tensor-memory lane
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     uint32_t wi = 0;
     bool ok = true;
-    long long t_wfull = 0, t_afree = 0;
     for (int p = 0; p < a.n_phases && ok; ++p) {
       if (phase_at(a, p).kind != CH_GEMM) continue;
       const ChRange r = chain_range(phase_at(a, p).n, phase_at(a, p).k, cta, grid);
       for (int g = r.g0; g < r.g1 && ok; ++g, ++wi) {
         const uint32_t s = wi % CH_W_STAGES, xs = wi % CH_X_STAGES;
-        long long c0 = clock64();
         ok = warp_wait(&w_full[s], (wi / CH_W_STAGES) & 1, failed, a.error_flag, 27);
         if (!ok) break;
-        long long c1 = clock64();
-        t_wfull += c1 - c0;
         // the tensor-memory stage is free once the MMAs of the unit that used it last have completed
         if (wi >= CH_X_STAGES) ok = warp_wait(&done[xs], ((wi / CH_X_STAGES) - 1) & 1, failed, a.error_flag, 28);
         if (!ok) break;
-        t_afree += clock64() - c1;
         tc_fence_after();
 #pragma unroll
         for (int b = 0; b < CH_UB; ++b) {
@@ -889,12 +878,9 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
         if (lane == 0) mbar_arrive(&ready[xs]);
       }
     }
-    if (a.trace && threadIdx.x == 128) {
-      a.trace[(size_t)blockIdx.x * 32 + 20] = (unsigned long long)t_wfull;
-      a.trace[(size_t)blockIdx.x * 32 + 21] = (unsigned long long)t_afree;
-    }
-  } else if (warp >= 8) {
+  } else {
     // ---------------------------------------------------------------- workers
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
     const int wt = (int)threadIdx.x - 256;
     const int ww = wt >> 5;
     const int q = ww & 3, half = ww >> 2;
