@@ -742,125 +742,141 @@ __global__ void decode_attention_generic_kernel(DecodeAttnArgs a) {
 
 // ------------------------------------------------------------------ prefill attention
 // causal_self_attention (src/models/gpt2/rust.rs:1580-1659) over concatenated sequences.
-// CTA = 128 queries of one (head, sequence). Four threads share a query's 64 dims (16 each) and
-// every such quad serves FOUR queries, so a key or value float4 read from shared memory feeds four
-// dot products: the kernel is bound by FMA issue, not by shared-memory bandwidth. Keys / values are
-// staged in tiles of 32 rows; softmax runs online in steps of 8 keys.
-constexpr int PA_Q = 128, PA_K = 32, PA_R = 4, PA_S = 8;
+// CTA = 64 queries of one (head, sequence), 128 threads, keys / values in tiles of 64. Both products
+// are register-tiled FP32 GEMMs out of shared memory: S = Q K^T with a 4 x 8 tile per thread
+// (rows ty + 16 i, key columns tx + 8 j: consecutive lanes read consecutive rows, conflict-free
+// with the 68-float row pitch), online softmax per row across the eight threads that share it,
+// P staged in shared memory, O += P V with a 4 x 8 tile per thread (value dims 4 tx .. and
+// 32 + 4 tx ..). About ten FMAs per 128-bit shared-memory load.
+constexpr int PA_Q = 64, PA_K = 64, PA_PITCH = 68;
+constexpr int PA_SMEM = (3 * PA_Q * PA_PITCH + PA_K * 64) * 4;  // Q, K, P padded; V unpadded
 template <int D>
-__global__ void __launch_bounds__(128, 2) prefill_attention_kernel(PrefillAttnArgs a) {
+__global__ void __launch_bounds__(128) prefill_attention_kernel(PrefillAttnArgs a) {
   static_assert(D == 64, "fast path is written for head_dim 64");
-  __shared__ float4 Ks[PA_K][D / 4];
-  __shared__ float4 Vs[PA_K][D / 4];
+  extern __shared__ float4 pa_smem4[];
+  float* Qs = reinterpret_cast<float*>(pa_smem4);  // [64][68]
+  float* Ks = Qs + PA_Q * PA_PITCH;                // [64][68]
+  float* Ps = Ks + PA_K * PA_PITCH;                // [64][68]
+  float* Vs = Ps + PA_Q * PA_PITCH;                // [64][64]
   const int h = blockIdx.x, qb = blockIdx.y, b = blockIdx.z;
-  const int tid = threadIdx.x, part = tid & 3, qd = tid >> 2;
+  const int tid = threadIdx.x, tx = tid & 7, ty = tid >> 3;
   const int c = a.n_head * D;
   const int r0 = a.seq_start[b], len = a.seq_start[b + 1] - r0;
   const int q0 = qb * PA_Q;
   if (q0 >= len) return;
-  int qpos[PA_R];
-  float4 q[PA_R][4], acc[PA_R][4];
-  float m[PA_R], l[PA_R];
-#pragma unroll
-  for (int r = 0; r < PA_R; ++r) {
-    qpos[r] = q0 + qd + 32 * r;  // the quad's queries are 32 apart: every warp sees a similar causal limit
-    const bool qok = qpos[r] < len;
-    if (!qok) qpos[r] = -1;  // no key position is <= -1: everything stays masked
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      q[r][i] = qok ? reinterpret_cast<const float4*>(a.qkv + (size_t)(r0 + qpos[r]) * 3 * c + h * D)[i * 4 + part]
-                    : make_float4(0, 0, 0, 0);
-      acc[r][i] = make_float4(0, 0, 0, 0);
-    }
-    m[r] = -INFINITY;
-    l[r] = 0.f;
-  }
   const float scale = 1.0f / sqrtf((float)D);
+
+  // Q tile: 64 rows x 16 float4 (rows past the sequence end are zero)
+  for (int i = tid; i < PA_Q * (D / 4); i += 128) {
+    const int r = i >> 4, d4 = i & 15;
+    float4 v = make_float4(0, 0, 0, 0);
+    if (q0 + r < len) v = reinterpret_cast<const float4*>(a.qkv + (size_t)(r0 + q0 + r) * 3 * c + h * D)[d4];
+    *reinterpret_cast<float4*>(Qs + r * PA_PITCH + d4 * 4) = v;
+  }
+  float m[4], l[4], o[4][8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    m[i] = -INFINITY;
+    l[i] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[i][j] = 0.f;
+  }
 
   const int kend = min(len, q0 + PA_Q);  // keys needed by the last query of this CTA
   for (int kt = 0; kt < kend; kt += PA_K) {
-    __syncthreads();
+    __syncthreads();  // previous tile's P and V reads are done (and Q is written, first time round)
     for (int i = tid; i < PA_K * (D / 4); i += 128) {
-      int j = i / (D / 4), d4 = i % (D / 4);
-      int kp = kt + j;
+      const int r = i >> 4, d4 = i & 15;
       float4 kv = make_float4(0, 0, 0, 0), vv = kv;
-      if (kp < len) {
-        const float* base = a.qkv + (size_t)(r0 + kp) * 3 * c + h * D;
+      if (kt + r < len) {
+        const float* base = a.qkv + (size_t)(r0 + kt + r) * 3 * c + h * D;
         kv = reinterpret_cast<const float4*>(base + c)[d4];
         vv = reinterpret_cast<const float4*>(base + 2 * c)[d4];
       }
-      Ks[j][d4] = kv;
-      Vs[j][d4] = vv;
+      *reinterpret_cast<float4*>(Ks + r * PA_PITCH + d4 * 4) = kv;
+      *reinterpret_cast<float4*>(Vs + r * D + d4 * 4) = vv;
     }
     __syncthreads();
-#pragma unroll 1
-    for (int sub = 0; sub < PA_K; sub += PA_S) {
-      if (kt + sub >= kend) break;
-      float s[PA_R][PA_S];
+    // ---- S = Q K^T
+    float s[4][8];
 #pragma unroll
-      for (int jj = 0; jj < PA_S; ++jj) {
-        const float4 k0 = Ks[sub + jj][part], k1 = Ks[sub + jj][4 + part], k2 = Ks[sub + jj][8 + part],
-                     k3 = Ks[sub + jj][12 + part];
+    for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int r = 0; r < PA_R; ++r) {
-          float d = dot4(q[r][0], k0, 0.f);
-          d = dot4(q[r][1], k1, d);
-          d = dot4(q[r][2], k2, d);
-          d = dot4(q[r][3], k3, d);
-          d += __shfl_xor_sync(FULL, d, 1);
-          d += __shfl_xor_sync(FULL, d, 2);
-          s[r][jj] = (kt + sub + jj <= qpos[r]) ? d * scale : -INFINITY;
-        }
+      for (int j = 0; j < 8; ++j) s[i][j] = 0.f;
+#pragma unroll 4
+    for (int d4 = 0; d4 < D / 4; ++d4) {
+      float4 qv[4], kv[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) qv[i] = *reinterpret_cast<const float4*>(Qs + (ty + 16 * i) * PA_PITCH + d4 * 4);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) kv[j] = *reinterpret_cast<const float4*>(Ks + (tx + 8 * j) * PA_PITCH + d4 * 4);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s[i][j] = dot4(qv[i], kv[j], s[i][j]);
+    }
+    // ---- scale, causal mask, online softmax per query row (shared by the 8 lanes tx = 0..7)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int qpos = q0 + ty + 16 * i;
+      float tmax = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int kpos = kt + tx + 8 * j;
+        s[i][j] = (kpos <= qpos && qpos < len) ? s[i][j] * scale : -INFINITY;
+        tmax = fmaxf(tmax, s[i][j]);
       }
+      tmax = fmaxf(tmax, __shfl_xor_sync(FULL, tmax, 1));
+      tmax = fmaxf(tmax, __shfl_xor_sync(FULL, tmax, 2));
+      tmax = fmaxf(tmax, __shfl_xor_sync(FULL, tmax, 4));
+      const float mn = fmaxf(m[i], tmax);
+      const float mref = (mn == -INFINITY) ? 0.f : mn;  // nothing unmasked yet: every term below is 0
+      const float corr = expf(m[i] - mref);             // m = -inf before the first unmasked key: 0
+      float ps = 0.f;
 #pragma unroll
-      for (int r = 0; r < PA_R; ++r) {
-        float tmax = s[r][0];
+      for (int j = 0; j < 8; ++j) {
+        const float p = expf(s[i][j] - mref);  // masked: expf(-inf) = 0
+        ps += p;
+        Ps[(ty + 16 * i) * PA_PITCH + tx + 8 * j] = p;
+      }
+      ps += __shfl_xor_sync(FULL, ps, 1);
+      ps += __shfl_xor_sync(FULL, ps, 2);
+      ps += __shfl_xor_sync(FULL, ps, 4);
+      l[i] = l[i] * corr + ps;
+      m[i] = mn;
 #pragma unroll
-        for (int jj = 1; jj < PA_S; ++jj) tmax = fmaxf(tmax, s[r][jj]);
-        const float mn = fmaxf(m[r], tmax);
-        const float mref = (mn == -INFINITY) ? 0.f : mn;  // nothing unmasked yet: every term below is 0
-        const float corr = expf(m[r] - mref);             // m = -inf before the first unmasked key: 0
-        float ls = l[r] * corr;
+      for (int j = 0; j < 8; ++j) o[i][j] *= corr;
+    }
+    __syncthreads();
+    // ---- O += P V
+#pragma unroll 4
+    for (int k4 = 0; k4 < PA_K / 4; ++k4) {
+      float4 pv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) pv[i] = *reinterpret_cast<const float4*>(Ps + (ty + 16 * i) * PA_PITCH + k4 * 4);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const float4 va = *reinterpret_cast<const float4*>(Vs + (k4 * 4 + kk) * D + tx * 4);
+        const float4 vb = *reinterpret_cast<const float4*>(Vs + (k4 * 4 + kk) * D + 32 + tx * 4);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          acc[r][i].x *= corr; acc[r][i].y *= corr; acc[r][i].z *= corr; acc[r][i].w *= corr;
-        }
-#pragma unroll
-        for (int jj = 0; jj < PA_S; ++jj) {
-          const float p = expf(s[r][jj] - mref);  // masked: expf(-inf) = 0
-          ls += p;
-          s[r][jj] = p;
-        }
-        l[r] = ls;
-        m[r] = mn;
-      }
-#pragma unroll
-      for (int jj = 0; jj < PA_S; ++jj) {
-        const float4 v0 = Vs[sub + jj][part], v1 = Vs[sub + jj][4 + part], v2 = Vs[sub + jj][8 + part],
-                     v3 = Vs[sub + jj][12 + part];
-#pragma unroll
-        for (int r = 0; r < PA_R; ++r) {
-          const float p = s[r][jj];
-          acc[r][0].x = fmaf(p, v0.x, acc[r][0].x); acc[r][0].y = fmaf(p, v0.y, acc[r][0].y);
-          acc[r][0].z = fmaf(p, v0.z, acc[r][0].z); acc[r][0].w = fmaf(p, v0.w, acc[r][0].w);
-          acc[r][1].x = fmaf(p, v1.x, acc[r][1].x); acc[r][1].y = fmaf(p, v1.y, acc[r][1].y);
-          acc[r][1].z = fmaf(p, v1.z, acc[r][1].z); acc[r][1].w = fmaf(p, v1.w, acc[r][1].w);
-          acc[r][2].x = fmaf(p, v2.x, acc[r][2].x); acc[r][2].y = fmaf(p, v2.y, acc[r][2].y);
-          acc[r][2].z = fmaf(p, v2.z, acc[r][2].z); acc[r][2].w = fmaf(p, v2.w, acc[r][2].w);
-          acc[r][3].x = fmaf(p, v3.x, acc[r][3].x); acc[r][3].y = fmaf(p, v3.y, acc[r][3].y);
-          acc[r][3].z = fmaf(p, v3.z, acc[r][3].z); acc[r][3].w = fmaf(p, v3.w, acc[r][3].w);
+          const float p = kk == 0 ? pv[i].x : kk == 1 ? pv[i].y : kk == 2 ? pv[i].z : pv[i].w;
+          o[i][0] = fmaf(p, va.x, o[i][0]); o[i][1] = fmaf(p, va.y, o[i][1]);
+          o[i][2] = fmaf(p, va.z, o[i][2]); o[i][3] = fmaf(p, va.w, o[i][3]);
+          o[i][4] = fmaf(p, vb.x, o[i][4]); o[i][5] = fmaf(p, vb.y, o[i][5]);
+          o[i][6] = fmaf(p, vb.z, o[i][6]); o[i][7] = fmaf(p, vb.w, o[i][7]);
         }
       }
     }
   }
 #pragma unroll
-  for (int r = 0; r < PA_R; ++r) {
-    if (qpos[r] >= 0) {
-      const float inv = 1.0f / l[r];
-      float4* o = reinterpret_cast<float4*>(a.out + (size_t)(r0 + qpos[r]) * c + h * D);
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        o[i * 4 + part] = make_float4(acc[r][i].x * inv, acc[r][i].y * inv, acc[r][i].z * inv, acc[r][i].w * inv);
+  for (int i = 0; i < 4; ++i) {
+    const int qpos = q0 + ty + 16 * i;
+    if (qpos < len) {
+      const float inv = 1.0f / l[i];
+      float* orow = a.out + (size_t)(r0 + qpos) * c + h * D;
+      *reinterpret_cast<float4*>(orow + tx * 4) = make_float4(o[i][0] * inv, o[i][1] * inv, o[i][2] * inv, o[i][3] * inv);
+      *reinterpret_cast<float4*>(orow + 32 + tx * 4) = make_float4(o[i][4] * inv, o[i][5] * inv, o[i][6] * inv, o[i][7] * inv);
     }
   }
 }
@@ -1182,7 +1198,7 @@ cudaError_t launch_decode_attention(const DecodeAttnArgs& a, bool pdl, cudaStrea
 cudaError_t launch_prefill_attention(const PrefillAttnArgs& a, cudaStream_t s) {
   if (a.head_dim == 64) {
     dim3 grid(a.n_head, (a.max_len + PA_Q - 1) / PA_Q, a.batch);
-    prefill_attention_kernel<64><<<grid, 128, 0, s>>>(a);
+    prefill_attention_kernel<64><<<grid, 128, PA_SMEM, s>>>(a);
   } else {
     if (a.head_dim > 128) return cudaErrorInvalidValue;
     dim3 grid(a.n_head, (a.max_len + 63) / 64, a.batch);
@@ -1225,6 +1241,7 @@ cudaError_t init_kernel_attributes() {
   PG_SET((linear_decode_kernel<4, EPI_GELU, true>), ln_smem / 2)
   PG_SET((linear_decode_kernel<4, EPI_RESID, true>), ln_smem / 2)
   PG_SET(decode_attention_kernel<64>, 64 * 1024)
+  PG_SET(prefill_attention_kernel<64>, PA_SMEM)
   PG_SET(decode_attention_generic_kernel, 64 * 1024)
   PG_SET(topk_rows_kernel, 220 * 1024)
 #undef PG_SET
