@@ -19,6 +19,14 @@ namespace pg {
 namespace {
 
 
+// tanh-GELU with the hardware tanh approximation (relative error about 2^-11): only for the single
+// TF32 pass of the prefill, whose products already carry 10-bit mantissas.
+__device__ __forceinline__ float gelu_fast(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978846f * (x + 0.044715f * x * x * x)));
+  return 0.5f * x * (1.0f + t);
+}
+
 // ------------------------------------------------------------------ single-pass TF32, SS
 // grid (ceil(n / BN), ceil(m / 128)); 192 threads: warp 0 TMA producer, warp 1 MMA issuer and
 // tensor-memory owner, warps 2..5 epilogue (warp w reads TMEM lanes 32 * (w % 4) ...).
@@ -103,22 +111,33 @@ __global__ void __launch_bounds__(192, 1)
       tc_fence_after();
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
+        const int col = n0 + c0 + lane;
+        // the block's 32 residual values of this lane's column go out first: they do not depend on
+        // the accumulator, and asked for one by one between the stores (which may alias them:
+        // the residual is updated in place) they would each cost a full memory round trip
+        float rv[32];
+        if (a.epilogue == EPI_RESID && col < a.n) {
+#pragma unroll
+          for (int rr = 0; rr < 32; ++rr) {
+            const int row = m0 + q * 32 + rr;
+            rv[rr] = row < a.m ? a.resid[(size_t)row * a.n + col] : 0.f;
+          }
+        }
         float v[32];
         tmem_ld32(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
 #pragma unroll
         for (int j = 0; j < 32; ++j) tile[lane * 33 + j] = v[j];
         __syncwarp();
-        const int col = n0 + c0 + lane;
         const float bias = (a.bias && col < a.n) ? a.bias[col] : 0.f;
         if (col < a.n) {
-#pragma unroll 4
+#pragma unroll
           for (int rr = 0; rr < 32; ++rr) {
             const int row = m0 + q * 32 + rr;
             if (row < a.m) {
               float r = tile[rr * 33 + lane];
               if (a.bias) r = bias + r;
-              if (a.epilogue == EPI_GELU) r = gelu_ref(r);
-              if (a.epilogue == EPI_RESID) r = a.resid[(size_t)row * a.n + col] + r;
+              if (a.epilogue == EPI_GELU) r = gelu_fast(r);
+              if (a.epilogue == EPI_RESID) r = rv[rr] + r;
               a.out[(size_t)row * a.n + col] = r;
             }
           }
