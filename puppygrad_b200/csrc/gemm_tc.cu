@@ -12,6 +12,8 @@
 //
 // Every wait on an mbarrier is bounded: on expiry the kernel raises an error flag in global
 // memory, stops issuing work, still frees its tensor memory and returns.
+#include <algorithm>
+
 #include "kernels.cuh"
 #include "tc_common.cuh"
 
@@ -50,12 +52,16 @@ __global__ void __launch_bounds__(192, 1)
   float* epi_tiles = reinterpret_cast<float*>(smem_b + (size_t)S::STAGES * S::B_BYTES);
   uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(epi_tiles) + S::EPI_BYTES);
   uint64_t* empty = full + S::STAGES;
-  uint64_t* d_full = empty + S::STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_full + 1);
+  uint64_t* d_full = empty + S::STAGES;   // [2]: accumulator buffer holds a finished tile
+  uint64_t* d_empty = d_full + 2;         // [2]: the epilogue warps have read it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + 2);
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  // Persistent over output tiles (tile = blockIdx.x, + gridDim.x, ...; column tiles of one row panel
+  // are neighbours, so the activation panel is reused from L2). Two accumulators in tensor memory:
+  // while the epilogue warps drain one tile, the MMAs of the next one already run.
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * TILE_M;
+  const int tiles_n = (a.n + BN - 1) / BN, tiles = tiles_n * ((a.m + TILE_M - 1) / TILE_M);
   const int nkb = a.k / BK;
 
   if (threadIdx.x == 0) {
@@ -63,43 +69,60 @@ __global__ void __launch_bounds__(192, 1)
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(d_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&d_full[i], 1);
+      mbar_init(&d_empty[i], 4);
+    }
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(tmem_slot, BN);
+  if (warp == 1) tmem_alloc(tmem_slot, 2 * BN);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_d = *tmem_slot;
+  const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < nkb; ++kb) {
-        const int s = kb % S::STAGES;
-        if (kb >= S::STAGES && !mbar_wait(&empty[s], ((kb / S::STAGES) - 1) & 1, failed, a.error_flag, 1)) break;
-        mbar_expect_tx(&full[s], S::A_BYTES + S::B_BYTES);
-        tma_load_2d(smem_a + (size_t)s * S::A_BYTES, &map_x, kb * BK, m0, &full[s]);
-        tma_load_2d(smem_b + (size_t)s * S::B_BYTES, &map_w, kb * BK, n0, &full[s]);
+      uint32_t it = 0;  // stage counter over all tiles of this CTA
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        const int n0 = (tile % tiles_n) * BN, m0 = (tile / tiles_n) * TILE_M;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const uint32_t s = it % S::STAGES;
+          if (it >= S::STAGES) ok = mbar_wait(&empty[s], ((it / S::STAGES) - 1) & 1, failed, a.error_flag, 1);
+          if (!ok) break;
+          mbar_expect_tx(&full[s], S::A_BYTES + S::B_BYTES);
+          tma_load_2d(smem_a + (size_t)s * S::A_BYTES, &map_x, kb * BK, m0, &full[s]);
+          tma_load_2d(smem_b + (size_t)s * S::B_BYTES, &map_w, kb * BK, n0, &full[s]);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_tf32(TILE_M, BN);
+      uint32_t it = 0, ti = 0;
       bool ok = true;
-      for (int kb = 0; kb < nkb && ok; ++kb) {
-        const int s = kb % S::STAGES;
-        ok = mbar_wait(&full[s], (kb / S::STAGES) & 1, failed, a.error_flag, 2);
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++ti) {
+        const uint32_t buf = ti & 1;
+        if (ti >= 2) ok = mbar_wait(&d_empty[buf], ((ti >> 1) - 1) & 1, failed, a.error_flag, 4);
         if (!ok) break;
         tc_fence_after();
-        const uint64_t da = umma_desc_sw128(smem_a + (size_t)s * S::A_BYTES);
-        const uint64_t db = umma_desc_sw128(smem_b + (size_t)s * S::B_BYTES);
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
+          const uint32_t s = it % S::STAGES;
+          ok = mbar_wait(&full[s], (it / S::STAGES) & 1, failed, a.error_flag, 2);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t da = umma_desc_sw128(smem_a + (size_t)s * S::A_BYTES);
+          const uint64_t db = umma_desc_sw128(smem_b + (size_t)s * S::B_BYTES);
 #pragma unroll
-        for (int k = 0; k < BK / 8; ++k)
-          umma_tf32_ss(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
-        umma_commit(&empty[s]);
+          for (int k = 0; k < BK / 8; ++k)
+            umma_tf32_ss(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+          umma_commit(&empty[s]);
+        }
+        if (ok) umma_commit(&d_full[buf]);
       }
-      umma_commit(d_full);
     }
   } else {
     // TMEM lane = output row, but a row-per-thread store touches 32 cache lines per instruction:
@@ -107,7 +130,15 @@ __global__ void __launch_bounds__(192, 1)
     // that residual loads and output stores are 128-byte coalesced.
     const int q = warp & 3;
     float* tile = epi_tiles + q * (32 * 33);
-    if (mbar_wait(d_full, 0, failed, a.error_flag, 3)) {
+    uint32_t ti = 0;
+    bool ok = true;
+    for (int tile_id = blockIdx.x; tile_id < tiles && ok; tile_id += gridDim.x, ++ti) {
+      const int n0 = (tile_id % tiles_n) * BN, m0 = (tile_id / tiles_n) * TILE_M;
+      const uint32_t buf = ti & 1;
+      const uint32_t tmem_d = tmem_base + buf * BN;
+      ok = mbar_wait(&d_full[buf], (ti >> 1) & 1, failed, a.error_flag, 3);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
       tc_fence_after();
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -144,11 +175,14 @@ __global__ void __launch_bounds__(192, 1)
         }
         __syncwarp();
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&d_empty[buf]);
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_d, BN);
+  if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
 }
 
 // ------------------------------------------------------------------ 3xTF32, weights via TMEM
@@ -545,7 +579,14 @@ cudaError_t launch_tc_gemm_tf32(const TcGemmArgs& a, cudaStream_t s) {
   if (!make_map(&mx, a.x, a.m, a.k, TILE_M) || !make_map(&mw, a.w, a.n, a.k, bn)) return cudaErrorInvalidValue;
   TcGemmArgs args = a;
   void* params[3] = {&mx, &mw, &args};
-  dim3 grid((a.n + bn - 1) / bn, (a.m + TILE_M - 1) / TILE_M);
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  const int tiles = ((a.n + bn - 1) / bn) * ((a.m + TILE_M - 1) / TILE_M);
+  dim3 grid((unsigned)std::min(tiles, sms));
   if (bn == 256) return launch_ex(tc_gemm_ss_kernel<256>, grid, SsSmem<256>::BYTES, s, false, params);
   return launch_ex(tc_gemm_ss_kernel<128>, grid, SsSmem<128>::BYTES, s, false, params);
 }
