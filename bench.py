@@ -197,8 +197,9 @@ def small_batch1(pg, synthetic, device):
 
 
 def xl_sampling(pg, synthetic, device, seqs=32, prompt_len=512, steps=48):
-    """GPT-2 XL with temperature 0.8 / top-k 40 sampling and one RNG seed per sequence (BASELINE
-    configs[3], one GPU's share of it: 256 sequences over 8 GPUs = 32 per GPU, 512-token prompts).
+    """GPT-2 XL with temperature 0.8 / top-k 40 sampling and one RNG seed per sequence (the
+    256-sequence sampling workload, one GPU's share of it: 256 sequences over 8 GPUs = 32 per GPU,
+    512-token prompts).
     Every step runs the persistent step kernel, the device top-k, and the host draw of the reference
     sampler; timed on the host clock through the public API (token ids in, top-k rows out)."""
     from puppygrad_b200.generation import LogitsSampler
@@ -224,7 +225,7 @@ def xl_sampling(pg, synthetic, device, seqs=32, prompt_len=512, steps=48):
 
 
 def prefill_small(pg, synthetic, device):
-    """GPT-2 small prefill, 8 prompts of 1024 tokens (BASELINE configs[1]): FP32 FMA path and the
+    """GPT-2 small prefill, 8 prompts of 1024 tokens (the prefill-only workload): FP32 FMA path and the
     single-pass TF32 tensor-core path. flops = linear GEMMs only (2*B*T*L*12*C^2), over the whole
     prefill time (attention, LayerNorm and the KV scatter included), so the rate is a lower bound."""
     cfg = synthetic.preset("small")
