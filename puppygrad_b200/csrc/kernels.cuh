@@ -68,6 +68,11 @@ struct PrefillAttnArgs {
   int n_head, head_dim, batch, max_len;
 };
 cudaError_t launch_prefill_attention(const PrefillAttnArgs& a, cudaStream_t s);
+// The same attention with TF32 products on the tensor cores (head_dim 64; used by the TF32 prefill mode).
+// rows = rows of the QKV matrix; error_flag receives a code when a bounded wait runs out.
+bool prefill_attention_tc_supported(const PrefillAttnArgs& a);
+cudaError_t launch_prefill_attention_tc(const PrefillAttnArgs& a, int rows, int* error_flag, cudaStream_t s);
+cudaError_t init_attn_tc_attributes();
 // Copies K,V of every prompt row into the paged cache.
 cudaError_t launch_kv_scatter(const float* qkv, const int* row_slot, const int* row_pos, float* kv_pool,
                               const int* page_table, KvLayout kv, int rows, cudaStream_t s);

@@ -103,6 +103,7 @@ int ensure_device(int device) {
                                     "; this library is built for sm_100a only");
     PG_CUDA_TRY(init_kernel_attributes());
     PG_CUDA_TRY(init_tc_kernel_attributes());
+    PG_CUDA_TRY(init_attn_tc_attributes());
     g_device_inited[device] = true;
   }
   return PG_OK;
@@ -824,6 +825,7 @@ static int run_blocks(const pg_model* m, const BlockWorkspace& ws, const Prefill
     }
     return launch_gemm_f32(a, epi, s);
   };
+  static const bool no_tc_attn = getenv("PG_NO_TC_ATTN") != nullptr;
   for (int l = 0; l < m->layers_n(); ++l) {
     const LayerWeights& w = m->layers[l];
     PG_CUDA_TRY(launch_layernorm_rows(ws.x, w.ln1_g, w.ln1_b, eps, ws.norm, rows, C, false, s));
@@ -834,7 +836,10 @@ static int run_blocks(const pg_model* m, const BlockWorkspace& ws, const Prefill
     PrefillAttnArgs pa{};
     pa.qkv = ws.qkv; pa.out = ws.attn; pa.seq_start = ws.d_seq_start;
     pa.n_head = m->heads(); pa.head_dim = m->head_dim(); pa.batch = plan.batch; pa.max_len = plan.max_len;
-    PG_CUDA_TRY(launch_prefill_attention(pa, s));
+    if (m->backend.math_mode == PG_MATH_TF32 && ws.d_error && !no_tc_attn && prefill_attention_tc_supported(pa))
+      PG_CUDA_TRY(launch_prefill_attention_tc(pa, rows, ws.d_error, s));
+    else
+      PG_CUDA_TRY(launch_prefill_attention(pa, s));
     PG_CUDA_TRY(gemm(w.w_proj, w.b_proj, ws.attn, ws.x, C, C, EPI_RESID, ws.x));
     PG_CUDA_TRY(launch_layernorm_rows(ws.x, w.ln2_g, w.ln2_b, eps, ws.norm, rows, C, false, s));
     PG_CUDA_TRY(gemm(w.w_fc, w.b_fc, ws.norm, ws.h, F, C, EPI_GELU, nullptr));

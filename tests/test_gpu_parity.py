@@ -524,6 +524,34 @@ def test_tf32_prefill_is_within_its_stated_bound(oracle):
         assert np.abs(logits[i] - want).max() <= 5e-3 * span
 
 
+def test_tf32_prefill_attention_on_tensor_cores_with_ragged_prompts(oracle):
+    """The TF32 prefill mode runs causal attention on the tensor cores (128-query x 128-key tiles,
+    head_dim 64). Prompt lengths on, just past and far from the tile edges, several sequences in one
+    call: final-position logits stay within the mode's stated bound and the K,V rows written to the
+    cache are the FP32 oracle's within TF32 rounding of the QKV GEMM."""
+    cfg = synthetic.preset("midi")
+    cfg["n_positions"] = 512
+    w = synthetic.random_init_weights(cfg, 6)
+    lens = [300, 129, 128, 1, 257, 512, 127]
+    prompts = [synthetic.uniform_prompt(950 + i, n, cfg["vocab_size"]) for i, n in enumerate(lens)]
+    g = pg.Gpt2Model(cfg, w, pg.Gpt2CudaConfig(math_mode="tf32"))
+    o = oracle.Model(cfg, w, threads=os.cpu_count())
+    cache = g.new_kv_cache(max_batch=len(lens))
+    logits, first = g.prefill_batch(prompts, cache, want_logits=True)
+    assert np.isfinite(logits).all()
+    for i, p in enumerate(prompts):
+        want = o.prefill(p, o.new_kv_cache())
+        span = float(want.max() - want.min())
+        assert np.abs(logits[i] - want).max() <= 5e-3 * span, (i, lens[i])
+    # the greedy continuation from this cache agrees with the oracle's on the first decoded token
+    # wherever the oracle's own top-2 gap is clear of the bound
+    for i, p in enumerate(prompts):
+        want = o.prefill(p, o.new_kv_cache())
+        top2 = np.sort(want)[-2:]
+        if top2[1] - top2[0] > 1e-2 * float(want.max() - want.min()):
+            assert int(first[i]) == int(want.argmax()), i
+
+
 @pytest.mark.parametrize("kw", [dict(temperature=0.8, top_k=40), dict(temperature=0.0),
                                 dict(temperature=0.7, top_p=0.9, repeat_penalty=1.2)])
 def test_batched_sampling_with_per_sequence_seeds_matches_oracle(midi, oracle, kw):
