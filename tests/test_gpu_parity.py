@@ -527,8 +527,8 @@ def test_tf32_prefill_is_within_its_stated_bound(oracle):
 def test_tf32_prefill_attention_on_tensor_cores_with_ragged_prompts(oracle):
     """The TF32 prefill mode runs causal attention on the tensor cores (128-query x 128-key tiles,
     head_dim 64). Prompt lengths on, just past and far from the tile edges, several sequences in one
-    call: final-position logits stay within the mode's stated bound and the K,V rows written to the
-    cache are the FP32 oracle's within TF32 rounding of the QKV GEMM."""
+    call: final-position logits stay within the mode's stated bound, and the first greedy token is
+    the oracle's wherever the oracle's own top-2 gap is clear of that bound."""
     cfg = synthetic.preset("midi")
     cfg["n_positions"] = 512
     w = synthetic.random_init_weights(cfg, 6)
@@ -543,12 +543,8 @@ def test_tf32_prefill_attention_on_tensor_cores_with_ragged_prompts(oracle):
         want = o.prefill(p, o.new_kv_cache())
         span = float(want.max() - want.min())
         assert np.abs(logits[i] - want).max() <= 5e-3 * span, (i, lens[i])
-    # the greedy continuation from this cache agrees with the oracle's on the first decoded token
-    # wherever the oracle's own top-2 gap is clear of the bound
-    for i, p in enumerate(prompts):
-        want = o.prefill(p, o.new_kv_cache())
         top2 = np.sort(want)[-2:]
-        if top2[1] - top2[0] > 1e-2 * float(want.max() - want.min()):
+        if top2[1] - top2[0] > 1e-2 * span:
             assert int(first[i]) == int(want.argmax()), i
 
 
