@@ -497,17 +497,27 @@ __device__ __forceinline__ size_t kv_row_offset(const KvLayout& kv, int page, in
   return ((((size_t)page * 2 + which) * kv.n_head + head) * kv.page_tokens + off) * kv.head_dim;
 }
 
-__global__ void kv_scatter_kernel(const float* qkv, const int* row_slot, const int* row_pos, float* pool,
-                                  const int* page_table, KvLayout kv, int rows) {
-  int r = blockIdx.x;
-  if (r >= rows) return;
+// One piece of VEC floats of a K or V row per thread (VEC = 4 when head_dim is a multiple of 4:
+// rows are 256-byte segments of the page for head_dim 64, and 16 consecutive threads fill one).
+template <int VEC>
+__global__ void kv_scatter_kernel(const float* __restrict__ qkv, const int* __restrict__ row_slot,
+                                  const int* __restrict__ row_pos, float* __restrict__ pool,
+                                  const int* __restrict__ page_table, KvLayout kv, int rows) {
   const int c = kv.n_head * kv.head_dim;
-  const int slot = row_slot[r], pos = row_pos[r];
-  const int page = page_table[(size_t)slot * kv.pages_per_seq + pos / kv.page_tokens];
-  const int off = pos % kv.page_tokens;
-  for (int i = threadIdx.x; i < 2 * c; i += blockDim.x) {
-    int which = i / c, j = i % c, h = j / kv.head_dim, d = j % kv.head_dim;
-    pool[kv_row_offset(kv, page, which, h, off) + d] = qkv[(size_t)r * 3 * c + c + i];
+  const int per_row = 2 * c / VEC;
+  const size_t total = (size_t)rows * per_row;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const int r = (int)(idx / per_row), i = (int)(idx % per_row) * VEC;
+    const int slot = __ldg(row_slot + r), pos = __ldg(row_pos + r);
+    const int page = __ldg(page_table + (size_t)slot * kv.pages_per_seq + pos / kv.page_tokens);
+    const int off = pos % kv.page_tokens;
+    const int which = i / c, j = i % c, h = j / kv.head_dim, d = j % kv.head_dim;
+    const float* src = qkv + (size_t)r * 3 * c + c + i;
+    float* dst = pool + kv_row_offset(kv, page, which, h, off) + d;
+    if (VEC == 4)
+      *reinterpret_cast<float4*>(dst) = __ldg(reinterpret_cast<const float4*>(src));
+    else
+      *dst = __ldg(src);
   }
 }
 
@@ -1209,7 +1219,13 @@ cudaError_t launch_prefill_attention(const PrefillAttnArgs& a, cudaStream_t s) {
 
 cudaError_t launch_kv_scatter(const float* qkv, const int* row_slot, const int* row_pos, float* kv_pool,
                               const int* page_table, KvLayout kv, int rows, cudaStream_t s) {
-  kv_scatter_kernel<<<rows, 256, 0, s>>>(qkv, row_slot, row_pos, kv_pool, page_table, kv, rows);
+  const int vec = kv.head_dim % 4 == 0 ? 4 : 1;
+  const size_t total = (size_t)rows * (2 * kv.n_head * kv.head_dim / vec);
+  const unsigned blocks = std::max(1u, (unsigned)std::min<size_t>((total + 255) / 256, (size_t)148 * 16));
+  if (vec == 4)
+    kv_scatter_kernel<4><<<blocks, 256, 0, s>>>(qkv, row_slot, row_pos, kv_pool, page_table, kv, rows);
+  else
+    kv_scatter_kernel<1><<<blocks, 256, 0, s>>>(qkv, row_slot, row_pos, kv_pool, page_table, kv, rows);
   return cudaGetLastError();
 }
 

@@ -2,6 +2,7 @@
 
     python -m puppygrad_b200.sweep linear --m 1 8 64 --n 4800 1600 6400 --k 1600 --math fp32 tf32x3
     python -m puppygrad_b200.sweep linear --preset xl
+    python -m puppygrad_b200.sweep prefill --model small --seqs 8 --prompt-len 1024 --math fp32 tf32
 
 Prints one JSON line per case: seconds per launch, algorithmic GB/s (4*(k*n + m*k + m*n + n) bytes)
 and TFLOP/s (2*m*n*k), plus the largest deviation from a float64 product of the same inputs.
@@ -59,9 +60,36 @@ def attention_case(batch, n_head, kv_len, splits, reps, seed=0):
             "us": sec * 1e6, "gbps": bytes_ / sec / 1e9, "max_rel_err_vs_f64": err}
 
 
+def prefill_case(preset, seqs, prompt_len, math, reps):
+    """Whole prefill of `seqs` prompts of `prompt_len` tokens (seeded random weights and ids),
+    device-timed; the best of `reps` runs after one warm-up."""
+    from . import synthetic
+    from .gpt2 import Gpt2CudaConfig, Gpt2Model
+    cfg = synthetic.preset(preset)
+    model = Gpt2Model(cfg, synthetic.random_init_weights(cfg, 0), Gpt2CudaConfig(math_mode=math))
+    prompts = [synthetic.uniform_prompt(s + 1, prompt_len, cfg["vocab_size"]) for s in range(seqs)]
+    cache = model.new_kv_cache(max_batch=seqs)
+    model.prefill_batch(prompts, cache)
+    best = None
+    for _ in range(reps):
+        cache.time_begin()
+        model.prefill_batch(prompts, cache)
+        sec = cache.time_end()
+        best = sec if best is None else min(best, sec)
+    c, layers, t = cfg["n_embd"], cfg["n_layer"], seqs * prompt_len
+    attn_flops = 4 * seqs * cfg["n_head"] * (c // cfg["n_head"]) * prompt_len * (prompt_len + 1) // 2 * layers
+    return {"op": "prefill", "preset": preset, "seqs": seqs, "prompt_len": prompt_len, "math": math,
+            "ms": best * 1e3, "prompt_tokens_per_s": t / best,
+            "linear_tflops": 2 * t * layers * 12 * c * c / best / 1e12,
+            "linear_plus_attention_tflops": (2 * t * layers * 12 * c * c + attn_flops) / best / 1e12}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["linear", "attention"])
+    ap.add_argument("op", choices=["linear", "attention", "prefill"])
+    ap.add_argument("--model", default="small", help="prefill: model preset")
+    ap.add_argument("--seqs", type=int, default=8, help="prefill: prompts per call")
+    ap.add_argument("--prompt-len", type=int, default=1024)
     ap.add_argument("--batch", type=int, nargs="+", default=[1, 32, 256])
     ap.add_argument("--kv", type=int, nargs="+", default=[128, 256, 512, 1024])
     ap.add_argument("--heads", type=int, default=25)
@@ -74,6 +102,10 @@ def main():
     ap.add_argument("--epilogue", default="none")
     ap.add_argument("--reps", type=int, default=10)
     a = ap.parse_args()
+    if a.op == "prefill":
+        for math in a.math:
+            print(json.dumps(prefill_case(a.model, a.seqs, a.prompt_len, math, a.reps)), flush=True)
+        return
     if a.op == "attention":
         for b in a.batch:
             for kv in a.kv:

@@ -62,20 +62,28 @@ def test_linear_tf32x3_one_launch_per_gemm_kernel_matches_oracle(oracle, monkeyp
     np.testing.assert_allclose(got, oracle_linear(oracle, x, w, b, epilogue, r), rtol=1e-3, atol=1e-4)
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 128, 32), (512, 4800, 1600), (1000, 770, 768), (4096, 1600, 6400)])
-def test_linear_tf32_single_pass_is_within_its_stated_bound(oracle, m, n, k):
+@pytest.mark.parametrize("m,n,k,epilogue", [(128, 128, 32, "none"), (512, 4800, 1600, "none"), (1000, 770, 768, "none"),
+                                            (4096, 1600, 6400, "none"), (1000, 770, 768, "gelu"),
+                                            (2300, 768, 3072, "resid"), (300, 771, 64, "resid"), (129, 515, 96, "gelu")])
+def test_linear_tf32_single_pass_is_within_its_stated_bound(oracle, m, n, k, epilogue):
     """One TF32 pass (10-bit mantissas, truncated): error <= 2e-3 of the output scale
-    sqrt(k) * |x| * |w|, the looser bound of the TF32 prefill variant."""
+    sqrt(k) * |x| * |w|, the looser bound of the TF32 prefill variant. Ragged row and column
+    counts (odd n takes the scalar store path of the epilogue), all three epilogues."""
     rng = np.random.default_rng(m + n + k)
     x = rng.standard_normal((m, k), dtype=np.float32)
     w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.05)
     b = rng.standard_normal(n, dtype=np.float32)
-    got, _ = ops.linear(x, w, b, None, "none", "tf32")
+    r = rng.standard_normal((m, n), dtype=np.float32) if epilogue == "resid" else None
+    got, _ = ops.linear(x, w, b, r, epilogue, "tf32")
     rows = slice(0, min(m, 64))
-    want = oracle_linear(oracle, x[rows], w, b, "none", None)
+    want = oracle_linear(oracle, x[rows], w, b, epilogue, None if r is None else r[rows])
     scale = float(np.abs(want).max())
     assert np.abs(got[rows] - want).max() <= 2e-3 * scale
     full = x.astype(np.float64) @ w.astype(np.float64).T + b
+    if epilogue == "gelu":
+        full = 0.5 * full * (1 + np.tanh(0.7978845608028654 * (full + 0.044715 * full ** 3)))
+    if epilogue == "resid":
+        full = full + r
     assert np.abs(got - full).max() <= 2e-3 * np.abs(full).max()
 
 
