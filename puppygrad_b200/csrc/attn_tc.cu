@@ -4,17 +4,18 @@
 //
 // CTA = 128 queries of one (sequence, head); keys / values in tiles of 128; two CTAs per SM, so
 // that the softmax of one overlaps the MMAs of the other.
-//   warp 0      TMA producer: Q once, then per tile K and, once S has been computed, V of the same
-//               keys into the same buffer (rows of the [rows, 3c] QKV matrix).
-//   warp 1      MMA issuer: S = Q K^T (both operands in shared memory, accumulator in tensor
-//               memory), then O += P V with P read from tensor memory (TS form) and V^T from
-//               shared memory. tcgen05 takes TF32 operands K-major only, so V cannot be used as
-//               it lies in memory: the softmax warps write a transposed, swizzled copy.
-//   warps 2-5   one thread per query row: row maximum, 2^x, P (cut to TF32) stored over S in tensor
-//               memory, running sum, rescaling of O only when the maximum moved by more than 2^8;
-//               the same 128 threads transpose the V tile (one key each: its 64 values go to 64
-//               rows of V^T, which consecutive lanes hit in consecutive words, without bank
-//               conflicts).
+//   warp 0      TMA producer: Q once, then per tile K and V (rows of the [rows, 3c] QKV matrix),
+//               each into its own buffer as soon as the previous tile has released it.
+//   warp 1      MMA issuer: S = Q K^T with Q read from tensor memory (TS form) and K from shared
+//               memory, then O += P V with P read from tensor memory and V^T from shared memory.
+//               tcgen05 takes TF32 operands K-major only, so V cannot be used as it lies in
+//               memory: the softmax warps write a transposed, swizzled copy.
+//   warps 2-5   one thread per query row: at the start it moves its row of Q into tensor memory;
+//               per tile it reads its 128 scores into registers in one go, takes the row maximum,
+//               writes P = 2^x (cut to TF32) over S, keeps the running sum, rescales O only when
+//               the maximum moved by more than 2^8, and transposes the V tile (one key each: its
+//               64 values go to 64 rows of V^T, which consecutive lanes hit in consecutive words,
+//               without bank conflicts).
 // Every mbarrier wait is bounded; on expiry the error word is raised and all roles fall through.
 #include "kernels.cuh"
 #include "tc_common.cuh"
@@ -24,11 +25,11 @@ namespace {
 
 constexpr int AT_Q = 128, AT_K = 128, AT_D = 64;
 constexpr int AT_TILE_BYTES = AT_K * AT_D * 4;  // 32 KB: two boxes of [128 rows][32 floats]
-// Q, one buffer that holds the K tile and then the V tile of the same keys, V^T, barriers (+ slack for
-// the 1024-byte alignment). 97 KB: two CTAs per SM, so that one CTA's softmax overlaps the other's MMAs.
+// K tile, V tile (Q passes through it on its way to tensor memory), V^T, slack for the 1024-byte
+// alignment. 97 KB: two CTAs per SM.
 constexpr size_t AT_TC_SMEM = (size_t)AT_TILE_BYTES * 3 + 1024;
-// P overwrites S in place (each thread rewrites its own row), O follows: 192 of 256 allocated columns.
-constexpr uint32_t AT_S_COL = 0, AT_O_COL = 128, AT_TMEM_COLS = 256;
+// P overwrites S in place (each thread rewrites its own row); O and Q follow: all 256 allocated columns.
+constexpr uint32_t AT_S_COL = 0, AT_O_COL = 128, AT_Q_COL = 192, AT_TMEM_COLS = 256;
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -42,41 +43,65 @@ __device__ __forceinline__ bool warp_wait_all(uint64_t* bar, uint32_t parity, vo
   return __all_sync(0xffffffffu, ok);
 }
 
-// Row maximum of this thread's 128 raw scores; MASK: keys after the query do not count.
+// 32 columns of this thread's row into r[OFF .. OFF + 31], without waiting for the data.
+template <int OFF>
+__device__ __forceinline__ void at_ld32(uint32_t taddr, uint32_t (&r)[128]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[OFF + 0]), "=r"(r[OFF + 1]), "=r"(r[OFF + 2]), "=r"(r[OFF + 3]), "=r"(r[OFF + 4]), "=r"(r[OFF + 5]),
+        "=r"(r[OFF + 6]), "=r"(r[OFF + 7]), "=r"(r[OFF + 8]), "=r"(r[OFF + 9]), "=r"(r[OFF + 10]), "=r"(r[OFF + 11]),
+        "=r"(r[OFF + 12]), "=r"(r[OFF + 13]), "=r"(r[OFF + 14]), "=r"(r[OFF + 15]), "=r"(r[OFF + 16]),
+        "=r"(r[OFF + 17]), "=r"(r[OFF + 18]), "=r"(r[OFF + 19]), "=r"(r[OFF + 20]), "=r"(r[OFF + 21]),
+        "=r"(r[OFF + 22]), "=r"(r[OFF + 23]), "=r"(r[OFF + 24]), "=r"(r[OFF + 25]), "=r"(r[OFF + 26]),
+        "=r"(r[OFF + 27]), "=r"(r[OFF + 28]), "=r"(r[OFF + 29]), "=r"(r[OFF + 30]), "=r"(r[OFF + 31])
+      : "r"(taddr + (uint32_t)OFF)
+      : "memory");
+}
+template <int OFF>
+__device__ __forceinline__ void at_st32(uint32_t taddr, const uint32_t (&r)[128]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr + (uint32_t)OFF),
+      "r"(r[OFF + 0]), "r"(r[OFF + 1]), "r"(r[OFF + 2]), "r"(r[OFF + 3]), "r"(r[OFF + 4]), "r"(r[OFF + 5]),
+      "r"(r[OFF + 6]), "r"(r[OFF + 7]), "r"(r[OFF + 8]), "r"(r[OFF + 9]), "r"(r[OFF + 10]), "r"(r[OFF + 11]),
+      "r"(r[OFF + 12]), "r"(r[OFF + 13]), "r"(r[OFF + 14]), "r"(r[OFF + 15]), "r"(r[OFF + 16]), "r"(r[OFF + 17]),
+      "r"(r[OFF + 18]), "r"(r[OFF + 19]), "r"(r[OFF + 20]), "r"(r[OFF + 21]), "r"(r[OFF + 22]), "r"(r[OFF + 23]),
+      "r"(r[OFF + 24]), "r"(r[OFF + 25]), "r"(r[OFF + 26]), "r"(r[OFF + 27]), "r"(r[OFF + 28]), "r"(r[OFF + 29]),
+      "r"(r[OFF + 30]), "r"(r[OFF + 31])
+      : "memory");
+}
+__device__ __forceinline__ void at_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Row maximum of the 128 raw scores in s; MASK: keys after the query do not count.
 template <bool MASK>
-__device__ __forceinline__ float at_row_max(uint32_t s_addr, int kt, int qpos) {
+__device__ __forceinline__ float at_row_max(const uint32_t (&s)[128], int kt, int qpos) {
   float tmax = -INFINITY;
-#pragma unroll 1
-  for (int c0 = 0; c0 < AT_K; c0 += 32) {
-    float v[32];
-    tmem_ld32(s_addr + (uint32_t)c0, v);
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (!MASK || kt + c0 + j <= qpos) tmax = fmaxf(tmax, v[j]);
-  }
+  for (int j = 0; j < AT_K; ++j)
+    if (!MASK || kt + j <= qpos) tmax = fmaxf(tmax, __uint_as_float(s[j]));
   return tmax;
 }
 
-// P = 2^(s * sl2 - mn), cut to TF32 (the bits the MMA reads) so that the returned sum is the sum the
-// MMA sees; written over S.
+// s <- P = 2^(s * sl2 - mn), cut to TF32 (the bits the MMA reads) so that the returned sum is the
+// sum the MMA sees.
 template <bool MASK>
-__device__ __forceinline__ float at_exp_rows(uint32_t s_addr, int kt, int qpos, float sl2, float mn) {
-  float ps = 0.f;
-#pragma unroll 1
-  for (int c0 = 0; c0 < AT_K; c0 += 32) {
-    float v[32];
-    uint32_t w[32];
-    tmem_ld32(s_addr + (uint32_t)c0, v);
+__device__ __forceinline__ float at_exp_rows(uint32_t (&s)[128], int kt, int qpos, float sl2, float mn) {
+  float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      uint32_t bits = __float_as_uint(ex2_approx(fmaf(v[j], sl2, -mn))) & 0xFFFFE000u;
-      if (MASK && kt + c0 + j > qpos) bits = 0u;
-      ps += __uint_as_float(bits);
-      w[j] = bits;
-    }
-    tmem_st32(s_addr + (uint32_t)c0, w);
+  for (int j = 0; j < AT_K; j += 2) {
+    uint32_t b0 = __float_as_uint(ex2_approx(fmaf(__uint_as_float(s[j]), sl2, -mn))) & 0xFFFFE000u;
+    uint32_t b1 = __float_as_uint(ex2_approx(fmaf(__uint_as_float(s[j + 1]), sl2, -mn))) & 0xFFFFE000u;
+    if (MASK && kt + j > qpos) b0 = 0u;
+    if (MASK && kt + j + 1 > qpos) b1 = 0u;
+    ps0 += __uint_as_float(b0);
+    ps1 += __uint_as_float(b1);
+    s[j] = b0;
+    s[j + 1] = b1;
   }
-  return ps;
+  return ps0 + ps1;
 }
 
 __global__ void __launch_bounds__(192, 2)
@@ -89,19 +114,20 @@ __global__ void __launch_bounds__(192, 2)
   const int q0 = qb * AT_Q;
   if (q0 >= len) return;  // the whole CTA: nothing allocated yet
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  uint8_t* q_s = smem;
-  uint8_t* kv_s = smem + AT_TILE_BYTES;                // K tile, then the V tile of the same keys
-  uint8_t* vt_s = smem + 2 * (size_t)AT_TILE_BYTES;    // V^T: [4 key blocks][64 rows d][32 keys]
-  __shared__ uint64_t bars[7];
+  uint8_t* k_s = smem;
+  uint8_t* v_s = smem + AT_TILE_BYTES;               // Q first, then the V tiles
+  uint8_t* vt_s = smem + 2 * (size_t)AT_TILE_BYTES;  // V^T: [4 key blocks][64 rows d][32 keys]
+  __shared__ uint64_t bars[8];
   __shared__ uint32_t tmem_slot;
   __shared__ int failed_word;
   uint64_t* q_full = &bars[0];
-  uint64_t* k_full = &bars[1];
-  uint64_t* v_full = &bars[2];
-  uint64_t* kv_free = &bars[3];   // the V tile has been transposed: the buffer may take the next K tile
-  uint64_t* s_full = &bars[4];    // S is in tensor memory; the K tile is no longer read
-  uint64_t* p_ready = &bars[5];
-  uint64_t* pv_done = &bars[6];
+  uint64_t* q_ready = &bars[1];  // Q is in tensor memory
+  uint64_t* k_full = &bars[2];
+  uint64_t* v_full = &bars[3];
+  uint64_t* v_free = &bars[4];   // the V buffer has been read (Q moved, or a V tile transposed)
+  uint64_t* s_full = &bars[5];   // S is in tensor memory; the K tile is no longer read
+  uint64_t* p_ready = &bars[6];
+  uint64_t* pv_done = &bars[7];
   volatile int* failed = &failed_word;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -110,9 +136,10 @@ __global__ void __launch_bounds__(192, 2)
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_ready, 4);
     mbar_init(k_full, 1);
     mbar_init(v_full, 1);
-    mbar_init(kv_free, 4);
+    mbar_init(v_free, 4);
     mbar_init(s_full, 1);
     mbar_init(p_ready, 4);
     mbar_init(pv_done, 1);
@@ -129,40 +156,40 @@ __global__ void __launch_bounds__(192, 2)
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_qkv) : "memory");
       mbar_expect_tx(q_full, AT_TILE_BYTES);
-      tma_load_2d(q_s, &map_qkv, h * AT_D, r0 + q0, q_full);
-      tma_load_2d(q_s + AT_TILE_BYTES / 2, &map_qkv, h * AT_D + 32, r0 + q0, q_full);
+      tma_load_2d(v_s, &map_qkv, h * AT_D, r0 + q0, q_full);
+      tma_load_2d(v_s + AT_TILE_BYTES / 2, &map_qkv, h * AT_D + 32, r0 + q0, q_full);
       bool ok = true;
       for (int i = 0; i < ntiles && ok; ++i) {
         const int row = r0 + i * AT_K;
-        if (i > 0) ok = mbar_wait(kv_free, (i - 1) & 1, failed, error_flag, 41);
+        if (i > 0) ok = mbar_wait(s_full, (i - 1) & 1, failed, error_flag, 40);  // the S MMAs have read K
         if (!ok) break;
         mbar_expect_tx(k_full, AT_TILE_BYTES);
-        tma_load_2d(kv_s, &map_qkv, c + h * AT_D, row, k_full);
-        tma_load_2d(kv_s + AT_TILE_BYTES / 2, &map_qkv, c + h * AT_D + 32, row, k_full);
-        ok = mbar_wait(s_full, i & 1, failed, error_flag, 40);  // the S MMAs have read K
+        tma_load_2d(k_s, &map_qkv, c + h * AT_D, row, k_full);
+        tma_load_2d(k_s + AT_TILE_BYTES / 2, &map_qkv, c + h * AT_D + 32, row, k_full);
+        ok = mbar_wait(v_free, i & 1, failed, error_flag, 41);  // Q moved (i = 0) / V of tile i - 1 transposed
         if (!ok) break;
         mbar_expect_tx(v_full, AT_TILE_BYTES);
-        tma_load_2d(kv_s, &map_qkv, 2 * c + h * AT_D, row, v_full);
-        tma_load_2d(kv_s + AT_TILE_BYTES / 2, &map_qkv, 2 * c + h * AT_D + 32, row, v_full);
+        tma_load_2d(v_s, &map_qkv, 2 * c + h * AT_D, row, v_full);
+        tma_load_2d(v_s + AT_TILE_BYTES / 2, &map_qkv, 2 * c + h * AT_D + 32, row, v_full);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc_tf32(128, AT_K), idesc_o = umma_idesc_tf32(128, AT_D);
-      bool ok = mbar_wait(q_full, 0, failed, error_flag, 42);
+      bool ok = mbar_wait(q_ready, 0, failed, error_flag, 42);
       for (int i = 0; i < ntiles && ok; ++i) {
-        // ---- S = Q K^T: two 32-wide blocks of the head dimension, four k steps each. S shares its
-        // columns with P of the previous tile, which the MMAs issued before these have read.
+        // ---- S = Q K^T: eight k steps over the head dimension. S shares its columns with P of the
+        // previous tile, which the MMAs issued before these have read.
         ok = mbar_wait(k_full, i & 1, failed, error_flag, 43);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb) {
-          const uint64_t dq = umma_desc_sw128(q_s + kb * (AT_TILE_BYTES / 2));
-          const uint64_t dk = umma_desc_sw128(kv_s + kb * (AT_TILE_BYTES / 2));
+          const uint64_t dk = umma_desc_sw128(k_s + kb * (AT_TILE_BYTES / 2));
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_tf32_ss(tmem_base + AT_S_COL, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_s, (kb | k) != 0);
+            umma_tf32_ts(tmem_base + AT_S_COL, tmem_base + AT_Q_COL + kb * 32 + k * 8, dk + (uint64_t)(k * 2), idesc_s,
+                         (kb | k) != 0);
         }
         umma_commit(s_full);
         // ---- O += P V once P and V^T of this tile are in place
@@ -185,29 +212,68 @@ __global__ void __launch_bounds__(192, 2)
     const int qpos = q0 + r;
     const float sl2 = 0.125f * 1.4426950408889634f;  // 1 / sqrt(64), in powers of two
     float m = -INFINITY, l = 0.f;                    // running maximum (log2 units) and sum
-    bool ok = true;
+    // row r of a [128][64] tile that TMA wrote as two boxes of [128][32] with the 128-byte swizzle:
+    // logical 16-byte chunk jj of the row sits at chunk jj ^ (r & 7)
+    const float4* row_lo = reinterpret_cast<const float4*>(v_s + (size_t)r * 128);
+    const float4* row_hi = reinterpret_cast<const float4*>(v_s + AT_TILE_BYTES / 2 + (size_t)r * 128);
+    bool ok = warp_wait_all(q_full, 0, failed, error_flag, 45);
+    if (ok) {  // Q: shared memory -> tensor memory
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const float4* src = half ? row_hi : row_lo;
+        uint32_t w[32];
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          const float4 x = src[jj ^ (r & 7)];
+          w[4 * jj + 0] = __float_as_uint(x.x);
+          w[4 * jj + 1] = __float_as_uint(x.y);
+          w[4 * jj + 2] = __float_as_uint(x.z);
+          w[4 * jj + 3] = __float_as_uint(x.w);
+        }
+        tmem_st32(tmem_base + AT_Q_COL + lane_addr + (uint32_t)(half * 32), w);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+    }
+    __syncwarp();
+    if (lane == 0) {
+      mbar_arrive(q_ready);
+      mbar_arrive(v_free);
+    }
     for (int i = 0; i < ntiles; ++i) {
       const int kt = i * AT_K;
       const bool diag = kt + AT_K - 1 > q0;  // some key of the tile lies after some query: mask
       if (ok) ok = warp_wait_all(s_full, i & 1, failed, error_flag, 46);
-      float tmax = 0.f;
       if (ok) {
         tc_fence_after();
-        tmax = (diag ? at_row_max<true>(s_addr, kt, qpos) : at_row_max<false>(s_addr, kt, qpos)) * sl2;
-        // the PV MMAs of the previous tile read P and V^T and write O: wait for them
-        if (i > 0) ok = warp_wait_all(pv_done, (i - 1) & 1, failed, error_flag, 47);
-      }
-      if (ok) {
-        tc_fence_after();
+        uint32_t s[128];
+        at_ld32<0>(s_addr, s);
+        at_ld32<32>(s_addr, s);
+        at_ld32<64>(s_addr, s);
+        at_ld32<96>(s_addr, s);
+        at_wait_ld();
+        const float tmax = (diag ? at_row_max<true>(s, kt, qpos) : at_row_max<false>(s, kt, qpos)) * sl2;
         // The maximum is only moved (and O rescaled) when some row of the warp outgrew it by 2^8;
         // until then P simply runs up to 256, harmless in FP32 accumulators. Key kt is visible to
         // every row of the tile, so the first tile sets a finite maximum.
-        if (__any_sync(0xffffffffu, tmax > m + 8.0f)) {
+        const bool move = __any_sync(0xffffffffu, tmax > m + 8.0f);
+        float corr = 1.0f;
+        if (move) {
           const float mn = fmaxf(m, tmax);
-          const float corr = ex2_approx(m - mn);  // 0 on the first tile (l is 0 and O not yet written)
+          corr = ex2_approx(m - mn);  // 0 on the first tile (l is 0 and O not yet written)
           l *= corr;
           m = mn;
-          if (i > 0) {
+        }
+        l += diag ? at_exp_rows<true>(s, kt, qpos, sl2, m) : at_exp_rows<false>(s, kt, qpos, sl2, m);
+        // the PV MMAs of the previous tile read P and V^T and write O: wait for them
+        if (i > 0) ok = warp_wait_all(pv_done, (i - 1) & 1, failed, error_flag, 47);
+        if (ok) {
+          tc_fence_after();
+          at_st32<0>(s_addr, s);
+          at_st32<32>(s_addr, s);
+          at_st32<64>(s_addr, s);
+          at_st32<96>(s_addr, s);
+          if (move && i > 0) {
 #pragma unroll 1
             for (int c0 = 0; c0 < AT_D; c0 += 32) {
               float v[32];
@@ -218,19 +284,18 @@ __global__ void __launch_bounds__(192, 2)
               tmem_st32(o_addr + (uint32_t)c0, w);
             }
           }
+          // V^T: this thread moves key r of the tile
+          ok = warp_wait_all(v_full, i & 1, failed, error_flag, 48);
         }
-        l += diag ? at_exp_rows<true>(s_addr, kt, qpos, sl2, m) : at_exp_rows<false>(s_addr, kt, qpos, sl2, m);
-        // V^T: this thread moves key r of the tile
-        ok = warp_wait_all(v_full, i & 1, failed, error_flag, 48);
         if (ok) {
           float* vt = reinterpret_cast<float*>(vt_s + (r >> 5) * 8192);
           const int kc = (r & 31) >> 2, kw = r & 3;  // 16-byte chunk and word of this key inside a V^T row
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
-            const float4* src = reinterpret_cast<const float4*>(kv_s + half * (AT_TILE_BYTES / 2) + (size_t)r * 128);
+            const float4* src = half ? row_hi : row_lo;
 #pragma unroll
             for (int jj = 0; jj < 8; ++jj) {
-              const float4 x = src[jj ^ (r & 7)];  // logical chunk jj of row r (undo the 128-byte swizzle)
+              const float4 x = src[jj ^ (r & 7)];
               const int d = half * 32 + jj * 4;
               vt[(d + 0) * 32 + ((kc ^ ((d + 0) & 7)) << 2) + kw] = x.x;
               vt[(d + 1) * 32 + ((kc ^ ((d + 1) & 7)) << 2) + kw] = x.y;
@@ -238,14 +303,14 @@ __global__ void __launch_bounds__(192, 2)
               vt[(d + 3) * 32 + ((kc ^ ((d + 3) & 7)) << 2) + kw] = x.w;
             }
           }
+          tmem_wait_st();
+          tc_fence_before();
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // V^T is read by the tensor core
         }
-        tmem_wait_st();
-        tc_fence_before();
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // V^T is read by the tensor core
       }
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(kv_free);
+        mbar_arrive(v_free);
         mbar_arrive(p_ready);
       }
     }
