@@ -247,11 +247,13 @@ struct pg_cache {
   int chain_ctas = 0;
   struct ChainProgram {  // whole-step phase list of the persistent chain kernel for one batch size
     ChainPhase* dev = nullptr;            // in device memory (nullptr: this batch size is not supported)
+    ChainPhase* dev_argmax_only = nullptr;  // the same list whose lm_head reduce phase keeps the row arg-max but stores no logits
     int n = 0;
     std::vector<int> bucket;              // profile bucket of every phase
     unsigned long long* d_times = nullptr;  // n + 1 time stamps, written in profiling runs
   };
   std::map<int, ChainProgram> chain_programs;
+  bool step_wants_logits = true;  // false: the caller of this step only reads the arg-max (greedy decoding)
   // single-kernel decode step (at most 8 sequences)
   MegaLayer* d_mega_layers = nullptr;
   unsigned* d_barrier = nullptr;
@@ -297,6 +299,7 @@ struct pg_cache {
     }
     for (auto& cp : chain_programs) {
       if (cp.second.dev) cudaFree(cp.second.dev);
+      if (cp.second.dev_argmax_only) cudaFree(cp.second.dev_argmax_only);
       if (cp.second.d_times) cudaFree(cp.second.d_times);
     }
     for (auto& g : graphs) cudaGraphExecDestroy(g.second);
@@ -572,6 +575,12 @@ static int ensure_chain_program(pg_cache* c, int batch) {
     PG_CUDA_TRY(cudaMalloc(&prog.dev, ph.size() * sizeof(ChainPhase)));
     PG_CUDA_TRY(cudaMemcpy(prog.dev, ph.data(), ph.size() * sizeof(ChainPhase), cudaMemcpyHostToDevice));
     PG_CUDA_TRY(cudaMalloc(&prog.d_times, (ph.size() + 1) * sizeof(unsigned long long)));
+    // 12.9 MB of logits per step of 64 sequences that greedy decoding never reads
+    std::vector<ChainPhase> lean = ph;
+    for (ChainPhase& p : lean)
+      if (p.kind == CH_ELEM && p.best) p.out = nullptr;
+    PG_CUDA_TRY(cudaMalloc(&prog.dev_argmax_only, lean.size() * sizeof(ChainPhase)));
+    PG_CUDA_TRY(cudaMemcpy(prog.dev_argmax_only, lean.data(), lean.size() * sizeof(ChainPhase), cudaMemcpyHostToDevice));
   }
   c->chain_programs[batch] = prog;
   return PG_OK;
@@ -619,7 +628,7 @@ static cudaError_t enqueue_decode_step(pg_cache* c, int batch, int splits, cudaS
     if (m->t_wte && prog != c->chain_programs.end() && prog->second.dev) {
       // the whole step, from the embedding to the token fed back, as one persistent cooperative kernel
       ChainArgs a = chain_base_args(c, batch);
-      a.phases_dev = prog->second.dev;
+      a.phases_dev = (c->step_wants_logits || prof) ? prog->second.dev : prog->second.dev_argmax_only;
       a.n_phases = prog->second.n;
       if (prof) a.phase_times = prog->second.d_times;  // per-phase time stamps for the operation profile
       cur_bucket = B_OTHER;
@@ -746,7 +755,7 @@ static int run_decode_step(pg_cache* c, int batch) {
     c->decode_launches += launches;
     return PG_OK;
   }
-  auto key = std::make_pair(batch, splits);
+  auto key = std::make_pair(batch, splits * 2 + (c->step_wants_logits ? 1 : 0));
   auto it = c->graphs.find(key);
   if (it == c->graphs.end()) {
     cudaGraph_t graph = nullptr;
@@ -1002,6 +1011,7 @@ static int do_forward_one(const pg_model* m, pg_cache* c, const int32_t* ids, in
   if (!ids) return set_error(PG_INVALID_INPUT, "null ids");
   if (k < 0 || k > MAX_TOPK) return set_error(PG_INVALID_INPUT, "k must be in 0.." + std::to_string(MAX_TOPK));
   if (int r = prepare_step(m, c, ids, batch)) return r;
+  c->step_wants_logits = logits_out != nullptr || k > 0;
   if (int r = run_decode_step(c, batch)) return r;
   for (int b = 0; b < batch; ++b) c->seq_len[b] += 1;
   return fetch_outputs(c, batch, logits_out, argmax_out, topk_vals, topk_idx, k);
@@ -1226,6 +1236,7 @@ int pg_decode_greedy(const pg_model* model, pg_cache* cache, const int32_t* firs
   std::vector<int> start(cache->seq_len.begin(), cache->seq_len.begin() + batch);
   for (int s = 0; s < steps; ++s) {
     if (int r = prepare_step(model, cache, s == 0 ? first_ids : nullptr, batch)) return r;
+    cache->step_wants_logits = false;
     if (int r = run_decode_step(cache, batch)) return r;
     for (int b = 0; b < batch; ++b) cache->seq_len[b] += 1;
   }

@@ -254,6 +254,34 @@ def test_page_sizes_and_attention_splits(oracle, page_tokens, splits):
         assert_logits_close(g.forward_one(int(t), gc), o.forward_one(int(t), oc))
 
 
+def test_greedy_steps_store_no_logits_and_later_steps_return_fresh_ones(midi, oracle):
+    """decode_greedy and arg-max-only forward_one calls run the persistent step with an lm_head reduce
+    phase that keeps the row arg-max but writes no logits; a later call that asks for logits must get
+    that step's logits, not a stale buffer, and the token streams must be the oracle's."""
+    cfg, w, _, o = midi
+    g = pg.Gpt2Model(cfg, w, pg.Gpt2CudaConfig(math_mode="tf32x3"))
+    batch = 10
+    prompts = [synthetic.uniform_prompt(700 + i, 9 + 5 * i, cfg["vocab_size"]) for i in range(batch)]
+    cache = g.new_kv_cache(max_batch=batch)
+    _, first = g.prefill_batch(prompts, cache)
+    steps = g.decode_greedy(first, cache, 4)                # [step, sequence]; steps without logits
+    _, am, _, _ = g.forward_one_batch(steps[-1], cache)     # arg-max only
+    logits, am2, _, _ = g.forward_one_batch(am, cache, want_logits=True)
+    for i, p in enumerate(prompts):
+        oc = o.new_kv_cache()
+        cur = oracle.argmax_logits(o.prefill(p, oc))
+        assert int(first[i]) == cur
+        want = []
+        for _ in range(5):
+            lo = o.forward_one(cur, oc)
+            cur = oracle.argmax_logits(lo)
+            want.append(cur)
+        assert [int(t) for t in steps[:, i]] + [int(am[i])] == want, i
+        lo = o.forward_one(cur, oc)
+        assert_logits_close(logits[i], lo)
+        assert int(am2[i]) == oracle.argmax_logits(lo)
+
+
 @pytest.mark.parametrize("page_tokens", [16, 32, 64])
 def test_batched_tensor_core_step_is_one_persistent_kernel(oracle, monkeypatch, page_tokens):
     """9..64 sequences in the tensor-core modes: the layers and the lm_head of a decode step run as
