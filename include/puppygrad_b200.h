@@ -244,6 +244,20 @@ int pg_op_decode_attention(const float* qkv, const float* keys, const float* val
                            int32_t n_head, int32_t head_dim, int32_t kv_len, int32_t page_tokens,
                            int32_t splits, int32_t device, int32_t reps, float* out,
                            double* seconds_per_launch);
+/* Row-wise symmetric int8 quantisation of a [rows, cols] FP32 matrix on the device:
+ * QuantizedRows::from_f32, src/models/cpu.rs:33-57 (scale = max|w| / 127, 1 for an all-zero row;
+ * q = clamp(round(w / scale), -127, 127)). q_out is [rows, cols] int8, scales_out [rows]. The bytes
+ * and scales equal the reference's. */
+int pg_op_quantize_rows(const float* w, int32_t rows, int32_t cols, int32_t device, int8_t* q_out,
+                        float* scales_out);
+/* out[m, n] = x[m, k] . dequant(q[n, k])^T + bias over int8 weights with one scale per output row:
+ * quantized_transposed_dense_projection_into + quantized_dot, src/models/cpu.rs:99-117, 173-184
+ * (the --quantized-weights variant of the four linears and of the lm_head,
+ * src/models/gpt2/rust.rs:1535-1578, 1815-1849). Decode-sized: m <= 8, k % 16 == 0; bias may be
+ * NULL (the lm_head has none). Timing as in pg_op_linear. */
+int pg_op_linear_q8(const float* x, const int8_t* q, const float* scales, const float* bias, int32_t m,
+                    int32_t n, int32_t k, int32_t device, int32_t reps, float* out,
+                    double* seconds_per_launch);
 /* No counterpart in the reference (its CPU path owns no device memory at all). The same decode
  * attention kernel as above for callers that must not allocate when they call it — a server
  * whose own pool already owns all of HBM, a plugin invoked where its embedder forbids cudaMalloc,

@@ -71,6 +71,9 @@ def lib():
         L.po_dot_scalar.argtypes = [fp, fp, C.c_size_t]
         L.po_transposed_dense_projection.argtypes = [fp, C.c_size_t, C.c_size_t, C.c_size_t, fp, fp, fp]
         L.po_dense_projection.argtypes = [fp, C.c_size_t, C.c_size_t, C.c_size_t, fp, fp, fp]
+        i8p = C.POINTER(C.c_int8)
+        L.po_quantize_rows.argtypes = [fp, C.c_size_t, C.c_size_t, i8p, fp]
+        L.po_quantized_projection.argtypes = [fp, C.c_size_t, C.c_size_t, C.c_size_t, i8p, fp, fp, fp]
         L.po_layer_norm_in_place.argtypes = [fp, C.c_size_t, C.c_size_t, fp, fp, C.c_float]
         L.po_gelu_in_place.argtypes = [fp, C.c_size_t]
         L.po_softmax_in_place.argtypes = [fp, C.c_size_t]
@@ -144,6 +147,25 @@ def transposed_dense_projection(x, rows, in_f, out_f, w, bias):
     bias = np.ascontiguousarray(bias, np.float32)
     out = np.empty(rows * out_f, np.float32)
     lib().po_transposed_dense_projection(_fp(x), rows, in_f, out_f, _fp(w), _fp(bias), _fp(out))
+    return out
+
+
+def quantize_rows(w, rows, cols):
+    """QuantizedRows::from_f32 (cpu.rs:33-57): returns (int8 values [rows, cols], f32 scales [rows])."""
+    w = np.ascontiguousarray(w, np.float32)
+    q = np.empty((rows, cols), np.int8)
+    scales = np.empty(rows, np.float32)
+    lib().po_quantize_rows(_fp(w), rows, cols, q.ctypes.data_as(C.POINTER(C.c_int8)), _fp(scales))
+    return q, scales
+
+
+def quantized_projection(x, rows, in_f, out_f, q, scales, bias):
+    """quantized_transposed_dense_projection_into (cpu.rs:99-117)."""
+    x = np.ascontiguousarray(x, np.float32); q = np.ascontiguousarray(q, np.int8)
+    scales = np.ascontiguousarray(scales, np.float32); bias = np.ascontiguousarray(bias, np.float32)
+    out = np.empty(rows * out_f, np.float32)
+    lib().po_quantized_projection(_fp(x), rows, in_f, out_f, q.ctypes.data_as(C.POINTER(C.c_int8)), _fp(scales),
+                                  _fp(bias), _fp(out))
     return out
 
 

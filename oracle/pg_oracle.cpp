@@ -535,6 +535,39 @@ void po_transposed_dense_projection(const float* x, size_t rows, size_t in_f, si
       out[r * out_f + o] = bias[o] + dot_avx(x + r * in_f, w + o * in_f, in_f);
 }
 
+// QuantizedRows::from_f32 (cpu.rs:33-57): per row scale = max|w| / 127 (1 for an all-zero row; f32::max
+// ignores NaN), q = clamp(round-half-away(w / scale), -127, 127) as i8 (NaN casts to 0).
+void po_quantize_rows(const float* w, size_t rows, size_t cols, int8_t* q, float* scales) {
+  for (size_t r = 0; r < rows; ++r) {
+    const float* src = w + r * cols;
+    float max_abs = 0.0f;
+    for (size_t i = 0; i < cols; ++i) {
+      const float v = std::fabs(src[i]);
+      if (!(v != v)) max_abs = v > max_abs ? v : max_abs;
+    }
+    const float scale = max_abs == 0.0f ? 1.0f : max_abs / 127.0f;
+    scales[r] = scale;
+    for (size_t i = 0; i < cols; ++i) {
+      float t = std::round(src[i] / scale);
+      t = t < -127.0f ? -127.0f : (t > 127.0f ? 127.0f : t);
+      q[r * cols + i] = (t != t) ? (int8_t)0 : (int8_t)t;
+    }
+  }
+}
+
+// quantized_transposed_dense_projection_into + quantized_dot (cpu.rs:99-117, 173-184): every weight is
+// dequantised on the fly as (q as f32) * scale; one sequential f32 sum per output, bias added last.
+void po_quantized_projection(const float* x, size_t rows, size_t in_f, size_t out_f, const int8_t* q,
+                             const float* scales, const float* bias, float* out) {
+  for (size_t r = 0; r < rows; ++r)
+    for (size_t o = 0; o < out_f; ++o) {
+      const float scale = scales[o];
+      float sum = 0.0f;
+      for (size_t i = 0; i < in_f; ++i) sum += x[r * in_f + i] * ((float)q[o * in_f + i] * scale);
+      out[r * out_f + o] = bias[o] + sum;
+    }
+}
+
 void po_dense_projection(const float* x, size_t rows, size_t in_f, size_t out_f, const float* w,
                          const float* bias, float* out) {
   for (size_t r = 0; r < rows; ++r)

@@ -62,6 +62,9 @@ void po_transposed_dense_projection(const float* x, size_t rows, size_t in_f, si
                                     const float* w, const float* bias, float* out); /* cpu.rs:58-75 */
 void po_dense_projection(const float* x, size_t rows, size_t in_f, size_t out_f, const float* w,
                          const float* bias, float* out);                            /* cpu.rs:77-97 */
+void po_quantize_rows(const float* w, size_t rows, size_t cols, int8_t* q, float* scales);  /* cpu.rs:33-57 */
+void po_quantized_projection(const float* x, size_t rows, size_t in_f, size_t out_f, const int8_t* q,
+                             const float* scales, const float* bias, float* out);    /* cpu.rs:99-117, 173-184 */
 void po_layer_norm_in_place(float* x, size_t rows, size_t cols, const float* gamma,
                             const float* beta, float eps);                          /* cpu.rs:119-143 */
 void po_gelu_in_place(float* v, size_t n);                                          /* cpu.rs:145-150 */

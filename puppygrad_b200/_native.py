@@ -88,6 +88,9 @@ SIGNATURES = {
                                C.c_int32, C.c_int32, _fp, C.POINTER(C.c_double)]),
     "pg_op_decode_attention": (C.c_int, [_fp, _fp, _fp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                          C.c_int32, C.c_int32, C.c_int32, _fp, C.POINTER(C.c_double)]),
+    "pg_op_quantize_rows": (C.c_int, [_fp, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int8), _fp]),
+    "pg_op_linear_q8": (C.c_int, [_fp, C.POINTER(C.c_int8), _fp, _fp, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                  C.c_int32, _fp, C.POINTER(C.c_double)]),
     "pg_decode_attention_noalloc": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                               C.c_int32, C.c_int32, C.c_int32, _vp]),
     "pg_generate_greedy": (C.c_int, [_vp, _ip, C.c_int32, C.c_uint64, _ip, _u64p]),

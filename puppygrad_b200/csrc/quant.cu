@@ -1,0 +1,229 @@
+// Row-wise symmetric int8 weights of the reference (QuantizedRows, src/models/cpu.rs:26-56) and the
+// decode-sized projection over them (quantized_transposed_dense_projection_into + quantized_dot,
+// cpu.rs:99-117, 173-184), as single operators behind the C ABI. HBM-bound integer/byte work: one
+// byte per weight is streamed once, 16 bytes per lane per load, nothing is reshaped for tensor cores.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+#include <string>
+
+#include "common.h"
+#include "kernels.cuh"
+
+namespace pg {
+int ensure_device(int device);  // model.cu
+
+namespace {
+
+// ------------------------------------------------------------------ QuantizedRows::from_f32
+// One block per row: scale = max|w| / 127 (1 for an all-zero row; NaN does not take part in the
+// maximum, as with f32::max), q = clamp(round-half-away(w / scale), -127, 127); NaN becomes 0 like
+// Rust's saturating `as i8`. IEEE division and roundf: the bytes equal the reference's.
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const float* __restrict__ w, int8_t* __restrict__ q,
+                                                            float* __restrict__ scales, int cols) {
+  __shared__ float red[8];
+  const size_t r = blockIdx.x;
+  const float* src = w + r * cols;
+  float mx = 0.f;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) mx = fmaxf(mx, fabsf(src[i]));  // fmaxf drops NaN
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) mx = fmaxf(mx, red[i]);
+  const float scale = mx == 0.f ? 1.f : __fdiv_rn(mx, 127.f);
+  if (threadIdx.x == 0) scales[r] = scale;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+    const float t = roundf(__fdiv_rn(src[i], scale));
+    // NaN first: fminf / fmaxf would replace it by the bound, f32::clamp keeps it and `as i8` makes it 0
+    q[r * cols + i] = (t != t) ? (int8_t)0 : (int8_t)fminf(fmaxf(t, -127.f), 127.f);
+  }
+}
+
+// ------------------------------------------------------------------ projection, at most 8 activation rows
+// int8 -> float without the quarter-rate conversion unit: with the sign bit flipped a byte is q + 128,
+// placed in the mantissa of 2^23 it reads 8388608 + q + 128, and one subtraction leaves q exactly.
+__device__ __forceinline__ float q8_to_float(uint32_t flipped_word, int byte) {
+  const uint32_t bits = __byte_perm(flipped_word, 0x4B000000u, 0x7650u | (uint32_t)byte);
+  return __uint_as_float(bits) - 8388736.0f;
+}
+
+// acc[r] += sum over the 16 weights of one load of x[r][i * 16 ..] * q
+template <int MT>
+__device__ __forceinline__ void q8_accumulate(const int4& pk, const float* __restrict__ x, int k, int i, int m,
+                                              float (&acc)[MT]) {
+  const uint32_t wd[4] = {(uint32_t)pk.x ^ 0x80808080u, (uint32_t)pk.y ^ 0x80808080u, (uint32_t)pk.z ^ 0x80808080u,
+                          (uint32_t)pk.w ^ 0x80808080u};
+  float wf[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) wf[j] = q8_to_float(wd[j >> 2], j & 3);
+#pragma unroll
+  for (int r = 0; r < MT; ++r) {
+    if (r < m) {
+      const float4* xr = reinterpret_cast<const float4*>(x + (size_t)r * k + (size_t)i * 16);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 xv = __ldg(xr + j);
+        acc[r] = fmaf(xv.x, wf[4 * j + 0], acc[r]);
+        acc[r] = fmaf(xv.y, wf[4 * j + 1], acc[r]);
+        acc[r] = fmaf(xv.z, wf[4 * j + 2], acc[r]);
+        acc[r] = fmaf(xv.w, wf[4 * j + 3], acc[r]);
+      }
+    }
+  }
+}
+
+// One warp per output row o: out[r][o] = bias[o] + scale[o] * sum_i x[r][i] * q[o][i]. The reference
+// scales every weight before the product (x * (q * scale)); taking the scale out of the sum changes
+// the rounding of the partial sums only (the operator is checked at FP32 tolerance, not bit for bit).
+// k is a multiple of 16: a lane reads 16 weights per load, a warp 512 contiguous bytes, and four
+// loads per lane are in flight before the first is used (the activations come from L1 / L2).
+template <int MT>
+__global__ void __launch_bounds__(256, 4) linear_q8_kernel(const int8_t* __restrict__ q, const float* __restrict__ scales,
+                                                        const float* __restrict__ bias, const float* __restrict__ x,
+                                                        float* __restrict__ out, int m, int n, int k) {
+  constexpr int U = 4;
+  const int lane = threadIdx.x & 31;
+  const int warps = (int)(gridDim.x * blockDim.x) >> 5;
+  const int k16 = k >> 4;
+  for (int o = (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5); o < n; o += warps) {
+    const int4* wrow = reinterpret_cast<const int4*>(q + (size_t)o * k);
+    float acc[MT];
+#pragma unroll
+    for (int r = 0; r < MT; ++r) acc[r] = 0.f;
+    for (int i0 = lane; i0 < k16; i0 += 32 * U) {
+      int4 pk[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i0 + 32 * u < k16) pk[u] = __ldcs(wrow + i0 + 32 * u);  // streamed once: not kept in L1 / L2
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i0 + 32 * u < k16) q8_accumulate<MT>(pk[u], x, k, i0 + 32 * u, m, acc);
+    }
+#pragma unroll
+    for (int r = 0; r < MT; ++r) {
+#pragma unroll
+      for (int s = 16; s > 0; s >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], s);
+    }
+    if (lane == 0) {
+      const float scale = scales[o], b = bias ? bias[o] : 0.f;
+#pragma unroll
+      for (int r = 0; r < MT; ++r)
+        if (r < m) out[(size_t)r * n + o] = b + acc[r] * scale;
+    }
+  }
+}
+
+cudaError_t launch_linear_q8(const int8_t* q, const float* scales, const float* bias, const float* x, float* out, int m,
+                             int n, int k, int sms, cudaStream_t s) {
+  const int blocks = std::max(1, std::min((n + 7) / 8, sms * 4));  // four resident blocks per SM: one wave
+  if (m <= 1) linear_q8_kernel<1><<<blocks, 256, 0, s>>>(q, scales, bias, x, out, m, n, k);
+  else if (m <= 2) linear_q8_kernel<2><<<blocks, 256, 0, s>>>(q, scales, bias, x, out, m, n, k);
+  else if (m <= 4) linear_q8_kernel<4><<<blocks, 256, 0, s>>>(q, scales, bias, x, out, m, n, k);
+  else linear_q8_kernel<8><<<blocks, 256, 0, s>>>(q, scales, bias, x, out, m, n, k);
+  return cudaGetLastError();
+}
+
+struct Buf {
+  void* p = nullptr;
+  ~Buf() {
+    if (p) cudaFree(p);
+  }
+};
+constexpr size_t Q8_FLUSH_BYTES = 256u << 20;  // larger than the 126 MB L2
+
+}  // namespace
+}  // namespace pg
+
+using namespace pg;
+
+#define PG_Q_TRY(expr)                                                                                \
+  do {                                                                                                \
+    cudaError_t _e = (expr);                                                                          \
+    if (_e != cudaSuccess) {                                                                          \
+      rc = set_error(PG_CUDA, std::string("CUDA error: ") + cudaGetErrorString(_e) + " (" #expr ")"); \
+      goto done;                                                                                      \
+    }                                                                                                 \
+  } while (0)
+
+extern "C" int pg_op_quantize_rows(const float* w, int32_t rows, int32_t cols, int32_t device, int8_t* q_out,
+                                   float* scales_out) {
+  if (!w || !q_out || !scales_out) return set_error(PG_INVALID_INPUT, "null argument");
+  if (rows <= 0 || cols <= 0) return set_error(PG_INVALID_INPUT, "rows and cols must be > 0");
+  if (int r = ensure_device(device)) return r;
+  int rc = PG_OK;
+  const size_t total = (size_t)rows * cols;
+  Buf dw, dq, ds;
+  PG_Q_TRY(cudaMalloc(&dw.p, total * sizeof(float)));
+  PG_Q_TRY(cudaMalloc(&dq.p, total));
+  PG_Q_TRY(cudaMalloc(&ds.p, (size_t)rows * sizeof(float)));
+  PG_Q_TRY(cudaMemcpy(dw.p, w, total * sizeof(float), cudaMemcpyHostToDevice));
+  quantize_rows_kernel<<<rows, 256>>>(static_cast<const float*>(dw.p), static_cast<int8_t*>(dq.p),
+                                      static_cast<float*>(ds.p), cols);
+  PG_Q_TRY(cudaGetLastError());
+  PG_Q_TRY(cudaMemcpy(q_out, dq.p, total, cudaMemcpyDeviceToHost));
+  PG_Q_TRY(cudaMemcpy(scales_out, ds.p, (size_t)rows * sizeof(float), cudaMemcpyDeviceToHost));
+done:
+  return rc;
+}
+
+extern "C" int pg_op_linear_q8(const float* x, const int8_t* q, const float* scales, const float* bias, int32_t m,
+                               int32_t n, int32_t k, int32_t device, int32_t reps, float* out,
+                               double* seconds_per_launch) {
+  if (!x || !q || !scales || !out) return set_error(PG_INVALID_INPUT, "null argument");
+  if (m <= 0 || n <= 0 || k <= 0) return set_error(PG_INVALID_INPUT, "m, n, k must be > 0");
+  if (m > 8) return set_error(PG_INVALID_INPUT, "the int8 projection is the decode path: m <= 8");
+  if (k % 16 != 0) return set_error(PG_INVALID_INPUT, "the int8 projection needs k to be a multiple of 16");
+  if (int r = ensure_device(device)) return r;
+  int rc = PG_OK;
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  Buf dx, dq, ds, db, dout, dflush;
+  cudaStream_t s = nullptr;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  PG_Q_TRY(cudaStreamCreate(&s));
+  PG_Q_TRY(cudaMalloc(&dx.p, (size_t)m * k * sizeof(float)));
+  PG_Q_TRY(cudaMalloc(&dq.p, (size_t)n * k));
+  PG_Q_TRY(cudaMalloc(&ds.p, (size_t)n * sizeof(float)));
+  PG_Q_TRY(cudaMalloc(&dout.p, (size_t)m * n * sizeof(float)));
+  PG_Q_TRY(cudaMemcpyAsync(dx.p, x, (size_t)m * k * sizeof(float), cudaMemcpyHostToDevice, s));
+  PG_Q_TRY(cudaMemcpyAsync(dq.p, q, (size_t)n * k, cudaMemcpyHostToDevice, s));
+  PG_Q_TRY(cudaMemcpyAsync(ds.p, scales, (size_t)n * sizeof(float), cudaMemcpyHostToDevice, s));
+  if (bias) {
+    PG_Q_TRY(cudaMalloc(&db.p, (size_t)n * sizeof(float)));
+    PG_Q_TRY(cudaMemcpyAsync(db.p, bias, (size_t)n * sizeof(float), cudaMemcpyHostToDevice, s));
+  }
+#define PG_Q_LAUNCH                                                                                               \
+  launch_linear_q8(static_cast<const int8_t*>(dq.p), static_cast<const float*>(ds.p), static_cast<const float*>(db.p), \
+                   static_cast<const float*>(dx.p), static_cast<float*>(dout.p), m, n, k, sms, s)
+  PG_Q_TRY(PG_Q_LAUNCH);
+  PG_Q_TRY(cudaMemcpyAsync(out, dout.p, (size_t)m * n * sizeof(float), cudaMemcpyDeviceToHost, s));
+  PG_Q_TRY(cudaStreamSynchronize(s));
+  if (reps > 0 && seconds_per_launch) {
+    PG_Q_TRY(cudaMalloc(&dflush.p, Q8_FLUSH_BYTES));
+    PG_Q_TRY(cudaEventCreate(&e0));
+    PG_Q_TRY(cudaEventCreate(&e1));
+    double total = 0.0;
+    for (int i = 0; i < reps + 3; ++i) {
+      PG_Q_TRY(cudaMemsetAsync(dflush.p, i, Q8_FLUSH_BYTES, s));
+      PG_Q_TRY(cudaEventRecord(e0, s));
+      PG_Q_TRY(PG_Q_LAUNCH);
+      PG_Q_TRY(cudaEventRecord(e1, s));
+      PG_Q_TRY(cudaEventSynchronize(e1));
+      float ms = 0.f;
+      PG_Q_TRY(cudaEventElapsedTime(&ms, e0, e1));
+      if (i >= 3) total += ms * 1e-3;
+    }
+    *seconds_per_launch = total / reps;
+  }
+#undef PG_Q_LAUNCH
+done:
+  if (s) cudaStreamSynchronize(s);
+  if (e0) cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  if (s) cudaStreamDestroy(s);
+  return rc;
+}

@@ -32,6 +32,37 @@ def linear(x, w, bias=None, resid=None, epilogue: str = "none", math_mode: str =
     return out, (float(sec.value) if reps > 0 else None)
 
 
+def quantize_rows(w, device: int = 0):
+    """Row-wise symmetric int8 quantisation on the device (QuantizedRows::from_f32 of the reference).
+    w [rows, cols] -> (int8 [rows, cols], float32 scales [rows])."""
+    w = np.ascontiguousarray(w, np.float32)
+    rows, cols = w.shape
+    q = np.empty((rows, cols), np.int8)
+    scales = np.empty(rows, np.float32)
+    check(N.lib.pg_op_quantize_rows(w.ctypes.data_as(C.POINTER(C.c_float)), rows, cols, device,
+                                    q.ctypes.data_as(C.POINTER(C.c_int8)),
+                                    scales.ctypes.data_as(C.POINTER(C.c_float))))
+    return q, scales
+
+
+def linear_q8(x, q, scales, bias=None, device: int = 0, reps: int = 0):
+    """out = x @ dequant(q).T (+ bias) over int8 weights with one scale per output row (the
+    reference's quantized projection); at most 8 rows of x. Returns (out, seconds_per_launch or None)."""
+    x = np.ascontiguousarray(x, np.float32)
+    q = np.ascontiguousarray(q, np.int8)
+    scales = np.ascontiguousarray(scales, np.float32)
+    m, k = x.shape
+    n = q.shape[0]
+    assert q.shape[1] == k and scales.shape == (n,)
+    out = np.empty((m, n), np.float32)
+    fp = lambda a: a.ctypes.data_as(C.POINTER(C.c_float)) if a is not None else None
+    bias = None if bias is None else np.ascontiguousarray(bias, np.float32)
+    sec = C.c_double(0.0)
+    check(N.lib.pg_op_linear_q8(fp(x), q.ctypes.data_as(C.POINTER(C.c_int8)), fp(scales), fp(bias), m, n, k, device,
+                                reps, fp(out), C.byref(sec)))
+    return out, (float(sec.value) if reps > 0 else None)
+
+
 def decode_attention(qkv, keys, values, page_tokens: int = 32, splits: int = 1, device: int = 0, reps: int = 0):
     """One new token per sequence against `kv_len` cached positions.
     qkv [batch, 3*c]; keys, values [batch, n_head, kv_len, head_dim]. Returns (out [batch, c], seconds)."""

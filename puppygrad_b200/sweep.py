@@ -2,6 +2,7 @@
 
     python -m puppygrad_b200.sweep linear --m 1 8 64 --n 4800 1600 6400 --k 1600 --math fp32 tf32x3
     python -m puppygrad_b200.sweep linear --preset xl
+    python -m puppygrad_b200.sweep linear_q8 --m 1 8 --n 4800 6400 --k 1600
     python -m puppygrad_b200.sweep prefill --model small --seqs 8 --prompt-len 1024 --math fp32 tf32
 
 Prints one JSON line per case: seconds per launch, algorithmic GB/s (4*(k*n + m*k + m*n + n) bytes)
@@ -60,6 +61,23 @@ def attention_case(batch, n_head, kv_len, splits, reps, seed=0):
             "us": sec * 1e6, "gbps": bytes_ / sec / 1e9, "max_rel_err_vs_f64": err}
 
 
+def linear_q8_case(m, n, k, reps, seed=0):
+    """Decode-sized projection over int8 row-quantised weights. Algorithmic bytes: n*k weights +
+    4*(n scales + n bias + m*k + m*n)."""
+    rng = np.random.default_rng(seed + 7 * m + 13 * n + 17 * k)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    w = rng.standard_normal((n, k), dtype=np.float32)
+    b = rng.standard_normal(n, dtype=np.float32)
+    q, scales = ops.quantize_rows(w)
+    out, sec = ops.linear_q8(x, q, scales, b, reps=reps)
+    deq = q[:4].astype(np.float64) * scales[:4, None].astype(np.float64)
+    want = x.astype(np.float64) @ deq.T + b[:4]
+    err = float(np.abs(out[:, :4] - want).max() / max(np.abs(want).max(), 1e-30))
+    bytes_ = n * k + 4 * (2 * n + m * k + m * n)
+    return {"op": "linear_q8", "m": m, "n": n, "k": k, "us": sec * 1e6, "gbps": bytes_ / sec / 1e9,
+            "fp32_equivalent_gbps": 4 * n * k / sec / 1e9, "max_rel_err_vs_f64": err}
+
+
 def prefill_case(preset, seqs, prompt_len, math, reps):
     """Whole prefill of `seqs` prompts of `prompt_len` tokens (seeded random weights and ids),
     device-timed; the best of `reps` runs after one warm-up."""
@@ -86,7 +104,7 @@ def prefill_case(preset, seqs, prompt_len, math, reps):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["linear", "attention", "prefill"])
+    ap.add_argument("op", choices=["linear", "linear_q8", "attention", "prefill"])
     ap.add_argument("--model", default="small", help="prefill: model preset")
     ap.add_argument("--seqs", type=int, default=8, help="prefill: prompts per call")
     ap.add_argument("--prompt-len", type=int, default=1024)
@@ -105,6 +123,12 @@ def main():
     if a.op == "prefill":
         for math in a.math:
             print(json.dumps(prefill_case(a.model, a.seqs, a.prompt_len, math, a.reps)), flush=True)
+        return
+    if a.op == "linear_q8":
+        for m in a.m:
+            for n in a.n:
+                for k in a.k:
+                    print(json.dumps(linear_q8_case(m, n, k, a.reps)), flush=True)
         return
     if a.op == "attention":
         for b in a.batch:

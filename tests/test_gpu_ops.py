@@ -3,6 +3,7 @@
 import numpy as np
 import pytest
 
+import puppygrad_b200 as pg
 from puppygrad_b200 import ops
 
 pytestmark = pytest.mark.gpu
@@ -85,6 +86,47 @@ def test_linear_tf32_single_pass_is_within_its_stated_bound(oracle, m, n, k, epi
     if epilogue == "resid":
         full = full + r
     assert np.abs(got - full).max() <= 2e-3 * np.abs(full).max()
+
+
+# ---- int8 row-quantised weights (the reference's --quantized-weights variant)
+@pytest.mark.parametrize("rows,cols", [(4, 3), (37, 768), (300, 1600), (5, 6400)])
+def test_quantize_rows_is_bit_identical_to_oracle(oracle, rows, cols):
+    """QuantizedRows::from_f32 (cpu.rs:33-57) on the device: integer / byte work, so the bytes and the
+    scales must equal the oracle's exactly, including an all-zero row and a NaN entry."""
+    rng = np.random.default_rng(rows + cols)
+    w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float32)
+    w[rows // 2] = 0.0
+    w[0, cols - 1] = np.nan
+    w[rows - 1, 0] = 3.0   # one dominant value: the rest of the row quantises to small integers
+    q, scales = ops.quantize_rows(w)
+    oq, oscales = oracle.quantize_rows(w, rows, cols)
+    assert np.array_equal(scales, oscales)
+    assert np.array_equal(q, oq)
+
+
+@pytest.mark.parametrize("m,n,k,with_bias", [(1, 4800, 1600, True), (8, 1600, 6400, True), (3, 50257, 768, False),
+                                             (2, 7, 48, True), (5, 3072, 768, True)])
+def test_linear_q8_matches_oracle(oracle, m, n, k, with_bias):
+    """quantized_transposed_dense_projection_into (cpu.rs:99-117): FP32 activations against int8 rows
+    dequantised on the fly. Same tolerance as the FP32 linears (1e-3 relative, 1e-4 absolute): the
+    kernel sums in a different order and applies the row scale after the sum."""
+    rng = np.random.default_rng(m + n + k)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.05)
+    b = rng.standard_normal(n, dtype=np.float32) if with_bias else None
+    q, scales = oracle.quantize_rows(w, n, k)
+    got, _ = ops.linear_q8(x, q, scales, b)
+    want = oracle.quantized_projection(x, m, k, n, q, scales, b if with_bias else np.zeros(n, np.float32)).reshape(m, n)
+    np.testing.assert_allclose(got, want, rtol=1e-3, atol=1e-4)
+
+
+def test_linear_q8_rejects_prefill_sized_inputs():
+    x = np.zeros((9, 32), np.float32)
+    q = np.zeros((4, 32), np.int8)
+    with pytest.raises(pg.Gpt2Error, match="m <= 8"):
+        ops.linear_q8(x, q, np.ones(4, np.float32))
+    with pytest.raises(pg.Gpt2Error, match="multiple of 16"):
+        ops.linear_q8(np.zeros((1, 24), np.float32), np.zeros((4, 24), np.int8), np.ones(4, np.float32))
 
 
 def oracle_attention(oracle, qkv, keys, values):

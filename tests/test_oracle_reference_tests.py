@@ -31,6 +31,43 @@ def test_transposed_dense_projection_matches_dense_projection(oracle):
     assert np.all(np.abs(dense - tdense) <= 1e-6)
 
 
+def test_quantized_projection_returns_finite_values(oracle):
+    """cpu.rs:327-343, plus what the reference's quantiser implies for the same inputs: the bytes and
+    scales equal an independent float32 restatement, and the projection equals the FP32 projection
+    over the dequantised weights."""
+    x = synthetic.patterned(6, 0.2)
+    weight = synthetic.patterned(12, 0.1)
+    bias = np.array([0.5, -0.25, 0.125, 0.0], np.float32)
+    wt = oracle.transpose_in_out(weight, 3, 4)
+    q, scales = oracle.quantize_rows(wt, 4, 3)
+    out = oracle.quantized_projection(x, 2, 3, 4, q, scales, bias)
+    assert out.shape == (8,) and np.isfinite(out).all()
+    rows = wt.reshape(4, 3)
+    want_scales = (np.abs(rows).max(axis=1) / np.float32(127.0)).astype(np.float32)
+    assert np.array_equal(scales, want_scales)
+    t = (rows / want_scales[:, None]).astype(np.float32).astype(np.float64)
+    want_q = np.clip(np.where(t >= 0, np.floor(t + 0.5), np.ceil(t - 0.5)), -127, 127).astype(np.int8)
+    assert np.array_equal(q, want_q)
+    deq = (q.astype(np.float32) * scales[:, None]).astype(np.float32)
+    assert np.all(np.abs(out - oracle.transposed_dense_projection(x, 2, 3, 4, deq, bias)) <= 1e-6)
+
+
+def test_quantized_rows_edge_cases(oracle):
+    """QuantizedRows::from_f32 (cpu.rs:33-57): an all-zero row gets scale 1 and zeros, the largest
+    magnitude of a row maps to +-127, every weight is reproduced within half a step, NaN does not
+    take part in the row maximum and becomes 0."""
+    rng = np.random.default_rng(3)
+    w = rng.standard_normal((5, 64)).astype(np.float32)
+    w[2] = 0.0
+    w[3, 7] = np.nan
+    q, scales = oracle.quantize_rows(w, 5, 64)
+    assert scales[2] == 1.0 and not q[2].any()
+    assert q[3, 7] == 0 and np.isfinite(scales[3])
+    for r in (0, 1, 4):
+        assert np.abs(q[r]).max() == 127
+        assert np.all(np.abs(q[r].astype(np.float32) * scales[r] - w[r]) <= 0.5 * scales[r] * (1 + 1e-6))
+
+
 def test_dot_lane_order_is_the_avx_one(oracle):
     """cpu.rs:231-254: lane j sums elements i = j (mod 8) unfused; lanes added 0..7; scalar tail."""
     rng = np.random.default_rng(5)
