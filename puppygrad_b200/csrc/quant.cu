@@ -117,12 +117,103 @@ __global__ void __launch_bounds__(256, 4) linear_q8_kernel(const int8_t* __restr
   }
 }
 
+// The same projection with the activations held in shared memory (the default; the kernel above is
+// the fallback when [MT][k] floats do not fit): read from L1 they cost 4 x MT 16-byte loads per lane
+// for every 16 weights and bound the kernel. One block of
+// 32 warps per SM stages x once ([MT][k] floats, at most 227 KB) and then walks its rows. Lane i reads
+// the four 16-byte units 4 i .. 4 i + 3 of a row; unit (i, j) is stored at 4 i + (j ^ ((i >> 1) & 3)),
+// so that the eight lanes of a quarter warp hit eight different bank groups.
+template <int MT>
+__global__ void __launch_bounds__(1024, 1) linear_q8_smem_kernel(const int8_t* __restrict__ q,
+                                                                 const float* __restrict__ scales,
+                                                                 const float* __restrict__ bias,
+                                                                 const float* __restrict__ x, float* __restrict__ out,
+                                                                 int m, int n, int k) {
+  extern __shared__ float4 xs[];
+  constexpr int U = 4;
+  const int lane = threadIdx.x & 31;
+  const int k4 = k >> 2, k16 = k >> 4;
+  for (int idx = threadIdx.x; idx < MT * k4; idx += blockDim.x) {
+    const int r = idx / k4, u = idx - r * k4;
+    const int i = u >> 2, j = u & 3;
+    const float4 v = r < m ? __ldg(reinterpret_cast<const float4*>(x) + (size_t)r * k4 + u) : make_float4(0.f, 0.f, 0.f, 0.f);
+    xs[r * k4 + 4 * i + (j ^ ((i >> 1) & 3))] = v;
+  }
+  __syncthreads();
+  const int warps = (int)(gridDim.x * blockDim.x) >> 5;
+  for (int o = (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5); o < n; o += warps) {
+    const int4* wrow = reinterpret_cast<const int4*>(q + (size_t)o * k);
+    float acc[MT];
+#pragma unroll
+    for (int r = 0; r < MT; ++r) acc[r] = 0.f;
+    for (int i0 = lane; i0 < k16; i0 += 32 * U) {
+      int4 pk[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i0 + 32 * u < k16) pk[u] = __ldcs(wrow + i0 + 32 * u);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = i0 + 32 * u;
+        if (i < k16) {
+          const uint32_t wd[4] = {(uint32_t)pk[u].x ^ 0x80808080u, (uint32_t)pk[u].y ^ 0x80808080u,
+                                  (uint32_t)pk[u].z ^ 0x80808080u, (uint32_t)pk[u].w ^ 0x80808080u};
+          const int sw = (i >> 1) & 3;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float w0 = q8_to_float(wd[j], 0), w1 = q8_to_float(wd[j], 1), w2 = q8_to_float(wd[j], 2),
+                        w3 = q8_to_float(wd[j], 3);
+#pragma unroll
+            for (int r = 0; r < MT; ++r) {
+              const float4 xv = xs[r * k4 + 4 * i + (j ^ sw)];
+              acc[r] = fmaf(xv.x, w0, acc[r]);
+              acc[r] = fmaf(xv.y, w1, acc[r]);
+              acc[r] = fmaf(xv.z, w2, acc[r]);
+              acc[r] = fmaf(xv.w, w3, acc[r]);
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < MT; ++r) {
+#pragma unroll
+      for (int s = 16; s > 0; s >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], s);
+    }
+    if (lane == 0) {
+      const float scale = scales[o], b = bias ? bias[o] : 0.f;
+#pragma unroll
+      for (int r = 0; r < MT; ++r)
+        if (r < m) out[(size_t)r * n + o] = b + acc[r] * scale;
+    }
+  }
+}
+
+constexpr size_t Q8_MAX_SMEM = 227 * 1024;
+
+template <int MT>
+cudaError_t launch_q8_smem(const int8_t* q, const float* scales, const float* bias, const float* x, float* out, int m,
+                           int n, int k, int sms, cudaStream_t s) {
+  const size_t smem = (size_t)MT * k * sizeof(float);
+  cudaError_t e = cudaFuncSetAttribute(linear_q8_smem_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  const int blocks = std::max(1, std::min((n + 31) / 32, sms));
+  linear_q8_smem_kernel<MT><<<blocks, 1024, smem, s>>>(q, scales, bias, x, out, m, n, k);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_linear_q8(const int8_t* q, const float* scales, const float* bias, const float* x, float* out, int m,
                              int n, int k, int sms, cudaStream_t s) {
+  const int mt = m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : 8;
+  if ((size_t)mt * k * sizeof(float) <= Q8_MAX_SMEM) {
+    if (mt == 1) return launch_q8_smem<1>(q, scales, bias, x, out, m, n, k, sms, s);
+    if (mt == 2) return launch_q8_smem<2>(q, scales, bias, x, out, m, n, k, sms, s);
+    if (mt == 4) return launch_q8_smem<4>(q, scales, bias, x, out, m, n, k, sms, s);
+    return launch_q8_smem<8>(q, scales, bias, x, out, m, n, k, sms, s);
+  }
   const int blocks = std::max(1, std::min((n + 7) / 8, sms * 4));  // four resident blocks per SM: one wave
-  if (m <= 1) linear_q8_kernel<1><<<blocks, 256, 0, s>>>(q, scales, bias, x, out, m, n, k);
-  else if (m <= 2) linear_q8_kernel<2><<<blocks, 256, 0, s>>>(q, scales, bias, x, out, m, n, k);
-  else if (m <= 4) linear_q8_kernel<4><<<blocks, 256, 0, s>>>(q, scales, bias, x, out, m, n, k);
+  if (mt == 1) linear_q8_kernel<1><<<blocks, 256, 0, s>>>(q, scales, bias, x, out, m, n, k);
+  else if (mt == 2) linear_q8_kernel<2><<<blocks, 256, 0, s>>>(q, scales, bias, x, out, m, n, k);
+  else if (mt == 4) linear_q8_kernel<4><<<blocks, 256, 0, s>>>(q, scales, bias, x, out, m, n, k);
   else linear_q8_kernel<8><<<blocks, 256, 0, s>>>(q, scales, bias, x, out, m, n, k);
   return cudaGetLastError();
 }
