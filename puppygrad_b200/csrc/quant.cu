@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(1024, 1) linear_q8_smem_kernel(const int8_t* _
                                                                  const float* __restrict__ x, float* __restrict__ out,
                                                                  int m, int n, int k) {
   extern __shared__ float4 xs[];
-  constexpr int U = 4;
+  constexpr int U = 2;  // loads in flight per lane and row
   const int lane = threadIdx.x & 31;
   const int k4 = k >> 2, k16 = k >> 4;
   for (int idx = threadIdx.x; idx < MT * k4; idx += blockDim.x) {
@@ -140,50 +140,75 @@ __global__ void __launch_bounds__(1024, 1) linear_q8_smem_kernel(const int8_t* _
     xs[r * k4 + 4 * i + (j ^ ((i >> 1) & 3))] = v;
   }
   __syncthreads();
+  // A warp walks two neighbouring output rows at a time: every activation read from shared memory
+  // then serves eight weights instead of four.
+  constexpr int R = 2;
   const int warps = (int)(gridDim.x * blockDim.x) >> 5;
-  for (int o = (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5); o < n; o += warps) {
+  for (int o = (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5) * R; o < n; o += warps * R) {
     const int4* wrow = reinterpret_cast<const int4*>(q + (size_t)o * k);
-    float acc[MT];
+    const bool two = o + 1 < n;
+    float acc[R][MT];
 #pragma unroll
-    for (int r = 0; r < MT; ++r) acc[r] = 0.f;
+    for (int rr = 0; rr < R; ++rr)
+#pragma unroll
+      for (int r = 0; r < MT; ++r) acc[rr][r] = 0.f;
     for (int i0 = lane; i0 < k16; i0 += 32 * U) {
-      int4 pk[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u)
-        if (i0 + 32 * u < k16) pk[u] = __ldcs(wrow + i0 + 32 * u);
+      int4 pk[R][U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int i = i0 + 32 * u;
         if (i < k16) {
-          const uint32_t wd[4] = {(uint32_t)pk[u].x ^ 0x80808080u, (uint32_t)pk[u].y ^ 0x80808080u,
-                                  (uint32_t)pk[u].z ^ 0x80808080u, (uint32_t)pk[u].w ^ 0x80808080u};
+          pk[0][u] = __ldcs(wrow + i);
+          pk[1][u] = two ? __ldcs(wrow + k16 + i) : make_int4(0, 0, 0, 0);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = i0 + 32 * u;
+        if (i < k16) {
           const int sw = (i >> 1) & 3;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const float w0 = q8_to_float(wd[j], 0), w1 = q8_to_float(wd[j], 1), w2 = q8_to_float(wd[j], 2),
-                        w3 = q8_to_float(wd[j], 3);
+            float w[R][4];
+#pragma unroll
+            for (int rr = 0; rr < R; ++rr) {
+              const int word = j == 0 ? pk[rr][u].x : j == 1 ? pk[rr][u].y : j == 2 ? pk[rr][u].z : pk[rr][u].w;
+              const uint32_t wd = (uint32_t)word ^ 0x80808080u;
+#pragma unroll
+              for (int e = 0; e < 4; ++e) w[rr][e] = q8_to_float(wd, e);
+            }
 #pragma unroll
             for (int r = 0; r < MT; ++r) {
               const float4 xv = xs[r * k4 + 4 * i + (j ^ sw)];
-              acc[r] = fmaf(xv.x, w0, acc[r]);
-              acc[r] = fmaf(xv.y, w1, acc[r]);
-              acc[r] = fmaf(xv.z, w2, acc[r]);
-              acc[r] = fmaf(xv.w, w3, acc[r]);
+#pragma unroll
+              for (int rr = 0; rr < R; ++rr) {
+                acc[rr][r] = fmaf(xv.x, w[rr][0], acc[rr][r]);
+                acc[rr][r] = fmaf(xv.y, w[rr][1], acc[rr][r]);
+                acc[rr][r] = fmaf(xv.z, w[rr][2], acc[rr][r]);
+                acc[rr][r] = fmaf(xv.w, w[rr][3], acc[rr][r]);
+              }
             }
           }
         }
       }
     }
 #pragma unroll
-    for (int r = 0; r < MT; ++r) {
+    for (int rr = 0; rr < R; ++rr)
 #pragma unroll
-      for (int s = 16; s > 0; s >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], s);
-    }
+      for (int r = 0; r < MT; ++r) {
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) acc[rr][r] += __shfl_xor_sync(0xffffffffu, acc[rr][r], s);
+      }
     if (lane == 0) {
-      const float scale = scales[o], b = bias ? bias[o] : 0.f;
 #pragma unroll
-      for (int r = 0; r < MT; ++r)
-        if (r < m) out[(size_t)r * n + o] = b + acc[r] * scale;
+      for (int rr = 0; rr < R; ++rr) {
+        if (o + rr < n) {
+          const float scale = scales[o + rr], b = bias ? bias[o + rr] : 0.f;
+#pragma unroll
+          for (int r = 0; r < MT; ++r)
+            if (r < m) out[(size_t)r * n + o + rr] = b + acc[rr][r] * scale;
+        }
+      }
     }
   }
 }
@@ -196,7 +221,7 @@ cudaError_t launch_q8_smem(const int8_t* q, const float* scales, const float* bi
   const size_t smem = (size_t)MT * k * sizeof(float);
   cudaError_t e = cudaFuncSetAttribute(linear_q8_smem_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  const int blocks = std::max(1, std::min((n + 31) / 32, sms));
+  const int blocks = std::max(1, std::min((n + 63) / 64, sms));  // 32 warps of two rows each
   linear_q8_smem_kernel<MT><<<blocks, 1024, smem, s>>>(q, scales, bias, x, out, m, n, k);
   return cudaGetLastError();
 }
