@@ -70,10 +70,12 @@ typedef struct {
   int32_t page_tokens;  /* KV page size in tokens: 16, 32 or 64 (default 32) */
   int32_t use_graphs;   /* 0 = default (on), 1 = on, 2 = off: one CUDA graph per decode step */
   int32_t attn_splits;  /* split-K factor of decode attention, 0 = choose from the batch */
-  int32_t persistent_step; /* 1 = run a decode step of at most 8 sequences as one persistent
-                              cooperative kernel (grid barriers between phases) instead of a graph
-                              of kernels; off by default (on B200 it measured 336 us against
-                              290 us per GPT-2 small token for the kernel graph) */
+  int32_t persistent_step; /* decode steps of at most 8 sequences (head_dim 64, n_positions <= 1024) can run as ONE
+                              persistent cooperative kernel whose weight stream runs ahead of the dependent
+                              operations and whose CTAs exchange activations as tagged words instead of meeting
+                              at grid barriers. 0 = where it measured faster than one kernel per operation in a
+                              CUDA graph (up to 4 sequences with FP32 weights; always with BF16 / int8 weights,
+                              which only that kernel reads), 1 = whenever the shapes allow, 2 = never */
   int32_t reserved[2];
 } pg_backend_config;
 
@@ -223,6 +225,14 @@ int pg_cache_time_begin(pg_cache* cache);
 int pg_cache_time_end(pg_cache* cache, double* seconds);
 /* Kernels launched so far by decode steps on this cache. No reference counterpart. */
 uint64_t pg_cache_kernel_launches(const pg_cache* cache);
+/* Test hook, no reference counterpart: makes one bounded wait of the NEXT decode step on this cache
+ * run out by its limit. The step's persistent kernel is launched with `spin_limit` polls per wait
+ * (a few thousand: microseconds) and is made to wait for a hand-over that never comes; every CTA
+ * gives up at the limit, records the error and ends, and the call that ran the step returns
+ * PG_TIMEOUT. Nothing faults and nothing waits without a limit. After a PG_TIMEOUT the cache's
+ * device-side synchronisation state is re-initialised by the library, but the sequences in it are
+ * undefined: clear the cache (or prefill again) before the next use. */
+int pg_cache_debug_expire_next_wait(pg_cache* cache, uint32_t spin_limit);
 
 /* One linear on host buffers, out[m, n] = x[m, k] . w[n, k]^T (+ bias[n]) then epilogue
  * (0 none, 1 tanh-GELU, 2 out = resid + value): transposed_dense_projection_into,

@@ -331,15 +331,18 @@ class Model:
                                                _u64(out), C.byref(n)))
         return [int(t) for t in out[:n.value]]
 
-    def forward_one_batch(self, tokens, caches, want_logits=False):
+    def forward_one_batch(self, tokens, caches, want_logits=False, want_argmax=True):
+        """One position for every sequence. With neither output asked for (prompt positions whose
+        logits nobody reads) the lm_head is skipped; the caches receive the same K and V."""
         tokens = np.ascontiguousarray(tokens, np.uint64)
         b = tokens.size
         handles = (C.c_void_p * b)(*[c._h for c in caches])
         logits = np.empty((b, self.vocab_size), np.float32) if want_logits else None
-        am = np.empty(b, np.uint64)
+        am = np.empty(b, np.uint64) if (want_argmax or want_logits) else None
         _check(lib().po_forward_one_batch(self._h, _u64(tokens), handles, b,
-                                          _fp(logits) if want_logits else None, _u64(am)))
-        return (logits if want_logits else None), am.astype(np.int64)
+                                          _fp(logits) if want_logits else None,
+                                          _u64(am) if am is not None else None))
+        return (logits if want_logits else None), (am.astype(np.int64) if am is not None else None)
 
 
 # ------------------------------------------------------------------ sampling

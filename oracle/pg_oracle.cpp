@@ -806,6 +806,10 @@ int po_forward_one_batch(const po_model* mp, const uint64_t* tokens, po_cache* c
     linear(mlp.data(), f, c, bl.c_proj_mlp_w.data(), bl.c_proj_mlp_b.data(), mp2.data());
     add_in_place(x.data(), mp2.data(), nb * c);
   }
+  if (!logits && !argmax) {  // prompt positions whose logits nobody reads: the cache is all that is kept
+    for (uint64_t b = 0; b < nb; ++b) caches[b]->seq_len += 1;
+    return PO_OK;
+  }
   layer_norm_in_place(x.data(), nb, c, m.ln_f_g.data(), m.ln_f_b.data(), m.cfg.layer_norm_epsilon);
   std::vector<float> local;
   float* lg = logits;

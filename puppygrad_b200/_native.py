@@ -84,6 +84,7 @@ SIGNATURES = {
     "pg_cache_time_begin": (C.c_int, [_vp]),
     "pg_cache_time_end": (C.c_int, [_vp, C.POINTER(C.c_double)]),
     "pg_cache_kernel_launches": (C.c_uint64, [_vp]),
+    "pg_cache_debug_expire_next_wait": (C.c_int, [_vp, C.c_uint32]),
     "pg_op_linear": (C.c_int, [_fp, _fp, _fp, _fp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                C.c_int32, C.c_int32, _fp, C.POINTER(C.c_double)]),
     "pg_op_decode_attention": (C.c_int, [_fp, _fp, _fp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,

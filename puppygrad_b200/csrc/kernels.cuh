@@ -204,35 +204,50 @@ unsigned long long chain_argmax_init();
 bool chain_supported(const ChainArgs& a, int grid, const ChainPhase* host_phases = nullptr);
 cudaError_t launch_chain(const ChainArgs& a, int grid, cudaStream_t s);
 
-// Whole decode step in one persistent cooperative kernel (decode_mega.cu), for at most 8 sequences
-// and head_dim 64: every CTA stays resident, phases are separated by a bounded grid barrier, and
-// each warp requests the weights of its next phase before it enters the barrier.
-struct MegaLayer {
-  const float *ln1_g, *ln1_b, *w_qkv, *b_qkv, *w_proj, *b_proj, *ln2_g, *ln2_b, *w_fc, *b_fc, *w_proj2, *b_proj2;
-  float* kv_pool;  // this layer's page pool
-};
-struct MegaArgs {
-  const MegaLayer* layers;  // device array [n_layer]
-  const float *wte, *wpe, *lnf_g, *lnf_b;
+// Whole decode step for at most 8 sequences (head_dim 64) as one persistent cooperative kernel
+// (decode_stream.cu): a producer warp per CTA streams that CTA's share of every weight matrix into a
+// shared-memory ring without ever waiting for a dependency, and activations move between CTAs as
+// 8-byte {value, tag} words, so there is no grid barrier. Weights: FP32, BF16 or row-quantised int8.
+enum StreamWeightType { STREAM_W_F32 = 0, STREAM_W_BF16 = 1, STREAM_W_I8 = 2 };
+struct StreamArgs {
+  // Layer 0's tensors; layer l's are `l * stride` further on (the arenas hold every layer in the same layout).
+  const unsigned char* w[4];  // weight rows [out, in] of c_attn, attn.c_proj, mlp.c_fc, mlp.c_proj in the weight type of the launch
+  const float* scale[4];      // int8: one scale per output row (else unused)
+  const float* bias[4];       // FP32
+  const float* ln_g[2];       // ln_1, ln_2
+  const float* ln_b[2];
+  long long w_stride;         // bytes from a layer's matrix to the next layer's
+  long long s_stride;         // floats from a layer's row scales to the next layer's
+  long long p_stride;         // floats from a layer's bias / LayerNorm vector to the next layer's
+  float* kv_pool;             // layer 0's page pool
+  long long kv_stride;        // floats of one layer's pool
+  const float *wte, *wpe;     // FP32 embedding tables
+  const unsigned char* w_head;  // the tied lm_head in the weight type of the launch ([vocab, n_embd])
+  const float* s_head;          // int8: row scales of the lm_head
+  const float *lnf_g, *lnf_b;
   int n_layer, c, f, v, n_positions;
   float eps;
-  int *ids, *pos, *argmax, *token_log;     // [m] / [m][n_positions]
-  float *x, *qkv, *attn, *h, *logits;      // [m, .] activations in global memory
+  int *ids, *pos, *argmax, *token_log;  // [m] / [m][n_positions]
+  float* logits;                        // [m, v] or nullptr (greedy steps read only the arg-max)
   const int* page_table;
   KvLayout kv;
-  float* attn_part;       // split-K partials of the attention phase
-  unsigned* attn_counters;
-  float* part_val;        // lm_head argmax partials [m][grid]
-  int* part_idx;
-  unsigned* barrier;      // two words: arrival count, generation; zero before the first launch
-  int* error_flag;
-  unsigned long long* trace;  // optional tuning aid: cycle counts of CTA 0 (total, barriers, attention, staging, lm_head)
-  int m, attn_splits;
+  // exchange buffers of 8-byte words (value | tag << 32), zero before the first launch
+  unsigned long long *ll_x, *ll_qkv, *ll_attn, *ll_h;  // [8][c], [8][3c], [8][c], [8][f]
+  unsigned long long* ll_part;                         // attention split partials [8 * n_head][8][66]
+  unsigned long long* ll_best;                         // lm_head arg-max partials [8][grid][2]
+  unsigned* epoch;            // one word: last tag used, carried from launch to launch
+  int* error_flag;            // set non-zero when a bounded wait expired
+  int m, attn_splits;         // attn_splits 0: chosen from the context length
+  unsigned spin_limit;        // polls before a wait gives up (0: default)
+  unsigned poison;            // test hook: XORed into one expected tag, so that the wait for it runs out
+  unsigned long long* trace;  // developer aid (builds with -DPG_STREAM_TRACE only), else nullptr
 };
-// Largest cooperative grid of the step kernel on this device (0 if it cannot be launched).
-int decode_mega_grid(int num_sms);
-bool decode_mega_supported(int m, int c, int f, int head_dim);
-cudaError_t launch_decode_mega(const MegaArgs& a, int grid, cudaStream_t s);
+// Cooperative grid of the kernel on this device (0: not launchable).
+int decode_stream_grid(int num_sms);
+int decode_stream_elem_bytes(int weight_type);
+bool decode_stream_supported(int m, int c, int f, int v, int head_dim, int n_positions, int page_tokens, int weight_type,
+                             int grid);
+cudaError_t launch_decode_stream(const StreamArgs& a, int weight_type, int grid, cudaStream_t s);
 // Plain argmax over rows of a [m, n] matrix (first strict maximum).
 cudaError_t launch_argmax_rows(const float* logits, int m, int n, int* out, cudaStream_t s);
 // k largest per row, descending, ties by lower index; k <= 64.

@@ -33,6 +33,10 @@ struct LayerWeights {
   float *ln1_g, *ln1_b, *w_qkv, *b_qkv, *w_proj, *b_proj, *ln2_g, *ln2_b, *w_fc, *b_fc, *w_proj2, *b_proj2;
   // copies in the tiled layout of the tensor-core decode kernel (nullptr in fp32 mode)
   float *t_qkv = nullptr, *t_proj = nullptr, *t_fc = nullptr, *t_proj2 = nullptr;
+  // packed copies for the single-kernel decode step (BF16 or row-quantised int8 weights), [out, in] rows, and,
+  // for int8, one scale per output row
+  void *p_qkv = nullptr, *p_proj = nullptr, *p_fc = nullptr, *p_proj2 = nullptr;
+  float *s_qkv = nullptr, *s_proj = nullptr, *s_fc = nullptr, *s_proj2 = nullptr;
 };
 
 static bool env_flag(const char* name) {
@@ -55,6 +59,11 @@ struct pg_model {
   size_t tiled_floats = 0;
   float* t_wte = nullptr;
   size_t arena_floats = 0;
+  int stream_weight_type = STREAM_W_F32;  // what the single-kernel decode step streams
+  unsigned char* packed_arena = nullptr;  // BF16 / int8 copies of the dense matrices and of wte
+  float* scale_arena = nullptr;           // int8: row scales
+  void* p_wte = nullptr;
+  float* s_wte = nullptr;
   float *wte = nullptr, *wpe = nullptr, *lnf_g = nullptr, *lnf_b = nullptr;
   std::vector<LayerWeights> layers;
   bool fused_ok = false;  // LayerNorm/argmax fusion needs n_embd % 4 == 0 and n_embd <= 2048
@@ -73,6 +82,8 @@ struct pg_model {
       cudaSetDevice(device);
       cudaFree(arena);
       if (tiled_arena) cudaFree(tiled_arena);
+      if (packed_arena) cudaFree(packed_arena);
+      if (scale_arena) cudaFree(scale_arena);
     }
   }
 };
@@ -254,11 +265,14 @@ struct pg_cache {
   };
   std::map<int, ChainProgram> chain_programs;
   bool step_wants_logits = true;  // false: the caller of this step only reads the arg-max (greedy decoding)
-  // single-kernel decode step (at most 8 sequences)
-  MegaLayer* d_mega_layers = nullptr;
-  unsigned* d_barrier = nullptr;
-  unsigned long long* d_mega_trace = nullptr;  // PG_MEGA_TRACE=1: cycle accounting printed when the cache is freed
-  int mega_grid = 0;
+  // single-kernel decode step (at most 8 sequences): layer table, tagged exchange buffers, tag counter
+  unsigned long long* d_stream_ll = nullptr;  // ll_x | ll_qkv | ll_attn | ll_h | ll_part | ll_best
+  unsigned* d_stream_epoch = nullptr;
+  int stream_grid = 0;
+  unsigned dbg_spin_limit = 0, dbg_poison = 0;  // pg_cache_debug_expire_next_wait: consumed by the next decode step
+#ifdef PG_STREAM_TRACE
+  unsigned long long* d_stream_trace = nullptr;
+#endif
   int *h_ids = nullptr, *h_out = nullptr;  // pinned staging
   // prefill workspace (grow-only)
   size_t pre_rows = 0;
@@ -275,13 +289,22 @@ struct pg_cache {
     if (!model) return;
     cudaSetDevice(model->device);
     if (stream) cudaStreamSynchronize(stream);
-    if (d_mega_trace) {
-      unsigned long long t[8] = {0};
-      if (cudaMemcpy(t, d_mega_trace, sizeof(t), cudaMemcpyDeviceToHost) == cudaSuccess && t[5])
-        fprintf(stderr, "mega trace (CTA 0, cycles per step over %llu steps): total %llu barriers %llu attention %llu "
-                        "staging %llu lm_head %llu qkv-linear %llu\n", t[5], t[0] / t[5], t[1] / t[5], t[2] / t[5], t[3] / t[5], t[4] / t[5], t[6] / t[5]);
-      cudaFree(d_mega_trace);
+#ifdef PG_STREAM_TRACE
+    if (d_stream_trace) {
+      const int L = model->layers_n();
+      std::vector<unsigned long long> t((size_t)2 * (L + 1) * 16 + 128);
+      if (cudaMemcpy(t.data(), d_stream_trace, t.size() * 8, cudaMemcpyDeviceToHost) == cudaSuccess) {
+        for (int cta = 0; cta < 2; ++cta)
+          for (int l = 0; l <= L; ++l) {
+            const unsigned long long* r = t.data() + ((size_t)cta * (L + 1) + l) * 16;
+            fprintf(stderr, "stream trace cta %d layer %2d:", cta ? 100 : 0, l);
+            for (int p = 1; p < 10; ++p) fprintf(stderr, " %6lld", r[p] ? (long long)(r[p] - r[p - 1]) : -1LL);
+            fprintf(stderr, "  | start %lld cycles\n", (long long)(r[0] - t[((size_t)cta * (L + 1)) * 16]));
+          }
+      }
+      cudaFree(d_stream_trace);
     }
+#endif
     if (d_chain_trace) {
       std::vector<unsigned long long> t((size_t)chain_ctas * 32 + 512);
       if (cudaMemcpy(t.data(), d_chain_trace, t.size() * 8, cudaMemcpyDeviceToHost) == cudaSuccess) {
@@ -307,7 +330,7 @@ struct pg_cache {
                     (void*)x, (void*)norm, (void*)qkv, (void*)attn, (void*)hbuf, (void*)logits, (void*)part_val,
                     (void*)part_idx, (void*)attn_part, (void*)attn_counters, (void*)topk_vals, (void*)topk_idx,
                     (void*)px, (void*)pnorm, (void*)pqkv, (void*)pattn, (void*)ph, (void*)prow, (void*)norm_lo,
-                    (void*)attn_lo, (void*)h_lo, (void*)d_error, (void*)d_mega_layers, (void*)d_barrier,
+                    (void*)attn_lo, (void*)h_lo, (void*)d_error, (void*)d_stream_ll, (void*)d_stream_epoch,
                     (void*)chain_partials, (void*)d_chain_barrier, (void*)d_chain_trace, (void*)d_chain_best})
       if (p) cudaFree(p);
     if (t0) cudaEventDestroy(t0);
@@ -322,6 +345,13 @@ namespace pg {
 
 constexpr int MAX_SPLITS = 16;
 constexpr int MAX_TOPK = 64;
+
+// Words of the tagged exchange buffers of the single-kernel decode step, in the order
+// ll_x [8][C], ll_qkv [8][3C], ll_attn [8][C], ll_h [8][F], ll_part [8 * H][8][66], ll_best [8][grid][2].
+static size_t stream_ll_words(const pg_model* m, int grid) {
+  const size_t C = m->c(), F = m->f(), H = m->heads();
+  return 8 * (C + 3 * C + C + F) + 8 * H * 8 * 66 + 8 * (size_t)grid * 2;
+}
 
 static int cache_new(const pg_model* m, int max_batch, pg_cache** out) {
   if (max_batch <= 0 || max_batch > 4096)
@@ -389,24 +419,19 @@ static int cache_new(const pg_model* m, int max_batch, pg_cache** out) {
       }
     }
   }
-  if (decode_mega_supported(1, C, F, D) && (m->backend.persistent_step == 1 || env_flag("PG_MEGA"))) {
-    c->mega_grid = decode_mega_grid(m->num_sms);
-    if (c->mega_grid > 0) {
-      std::vector<MegaLayer> ml(m->layers_n());
-      for (int l = 0; l < m->layers_n(); ++l) {
-        const LayerWeights& w = m->layers[l];
-        ml[l] = MegaLayer{w.ln1_g, w.ln1_b, w.w_qkv, w.b_qkv, w.w_proj, w.b_proj, w.ln2_g, w.ln2_b,
-                          w.w_fc, w.b_fc, w.w_proj2, w.b_proj2, c->layer_pool(l)};
-      }
-      PG_CUDA_TRY(cudaMalloc(&c->d_mega_layers, ml.size() * sizeof(MegaLayer)));
-      PG_CUDA_TRY(cudaMemcpyAsync(c->d_mega_layers, ml.data(), ml.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice, c->stream));
-      PG_CUDA_TRY(cudaMalloc(&c->d_barrier, 2 * sizeof(unsigned)));
-      PG_CUDA_TRY(cudaMemsetAsync(c->d_barrier, 0, 2 * sizeof(unsigned), c->stream));
-      if (env_flag("PG_MEGA_TRACE")) {
-        PG_CUDA_TRY(cudaMalloc(&c->d_mega_trace, 8 * sizeof(unsigned long long)));
-        PG_CUDA_TRY(cudaMemsetAsync(c->d_mega_trace, 0, 8 * sizeof(unsigned long long), c->stream));
-      }
-      PG_CUDA_TRY(cudaStreamSynchronize(c->stream));  // `ml` is a pageable temporary
+  if (m->backend.persistent_step != 2 && !env_flag("PG_NO_STREAM")) {
+    const int grid = decode_stream_grid(m->num_sms);
+    if (decode_stream_supported(1, C, F, V, D, P, c->kv.page_tokens, m->stream_weight_type, grid)) {
+      c->stream_grid = grid;
+      const size_t words = stream_ll_words(m, grid);
+      PG_CUDA_TRY(cudaMalloc(&c->d_stream_ll, words * sizeof(unsigned long long)));
+      PG_CUDA_TRY(cudaMemsetAsync(c->d_stream_ll, 0, words * sizeof(unsigned long long), c->stream));
+      PG_CUDA_TRY(cudaMalloc(&c->d_stream_epoch, sizeof(unsigned)));
+      PG_CUDA_TRY(cudaMemsetAsync(c->d_stream_epoch, 0, sizeof(unsigned), c->stream));
+#ifdef PG_STREAM_TRACE
+      PG_CUDA_TRY(cudaMalloc(&c->d_stream_trace, ((size_t)2 * (m->layers_n() + 1) * 16 + 128) * 8));
+      PG_CUDA_TRY(cudaMemsetAsync(c->d_stream_trace, 0, ((size_t)2 * (m->layers_n() + 1) * 16 + 128) * 8, c->stream));
+#endif
     }
   }
   PG_CUDA_TRY(cudaMallocHost(&c->h_ids, B * sizeof(int)));
@@ -590,22 +615,52 @@ static int ensure_chain_program(pg_cache* c, int batch) {
 // forward_one_profiled_with_scratch + block_forward_one_profiled (rust.rs:943-1006, 1136-1250).
 static cudaError_t enqueue_decode_step(pg_cache* c, int batch, int splits, cudaStream_t s, uint64_t* launches,
                                        StepProfiler* prof = nullptr) {
-  if (!prof && c->mega_grid > 0 && decode_mega_supported(batch, c->model->c(), c->model->f(), c->model->head_dim()) &&
-      c->mega_grid <= c->part_stride) {
+  // FP32 weights: the single-kernel step wins up to 4 sequences (measured on B200: 279 against 306 us for one GPT-2
+  // small sequence, 1014 against 1168 us for four GPT-2 medium ones; at eight it loses, 1806 against 1548 us);
+  // packed weights (BF16, int8) are only read by that kernel
+  const bool stream_wanted = c->model->stream_weight_type != STREAM_W_F32 || batch <= 4 || c->model->backend.persistent_step == 1;
+  if (!prof && c->stream_grid > 0 && stream_wanted &&
+      decode_stream_supported(batch, c->model->c(), c->model->f(), c->model->v(), c->model->head_dim(),
+                              c->model->positions(), c->kv.page_tokens, c->model->stream_weight_type, c->stream_grid)) {
     // the whole step in one persistent cooperative kernel
     const pg_model* m = c->model;
-    MegaArgs a{};
-    a.layers = c->d_mega_layers; a.wte = m->wte; a.wpe = m->wpe; a.lnf_g = m->lnf_g; a.lnf_b = m->lnf_b;
+    const size_t C = m->c(), F = m->f(), H = m->heads();
+    const LayerWeights& w0 = m->layers[0];
+    const LayerWeights& w1 = m->layers[m->layers_n() > 1 ? 1 : 0];
+    const bool packed = m->stream_weight_type != STREAM_W_F32;
+    StreamArgs a{};
+    auto bytes = [](const void* p) { return reinterpret_cast<const unsigned char*>(p); };
+    if (packed) {
+      a.w[0] = bytes(w0.p_qkv); a.w[1] = bytes(w0.p_proj); a.w[2] = bytes(w0.p_fc); a.w[3] = bytes(w0.p_proj2);
+      a.w_stride = bytes(w1.p_qkv) - bytes(w0.p_qkv);
+      a.scale[0] = w0.s_qkv; a.scale[1] = w0.s_proj; a.scale[2] = w0.s_fc; a.scale[3] = w0.s_proj2;
+      a.s_stride = w0.s_qkv ? w1.s_qkv - w0.s_qkv : 0;
+      a.w_head = bytes(m->p_wte); a.s_head = m->s_wte;
+    } else {
+      a.w[0] = bytes(w0.w_qkv); a.w[1] = bytes(w0.w_proj); a.w[2] = bytes(w0.w_fc); a.w[3] = bytes(w0.w_proj2);
+      a.w_stride = bytes(w1.w_qkv) - bytes(w0.w_qkv);
+      a.w_head = bytes(m->wte);
+    }
+    a.bias[0] = w0.b_qkv; a.bias[1] = w0.b_proj; a.bias[2] = w0.b_fc; a.bias[3] = w0.b_proj2;
+    a.ln_g[0] = w0.ln1_g; a.ln_g[1] = w0.ln2_g; a.ln_b[0] = w0.ln1_b; a.ln_b[1] = w0.ln2_b;
+    a.p_stride = w1.b_qkv - w0.b_qkv;
+    a.kv_pool = c->layer_pool(0); a.kv_stride = (long long)c->num_pages * (long long)c->page_floats;
+    a.wte = m->wte; a.wpe = m->wpe; a.lnf_g = m->lnf_g; a.lnf_b = m->lnf_b;
     a.n_layer = m->layers_n(); a.c = m->c(); a.f = m->f(); a.v = m->v(); a.n_positions = m->positions();
     a.eps = m->cfg.layer_norm_epsilon;
     a.ids = c->d_ids; a.pos = c->d_pos; a.argmax = c->d_argmax; a.token_log = c->d_token_log;
-    a.x = c->x; a.qkv = c->qkv; a.attn = c->attn; a.h = c->hbuf; a.logits = c->logits;
-    a.page_table = c->d_table; a.kv = c->kv; a.attn_part = c->attn_part; a.attn_counters = c->attn_counters;
-    a.part_val = c->part_val; a.part_idx = c->part_idx; a.barrier = c->d_barrier; a.error_flag = c->d_error;
-    a.trace = c->d_mega_trace;
-    a.m = batch; a.attn_splits = splits;
+    a.logits = c->step_wants_logits ? c->logits : nullptr;
+    a.page_table = c->d_table; a.kv = c->kv;
+    a.ll_x = c->d_stream_ll; a.ll_qkv = a.ll_x + 8 * C; a.ll_attn = a.ll_qkv + 8 * 3 * C; a.ll_h = a.ll_attn + 8 * C;
+    a.ll_part = a.ll_h + 8 * F; a.ll_best = a.ll_part + 8 * H * 8 * 66;
+    a.epoch = c->d_stream_epoch; a.error_flag = c->d_error;
+    a.m = batch; a.attn_splits = m->backend.attn_splits > 8 ? 8 : m->backend.attn_splits;
+    a.spin_limit = c->dbg_spin_limit; a.poison = c->dbg_poison;
+#ifdef PG_STREAM_TRACE
+    a.trace = c->d_stream_trace;
+#endif
     if (launches) *launches = 1;
-    return launch_decode_mega(a, c->mega_grid, s);
+    return launch_decode_stream(a, m->stream_weight_type, c->stream_grid, s);
   }
   const pg_model* m = c->model;
   const int C = m->c(), F = m->f(), V = m->v();
@@ -750,8 +805,10 @@ static int run_decode_step(pg_cache* c, int batch) {
   if (m->t_wte) {
     if (int r = ensure_chain_program(c, batch)) return r;
   }
-  if (!graphs) {
-    PG_CUDA_TRY(enqueue_decode_step(c, batch, splits, c->stream, &launches));
+  if (!graphs || c->dbg_poison) {
+    cudaError_t e = enqueue_decode_step(c, batch, splits, c->stream, &launches);
+    c->dbg_poison = c->dbg_spin_limit = 0;  // the test hook covers one step
+    PG_CUDA_TRY(e);
     c->decode_launches += launches;
     return PG_OK;
   }
@@ -891,6 +948,41 @@ static int check_cache(const pg_model* m, const pg_cache* c) {
   return PG_OK;
 }
 
+// After a bounded device-side wait expired (the stream is idle, d_error holds the code): puts the
+// device-side synchronisation state back to what a fresh cache has, so that later launches do not
+// inherit a half-passed barrier or tags of the failed step, and reports PG_TIMEOUT. The sequences in
+// the cache are undefined afterwards.
+static int recover_after_timeout(pg_cache* c, int code) {
+  cudaMemsetAsync(c->d_error, 0, sizeof(int), c->stream);
+  if (c->d_chain_barrier) cudaMemsetAsync(c->d_chain_barrier, 0, sizeof(unsigned), c->stream);
+  if (c->d_chain_best) {
+    const std::vector<unsigned long long> init(64, chain_argmax_init());
+    cudaMemcpyAsync(c->d_chain_best, init.data(), init.size() * sizeof(unsigned long long), cudaMemcpyHostToDevice, c->stream);
+  }
+  cudaMemsetAsync(c->attn_counters, 0, (size_t)c->max_batch * c->model->heads() * sizeof(unsigned), c->stream);
+  if (c->d_stream_epoch) {
+    // tags of the failed step may sit in the exchange buffers: move the counter far past them
+    unsigned e = 0;
+    cudaMemcpyAsync(&e, c->d_stream_epoch, sizeof(unsigned), cudaMemcpyDeviceToHost, c->stream);
+    cudaStreamSynchronize(c->stream);
+    e += 1u << 20;
+    cudaMemcpyAsync(c->d_stream_epoch, &e, sizeof(unsigned), cudaMemcpyHostToDevice, c->stream);
+  }
+  cudaStreamSynchronize(c->stream);
+  cudaGetLastError();
+  return set_error(PG_TIMEOUT, "a bounded wait inside a device kernel expired (code " + std::to_string(code) +
+                                   "); the cache's sequences are undefined until it is cleared");
+}
+
+// Reads the error word of the finished stream work; PG_TIMEOUT (after recovery) when it is set.
+static int check_device_error(pg_cache* c) {
+  int* h_err = c->h_out + (size_t)c->max_batch * (1 + 2 * MAX_TOPK);
+  PG_CUDA_TRY(cudaMemcpyAsync(h_err, c->d_error, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+  PG_CUDA_TRY(cudaStreamSynchronize(c->stream));
+  if (*h_err) return recover_after_timeout(c, *h_err);
+  return PG_OK;
+}
+
 // Copies the requested results of the last step to the host and waits for the stream.
 static int fetch_outputs(pg_cache* c, int batch, float* logits_out, int32_t* argmax_out, float* topk_vals,
                          int32_t* topk_idx, int k) {
@@ -909,8 +1001,7 @@ static int fetch_outputs(pg_cache* c, int batch, float* logits_out, int32_t* arg
   int* h_err = c->h_out + (size_t)c->max_batch * (1 + 2 * MAX_TOPK);
   PG_CUDA_TRY(cudaMemcpyAsync(h_err, c->d_error, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
   PG_CUDA_TRY(cudaStreamSynchronize(c->stream));
-  if (*h_err)
-    return set_error(PG_TIMEOUT, "a bounded wait inside a device kernel expired (code " + std::to_string(*h_err) + ")");
+  if (*h_err) return recover_after_timeout(c, *h_err);
   if (argmax_out) memcpy(argmax_out, c->h_out, batch * sizeof(int));
   if (k > 0 && topk_vals) memcpy(topk_vals, c->h_out + c->max_batch, (size_t)batch * k * sizeof(float));
   if (k > 0 && topk_idx) memcpy(topk_idx, c->h_out + c->max_batch + (size_t)c->max_batch * MAX_TOPK, (size_t)batch * k * sizeof(int));
@@ -1244,13 +1335,15 @@ int pg_decode_greedy(const pg_model* model, pg_cache* cache, const int32_t* firs
   const int P = model->positions();
   std::vector<int> log((size_t)batch * P);
   PG_CUDA_TRY(cudaMemcpyAsync(log.data(), cache->d_token_log, log.size() * sizeof(int), cudaMemcpyDeviceToHost, cache->stream));
-  PG_CUDA_TRY(cudaStreamSynchronize(cache->stream));
+  if (int r = check_device_error(cache)) return r;  // also waits for the stream
   for (int s = 0; s < steps; ++s)
     for (int b = 0; b < batch; ++b) {
       int p = start[b] + s + 1;
       tokens_out[(size_t)s * batch + b] = p < P ? log[(size_t)b * P + p] : -1;
     }
-  if (start.size() && start[0] + steps >= P) {
+  bool fills = false;
+  for (int b = 0; b < batch; ++b) fills = fills || start[b] + steps >= P;
+  if (fills) {
     // the last loggable position is P-1; a step that fills the cache reports its argmax directly
     std::vector<int> last(batch);
     PG_CUDA_TRY(cudaMemcpy(last.data(), cache->d_argmax, batch * sizeof(int), cudaMemcpyDeviceToHost));
@@ -1269,8 +1362,8 @@ int pg_profile_forward_one(const pg_model* model, pg_cache* cache, const int32_t
   StepProfiler prof;
   uint64_t launches = 0;
   PG_CUDA_TRY(enqueue_decode_step(cache, batch, choose_splits(cache, batch, max_len), cache->stream, &launches, &prof));
-  PG_CUDA_TRY(cudaStreamSynchronize(cache->stream));
   for (int b = 0; b < batch; ++b) cache->seq_len[b] += 1;
+  if (int r = check_device_error(cache)) return r;  // also waits for the stream
   cache->decode_launches += launches;
   double sec[B_COUNT] = {0};
   uint64_t cnt[B_COUNT] = {0};
@@ -1342,6 +1435,15 @@ int pg_cache_time_end(pg_cache* cache, double* seconds) {
 }
 
 uint64_t pg_cache_kernel_launches(const pg_cache* cache) { return cache ? cache->decode_launches : 0; }
+
+int pg_cache_debug_expire_next_wait(pg_cache* cache, uint32_t spin_limit) {
+  if (!cache) return set_error(PG_INVALID_INPUT, "null cache");
+  if (spin_limit == 0 || spin_limit > (1u << 20))
+    return set_error(PG_INVALID_INPUT, "spin_limit must be in 1..1048576");
+  cache->dbg_spin_limit = spin_limit;
+  cache->dbg_poison = 0x5a5a5a5au;
+  return PG_OK;
+}
 
 int pg_generate_greedy(const pg_model* model, const int32_t* ids, int32_t n_ids, uint64_t max_new_tokens,
                        int32_t* out_tokens, uint64_t* out_len) {

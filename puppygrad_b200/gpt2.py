@@ -71,7 +71,9 @@ class Gpt2CudaConfig:
     page_tokens: int = 32
     use_graphs: bool = True
     attn_splits: int = 0
-    persistent_step: bool = False  # one cooperative kernel per decode step (<= 8 sequences)
+    # one cooperative kernel per decode step of <= 8 sequences: None = where it is the faster path, True = whenever
+    # the shapes allow, False = never (a CUDA graph of one kernel per operation)
+    persistent_step: Optional[bool] = None
 
     def to_native(self) -> N.PgBackendConfig:
         if self.math_mode not in _MATH:
@@ -79,7 +81,7 @@ class Gpt2CudaConfig:
         b = N.PgBackendConfig()
         b.device, b.math_mode, b.page_tokens = self.device, _MATH[self.math_mode], self.page_tokens
         b.use_graphs, b.attn_splits = (1 if self.use_graphs else 2), self.attn_splits
-        b.persistent_step = 1 if self.persistent_step else 0
+        b.persistent_step = 0 if self.persistent_step is None else (1 if self.persistent_step else 2)
         return b
 
 
@@ -161,6 +163,10 @@ class Gpt2KvCache:
 
     def kernel_launches(self) -> int:
         return int(N.lib.pg_cache_kernel_launches(self._h))
+
+    def debug_expire_next_wait(self, spin_limit: int = 4096) -> None:
+        """Test hook: one bounded device-side wait of the next decode step runs out by its limit."""
+        check(N.lib.pg_cache_debug_expire_next_wait(self._h, spin_limit))
 
     def read_layer(self, layer: int, slot: int = 0):
         """Keys and values in the reference layout [head][max_seq_len][head_dim]."""

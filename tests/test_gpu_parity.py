@@ -342,11 +342,14 @@ def test_graphs_and_plain_launches_agree_bitwise(oracle):
     assert np.array_equal(outs[0], outs[1])
 
 
-@pytest.mark.parametrize("batch", [1, 3, 8])
-def test_persistent_step_kernel_matches_oracle(midi, oracle, batch):
-    """The whole decode step as one cooperative kernel with grid barriers (opt-in)."""
+@pytest.mark.parametrize("persistent", [True, False])
+@pytest.mark.parametrize("batch", [1, 2, 3, 5, 8])
+def test_small_batch_step_matches_oracle(midi, oracle, batch, persistent):
+    """A decode step of at most 8 sequences: as ONE persistent kernel (the default: weight stream through a
+    shared-memory ring, tagged hand-over of activations between CTAs) and as a graph of one kernel per
+    operation."""
     cfg, w, _, o = midi
-    g = pg.Gpt2Model(cfg, w, pg.Gpt2CudaConfig(persistent_step=True, attn_splits=2 if batch == 3 else 0))
+    g = pg.Gpt2Model(cfg, w, pg.Gpt2CudaConfig(persistent_step=persistent, attn_splits=2 if batch == 3 else 0))
     prompts = [synthetic.uniform_prompt(800 + i, 40 + 9 * i, cfg["vocab_size"]) for i in range(batch)]
     cache = g.new_kv_cache(max_batch=batch)
     _, cur = g.prefill_batch(prompts, cache)
@@ -356,12 +359,93 @@ def test_persistent_step_kernel_matches_oracle(midi, oracle, batch):
         o.prefill(p, c)
         ocaches.append(c)
     for step in range(5):
+        n0 = cache.kernel_launches()
         logits, am, _, _ = g.forward_one_batch(cur, cache, want_logits=True)
+        assert (cache.kernel_launches() - n0 == 1) == persistent
         ol = np.stack([o.forward_one(int(cur[i]), ocaches[i]) for i in range(batch)])
         assert_logits_close(logits, ol)
         assert list(am) == [oracle.argmax_logits(l) for l in ol]
         cur = am.copy()
     np.testing.assert_allclose(cache.read_layer(1, batch - 1)[0], ocaches[-1].read_layer(1)[0], rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("splits", [0, 1, 3, 8])
+def test_small_batch_step_over_long_and_ragged_contexts(oracle, splits):
+    """Contexts of 5, 130 and 700 cached positions in one batch of the persistent step: attention over one
+    and several 128-key rounds, split over CTAs with the partial results merged by the first split's CTA,
+    keys and values of pages that another sequence used before."""
+    cfg = dict(vocab_size=3001, n_positions=1024, n_embd=256, n_layer=2, n_head=4, n_inner=1024,
+               layer_norm_epsilon=1e-5)
+    w = synthetic.perturbed_weights(cfg, 77)
+    g = pg.Gpt2Model(cfg, w, pg.Gpt2CudaConfig(attn_splits=splits, page_tokens=16))
+    o = oracle.Model(cfg, w, threads=8)
+    lens = [700, 130, 5]
+    prompts = [synthetic.uniform_prompt(900 + i, n, cfg["vocab_size"]) for i, n in enumerate(lens)]
+    cache = g.new_kv_cache(max_batch=3)
+    g.prefill_batch(prompts[::-1], cache)  # scatter the pages
+    cache.clear()
+    _, cur = g.prefill_batch(prompts, cache)
+    ocaches = [o.new_kv_cache() for _ in prompts]
+    ocur = [oracle.argmax_logits(o.prefill(p, c)) for p, c in zip(prompts, ocaches)]
+    assert list(cur) == ocur
+    for step in range(4):
+        n0 = cache.kernel_launches()
+        logits, am, _, _ = g.forward_one_batch(cur, cache, want_logits=True)
+        assert cache.kernel_launches() - n0 == 1
+        ol = np.stack([o.forward_one(int(cur[i]), ocaches[i]) for i in range(3)])
+        assert_logits_close(logits, ol)
+        assert list(am) == [oracle.argmax_logits(l) for l in ol]
+        cur = am.copy()
+    for layer in range(2):
+        k, v = cache.read_layer(layer, 0)
+        ok, ov = ocaches[0].read_layer(layer)
+        np.testing.assert_allclose(k, ok, rtol=1e-4, atol=1e-5)
+        np.testing.assert_allclose(v, ov, rtol=1e-4, atol=1e-5)
+
+
+def test_small_batch_step_fills_the_context_to_its_last_position(midi, oracle):
+    """Greedy decode fed back on the device until the cache is full (ragged starts: only one sequence reaches
+    n_positions), then the error of the reference for a full cache (rust.rs:957-962)."""
+    cfg, w, g, o = midi
+    P = cfg["n_positions"]
+    prompts = [synthetic.uniform_prompt(950, P - 6, cfg["vocab_size"]), synthetic.uniform_prompt(951, 10, cfg["vocab_size"])]
+    cache = g.new_kv_cache(max_batch=2)
+    _, first = g.prefill_batch(prompts[::-1], cache)  # slot 0 is the short one
+    toks = g.decode_greedy(first, cache, 6)
+    assert (toks >= 0).all()
+    for i, p in enumerate(prompts[::-1]):
+        oc = o.new_kv_cache()
+        want = [oracle.argmax_logits(o.prefill(p, oc))]
+        for _ in range(6):
+            want.append(oracle.argmax_logits(o.forward_one(want[-1], oc)))
+        assert [int(first[i])] + [int(t) for t in toks[:, i]] == want
+    assert cache.seq_len_of(1) == P
+    with pytest.raises(pg.Gpt2Error, match=f"cache is full at seq_len {P}"):
+        g.forward_one_batch([1, 1], cache)
+
+
+def test_a_wait_that_runs_out_returns_timeout_and_the_cache_recovers(midi, oracle):
+    """Every device-side wait has a limit. The test hook gives the next step a limit of a few thousand polls
+    and makes it wait for a hand-over that never comes: every CTA gives up, the call returns PG_TIMEOUT
+    (nothing faults, nothing hangs), and after a clear the same cache decodes correctly again."""
+    cfg, w, g, o = midi
+    for batch in (1, 4):
+        prompts = [synthetic.uniform_prompt(960 + i, 20 + i, cfg["vocab_size"]) for i in range(batch)]
+        cache = g.new_kv_cache(max_batch=batch)
+        _, cur = g.prefill_batch(prompts, cache)
+        cache.debug_expire_next_wait(2000)
+        with pytest.raises(pg.Gpt2Error, match="bounded wait") as e:
+            g.forward_one_batch(cur, cache)
+        assert e.value.kind == "Timeout"
+        cache.debug_expire_next_wait(2000)
+        with pytest.raises(pg.Gpt2Error, match="bounded wait"):
+            g.decode_greedy(cur, cache, 3)
+        cache.clear()
+        _, cur = g.prefill_batch(prompts, cache)
+        toks = g.decode_greedy(cur, cache, 8)
+        for i, p in enumerate(prompts):
+            want = o.generate_greedy_cached(p, 9)[len(p):]
+            assert [int(cur[i])] + [int(t) for t in toks[:, i]] == want
 
 
 def test_odd_inner_dimension_takes_the_generic_path(oracle):
