@@ -59,7 +59,12 @@ typedef enum {
                          token-exact tests; everything else as PG_MATH_FP32 */
   PG_MATH_TF32 = 2,   /* as TF32X3 for decode; single-pass TF32 is available per operator
                          (pg_op_linear) with its looser bound */
-  PG_MATH_BF16 = 3    /* reserved: rejected by this build */
+  PG_MATH_BF16 = 3    /* BF16 WEIGHTS, FP32 activations and sums: the four dense matrices of every block and the
+                         tied embedding are rounded to BF16 (nearest even) at load; what the model computes is
+                         the FP32 path of the reference on those rounded weights. Decode steps of at most 8
+                         sequences stream the 2-byte copies; prefill and larger batches multiply the rounded
+                         values as PG_MATH_TF32X3 does. No reference counterpart (it rejects every dtype but F32,
+                         src/models/safetensors.rs:126-130) */
 } pg_math_mode;
 
 /* Stands where Gpt2BackendConfig::Rust(Gpt2RustConfig) stands in the reference
@@ -76,7 +81,12 @@ typedef struct {
                               at grid barriers. 0 = where it measured faster than one kernel per operation in a
                               CUDA graph (up to 4 sequences with FP32 weights; always with BF16 / int8 weights,
                               which only that kernel reads), 1 = whenever the shapes allow, 2 = never */
-  int32_t reserved[2];
+  int32_t quantized_weights; /* Gpt2RustConfig::quantized_weights (src/models/gpt2/options.rs:62-104): 1 = the four
+                                dense matrices of every block and the lm_head as row-wise int8 (QuantizedRows,
+                                src/models/cpu.rs:26-56; quantize_weights, rust.rs:1354-1376); the embedding lookup
+                                keeps FP32 rows as in the reference. Decode steps of at most 8 sequences stream the
+                                1-byte copies; prefill and larger batches multiply the dequantised values q * scale */
+  int32_t reserved[1];
 } pg_backend_config;
 
 /* TextGenerationConfig, src/models/generation.rs:60-85. None is encoded as a negative value. */

@@ -82,6 +82,7 @@ def lib():
         L.po_model_new.argtypes = [C.POINTER(PoConfig), C.POINTER(fp), u64p, C.c_uint64,
                                    C.POINTER(PoRustConfig), C.POINTER(vp)]
         L.po_model_free.argtypes = [vp]
+        L.po_model_quantize_weights.argtypes = [vp]
         L.po_config_validate.argtypes = [C.POINTER(PoConfig)]
         L.po_cache_new.argtypes = [vp, C.POINTER(vp)]
         L.po_cache_free.argtypes = [vp]
@@ -269,7 +270,8 @@ class Cache:
 class Model:
     """Mirror of the reference `Gpt2Model` (rust.rs:798-1027) over the C++ restatement."""
 
-    def __init__(self, cfg: dict, weights, threads: int = 1, rust_config: dict | None = None):
+    def __init__(self, cfg: dict, weights, threads: int = 1, rust_config: dict | None = None,
+                 quantized_weights: bool = False):
         self.cfg = dict(cfg)
         self.cfg.setdefault("n_inner", 4 * cfg["n_embd"])
         self.cfg.setdefault("layer_norm_epsilon", 1e-5)
@@ -287,6 +289,8 @@ class Model:
         self._h = C.c_void_p()
         _check(lib().po_model_new(C.byref(pc), ptrs, _u64(lens), n, C.byref(rc), C.byref(self._h)))
         self.vocab_size = int(self.cfg["vocab_size"])
+        if quantized_weights:  # Gpt2RustConfig::quantized_weights (options.rs:62-104)
+            lib().po_model_quantize_weights(self._h)
 
     def __del__(self):
         if getattr(self, "_h", None):

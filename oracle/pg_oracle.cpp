@@ -200,11 +200,24 @@ struct Block {  // rust.rs:111-125; dense matrices stored [out,in] after rust.rs
 
 }  // namespace
 
+struct QRows {  // QuantizedRows, cpu.rs:26-31
+  std::vector<int8_t> q;
+  std::vector<float> scales;
+  size_t cols = 0;
+};
+struct QBlock {  // Gpt2QuantizedBlockWeights
+  QRows c_attn_w, c_proj_w, c_fc_w, c_proj_mlp_w;
+};
+
 struct po_model {
   po_config cfg;
   po_rust_config rc;
   std::vector<float> wte, wpe, ln_f_g, ln_f_b;
   std::vector<Block> blocks;
+  // Gpt2RustConfig::quantized_weights (options.rs:62-104): Some(Gpt2QuantizedWeights) when set (rust.rs:812-822)
+  bool quantized = false;
+  QRows qwte;
+  std::vector<QBlock> qblocks;
   std::unique_ptr<Pool> pool;
   size_t head_dim() const { return cfg.n_embd / cfg.n_head; }
 };
@@ -242,12 +255,52 @@ void block_linear(const po_model& m, size_t layer, Which w, const float** weight
   }
 }
 
-// rust.rs:1481-1532 (f32 branch) + cpu.rs:58-75
+// quantized_dot, cpu.rs:173-184: every weight dequantised on the fly, one sequential f32 sum
+inline float quantized_dot(const float* a, const QRows& rows, size_t row_index) {
+  const int8_t* values = rows.q.data() + row_index * rows.cols;
+  const float scale = rows.scales[row_index];
+  float sum = 0.0f;
+  for (size_t i = 0; i < rows.cols; ++i) sum += a[i] * ((float)values[i] * scale);
+  return sum;
+}
+
+const QRows& quantized_block_linear(const po_model& m, size_t layer, Which w) {  // rust.rs:1438-1452
+  const QBlock& b = m.qblocks[layer];
+  switch (w) {
+    case CAttn: return b.c_attn_w;
+    case AttnProj: return b.c_proj_w;
+    case MlpFc: return b.c_fc_w;
+    default: return b.c_proj_mlp_w;
+  }
+}
+
+// rust.rs:1481-1532 + cpu.rs:58-75; with quantised weights quantized_linear_into, rust.rs:1535-1578
 void linear_block_into(const po_model& m, const float* x, size_t rows, size_t in_f, size_t out_f,
                        size_t layer, Which which, std::vector<float>& out) {
   const float *weight, *bias;
   block_linear(m, layer, which, &weight, &bias);
   Pool& pool = *m.pool;
+  if (m.quantized) {
+    const QRows& qw = quantized_block_linear(m, layer, which);
+    if (pool.threads() == 1 || rows * in_f * out_f < m.rc.dense_parallel_threshold) {
+      out.assign(rows * out_f, 0.0f);
+      for (size_t r = 0; r < rows; ++r)
+        for (size_t o = 0; o < out_f; ++o) out[r * out_f + o] = bias[o] + quantized_dot(x + r * in_f, qw, o);
+      return;
+    }
+    auto chunks = pool.scoped_parallel_chunks(
+        rows * out_f, chunk_size_of(m.rc, which), [&](size_t s, size_t e, std::vector<float>& v) {
+          v.reserve(e - s);
+          for (size_t idx = s; idx < e; ++idx) {
+            size_t r = idx / out_f, o = idx % out_f;
+            v.push_back(bias[o] + quantized_dot(x + r * in_f, qw, o));
+          }
+        });
+    out.clear();
+    out.reserve(rows * out_f);
+    for (auto& c : chunks) out.insert(out.end(), c.begin(), c.end());
+    return;
+  }
   if (pool.threads() == 1 || rows * in_f * out_f < m.rc.dense_parallel_threshold) {
     out.assign(rows * out_f, 0.0f);
     for (size_t r = 0; r < rows; ++r)
@@ -361,10 +414,26 @@ void cached_self_attention_into(const po_model& m, const float* qkv, size_t pos,
   for (size_t h = 0; h < n_head; ++h) cached_head(qkv, pos, c, layer, h, scale, &out[h * head_dim], scores);
 }
 
-// rust.rs:1767-1813 (f32 branch)
+// rust.rs:1767-1813; with quantised weights quantized_logits_from_hidden_into, rust.rs:1815-1849
 void logits_from_hidden_into(const po_model& m, const float* hidden, std::vector<float>& logits) {
   size_t v = m.cfg.vocab_size, c = m.cfg.n_embd;
   Pool& pool = *m.pool;
+  if (m.quantized) {
+    if (pool.threads() == 1) {
+      logits.assign(v, 0.0f);
+      for (size_t t = 0; t < v; ++t) logits[t] = quantized_dot(hidden, m.qwte, t);
+      return;
+    }
+    auto chunks = pool.scoped_parallel_chunks(v, m.rc.logits_chunk_size,
+                                              [&](size_t s, size_t e, std::vector<float>& out) {
+                                                out.reserve(e - s);
+                                                for (size_t t = s; t < e; ++t) out.push_back(quantized_dot(hidden, m.qwte, t));
+                                              });
+    logits.clear();
+    logits.reserve(v);
+    for (auto& ch : chunks) logits.insert(logits.end(), ch.begin(), ch.end());
+    return;
+  }
   if (pool.threads() == 1) {
     logits.assign(v, 0.0f);
     for (size_t t = 0; t < v; ++t) logits[t] = dot_avx(hidden, m.wte.data() + t * c, c);
@@ -655,6 +724,26 @@ int po_model_new(const po_config* cfg, const float* const* t, const uint64_t* le
 }
 void po_model_free(po_model* m) { delete m; }
 
+// quantize_weights, rust.rs:1354-1376: the (already transposed) dense matrices and the tied embedding
+// as QuantizedRows; from then on every linear and the lm_head use them (the embedding lookup does not).
+void po_model_quantize_weights(po_model* m) {
+  auto rows_of = [](const std::vector<float>& w, size_t rows, size_t cols) {
+    QRows r;
+    r.cols = cols;
+    r.q.resize(rows * cols);
+    r.scales.resize(rows);
+    po_quantize_rows(w.data(), rows, cols, r.q.data(), r.scales.data());
+    return r;
+  };
+  const size_t c = m->cfg.n_embd, f = m->cfg.n_inner;
+  m->qwte = rows_of(m->wte, m->cfg.vocab_size, c);
+  m->qblocks.clear();
+  for (const Block& b : m->blocks)
+    m->qblocks.push_back(QBlock{rows_of(b.c_attn_w, 3 * c, c), rows_of(b.c_proj_w, c, c), rows_of(b.c_fc_w, f, c),
+                                rows_of(b.c_proj_mlp_w, c, f)});
+  m->quantized = true;
+}
+
 int po_cache_new(const po_model* m, po_cache** out) {
   auto c = std::make_unique<po_cache>();
   size_t len = m->cfg.n_positions * m->cfg.n_head * m->head_dim();
@@ -778,18 +867,21 @@ int po_forward_one_batch(const po_model* mp, const uint64_t* tokens, po_cache* c
     for (size_t i = 0; i < c; ++i)
       x[b * c + i] = m.wte[tokens[b] * c + i] + m.wpe[caches[b]->seq_len * c + i];
   // out[b][o] = bias[o] + dot(x[b], W[o]): the same expression as linear_block_into, weight row outermost
-  auto linear = [&](const float* in, size_t in_f, size_t out_f, const float* w, const float* bias, float* out) {
+  auto linear = [&](const float* in, size_t in_f, size_t out_f, const float* w, const float* bias, float* out,
+                    const QRows* qw = nullptr) {
     pool.scoped_parallel_chunks(out_f, 64, [&](size_t s, size_t e, std::vector<float>&) {
       for (size_t o = s; o < e; ++o)
         for (uint64_t b = 0; b < nb; ++b)
-          out[b * out_f + o] = (bias ? bias[o] : 0.0f) + dot_avx(in + b * in_f, w + o * in_f, in_f);
+          out[b * out_f + o] = (bias ? bias[o] : 0.0f) +
+                               (qw ? quantized_dot(in + b * in_f, *qw, o) : dot_avx(in + b * in_f, w + o * in_f, in_f));
     });
   };
   for (size_t layer = 0; layer < m.blocks.size(); ++layer) {
     const Block& bl = m.blocks[layer];
     norm = x;
     layer_norm_in_place(norm.data(), nb, c, bl.ln_1_g.data(), bl.ln_1_b.data(), m.cfg.layer_norm_epsilon);
-    linear(norm.data(), c, 3 * c, bl.c_attn_w.data(), bl.c_attn_b.data(), qkv.data());
+    const QBlock* qb = m.quantized ? &m.qblocks[layer] : nullptr;
+    linear(norm.data(), c, 3 * c, bl.c_attn_w.data(), bl.c_attn_b.data(), qkv.data(), qb ? &qb->c_attn_w : nullptr);
     pool.scoped_parallel_chunks(nb, 1, [&](size_t s, size_t e, std::vector<float>&) {
       std::vector<float> o;
       for (size_t b = s; b < e; ++b) {
@@ -797,13 +889,13 @@ int po_forward_one_batch(const po_model* mp, const uint64_t* tokens, po_cache* c
         std::memcpy(attn.data() + b * c, o.data(), c * 4);
       }
     });
-    linear(attn.data(), c, c, bl.c_proj_w.data(), bl.c_proj_b.data(), ap.data());
+    linear(attn.data(), c, c, bl.c_proj_w.data(), bl.c_proj_b.data(), ap.data(), qb ? &qb->c_proj_w : nullptr);
     add_in_place(x.data(), ap.data(), nb * c);  // residual = x + attn_proj
     norm = x;
     layer_norm_in_place(norm.data(), nb, c, bl.ln_2_g.data(), bl.ln_2_b.data(), m.cfg.layer_norm_epsilon);
-    linear(norm.data(), c, f, bl.c_fc_w.data(), bl.c_fc_b.data(), mlp.data());
+    linear(norm.data(), c, f, bl.c_fc_w.data(), bl.c_fc_b.data(), mlp.data(), qb ? &qb->c_fc_w : nullptr);
     gelu_in_place(mlp.data(), mlp.size());
-    linear(mlp.data(), f, c, bl.c_proj_mlp_w.data(), bl.c_proj_mlp_b.data(), mp2.data());
+    linear(mlp.data(), f, c, bl.c_proj_mlp_w.data(), bl.c_proj_mlp_b.data(), mp2.data(), qb ? &qb->c_proj_mlp_w : nullptr);
     add_in_place(x.data(), mp2.data(), nb * c);
   }
   if (!logits && !argmax) {  // prompt positions whose logits nobody reads: the cache is all that is kept
@@ -820,7 +912,8 @@ int po_forward_one_batch(const po_model* mp, const uint64_t* tokens, po_cache* c
   // logits[v] = dot(hidden, wte[v]) with no bias term at all (rust.rs:1787-1790)
   pool.scoped_parallel_chunks(v, 256, [&](size_t s, size_t e, std::vector<float>&) {
     for (size_t o = s; o < e; ++o)
-      for (uint64_t b = 0; b < nb; ++b) lg[b * v + o] = dot_avx(x.data() + b * c, m.wte.data() + o * c, c);
+      for (uint64_t b = 0; b < nb; ++b)
+        lg[b * v + o] = m.quantized ? quantized_dot(x.data() + b * c, m.qwte, o) : dot_avx(x.data() + b * c, m.wte.data() + o * c, c);
   });
   for (uint64_t b = 0; b < nb; ++b) {
     caches[b]->seq_len += 1;

@@ -81,6 +81,9 @@ void po_transpose_in_out(const float* w, size_t in_f, size_t out_f, float* out);
 int po_model_new(const po_config* cfg, const float* const* tensors, const uint64_t* lens,
                  uint64_t n_tensors, const po_rust_config* rc, po_model** out);
 void po_model_free(po_model* m);
+/* Gpt2RustConfig::quantized_weights = true (options.rs:62-104; quantize_weights, rust.rs:1354-1376;
+ * quantized_linear_into, rust.rs:1535-1578; quantized_logits_from_hidden_into, rust.rs:1815-1849) */
+void po_model_quantize_weights(po_model* m);
 int po_config_validate(const po_config* cfg);
 
 int po_cache_new(const po_model* m, po_cache** out); /* rust.rs:186-200 */

@@ -23,7 +23,7 @@ class PgConfig(C.Structure):
 class PgBackendConfig(C.Structure):
     _fields_ = [("device", C.c_int32), ("math_mode", C.c_int32), ("page_tokens", C.c_int32),
                 ("use_graphs", C.c_int32), ("attn_splits", C.c_int32), ("persistent_step", C.c_int32),
-                ("reserved", C.c_int32 * 2)]
+                ("quantized_weights", C.c_int32), ("reserved", C.c_int32 * 1)]
 
 
 class PgGenerationConfig(C.Structure):

@@ -248,6 +248,11 @@ int decode_stream_elem_bytes(int weight_type);
 bool decode_stream_supported(int m, int c, int f, int v, int head_dim, int n_positions, int page_tokens, int weight_type,
                              int grid);
 cudaError_t launch_decode_stream(const StreamArgs& a, int weight_type, int grid, cudaStream_t s);
+// Row-wise int8 quantisation (QuantizedRows::from_f32, cpu.rs:33-57), its inverse w = q * scale, and BF16 rounding
+// (nearest even) of an FP32 array in place with a packed 2-byte copy: the narrow weight copies made at model load.
+cudaError_t launch_quantize_rows(const float* w, int rows, int cols, int8_t* q, float* scales, cudaStream_t s);
+cudaError_t launch_dequantize_rows(const int8_t* q, const float* scales, int rows, int cols, float* w, cudaStream_t s);
+cudaError_t launch_round_bf16(float* w, size_t n, uint16_t* packed, cudaStream_t s);
 // Plain argmax over rows of a [m, n] matrix (first strict maximum).
 cudaError_t launch_argmax_rows(const float* logits, int m, int n, int* out, cudaStream_t s);
 // k largest per row, descending, ties by lower index; k <= 64.

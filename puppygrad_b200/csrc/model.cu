@@ -64,6 +64,8 @@ struct pg_model {
   float* scale_arena = nullptr;           // int8: row scales
   void* p_wte = nullptr;
   float* s_wte = nullptr;
+  float* head_w = nullptr;      // FP32 rows of the lm_head: wte itself, or (int8) its dequantised copy
+  float* head_deq = nullptr;    // owned storage of that copy
   float *wte = nullptr, *wpe = nullptr, *lnf_g = nullptr, *lnf_b = nullptr;
   std::vector<LayerWeights> layers;
   bool fused_ok = false;  // LayerNorm/argmax fusion needs n_embd % 4 == 0 and n_embd <= 2048
@@ -84,6 +86,7 @@ struct pg_model {
       if (tiled_arena) cudaFree(tiled_arena);
       if (packed_arena) cudaFree(packed_arena);
       if (scale_arena) cudaFree(scale_arena);
+      if (head_deq) cudaFree(head_deq);
     }
   }
 };
@@ -133,8 +136,10 @@ static int build_model(const pg_gpt2_config& cfg, const float* const* tensors, c
     return set_error(PG_INVALID_CONFIG, "cuda page_tokens must be 16, 32 or 64");
   if (be.math_mode < PG_MATH_FP32 || be.math_mode > PG_MATH_BF16)
     return set_error(PG_INVALID_CONFIG, "cuda math_mode must be one of fp32, tf32x3, tf32, bf16");
-  if (be.math_mode == PG_MATH_BF16)
-    return set_error(PG_INVALID_CONFIG, "cuda math_mode bf16 is not available in this build");
+  if (be.quantized_weights < 0 || be.quantized_weights > 1)
+    return set_error(PG_INVALID_CONFIG, "cuda quantized_weights must be 0 or 1");
+  if (be.math_mode == PG_MATH_BF16 && be.quantized_weights)
+    return set_error(PG_INVALID_CONFIG, "cuda math_mode bf16 and quantized_weights exclude each other");
   if (be.attn_splits < 0 || be.attn_splits > 16)
     return set_error(PG_INVALID_CONFIG, "cuda attn_splits must be in 0..16");
   if (cfg.vocab_size > 0x7fffffffULL || cfg.n_positions > 65536 || cfg.n_embd > 65536 || cfg.n_inner > 262144)
@@ -195,7 +200,61 @@ static int build_model(const pg_gpt2_config& cfg, const float* const* tensors, c
   }
   cudaFree(staging);
   if (rc != PG_OK) return rc;
-  if (be.math_mode != PG_MATH_FP32 && C % 32 == 0 && F % 32 == 0) {
+  m->head_w = m->wte;
+  if (be.math_mode == PG_MATH_BF16 || be.quantized_weights) {
+    // A second, narrow copy of the dense matrices and of the tied lm_head, every layer laid out alike:
+    //  int8: QuantizedRows::from_f32 of the transposed matrices (quantize_weights, rust.rs:1354-1376); the FP32
+    //        arena then holds q * scale, what quantized_dot multiplies by (cpu.rs:173-184), so that every FP32
+    //        kernel of this library (prefill, batches above 8) computes the quantised model too; wte keeps its
+    //        FP32 rows for the embedding lookup and gets a dequantised twin for the lm_head;
+    //  bf16: round-to-nearest-even of the same tensors, written back into the FP32 arena as well.
+    const bool q8 = be.quantized_weights != 0;
+    const size_t eb = q8 ? 1 : 2;
+    const int V = (int)cfg.vocab_size;
+    auto al = [](size_t n) { return (n + 255) / 256 * 256; };
+    const size_t lay_bytes = al((size_t)3 * C * C * eb) + al((size_t)C * C * eb) + 2 * al((size_t)C * F * eb);
+    const size_t lay_scales = (size_t)(3 * C + C + F + C + 63) / 64 * 64;
+    PG_CUDA_TRY(cudaMalloc(&m->packed_arena, lay_bytes * cfg.n_layer + al((size_t)V * C * eb)));
+    if (q8) {
+      PG_CUDA_TRY(cudaMalloc(&m->scale_arena, (lay_scales * cfg.n_layer + (size_t)V) * sizeof(float)));
+      PG_CUDA_TRY(cudaMalloc(&m->head_deq, (size_t)V * C * sizeof(float)));
+      m->head_w = m->head_deq;
+    }
+    m->stream_weight_type = q8 ? STREAM_W_I8 : STREAM_W_BF16;
+    auto pack = [&](float* w, int rows, int cols, void* packed, float* scales, float* deq_out) -> int {
+      if (q8) {
+        PG_CUDA_TRY(launch_quantize_rows(w, rows, cols, static_cast<int8_t*>(packed), scales, 0));
+        PG_CUDA_TRY(launch_dequantize_rows(static_cast<const int8_t*>(packed), scales, rows, cols, deq_out, 0));
+      } else {
+        PG_CUDA_TRY(launch_round_bf16(w, (size_t)rows * cols, static_cast<uint16_t*>(packed), 0));
+      }
+      return PG_OK;
+    };
+    for (uint64_t l = 0; l < cfg.n_layer; ++l) {
+      LayerWeights& w = m->layers[l];
+      unsigned char* p = m->packed_arena + l * lay_bytes;
+      float* sc = q8 ? m->scale_arena + l * lay_scales : nullptr;
+      w.p_qkv = p; p += al((size_t)3 * C * C * eb);
+      w.p_proj = p; p += al((size_t)C * C * eb);
+      w.p_fc = p; p += al((size_t)C * F * eb);
+      w.p_proj2 = p;
+      if (q8) {
+        w.s_qkv = sc; w.s_proj = sc + 3 * C; w.s_fc = sc + 4 * C; w.s_proj2 = sc + 4 * C + F;
+      }
+      if (int r = pack(w.w_qkv, 3 * C, C, w.p_qkv, w.s_qkv, w.w_qkv)) return r;
+      if (int r = pack(w.w_proj, C, C, w.p_proj, w.s_proj, w.w_proj)) return r;
+      if (int r = pack(w.w_fc, F, C, w.p_fc, w.s_fc, w.w_fc)) return r;
+      if (int r = pack(w.w_proj2, C, F, w.p_proj2, w.s_proj2, w.w_proj2)) return r;
+    }
+    m->p_wte = m->packed_arena + lay_bytes * cfg.n_layer;
+    if (q8) m->s_wte = m->scale_arena + lay_scales * cfg.n_layer;
+    if (int r = pack(m->wte, V, C, m->p_wte, m->s_wte, m->head_deq)) return r;
+    PG_CUDA_TRY(cudaDeviceSynchronize());
+  }
+  // BF16 mode: everything that is not the single-kernel step multiplies the rounded FP32 values, on the tensor
+  // cores as three TF32 products where the FP32-grade mode would
+  const bool tc_modes = be.math_mode != PG_MATH_FP32;
+  if (tc_modes && C % 32 == 0 && F % 32 == 0) {
     const int V = (int)cfg.vocab_size;
     const size_t per_layer = tc_tiled_weight_floats(3 * C, C) + tc_tiled_weight_floats(C, C) +
                              tc_tiled_weight_floats(F, C) + tc_tiled_weight_floats(C, F);
@@ -215,7 +274,7 @@ static int build_model(const pg_gpt2_config& cfg, const float* const* tensors, c
       if (int r = tile(w.w_fc, F, C, &w.t_fc)) return r;
       if (int r = tile(w.w_proj2, C, F, &w.t_proj2)) return r;
     }
-    if (int r = tile(m->wte, V, C, &m->t_wte)) return r;
+    if (int r = tile(m->head_w, V, C, &m->t_wte)) return r;
     PG_CUDA_TRY(cudaDeviceSynchronize());
   }
   *out = m.release();
@@ -639,7 +698,7 @@ static cudaError_t enqueue_decode_step(pg_cache* c, int batch, int splits, cudaS
     } else {
       a.w[0] = bytes(w0.w_qkv); a.w[1] = bytes(w0.w_proj); a.w[2] = bytes(w0.w_fc); a.w[3] = bytes(w0.w_proj2);
       a.w_stride = bytes(w1.w_qkv) - bytes(w0.w_qkv);
-      a.w_head = bytes(m->wte);
+      a.w_head = bytes(m->head_w);
     }
     a.bias[0] = w0.b_qkv; a.bias[1] = w0.b_proj; a.bias[2] = w0.b_fc; a.bias[3] = w0.b_proj2;
     a.ln_g[0] = w0.ln1_g; a.ln_g[1] = w0.ln2_g; a.ln_b[0] = w0.ln1_b; a.ln_b[1] = w0.ln2_b;
@@ -779,13 +838,13 @@ static cudaError_t enqueue_decode_step(pg_cache* c, int batch, int splits, cudaS
   fa.token_log = c->d_token_log; fa.n_positions = m->positions();
   if (fuse) {
     LinearArgs a{};
-    a.w = m->wte; a.x = c->x; a.out = c->logits; a.ln_g = m->lnf_g; a.ln_b = m->lnf_b; a.eps = eps;
+    a.w = m->head_w; a.x = c->x; a.out = c->logits; a.ln_g = m->lnf_g; a.ln_b = m->lnf_b; a.eps = eps;
     a.m = batch; a.n = V; a.k = C; a.part_val = c->part_val; a.part_idx = c->part_idx;
     int grid = 0;
     PG_E(launch_linear_decode(a, EPI_NONE, pdl, s, &grid));
     fa.part_val = c->part_val; fa.part_idx = c->part_idx; fa.parts = grid;
   } else {
-    PG_E(linear(m->wte, nullptr, c->x, c->logits, V, C, EPI_NONE, nullptr, m->lnf_g, m->lnf_b));
+    PG_E(linear(m->head_w, nullptr, c->x, c->logits, V, C, EPI_NONE, nullptr, m->lnf_g, m->lnf_b));
     PG_E(launch_argmax_rows(c->logits, batch, V, c->d_argmax, s));
   }
   cur_bucket = B_OTHER;
@@ -1064,7 +1123,7 @@ static int do_prefill(const pg_model* m, pg_cache* c, const int32_t* ids, const 
   PG_CUDA_TRY(launch_gather_rows(c->px, d_last, c->x, batch, m->c(), s));
   PG_CUDA_TRY(launch_layernorm_rows(c->x, m->lnf_g, m->lnf_b, m->cfg.layer_norm_epsilon, c->norm, batch, m->c(), false, s));
   LinearArgs a{};
-  a.w = m->wte; a.x = c->norm; a.out = c->logits; a.m = batch; a.n = m->v(); a.k = m->c();
+  a.w = m->head_w; a.x = c->norm; a.out = c->logits; a.m = batch; a.n = m->v(); a.k = m->c();
   if (batch > 64 && a.k % 4 == 0) PG_CUDA_TRY(launch_gemm_f32(a, EPI_NONE, s));
   else PG_CUDA_TRY(launch_linear_decode(a, EPI_NONE, false, s, nullptr));
   PG_CUDA_TRY(launch_argmax_rows(c->logits, batch, m->v(), c->d_argmax, s));
@@ -1145,7 +1204,7 @@ static int do_forward(const pg_model* m, const int32_t* ids, int t, float* logit
     const float* hidden = last_only ? x + (R - 1) * C : x;
     PG_CUDA_TRY(launch_layernorm_rows(hidden, m->lnf_g, m->lnf_b, m->cfg.layer_norm_epsilon, norm, (int)out_rows, (int)C, false, s));
     LinearArgs a{};
-    a.w = m->wte; a.x = norm; a.out = logits; a.m = (int)out_rows; a.n = (int)V; a.k = (int)C;
+    a.w = m->head_w; a.x = norm; a.out = logits; a.m = (int)out_rows; a.n = (int)V; a.k = (int)C;
     if (out_rows > 16 && C % 4 == 0) PG_CUDA_TRY(launch_gemm_f32(a, EPI_NONE, s));
     else PG_CUDA_TRY(launch_linear_decode(a, EPI_NONE, false, s, nullptr));
     PG_CUDA_TRY(cudaMemcpyAsync(logits_out, logits, out_rows * V * sizeof(float), cudaMemcpyDeviceToHost, s));

@@ -43,6 +43,26 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const float* __restr
   }
 }
 
+// w[r][i] = (q as f32) * scale[r]: the factor quantized_dot multiplies every activation by (cpu.rs:173-184)
+__global__ void __launch_bounds__(256) dequantize_rows_kernel(const int8_t* __restrict__ q, const float* __restrict__ scales,
+                                                              float* __restrict__ w, int cols) {
+  const size_t r = blockIdx.x;
+  const float scale = scales[r];
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) w[r * cols + i] = (float)q[r * cols + i] * scale;
+}
+
+// BF16 (round to nearest even; NaN stays NaN) of every value, packed, and written back as FP32
+__global__ void __launch_bounds__(256) round_bf16_kernel(float* __restrict__ w, size_t n, uint16_t* __restrict__ packed) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const uint32_t u = __float_as_uint(w[i]);
+    uint32_t hi;
+    if ((u & 0x7fffffffu) > 0x7f800000u) hi = (u >> 16) | 0x40u;  // quiet NaN
+    else hi = (u + 0x7fffu + ((u >> 16) & 1u)) >> 16;
+    packed[i] = (uint16_t)hi;
+    w[i] = __uint_as_float(hi << 16);
+  }
+}
+
 // ------------------------------------------------------------------ projection, at most 8 activation rows
 // int8 -> float without the quarter-rate conversion unit: with the sign bit flipped a byte is q + 128,
 // placed in the mantissa of 2^23 it reads 8388608 + q + 128, and one subtraction leaves q exactly.
@@ -252,6 +272,21 @@ struct Buf {
 constexpr size_t Q8_FLUSH_BYTES = 256u << 20;  // larger than the 126 MB L2
 
 }  // namespace
+
+cudaError_t launch_quantize_rows(const float* w, int rows, int cols, int8_t* q, float* scales, cudaStream_t s) {
+  quantize_rows_kernel<<<rows, 256, 0, s>>>(w, q, scales, cols);
+  return cudaGetLastError();
+}
+cudaError_t launch_dequantize_rows(const int8_t* q, const float* scales, int rows, int cols, float* w, cudaStream_t s) {
+  dequantize_rows_kernel<<<rows, 256, 0, s>>>(q, scales, w, cols);
+  return cudaGetLastError();
+}
+cudaError_t launch_round_bf16(float* w, size_t n, uint16_t* packed, cudaStream_t s) {
+  const int blocks = (int)std::min<size_t>((n + 255) / 256, 148 * 16);
+  round_bf16_kernel<<<blocks, 256, 0, s>>>(w, n, packed);
+  return cudaGetLastError();
+}
+
 }  // namespace pg
 
 using namespace pg;

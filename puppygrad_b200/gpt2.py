@@ -74,6 +74,7 @@ class Gpt2CudaConfig:
     # one cooperative kernel per decode step of <= 8 sequences: None = where it is the faster path, True = whenever
     # the shapes allow, False = never (a CUDA graph of one kernel per operation)
     persistent_step: Optional[bool] = None
+    quantized_weights: bool = False  # Gpt2RustConfig::quantized_weights: row-wise int8 dense matrices and lm_head
 
     def to_native(self) -> N.PgBackendConfig:
         if self.math_mode not in _MATH:
@@ -82,6 +83,7 @@ class Gpt2CudaConfig:
         b.device, b.math_mode, b.page_tokens = self.device, _MATH[self.math_mode], self.page_tokens
         b.use_graphs, b.attn_splits = (1 if self.use_graphs else 2), self.attn_splits
         b.persistent_step = 0 if self.persistent_step is None else (1 if self.persistent_step else 2)
+        b.quantized_weights = 1 if self.quantized_weights else 0
         return b
 
 

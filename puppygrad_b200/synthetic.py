@@ -83,6 +83,23 @@ def perturbed_weights(cfg: dict, seed: int = 0) -> dict[str, np.ndarray]:
     return w
 
 
+def round_bf16(a: np.ndarray) -> np.ndarray:
+    """float32 values rounded to the nearest BF16 (ties to even), returned as float32."""
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32)
+    r = ((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)) << np.uint32(16)
+    return r.view(np.float32).reshape(a.shape)
+
+
+def bf16_rounded_weights(w: dict[str, np.ndarray]) -> dict[str, np.ndarray]:
+    """What math_mode "bf16" computes with: the four dense matrices of every block and the tied embedding rounded
+    to BF16, everything else (biases, LayerNorm, position embedding) unchanged."""
+    out = dict(w)
+    for name, a in w.items():
+        if name == "wte.weight" or (a.ndim == 2 and name.startswith("h.")):
+            out[name] = round_bf16(a)
+    return out
+
+
 def patterned(n: int, scale: float) -> np.ndarray:
     """The reference tests' deterministic fill (rust.rs:2117-2121, cpu.rs:348-352)."""
     i = np.arange(n, dtype=np.int64)

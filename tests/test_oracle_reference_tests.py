@@ -165,6 +165,33 @@ def test_threaded_logits_are_bit_identical_on_a_larger_model(oracle):
     assert np.array_equal(a.forward(ids), b.forward(ids))
 
 
+def test_quantized_rust_forward_returns_finite_logits(oracle):
+    """rust.rs:1996-2013, plus what the reference's code implies for the quantised model: threads do not
+    matter, cached == full, the batched loop is the same arithmetic, and the result stays close to FP32."""
+    cfg = synthetic.preset("tiny")
+    w = synthetic.tiny_weights(cfg)
+    q = oracle.Model(cfg, w, quantized_weights=True)
+    out = q.forward([1, 2, 3])
+    assert out.shape == (3, cfg["vocab_size"]) and np.isfinite(out).all()
+    assert np.array_equal(out, oracle.Model(cfg, w, threads=3, quantized_weights=True).forward([1, 2, 3]))
+    cache = q.new_kv_cache()
+    assert np.all(np.abs(q.prefill([1, 2, 3], cache) - out[-1]) <= 1e-5)
+
+    cfg = synthetic.preset("mini")
+    w = synthetic.perturbed_weights(cfg, 5)
+    ids = synthetic.uniform_prompt(4, 9, cfg["vocab_size"])
+    qm = oracle.Model(cfg, w, quantized_weights=True)
+    c1, c2 = qm.new_kv_cache(), qm.new_kv_cache()
+    qm.prefill(ids[:5], c1)
+    qm.prefill(ids[:5], c2)
+    one = np.stack([qm.forward_one(int(t), c) for t, c in ((ids[5], c1), (ids[6], c2))])
+    c1.seq_len = c2.seq_len = 5
+    both, am = qm.forward_one_batch([int(ids[5]), int(ids[6])], [c1, c2], want_logits=True)
+    assert np.array_equal(one, both) and list(am) == [oracle.argmax_logits(r) for r in one]
+    fp32 = oracle.Model(cfg, w).forward(ids)
+    assert np.abs(qm.forward(ids) - fp32).max() < 0.05 * np.abs(fp32).max() + 0.05
+
+
 def test_input_validation_messages(oracle):
     """rust.rs:1029-1051, 950-962"""
     cfg, w = tiny()
