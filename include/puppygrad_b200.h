@@ -264,6 +264,17 @@ int pg_op_decode_attention(const float* qkv, const float* keys, const float* val
                            int32_t n_head, int32_t head_dim, int32_t kv_len, int32_t page_tokens,
                            int32_t splits, int32_t device, int32_t reps, float* out,
                            double* seconds_per_launch);
+/* LayerNorm of `rows` rows of `cols` values on host buffers: layer_norm_in_place, src/models/cpu.rs:119-143
+ * (mean, biased variance of the centred values, (v - mean) / sqrt(var + eps) * gamma + beta). Timing as in
+ * pg_op_linear. */
+int pg_op_layernorm(const float* x, const float* gamma, const float* beta, float eps, int32_t rows, int32_t cols,
+                    int32_t device, int32_t reps, float* out, double* seconds_per_launch);
+/* The end of a decode step on host buffers: logits[m, vocab] = hidden[m, k] . wte[vocab, k]^T without bias
+ * (logits_from_hidden_into, src/models/gpt2/rust.rs:1767-1813) with the row arg-max fused into the same pass
+ * (argmax_logits, src/models/generation.rs:269-279: first strict maximum, NaN never wins). 1 <= m <= 8.
+ * logits_out may be NULL. Timing as in pg_op_linear (both launches of the operator are inside the timed region). */
+int pg_op_lm_head_argmax(const float* hidden, const float* wte, int32_t m, int32_t vocab, int32_t k, int32_t device,
+                         int32_t reps, float* logits_out, int32_t* argmax_out, double* seconds_per_launch);
 /* Row-wise symmetric int8 quantisation of a [rows, cols] FP32 matrix on the device:
  * QuantizedRows::from_f32, src/models/cpu.rs:33-57 (scale = max|w| / 127, 1 for an all-zero row;
  * q = clamp(round(w / scale), -127, 127)). q_out is [rows, cols] int8, scales_out [rows]. The bytes
@@ -293,7 +304,10 @@ int pg_op_linear_q8(const float* x, const int8_t* q, const float* scales, const 
  * larger requests fail with PG_INVALID_INPUT. The first call on a device looks up that array's
  * address for the device and sets kernel attributes; make that first call before any stream
  * capture begins. Every call shares the one array: two calls whose kernels overlap on the GPU
- * (different streams, different threads) race on it, so keep calls on one device ordered. */
+ * (different streams, different threads) race on it, so keep calls on one device ordered.
+ * Preconditions the host cannot check: every d_pos[b] < pages_per_seq * page_tokens (the page-table row is
+ * indexed by it) and every page number in d_page_table lies inside d_kv_pool. `device` is current only for
+ * the duration of the call; the calling thread's current device is restored before it returns. */
 int pg_decode_attention_noalloc(const float* d_qkv, float* d_out, float* d_kv_pool,
                                 const int32_t* d_page_table, const int32_t* d_pos, int32_t batch,
                                 int32_t n_head, int32_t head_dim, int32_t page_tokens,

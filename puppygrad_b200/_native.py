@@ -89,6 +89,10 @@ SIGNATURES = {
                                C.c_int32, C.c_int32, _fp, C.POINTER(C.c_double)]),
     "pg_op_decode_attention": (C.c_int, [_fp, _fp, _fp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                          C.c_int32, C.c_int32, C.c_int32, _fp, C.POINTER(C.c_double)]),
+    "pg_op_layernorm": (C.c_int, [_fp, _fp, _fp, C.c_float, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _fp,
+                                  C.POINTER(C.c_double)]),
+    "pg_op_lm_head_argmax": (C.c_int, [_fp, _fp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _fp, _ip,
+                                       C.POINTER(C.c_double)]),
     "pg_op_quantize_rows": (C.c_int, [_fp, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int8), _fp]),
     "pg_op_linear_q8": (C.c_int, [_fp, C.POINTER(C.c_int8), _fp, _fp, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                   C.c_int32, _fp, C.POINTER(C.c_double)]),

@@ -18,7 +18,7 @@ OBJ_DIR = os.path.join(CSRC, "build")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-I", INCLUDE, "-I", CSRC]
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-I", INCLUDE, "-I", CSRC]
-# developer aid: extra compiler flags (e.g. PG_NVCC_EXTRA="-DPG_STREAM_TRACE"); rebuild with --force after changing it
+# developer aid: extra compiler flags (e.g. PG_NVCC_EXTRA="-DPG_DEV_TRACE"); rebuild with --force after changing it
 NVCC_FLAGS += os.environ.get("PG_NVCC_EXTRA", "").split()
 
 

@@ -54,9 +54,9 @@ constexpr int ST_MAX_PAGES = 64;           // page-table entries per sequence (1
 
 typedef unsigned long long u64;
 
-// Developer aid, compiled in only with -DPG_STREAM_TRACE: CTAs 0 and 100 stamp clock64() at the phase
+// Developer aid, compiled in only with -DPG_DEV_TRACE: CTAs 0 and 100 stamp clock64() at the phase
 // boundaries of every layer into StreamArgs::trace ([2][n_layer + 1][16] words).
-#ifdef PG_STREAM_TRACE
+#ifdef PG_DEV_TRACE
 #define ST_TRACE(layer, point)                                                                              \
   do {                                                                                                      \
     if (sh.args.trace && threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == 100))                        \
@@ -542,14 +542,34 @@ __device__ __forceinline__ void stage_input(const u64* ll, unsigned tag, int k, 
       for (int col = tid; col < k; col += ST_CT) xs[b * k + col] = te[col] + pe[col];
     }
   } else {
+    // sixteen words per thread in flight while there are that many (eight sequences of 4096 values are 68
+    // words per thread: four words at a time would be seventeen dependent round trips to L2)
 #pragma unroll 1
-    for (int base = tid; base < total; base += ST_CT * 4) {
-      const int n = min(4, (total - base + ST_CT - 1) / ST_CT);
-      const float4 r = ll_poll4(ll + base, ST_CT, n, tag, 44);
-      xs[base] = r.x;
-      if (n > 1) xs[base + ST_CT] = r.y;
-      if (n > 2) xs[base + 2 * ST_CT] = r.z;
-      if (n > 3) xs[base + 3 * ST_CT] = r.w;
+    for (int base = tid; base < total; base += ST_CT * 16) {
+      const int n = min(16, (total - base + ST_CT - 1) / ST_CT);
+      if (n == 16) {
+        u64 v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = ll_ld(ll + base + j * ST_CT);
+        bool all = true;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) all = all && (unsigned)(v[j] >> 32) == tag;
+        if (all) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) xs[base + j * ST_CT] = __uint_as_float((unsigned)v[j]);
+          continue;
+        }
+      }
+#pragma unroll 1
+      for (int j0 = 0; j0 < n; j0 += 4) {  // not all there yet (or a short tail): four at a time, waiting
+        const int m4 = min(4, n - j0);
+        const float4 r = ll_poll4(ll + base + j0 * ST_CT, ST_CT, m4, tag, 44);
+        float* dst = xs + base + j0 * ST_CT;
+        dst[0] = r.x;
+        if (m4 > 1) dst[ST_CT] = r.y;
+        if (m4 > 2) dst[2 * ST_CT] = r.z;
+        if (m4 > 3) dst[3 * ST_CT] = r.w;
+      }
     }
   }
   for (int i = total + tid; i < MT * k; i += ST_CT) xs[i] = 0.f;

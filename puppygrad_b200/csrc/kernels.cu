@@ -1351,7 +1351,18 @@ extern "C" int pg_decode_attention_noalloc(const float* d_qkv, float* d_out, flo
                                            " exceeds the built-in scratch limit of " + std::to_string(NOALLOC_MAX_PAIRS));
   if ((int64_t)pages_per_seq * page_tokens > 16320 * (int64_t)splits)
     return set_error(PG_INVALID_INPUT, "context too long for the kernel's score buffer");
-  if (int r = ensure_device(device)) return r;  // makes `device` current; allocates nothing
+  // `device` is made current for the launch and the caller's current device is put back on every way out: an
+  // embedder that calls this from a thread bound to another device must not find it changed
+  struct DeviceGuard {
+    int prev = -1;
+    DeviceGuard() {
+      if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+    }
+    ~DeviceGuard() {
+      if (prev >= 0) cudaSetDevice(prev);
+    }
+  } guard;
+  if (int r = ensure_device(device)) return r;  // allocates nothing
   float* scratch = nullptr;
   if (int r = noalloc_scratch(device, &scratch)) return r;
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -240,7 +240,7 @@ struct StreamArgs {
   int m, attn_splits;         // attn_splits 0: chosen from the context length
   unsigned spin_limit;        // polls before a wait gives up (0: default)
   unsigned poison;            // test hook: XORed into one expected tag, so that the wait for it runs out
-  unsigned long long* trace;  // developer aid (builds with -DPG_STREAM_TRACE only), else nullptr
+  unsigned long long* trace;  // developer aid (builds with -DPG_DEV_TRACE only), else nullptr
 };
 // Cooperative grid of the kernel on this device (0: not launchable).
 int decode_stream_grid(int num_sms);

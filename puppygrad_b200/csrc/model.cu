@@ -313,7 +313,7 @@ struct pg_cache {
   float* chain_partials = nullptr;
   unsigned* d_chain_barrier = nullptr;
   unsigned long long* d_chain_best = nullptr;  // row arg-max accumulators of the lm_head phase
-  unsigned long long* d_chain_trace = nullptr;  // PG_CHAIN_TRACE=1
+  unsigned long long* d_chain_trace = nullptr;  // developer aid: only allocated in builds with -DPG_DEV_TRACE
   int chain_ctas = 0;
   struct ChainProgram {  // whole-step phase list of the persistent chain kernel for one batch size
     ChainPhase* dev = nullptr;            // in device memory (nullptr: this batch size is not supported)
@@ -329,7 +329,7 @@ struct pg_cache {
   unsigned* d_stream_epoch = nullptr;
   int stream_grid = 0;
   unsigned dbg_spin_limit = 0, dbg_poison = 0;  // pg_cache_debug_expire_next_wait: consumed by the next decode step
-#ifdef PG_STREAM_TRACE
+#ifdef PG_DEV_TRACE
   unsigned long long* d_stream_trace = nullptr;
 #endif
   int *h_ids = nullptr, *h_out = nullptr;  // pinned staging
@@ -348,7 +348,7 @@ struct pg_cache {
     if (!model) return;
     cudaSetDevice(model->device);
     if (stream) cudaStreamSynchronize(stream);
-#ifdef PG_STREAM_TRACE
+#ifdef PG_DEV_TRACE
     if (d_stream_trace) {
       const int L = model->layers_n();
       std::vector<unsigned long long> t((size_t)2 * (L + 1) * 16 + 128);
@@ -364,6 +364,7 @@ struct pg_cache {
       cudaFree(d_stream_trace);
     }
 #endif
+#ifdef PG_DEV_TRACE
     if (d_chain_trace) {
       std::vector<unsigned long long> t((size_t)chain_ctas * 32 + 512);
       if (cudaMemcpy(t.data(), d_chain_trace, t.size() * 8, cudaMemcpyDeviceToHost) == cudaSuccess) {
@@ -379,6 +380,7 @@ struct pg_cache {
         }
       }
     }
+#endif
     for (auto& cp : chain_programs) {
       if (cp.second.dev) cudaFree(cp.second.dev);
       if (cp.second.dev_argmax_only) cudaFree(cp.second.dev_argmax_only);
@@ -472,10 +474,12 @@ static int cache_new(const pg_model* m, int max_batch, pg_cache** out) {
         PG_CUDA_TRY(cudaMalloc(&c->d_chain_best, init.size() * sizeof(unsigned long long)));
         PG_CUDA_TRY(cudaMemcpy(c->d_chain_best, init.data(), init.size() * sizeof(unsigned long long), cudaMemcpyHostToDevice));
       }
+#ifdef PG_DEV_TRACE
       if (env_flag("PG_CHAIN_TRACE")) {
         PG_CUDA_TRY(cudaMalloc(&c->d_chain_trace, ((size_t)c->chain_ctas * 32 + 512) * sizeof(unsigned long long)));
         PG_CUDA_TRY(cudaMemsetAsync(c->d_chain_trace, 0, ((size_t)c->chain_ctas * 32 + 512) * sizeof(unsigned long long), c->stream));
       }
+#endif
     }
   }
   if (m->backend.persistent_step != 2 && !env_flag("PG_NO_STREAM")) {
@@ -487,7 +491,7 @@ static int cache_new(const pg_model* m, int max_batch, pg_cache** out) {
       PG_CUDA_TRY(cudaMemsetAsync(c->d_stream_ll, 0, words * sizeof(unsigned long long), c->stream));
       PG_CUDA_TRY(cudaMalloc(&c->d_stream_epoch, sizeof(unsigned)));
       PG_CUDA_TRY(cudaMemsetAsync(c->d_stream_epoch, 0, sizeof(unsigned), c->stream));
-#ifdef PG_STREAM_TRACE
+#ifdef PG_DEV_TRACE
       PG_CUDA_TRY(cudaMalloc(&c->d_stream_trace, ((size_t)2 * (m->layers_n() + 1) * 16 + 128) * 8));
       PG_CUDA_TRY(cudaMemsetAsync(c->d_stream_trace, 0, ((size_t)2 * (m->layers_n() + 1) * 16 + 128) * 8, c->stream));
 #endif
@@ -715,7 +719,7 @@ static cudaError_t enqueue_decode_step(pg_cache* c, int batch, int splits, cudaS
     a.epoch = c->d_stream_epoch; a.error_flag = c->d_error;
     a.m = batch; a.attn_splits = m->backend.attn_splits > 8 ? 8 : m->backend.attn_splits;
     a.spin_limit = c->dbg_spin_limit; a.poison = c->dbg_poison;
-#ifdef PG_STREAM_TRACE
+#ifdef PG_DEV_TRACE
     a.trace = c->d_stream_trace;
 #endif
     if (launches) *launches = 1;
@@ -1167,56 +1171,81 @@ static int do_forward_one(const pg_model* m, pg_cache* c, const int32_t* ids, in
   return fetch_outputs(c, batch, logits_out, argmax_out, topk_vals, topk_idx, k);
 }
 
-// Full-sequence forward without a cache (Gpt2Model::forward, rust.rs:831-882). When
-// `last_only`, only the last position's logits are produced (what generate_greedy consumes).
-static int do_forward(const pg_model* m, const int32_t* ids, int t, float* logits_out, bool last_only) {
-  if (!m) return set_error(PG_INVALID_INPUT, "null model");
-  if (int r = validate_sequence(m, ids, t)) return r;
-  if (int r = ensure_device(m->device)) return r;
-  const size_t C = m->c(), F = m->f(), V = m->v(), R = t;
+// Device buffers and stream of the cache-less full-sequence forward, sized for `rows` positions and re-used
+// from call to call (generate_greedy runs one forward per token).
+struct ForwardWorkspace {
+  size_t rows = 0, out_rows = 0;
   float *x = nullptr, *norm = nullptr, *qkv = nullptr, *attn = nullptr, *h = nullptr, *logits = nullptr;
   int* meta = nullptr;
   cudaStream_t s = nullptr;
-  int rc = PG_OK;
-  auto body = [&]() -> int {
-    PG_CUDA_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
-    PG_CUDA_TRY(cudaMalloc(&x, R * C * sizeof(float)));
-    PG_CUDA_TRY(cudaMalloc(&norm, R * C * sizeof(float)));
-    PG_CUDA_TRY(cudaMalloc(&qkv, R * 3 * C * sizeof(float)));
-    PG_CUDA_TRY(cudaMalloc(&attn, R * C * sizeof(float)));
-    PG_CUDA_TRY(cudaMalloc(&h, R * F * sizeof(float)));
-    const size_t out_rows = last_only ? 1 : R;
-    PG_CUDA_TRY(cudaMalloc(&logits, out_rows * V * sizeof(float)));
-    PG_CUDA_TRY(cudaMalloc(&meta, (2 * R + 2) * sizeof(int)));
-    PrefillPlan plan;
-    plan.rows = t; plan.batch = 1; plan.max_len = t;
-    std::vector<int> hm(2 * R + 2);
-    for (int i = 0; i < t; ++i) {
-      hm[i] = ids[i];
-      hm[R + i] = i;
+  ~ForwardWorkspace() {
+    if (s) cudaStreamSynchronize(s);
+    for (void* p : {(void*)x, (void*)norm, (void*)qkv, (void*)attn, (void*)h, (void*)logits, (void*)meta})
+      if (p) cudaFree(p);
+    if (s) cudaStreamDestroy(s);
+  }
+  int reserve(const pg_model* m, size_t r, size_t o) {
+    if (!s) PG_CUDA_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    const size_t C = m->c(), F = m->f(), V = m->v();
+    if (r > rows) {
+      for (void* p : {(void*)x, (void*)norm, (void*)qkv, (void*)attn, (void*)h, (void*)meta})
+        if (p) cudaFree(p);
+      x = norm = qkv = attn = h = nullptr;
+      meta = nullptr;
+      rows = 0;
+      PG_CUDA_TRY(cudaMalloc(&x, r * C * sizeof(float)));
+      PG_CUDA_TRY(cudaMalloc(&norm, r * C * sizeof(float)));
+      PG_CUDA_TRY(cudaMalloc(&qkv, r * 3 * C * sizeof(float)));
+      PG_CUDA_TRY(cudaMalloc(&attn, r * C * sizeof(float)));
+      PG_CUDA_TRY(cudaMalloc(&h, r * F * sizeof(float)));
+      PG_CUDA_TRY(cudaMalloc(&meta, (2 * r + 2) * sizeof(int)));
+      rows = r;
     }
-    hm[2 * R] = 0;
-    hm[2 * R + 1] = t;
-    PG_CUDA_TRY(cudaMemcpyAsync(meta, hm.data(), hm.size() * sizeof(int), cudaMemcpyHostToDevice, s));
-    PG_CUDA_TRY(launch_embed(m->wte, m->wpe, meta, meta + R, x, t, (int)C, false, s));
-    BlockWorkspace ws{x, norm, qkv, attn, h, nullptr, meta + R, meta + 2 * R, nullptr};
-    if (int r = run_blocks(m, ws, plan, nullptr, s)) return r;
-    const float* hidden = last_only ? x + (R - 1) * C : x;
-    PG_CUDA_TRY(launch_layernorm_rows(hidden, m->lnf_g, m->lnf_b, m->cfg.layer_norm_epsilon, norm, (int)out_rows, (int)C, false, s));
-    LinearArgs a{};
-    a.w = m->head_w; a.x = norm; a.out = logits; a.m = (int)out_rows; a.n = (int)V; a.k = (int)C;
-    if (out_rows > 16 && C % 4 == 0) PG_CUDA_TRY(launch_gemm_f32(a, EPI_NONE, s));
-    else PG_CUDA_TRY(launch_linear_decode(a, EPI_NONE, false, s, nullptr));
-    PG_CUDA_TRY(cudaMemcpyAsync(logits_out, logits, out_rows * V * sizeof(float), cudaMemcpyDeviceToHost, s));
-    PG_CUDA_TRY(cudaStreamSynchronize(s));
+    if (o > out_rows) {
+      if (logits) cudaFree(logits);
+      logits = nullptr;
+      out_rows = 0;
+      PG_CUDA_TRY(cudaMalloc(&logits, o * V * sizeof(float)));
+      out_rows = o;
+    }
     return PG_OK;
-  };
-  rc = body();
-  if (s) cudaStreamSynchronize(s);
-  for (void* p : {(void*)x, (void*)norm, (void*)qkv, (void*)attn, (void*)h, (void*)logits, (void*)meta})
-    if (p) cudaFree(p);
-  if (s) cudaStreamDestroy(s);
-  return rc;
+  }
+};
+
+// Full-sequence forward without a cache (Gpt2Model::forward, rust.rs:831-882). When
+// `last_only`, only the last position's logits are produced (what generate_greedy consumes).
+// `reserve_rows`: positions the workspace should be sized for when it has to grow.
+static int do_forward(const pg_model* m, const int32_t* ids, int t, float* logits_out, bool last_only,
+                      ForwardWorkspace& ws, size_t reserve_rows) {
+  if (!m) return set_error(PG_INVALID_INPUT, "null model");
+  if (int r = validate_sequence(m, ids, t)) return r;
+  if (int r = ensure_device(m->device)) return r;
+  const size_t C = m->c(), V = m->v(), R = t;
+  const size_t out_rows = last_only ? 1 : R;
+  if (int r = ws.reserve(m, std::max(R, reserve_rows), out_rows)) return r;
+  cudaStream_t s = ws.s;
+  PrefillPlan plan;
+  plan.rows = t; plan.batch = 1; plan.max_len = t;
+  std::vector<int> hm(2 * R + 2);
+  for (int i = 0; i < t; ++i) {
+    hm[i] = ids[i];
+    hm[R + i] = i;
+  }
+  hm[2 * R] = 0;
+  hm[2 * R + 1] = t;
+  PG_CUDA_TRY(cudaMemcpyAsync(ws.meta, hm.data(), hm.size() * sizeof(int), cudaMemcpyHostToDevice, s));
+  PG_CUDA_TRY(launch_embed(m->wte, m->wpe, ws.meta, ws.meta + R, ws.x, t, (int)C, false, s));
+  BlockWorkspace bw{ws.x, ws.norm, ws.qkv, ws.attn, ws.h, nullptr, ws.meta + R, ws.meta + 2 * R, nullptr};
+  if (int r = run_blocks(m, bw, plan, nullptr, s)) return r;
+  const float* hidden = last_only ? ws.x + (R - 1) * C : ws.x;
+  PG_CUDA_TRY(launch_layernorm_rows(hidden, m->lnf_g, m->lnf_b, m->cfg.layer_norm_epsilon, ws.norm, (int)out_rows, (int)C, false, s));
+  LinearArgs a{};
+  a.w = m->head_w; a.x = ws.norm; a.out = ws.logits; a.m = (int)out_rows; a.n = (int)V; a.k = (int)C;
+  if (out_rows > 16 && C % 4 == 0) PG_CUDA_TRY(launch_gemm_f32(a, EPI_NONE, s));
+  else PG_CUDA_TRY(launch_linear_decode(a, EPI_NONE, false, s, nullptr));
+  PG_CUDA_TRY(cudaMemcpyAsync(logits_out, ws.logits, out_rows * V * sizeof(float), cudaMemcpyDeviceToHost, s));
+  PG_CUDA_TRY(cudaStreamSynchronize(s));  // also keeps `hm` alive long enough
+  return PG_OK;
 }
 
 static double now_s() {
@@ -1284,10 +1313,16 @@ uint64_t pg_model_weight_bytes_per_step(const pg_model* model) {
   if (!model) return 0;
   const pg_gpt2_config& c = model->cfg;
   // every block matrix, bias and LayerNorm vector once; the tied embedding once as lm_head;
-  // ln_f; one wte row and one wpe row are negligible and not counted
-  uint64_t per_layer = c.n_embd * 3 * c.n_embd + 3 * c.n_embd + c.n_embd * c.n_embd + c.n_embd +
-                       2 * c.n_embd * c.n_inner + c.n_inner + c.n_embd + 4 * c.n_embd;
-  return 4 * (c.n_layer * per_layer + c.vocab_size * c.n_embd + 2 * c.n_embd);
+  // ln_f; one wte row and one wpe row are negligible and not counted. With BF16 / int8 weights the
+  // matrices and the lm_head count at their narrow size (what decode steps of at most 8 sequences read),
+  // int8 with one FP32 scale per row
+  const uint64_t dense = c.n_embd * 3 * c.n_embd + c.n_embd * c.n_embd + 2 * c.n_embd * c.n_inner;
+  const uint64_t dense_rows = 3 * c.n_embd + c.n_embd + c.n_inner + c.n_embd;
+  const uint64_t vectors = 3 * c.n_embd + c.n_embd + c.n_inner + c.n_embd + 4 * c.n_embd;
+  const uint64_t eb = model->stream_weight_type == STREAM_W_F32 ? 4 : model->stream_weight_type == STREAM_W_BF16 ? 2 : 1;
+  const uint64_t scales = model->stream_weight_type == STREAM_W_I8 ? 4 : 0;
+  return c.n_layer * (dense * eb + dense_rows * scales + vectors * 4) + c.vocab_size * (c.n_embd * eb + scales) +
+         2 * c.n_embd * 4;
 }
 
 void pg_model_free(pg_model* model) { delete model; }
@@ -1370,7 +1405,8 @@ int pg_forward_one(const pg_model* model, pg_cache* cache, const int32_t* ids, i
 
 int pg_forward(const pg_model* model, const int32_t* ids, int32_t t, float* logits_out) {
   if (!logits_out) return set_error(PG_INVALID_INPUT, "null logits_out");
-  return do_forward(model, ids, t, logits_out, false);
+  ForwardWorkspace ws;
+  return do_forward(model, ids, t, logits_out, false, ws, 0);
 }
 
 int pg_decode_greedy(const pg_model* model, pg_cache* cache, const int32_t* first_ids, int32_t batch,
@@ -1384,6 +1420,11 @@ int pg_decode_greedy(const pg_model* model, pg_cache* cache, const int32_t* firs
     if (cache->seq_len[b] + steps > model->positions())
       return set_error(PG_INVALID_INPUT, "cache is full at seq_len " + std::to_string(model->positions()));
   std::vector<int> start(cache->seq_len.begin(), cache->seq_len.begin() + batch);
+  // pages for the whole run now: one page-table upload instead of a host round trip at every page boundary
+  PG_CUDA_TRY(cudaSetDevice(model->device));
+  for (int b = 0; b < batch; ++b)
+    if (int r = ensure_pages(cache, b, cache->seq_len[b] + steps)) return r;
+  if (int r = sync_table(cache)) return r;
   for (int s = 0; s < steps; ++s) {
     if (int r = prepare_step(model, cache, s == 0 ? first_ids : nullptr, batch)) return r;
     cache->step_wants_logits = false;
@@ -1447,7 +1488,11 @@ int pg_profile_forward_one(const pg_model* model, pg_cache* cache, const int32_t
       std::vector<unsigned long long> ts((size_t)it->second.n + 1);
       PG_CUDA_TRY(cudaMemcpy(ts.data(), it->second.d_times, ts.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
       double covered = 0.0;
+#ifdef PG_DEV_TRACE
       const bool dump = env_flag("PG_PHASE_DUMP");  // tuning aid: every phase's duration
+#else
+      constexpr bool dump = false;
+#endif
       for (int p = 0; p < it->second.n; ++p) {
         const double d = (double)(ts[p + 1] - ts[p]) * 1e-9;
         if (dump) fprintf(stderr, "phase %3d bucket %d %8.2f us\n", p, it->second.bucket[p], d * 1e6);
@@ -1510,9 +1555,11 @@ int pg_generate_greedy(const pg_model* model, const int32_t* ids, int32_t n_ids,
   if (int r = validate_sequence(model, ids, n_ids)) return r;
   std::vector<int32_t> tokens(ids, ids + n_ids);
   std::vector<float> logits(model->cfg.vocab_size);
+  ForwardWorkspace ws;  // one set of buffers for every token of this call
+  const size_t longest = std::min<uint64_t>(model->cfg.n_positions, (uint64_t)n_ids + max_new_tokens);
   for (uint64_t i = 0; i < max_new_tokens; ++i) {
     if (tokens.size() >= model->cfg.n_positions) break;
-    if (int r = do_forward(model, tokens.data(), (int)tokens.size(), logits.data(), true)) return r;
+    if (int r = do_forward(model, tokens.data(), (int)tokens.size(), logits.data(), true, ws, longest)) return r;
     tokens.push_back((int32_t)argmax_logits(logits.data(), logits.size()));
   }
   memcpy(out_tokens, tokens.data(), tokens.size() * sizeof(int32_t));
@@ -1558,7 +1605,8 @@ int pg_generate_with_config(const pg_model* model, const int32_t* ids, int32_t n
   const bool greedy = cfg->temperature <= 0.0f;
   // what each step must bring back from the device
   const bool use_argmax = greedy && !penalty;
-  const bool use_topk = !greedy && !penalty && cfg->top_k > 0 && cfg->top_k <= MAX_TOPK;
+  // the device top-k keeps one key per vocabulary entry in shared memory; larger vocabularies sample on the host
+  const bool use_topk = !greedy && !penalty && cfg->top_k > 0 && cfg->top_k <= MAX_TOPK && V * sizeof(int) <= 220 * 1024;
   const int k = use_topk ? (int)cfg->top_k : 0;
   std::vector<float> logits(use_argmax || use_topk ? 0 : V);
   std::vector<float> tv(k);

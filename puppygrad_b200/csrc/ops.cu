@@ -55,7 +55,11 @@ extern "C" int pg_op_linear(const float* x, const float* w, const float* bias, c
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   const size_t xs = (size_t)m * k, ws = (size_t)n * k, os = (size_t)m * n;
   DeviceBuf dx, dw, dwt, db, dr, dout, dhi, dlo, derr, dflush, dtrace, dpart, dbar;
-  const bool want_trace = getenv("PG_TRACE") != nullptr;
+#ifdef PG_DEV_TRACE
+  const bool want_trace = getenv("PG_TRACE") != nullptr;  // developer aid: phase time stamps of the kernel, printed below
+#else
+  constexpr bool want_trace = false;
+#endif
   // tf32x3 runs on the persistent chain kernel (one GEMM phase + its reduce phase) unless PG_NO_CHAIN is set
   int chain_ctas = 0;
   ChainArgs chain{};
@@ -309,5 +313,117 @@ done:
   if (e0) cudaEventDestroy(e0);
   if (e1) cudaEventDestroy(e1);
   if (s) cudaStreamDestroy(s);
+  return rc;
+}
+
+// Times `run` reps times on `s` with the operands evicted from L2 before each launch; mean seconds.
+template <typename F>
+static cudaError_t time_launches(F&& run, cudaStream_t s, int reps, double* seconds) {
+  void* flush = nullptr;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  cudaError_t e = cudaMalloc(&flush, FLUSH_BYTES);
+  if (e == cudaSuccess) e = cudaEventCreate(&e0);
+  if (e == cudaSuccess) e = cudaEventCreate(&e1);
+  double total = 0.0;
+  for (int i = 0; i < reps + 3 && e == cudaSuccess; ++i) {
+    e = cudaMemsetAsync(flush, i, FLUSH_BYTES, s);
+    if (e == cudaSuccess) e = cudaEventRecord(e0, s);
+    if (e == cudaSuccess) e = run(s);
+    if (e == cudaSuccess) e = cudaEventRecord(e1, s);
+    if (e == cudaSuccess) e = cudaEventSynchronize(e1);
+    float ms = 0.f;
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+    if (i >= 3) total += ms * 1e-3;
+  }
+  if (e0) cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  if (flush) cudaFree(flush);
+  if (e == cudaSuccess) *seconds = total / reps;
+  return e;
+}
+
+extern "C" int pg_op_layernorm(const float* x, const float* gamma, const float* beta, float eps, int32_t rows,
+                               int32_t cols, int32_t device, int32_t reps, float* out, double* seconds_per_launch) {
+  if (!x || !gamma || !beta || !out) return set_error(PG_INVALID_INPUT, "null argument");
+  if (rows <= 0 || cols <= 0) return set_error(PG_INVALID_INPUT, "rows and cols must be > 0");
+  if (int r = ensure_device(device)) return r;
+  int rc = PG_OK;
+  const size_t n = (size_t)rows * cols;
+  DeviceBuf dx, dg, db, dout;
+  cudaStream_t s = nullptr;
+  auto run = [&](cudaStream_t st) {
+    return launch_layernorm_rows(dx.as<float>(), dg.as<float>(), db.as<float>(), eps, dout.as<float>(), rows, cols, false, st);
+  };
+  PG_OP_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  PG_OP_TRY(cudaMalloc(&dx.p, n * 4));
+  PG_OP_TRY(cudaMalloc(&dout.p, n * 4));
+  PG_OP_TRY(cudaMalloc(&dg.p, (size_t)cols * 4));
+  PG_OP_TRY(cudaMalloc(&db.p, (size_t)cols * 4));
+  PG_OP_TRY(cudaMemcpyAsync(dx.p, x, n * 4, cudaMemcpyHostToDevice, s));
+  PG_OP_TRY(cudaMemcpyAsync(dg.p, gamma, (size_t)cols * 4, cudaMemcpyHostToDevice, s));
+  PG_OP_TRY(cudaMemcpyAsync(db.p, beta, (size_t)cols * 4, cudaMemcpyHostToDevice, s));
+  PG_OP_TRY(run(s));
+  PG_OP_TRY(cudaMemcpyAsync(out, dout.p, n * 4, cudaMemcpyDeviceToHost, s));
+  PG_OP_TRY(cudaStreamSynchronize(s));
+  if (reps > 0 && seconds_per_launch) PG_OP_TRY(time_launches(run, s, reps, seconds_per_launch));
+done:
+  if (s) {
+    cudaStreamSynchronize(s);
+    cudaStreamDestroy(s);
+  }
+  return rc;
+}
+
+extern "C" int pg_op_lm_head_argmax(const float* hidden, const float* wte, int32_t m, int32_t vocab, int32_t k,
+                                    int32_t device, int32_t reps, float* logits_out, int32_t* argmax_out,
+                                    double* seconds_per_launch) {
+  if (!hidden || !wte || !argmax_out) return set_error(PG_INVALID_INPUT, "null argument");
+  if (m <= 0 || m > 8 || vocab <= 0 || k <= 0 || k % 4 != 0)
+    return set_error(PG_INVALID_INPUT, "lm_head with fused arg-max is the decode operator: 1 <= m <= 8, k a multiple of 4");
+  if (int r = ensure_device(device)) return r;
+  int rc = PG_OK;
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  const int stride = linear_decode_grid(vocab, sms);
+  DeviceBuf dx, dw, dlog, dpv, dpi, dam, dids, dpos, dtok;
+  cudaStream_t s = nullptr;
+  // the same two launches that end a decode step: the lm_head GEMV that also writes one (value, index) candidate
+  // per CTA and row, and the kernel that reduces the candidates (first strict maximum, generation.rs:269-279)
+  auto run = [&](cudaStream_t st) -> cudaError_t {
+    LinearArgs a{};
+    a.w = dw.as<float>(); a.x = dx.as<float>(); a.out = dlog.as<float>(); a.m = m; a.n = vocab; a.k = k;
+    a.part_val = dpv.as<float>(); a.part_idx = dpi.as<int>();
+    int grid = 0;
+    cudaError_t e = launch_linear_decode(a, EPI_NONE, false, st, &grid);
+    if (e != cudaSuccess) return e;
+    FinalizeArgs f{};
+    f.part_val = dpv.as<float>(); f.part_idx = dpi.as<int>(); f.parts = grid; f.m = m;
+    f.argmax_out = dam.as<int>(); f.next_ids = dids.as<int>(); f.pos = dpos.as<int>(); f.token_log = dtok.as<int>();
+    f.n_positions = 1;
+    return launch_finalize(f, false, st);
+  };
+  PG_OP_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  PG_OP_TRY(cudaMalloc(&dx.p, (size_t)m * k * 4));
+  PG_OP_TRY(cudaMalloc(&dw.p, (size_t)vocab * k * 4));
+  PG_OP_TRY(cudaMalloc(&dlog.p, (size_t)m * vocab * 4));
+  PG_OP_TRY(cudaMalloc(&dpv.p, (size_t)m * stride * 4));
+  PG_OP_TRY(cudaMalloc(&dpi.p, (size_t)m * stride * 4));
+  PG_OP_TRY(cudaMalloc(&dam.p, (size_t)m * 4));
+  PG_OP_TRY(cudaMalloc(&dids.p, (size_t)m * 4));
+  PG_OP_TRY(cudaMalloc(&dpos.p, (size_t)m * 4));
+  PG_OP_TRY(cudaMalloc(&dtok.p, (size_t)m * 4));
+  PG_OP_TRY(cudaMemsetAsync(dpos.p, 0, (size_t)m * 4, s));
+  PG_OP_TRY(cudaMemcpyAsync(dx.p, hidden, (size_t)m * k * 4, cudaMemcpyHostToDevice, s));
+  PG_OP_TRY(cudaMemcpyAsync(dw.p, wte, (size_t)vocab * k * 4, cudaMemcpyHostToDevice, s));
+  PG_OP_TRY(run(s));
+  PG_OP_TRY(cudaMemcpyAsync(argmax_out, dam.p, (size_t)m * 4, cudaMemcpyDeviceToHost, s));
+  if (logits_out) PG_OP_TRY(cudaMemcpyAsync(logits_out, dlog.p, (size_t)m * vocab * 4, cudaMemcpyDeviceToHost, s));
+  PG_OP_TRY(cudaStreamSynchronize(s));
+  if (reps > 0 && seconds_per_launch) PG_OP_TRY(time_launches(run, s, reps, seconds_per_launch));
+done:
+  if (s) {
+    cudaStreamSynchronize(s);
+    cudaStreamDestroy(s);
+  }
   return rc;
 }

@@ -32,6 +32,36 @@ def linear(x, w, bias=None, resid=None, epilogue: str = "none", math_mode: str =
     return out, (float(sec.value) if reps > 0 else None)
 
 
+def layernorm(x, gamma, beta, eps: float = 1e-5, device: int = 0, reps: int = 0):
+    """LayerNorm of every row of x [rows, cols] (layer_norm_in_place of the reference). Returns (out, seconds)."""
+    x = np.ascontiguousarray(x, np.float32)
+    gamma = np.ascontiguousarray(gamma, np.float32)
+    beta = np.ascontiguousarray(beta, np.float32)
+    rows, cols = x.shape
+    out = np.empty_like(x)
+    fp = lambda a: a.ctypes.data_as(C.POINTER(C.c_float))
+    sec = C.c_double(0.0)
+    check(N.lib.pg_op_layernorm(fp(x), fp(gamma), fp(beta), eps, rows, cols, device, reps, fp(out), C.byref(sec)))
+    return out, (float(sec.value) if reps > 0 else None)
+
+
+def lm_head_argmax(hidden, wte, want_logits: bool = True, device: int = 0, reps: int = 0):
+    """logits = hidden @ wte.T (no bias) with the row arg-max found in the same pass; at most 8 rows.
+    Returns (logits or None, argmax [m], seconds)."""
+    hidden = np.ascontiguousarray(hidden, np.float32)
+    wte = np.ascontiguousarray(wte, np.float32)
+    m, k = hidden.shape
+    v = wte.shape[0]
+    assert wte.shape[1] == k
+    logits = np.empty((m, v), np.float32) if want_logits else None
+    am = np.empty(m, np.int32)
+    fp = lambda a: a.ctypes.data_as(C.POINTER(C.c_float)) if a is not None else None
+    sec = C.c_double(0.0)
+    check(N.lib.pg_op_lm_head_argmax(fp(hidden), fp(wte), m, v, k, device, reps, fp(logits),
+                                     am.ctypes.data_as(C.POINTER(C.c_int32)), C.byref(sec)))
+    return logits, am, (float(sec.value) if reps > 0 else None)
+
+
 def quantize_rows(w, device: int = 0):
     """Row-wise symmetric int8 quantisation on the device (QuantizedRows::from_f32 of the reference).
     w [rows, cols] -> (int8 [rows, cols], float32 scales [rows])."""

@@ -4,6 +4,9 @@
     python -m puppygrad_b200.sweep linear --preset xl
     python -m puppygrad_b200.sweep linear_q8 --m 1 8 --n 4800 6400 --k 1600
     python -m puppygrad_b200.sweep prefill --model small --seqs 8 --prompt-len 1024 --math fp32 tf32
+    python -m puppygrad_b200.sweep layernorm --m 1 64 4096 --k 1600
+    python -m puppygrad_b200.sweep lm_head --m 1 8 --k 1600
+    python -m puppygrad_b200.sweep xl_table        # every case of the GPT-2 XL kernel sweep as one markdown table
 
 Prints one JSON line per case: seconds per launch, algorithmic GB/s (4*(k*n + m*k + m*n + n) bytes)
 and TFLOP/s (2*m*n*k), plus the largest deviation from a float64 product of the same inputs.
@@ -78,6 +81,63 @@ def linear_q8_case(m, n, k, reps, seed=0):
             "fp32_equivalent_gbps": 4 * n * k / sec / 1e9, "max_rel_err_vs_f64": err}
 
 
+def layernorm_case(rows, d, reps, seed=0):
+    """LayerNorm of `rows` rows of width d. Algorithmic bytes: 4 * (2 * rows * d + 2 * d)."""
+    rng = np.random.default_rng(seed + rows + 3 * d)
+    x = rng.standard_normal((rows, d), dtype=np.float32)
+    g = rng.standard_normal(d, dtype=np.float32)
+    b = rng.standard_normal(d, dtype=np.float32)
+    out, sec = ops.layernorm(x, g, b, 1e-5, reps=reps)
+    x64 = x[:4].astype(np.float64)
+    want = (x64 - x64.mean(1, keepdims=True)) / np.sqrt(x64.var(1, keepdims=True) + 1e-5) * g + b
+    err = float(np.abs(out[:4] - want).max() / max(np.abs(want).max(), 1e-30))
+    bytes_ = 4 * (2 * rows * d + 2 * d)
+    return {"op": "layernorm", "rows": rows, "d": d, "us": sec * 1e6, "gbps": bytes_ / sec / 1e9, "max_rel_err_vs_f64": err}
+
+
+def lm_head_case(m, k, vocab, reps, seed=0):
+    """Tied lm_head GEMV with the arg-max fused. Algorithmic bytes: 4 * (vocab * k + m * k + m * vocab)."""
+    rng = np.random.default_rng(seed + m + 3 * k)
+    h = rng.standard_normal((m, k), dtype=np.float32)
+    w = rng.standard_normal((vocab, k), dtype=np.float32)
+    logits, am, sec = ops.lm_head_argmax(h, w, reps=reps)
+    want = h.astype(np.float64) @ w.astype(np.float64).T
+    err = float(np.abs(logits - want).max() / max(np.abs(want).max(), 1e-30))
+    bytes_ = 4 * (vocab * k + m * k + m * vocab)
+    return {"op": "lm_head_argmax", "m": m, "k": k, "vocab": vocab, "us": sec * 1e6, "gbps": bytes_ / sec / 1e9,
+            "argmax_equal_f64": bool((am == want.argmax(1)).all()), "max_rel_err_vs_f64": err}
+
+
+def xl_table(reps, hbm_gbs, tf32_tflops):
+    """Every case of the kernel sweep on GPT-2 XL shapes, one markdown row each: time, algorithmic GB/s or
+    TFLOP/s, the fraction of the given peak that bounds the case, error against a float64 product."""
+    c, f, v = XL["c"], XL["f"], 50257
+    rows = ["| operator | shape | path | us | GB/s | TFLOP/s | bound | fraction of peak | max rel. error vs float64 |",
+            "|---|---|---|---|---|---|---|---|---|"]
+
+    def add(name, shape, path, r, bound):
+        frac = r["gbps"] / hbm_gbs if bound == "hbm" else r.get("tflops", 0.0) / tf32_tflops
+        rows.append(f"| {name} | {shape} | {path} | {r['us']:.1f} | {r['gbps']:.0f} | {r.get('tflops', 0.0):.1f} | {bound} | "
+                    f"{frac:.3f} | {r['max_rel_err_vs_f64']:.1e} |")
+        print(rows[-1], flush=True)
+
+    for m in (1, 8, 64, 512, 4096):
+        for (n, k) in ((3 * c, c), (c, c), (f, c), (c, f)):
+            maths = ["fp32"] + (["tf32x3"] if 8 < m <= 64 else []) + (["tf32"] if m >= 128 else [])
+            for math in maths:
+                r = linear_case(m, n, k, math, "none", reps)
+                add("linear", f"{m} x {k} -> {n}", math, r, "hbm" if m <= 64 else ("tensor" if math == "tf32" else "fp32 fma"))
+    for b in (1, 32, 256):
+        for kv in (128, 256, 512, 1024):
+            sp = max(1, min(8, (2 * 148 + b * 25 - 1) // (b * 25), (kv + 128) // 128))
+            add("decode attention", f"batch {b}, 25 heads, {kv} keys", f"{sp} splits", attention_case(b, 25, kv, sp, reps), "hbm")
+    for rws in (1, 64, 4096):
+        add("layernorm", f"{rws} x {c}", "fp32", layernorm_case(rws, c, reps), "hbm")
+    for m in (1, 8):
+        add("lm_head + arg-max", f"{m} x {c} -> {v}", "fp32", lm_head_case(m, c, v, reps), "hbm")
+    return rows
+
+
 def prefill_case(preset, seqs, prompt_len, math, reps):
     """Whole prefill of `seqs` prompts of `prompt_len` tokens (seeded random weights and ids),
     device-timed; the best of `reps` runs after one warm-up."""
@@ -104,7 +164,10 @@ def prefill_case(preset, seqs, prompt_len, math, reps):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["linear", "linear_q8", "attention", "prefill"])
+    ap.add_argument("op", choices=["linear", "linear_q8", "attention", "prefill", "layernorm", "lm_head", "xl_table"])
+    ap.add_argument("--hbm-gbs", type=float, default=6534.5, help="xl_table: HBM peak the fractions are taken of")
+    ap.add_argument("--tf32-tflops", type=float, default=838.0, help="xl_table: TF32 tensor peak (half the BF16 peak)")
+    ap.add_argument("--vocab", type=int, default=50257)
     ap.add_argument("--model", default="small", help="prefill: model preset")
     ap.add_argument("--seqs", type=int, default=8, help="prefill: prompts per call")
     ap.add_argument("--prompt-len", type=int, default=1024)
@@ -120,6 +183,19 @@ def main():
     ap.add_argument("--epilogue", default="none")
     ap.add_argument("--reps", type=int, default=10)
     a = ap.parse_args()
+    if a.op == "xl_table":
+        xl_table(a.reps, a.hbm_gbs, a.tf32_tflops)
+        return
+    if a.op == "layernorm":
+        for m in a.m:
+            for k in a.k:
+                print(json.dumps(layernorm_case(m, k, a.reps)), flush=True)
+        return
+    if a.op == "lm_head":
+        for m in a.m:
+            for k in a.k:
+                print(json.dumps(lm_head_case(m, k, a.vocab, a.reps)), flush=True)
+        return
     if a.op == "prefill":
         for math in a.math:
             print(json.dumps(prefill_case(a.model, a.seqs, a.prompt_len, math, a.reps)), flush=True)

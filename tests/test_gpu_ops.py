@@ -161,3 +161,33 @@ def test_decode_attention_matches_oracle(oracle, batch, n_head, d, kv_len, page,
     values = rng.standard_normal((batch, n_head, kv_len, d), dtype=np.float32)
     got, _ = ops.decode_attention(qkv, keys, values, page_tokens=page, splits=splits)
     np.testing.assert_allclose(got, oracle_attention(oracle, qkv, keys, values), rtol=1e-3, atol=1e-4)
+
+
+@pytest.mark.parametrize("rows", [1, 7, 300])
+def test_layernorm_operator_matches_oracle(oracle, rows):
+    """layer_norm_in_place (cpu.rs:119-143) at the width of GPT-2 XL."""
+    rng = np.random.default_rng(rows)
+    d = 1600
+    x = rng.standard_normal((rows, d), dtype=np.float32) * 3 + 0.5
+    g = rng.standard_normal(d, dtype=np.float32)
+    b = rng.standard_normal(d, dtype=np.float32)
+    got, _ = ops.layernorm(x, g, b, 1e-5)
+    want = oracle.layer_norm(x, rows, d, g, b, 1e-5).reshape(rows, d)
+    np.testing.assert_allclose(got, want, rtol=1e-3, atol=1e-4)
+
+
+@pytest.mark.parametrize("m", [1, 3, 8])
+def test_lm_head_with_fused_argmax_matches_oracle(oracle, m):
+    """logits_from_hidden_into (rust.rs:1767-1813) + argmax_logits (generation.rs:269-279), 1600 -> 50257."""
+    rng = np.random.default_rng(m)
+    k, v = 1600, 50257
+    h = rng.standard_normal((m, k), dtype=np.float32)
+    w = rng.standard_normal((v, k), dtype=np.float32) * 0.02
+    w[4321] = w[1234]  # an exact tie must go to the lower index
+    h[0] = w[1234] * 40  # ... and be the row maximum of the first row
+    logits, am, _ = ops.lm_head_argmax(h, w)
+    want = oracle.transposed_dense_projection(h, m, k, v, w, np.zeros(v, np.float32)).reshape(m, v)
+    np.testing.assert_allclose(logits, want, rtol=1e-3, atol=1e-4)
+    assert list(am) == [oracle.argmax_logits(r) for r in want] and am[0] == 1234
+    _, am2, _ = ops.lm_head_argmax(h, w, want_logits=False)
+    assert list(am2) == list(am)
