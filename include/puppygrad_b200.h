@@ -333,6 +333,37 @@ int pg_generate_with_config(const pg_model* model, const int32_t* ids, int32_t n
                             const pg_generation_config* cfg, pg_token_callback on_token, void* user,
                             int32_t* out_tokens, uint64_t* out_len, pg_generation_stats* stats);
 
+/* ------------------------------------------------------------------ text streaming and statistics (host side) */
+/* TokenDecoder::decode_tokens, src/models/streaming.rs:1-9, as a callback: writes the UTF-8 text of the `n` token
+ * ids into out[0..cap) and the length it needs into *out_len (when that exceeds cap the library calls again with a
+ * larger buffer); non-zero return = the decoder's error. The tokenizer itself stays with the caller
+ * (Gpt2Tokenizer, rust.rs:270-302, wraps the `tokenizers` crate and a tokenizer.json). */
+typedef int (*pg_decode_tokens_fn)(const uint64_t* token_ids, size_t n, char* out, size_t cap, size_t* out_len,
+                                   void* user);
+/* the `on_text` closure of stream_token; non-zero return aborts */
+typedef int (*pg_text_callback)(const char* text, size_t len, void* user);
+typedef struct pg_text_streamer pg_text_streamer;
+/* IncrementalTextStreamer::new / decoded / stream_token, src/models/streaming.rs:32-74: emits the token's own text
+ * when it is safe to (not empty, no U+FFFD), otherwise decodes all output ids and emits what was added. */
+int pg_text_streamer_new(const char* decoded, size_t len, pg_text_streamer** out);
+void pg_text_streamer_free(pg_text_streamer* streamer);
+int pg_text_streamer_decoded(const pg_text_streamer* streamer, const char** text, size_t* len);
+int pg_text_streamer_stream_token(pg_text_streamer* streamer, pg_decode_tokens_fn decoder, void* decoder_user,
+                                  const uint64_t* output_ids, size_t n_ids, uint64_t token_id,
+                                  pg_text_callback on_text, void* text_user);
+/* is_incremental_decode_safe, streaming.rs:76-78 (1 = safe) */
+int pg_is_incremental_decode_safe(const char* text, size_t len);
+/* escape_raw_token, streaming.rs:17-30 (the --stream-raw-tokens output): *out_len receives the escaped length;
+ * the text is written when it fits cap. */
+int pg_escape_raw_token(const char* token, size_t len, char* out, size_t cap, size_t* out_len);
+/* GenerationStats::{total_model_tokens, prefill_/decode_/total_tokens_per_second, average_decode_token_time},
+ * src/models/generation.rs:140-181; the last returns seconds, < 0 = None. */
+uint64_t pg_generation_stats_total_model_tokens(const pg_generation_stats* stats);
+double pg_generation_stats_prefill_tokens_per_second(const pg_generation_stats* stats);
+double pg_generation_stats_decode_tokens_per_second(const pg_generation_stats* stats);
+double pg_generation_stats_total_tokens_per_second(const pg_generation_stats* stats);
+double pg_generation_stats_average_decode_token_time(const pg_generation_stats* stats);
+
 /* ------------------------------------------------------------------ sampling (host side) */
 /* argmax_logits, src/models/generation.rs:269-279 */
 uint64_t pg_argmax_logits(const float* logits, size_t n);

@@ -47,6 +47,9 @@ class PgOperationProfile(C.Structure):
 
 
 TOKEN_CALLBACK = C.CFUNCTYPE(C.c_int, C.c_uint64, C.c_void_p)
+DECODE_TOKENS_FN = C.CFUNCTYPE(C.c_int, C.POINTER(C.c_uint64), C.c_size_t, C.POINTER(C.c_char), C.c_size_t,
+                               C.POINTER(C.c_size_t), C.c_void_p)
+TEXT_CALLBACK = C.CFUNCTYPE(C.c_int, C.POINTER(C.c_char), C.c_size_t, C.c_void_p)
 
 _fp, _ip = C.POINTER(C.c_float), C.POINTER(C.c_int32)
 _u64p, _vp = C.POINTER(C.c_uint64), C.c_void_p
@@ -102,6 +105,18 @@ SIGNATURES = {
     "pg_stream_greedy_tokens": (C.c_int, [_vp, _ip, C.c_int32, C.c_uint64, TOKEN_CALLBACK, _vp, _ip, _u64p]),
     "pg_generate_with_config": (C.c_int, [_vp, _ip, C.c_int32, C.POINTER(PgGenerationConfig), TOKEN_CALLBACK,
                                           _vp, _ip, _u64p, C.POINTER(PgGenerationStats)]),
+    "pg_text_streamer_new": (C.c_int, [C.c_char_p, C.c_size_t, C.POINTER(_vp)]),
+    "pg_text_streamer_free": (None, [_vp]),
+    "pg_text_streamer_decoded": (C.c_int, [_vp, C.POINTER(C.c_char_p), C.POINTER(C.c_size_t)]),
+    "pg_text_streamer_stream_token": (C.c_int, [_vp, DECODE_TOKENS_FN, _vp, _u64p, C.c_size_t, C.c_uint64,
+                                                TEXT_CALLBACK, _vp]),
+    "pg_is_incremental_decode_safe": (C.c_int, [C.c_char_p, C.c_size_t]),
+    "pg_escape_raw_token": (C.c_int, [C.c_char_p, C.c_size_t, C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t)]),
+    "pg_generation_stats_total_model_tokens": (C.c_uint64, [C.POINTER(PgGenerationStats)]),
+    "pg_generation_stats_prefill_tokens_per_second": (C.c_double, [C.POINTER(PgGenerationStats)]),
+    "pg_generation_stats_decode_tokens_per_second": (C.c_double, [C.POINTER(PgGenerationStats)]),
+    "pg_generation_stats_total_tokens_per_second": (C.c_double, [C.POINTER(PgGenerationStats)]),
+    "pg_generation_stats_average_decode_token_time": (C.c_double, [C.POINTER(PgGenerationStats)]),
     "pg_argmax_logits": (C.c_uint64, [_fp, C.c_size_t]),
     "pg_sampler_new": (C.c_int, [C.c_uint64, C.POINTER(_vp)]),
     "pg_sampler_free": (None, [_vp]),

@@ -57,26 +57,26 @@ class GenerationStats:
     total_generation_time: float = 0.0
     first_token_time: Optional[float] = None
 
-    @staticmethod
-    def _rate(tokens: int, seconds: float) -> float:
-        return 0.0 if seconds == 0.0 else tokens / seconds
+    def to_native(self) -> "N.PgGenerationStats":
+        return N.PgGenerationStats(self.prompt_tokens, self.generated_tokens, self.tokenize_time, self.prefill_time,
+                                   self.decode_time, self.total_generation_time,
+                                   -1.0 if self.first_token_time is None else self.first_token_time)
 
     def total_model_tokens(self) -> int:
-        return self.prompt_tokens + self.generated_tokens
+        return int(N.lib.pg_generation_stats_total_model_tokens(C.byref(self.to_native())))
 
     def prefill_tokens_per_second(self) -> float:
-        return self._rate(self.prompt_tokens, self.prefill_time)
+        return float(N.lib.pg_generation_stats_prefill_tokens_per_second(C.byref(self.to_native())))
 
     def decode_tokens_per_second(self) -> float:
-        return self._rate(self.generated_tokens, self.decode_time)
+        return float(N.lib.pg_generation_stats_decode_tokens_per_second(C.byref(self.to_native())))
 
     def total_tokens_per_second(self) -> float:
-        return self._rate(self.total_model_tokens(), self.total_generation_time)
+        return float(N.lib.pg_generation_stats_total_tokens_per_second(C.byref(self.to_native())))
 
     def average_decode_token_time(self) -> Optional[float]:
-        if self.generated_tokens == 0:
-            return None
-        return self.decode_time / self.generated_tokens
+        t = float(N.lib.pg_generation_stats_average_decode_token_time(C.byref(self.to_native())))
+        return None if t < 0 else t
 
 
 def argmax_logits(values: Sequence[float]) -> int:

@@ -204,9 +204,15 @@ class Gpt2Model:
                                                C.byref(b), C.byref(self._h)))
 
     @classmethod
-    def from_dir(cls, model_dir: str, cuda_config: Optional[Gpt2CudaConfig] = None) -> "Gpt2Model":
-        """The model half of Gpt2Runtime::from_dir_with_backend (rust.rs:382-396)."""
+    def from_dir(cls, model_dir: str, cuda_config: Optional[Gpt2CudaConfig] = None, use_tuning: bool = True,
+                 tuning_file: Optional[str] = None) -> "Gpt2Model":
+        """The model half of Gpt2Runtime::from_dir_with_backend (rust.rs:382-396). Without an explicit
+        configuration the tuning file of the model directory is used when it exists (the reference's
+        `puppygrad-tune.json` behaviour, main.rs:1333-1342, 2564-2585; `use_tuning=False` is its --no-tuning)."""
         self = cls.__new__(cls)
+        if cuda_config is None and use_tuning:
+            from .autotune import load_tuning
+            cuda_config = load_tuning(str(model_dir), tuning_file)
         self.cuda_config = cuda_config or Gpt2CudaConfig()
         b = self.cuda_config.to_native()
         self._h = C.c_void_p()

@@ -152,6 +152,24 @@ def write_safetensors(path: str, tensors: dict[str, np.ndarray], prefix: str = "
             f.write(np.ascontiguousarray(tensors[name]).astype("<f4", copy=False).tobytes())
 
 
+def read_safetensors(path: str) -> dict[str, np.ndarray]:
+    """Reads the F32 tensors of a safetensors file by name (an optional "transformer." prefix is dropped)."""
+    with open(path, "rb") as f:
+        n = int.from_bytes(f.read(8), "little")
+        header = json.loads(f.read(n))
+        data = f.read()
+    out = {}
+    for name, e in header.items():
+        if name == "__metadata__":
+            continue
+        if e["dtype"] != "F32":
+            raise ValueError(f"tensor {name} has dtype {e['dtype']}, expected F32")
+        b, e_ = e["data_offsets"]
+        key = name[len("transformer."):] if name.startswith("transformer.") else name
+        out[key] = np.frombuffer(data[b:e_], "<f4").reshape(e["shape"]).copy()
+    return out
+
+
 def write_model_dir(path: str, cfg: dict, weights: dict[str, np.ndarray], prefix: str = "") -> str:
     """`config.json` + `model.safetensors`, the two files the loader needs
     (puppygrad src/models/gpt2/assets.rs:6-30)."""

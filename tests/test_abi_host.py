@@ -228,3 +228,73 @@ def test_generation_stats_report_token_rates():
     assert s.total_tokens_per_second() == pytest.approx(200.0)
     assert s.average_decode_token_time() == pytest.approx(0.005)
     assert pg.GenerationStats().decode_tokens_per_second() == 0.0
+
+
+# ------------------------------------------------------------------ text streaming (streaming.rs:80-146) and stats
+class MockDecoder:
+    """streaming.rs:84-100"""
+
+    def decode_tokens(self, token_ids):
+        return "".join({0: "hello", 1: " world", 2: ""}.get(t, "�") for t in token_ids)
+
+
+def test_streams_safe_token_text_incrementally():
+    from puppygrad_b200.streaming import IncrementalTextStreamer
+    s = IncrementalTextStreamer("hello")
+    chunks = []
+    s.stream_token(MockDecoder(), [0, 1], 1, chunks.append)
+    assert chunks == [" world"] and s.decoded() == "hello world"
+
+
+def test_falls_back_to_full_decode_for_unsafe_token_text():
+    from puppygrad_b200.streaming import IncrementalTextStreamer
+    s = IncrementalTextStreamer("hello")
+    chunks = []
+    s.stream_token(MockDecoder(), [0, 1, 2], 2, chunks.append)
+    assert chunks == [" world"] and s.decoded() == "hello world"
+    # a decode that does not extend what was streamed emits the token's own text (streaming.rs:66-70)
+    s2 = IncrementalTextStreamer("other")
+    chunks = []
+    s2.stream_token(MockDecoder(), [0, 3], 3, chunks.append)
+    assert chunks == ["�"] and s2.decoded() == "hello�"
+    # long texts take the decoder's second call with a larger buffer
+    class Long:
+        def decode_tokens(self, ids):
+            return "x" * 1000 * len(ids)
+    s3 = IncrementalTextStreamer("")
+    chunks = []
+    s3.stream_token(Long(), [7], 7, chunks.append)
+    assert chunks == ["x" * 1000] and s3.decoded() == "x" * 1000
+    # errors of the decoder and of the text callback come back to the caller
+    class Broken:
+        def decode_tokens(self, ids):
+            raise KeyError("no such token")
+    with pytest.raises(KeyError):
+        IncrementalTextStreamer("").stream_token(Broken(), [1], 1, chunks.append)
+
+
+def test_incremental_decode_rejects_empty_and_replacement_text():
+    from puppygrad_b200.streaming import is_incremental_decode_safe
+    assert is_incremental_decode_safe(" hello")
+    assert not is_incremental_decode_safe("")
+    assert not is_incremental_decode_safe("�")
+    assert not is_incremental_decode_safe("a�")
+
+
+def test_escapes_raw_tokens_for_line_streams():
+    from puppygrad_b200.streaming import escape_raw_token
+    assert escape_raw_token("<|en|>") == "<|en|>"
+    assert escape_raw_token("ĠI") == "ĠI"
+    assert escape_raw_token("a\tb\nc") == "a\\tb\\nc"
+    assert escape_raw_token("back\\slash\r") == "back\\\\slash\\r"
+    assert escape_raw_token("\x01\x7f\u0085é😀") == "\\u{1}\\u{7f}\\u{85}é😀"
+
+
+def test_generation_stats_rates():
+    """generation.rs:129-181"""
+    s = pg.GenerationStats(prompt_tokens=10, generated_tokens=5, prefill_time=2.0, decode_time=0.5, total_generation_time=3.0)
+    assert s.total_model_tokens() == 15
+    assert s.prefill_tokens_per_second() == 5.0 and s.decode_tokens_per_second() == 10.0
+    assert s.total_tokens_per_second() == 5.0 and s.average_decode_token_time() == 0.1
+    z = pg.GenerationStats()
+    assert z.decode_tokens_per_second() == 0.0 and z.average_decode_token_time() is None
