@@ -193,6 +193,181 @@ __global__ void __launch_bounds__(192, 1)
 // into hi/lo in tensor memory; the MMA warp then issues, per 8-wide k step, hi*hi, hi*lo and
 // lo*hi into the same accumulator. Split-K partials are exchanged through distributed shared
 // memory and added in split order, so the result does not depend on scheduling.
+struct Ss3Smem {
+  static constexpr int BN = 128;
+  static constexpr int STAGES = 3;
+  static constexpr int A_BYTES = TILE_M * BK * 4, B_BYTES = BN * BK * 4;
+  static constexpr int EPI_BYTES = 4 * 32 * 33 * 4;  // one padded 32x32 transpose tile per epilogue warp
+  static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;  // x, x_lo, w, w_lo tiles of one k block
+  static constexpr size_t BYTES = (size_t)STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+// out[m, n] = x[m, k] . w[n, k]^T at FP32 grade on the tensor cores: the tensor core reads the upper 19 bits of
+// every FP32 operand (its TF32 "hi" part), so with lo = v - hi(v) kept in a second array the product is
+// x.w + x.w_lo + x_lo.w, three TF32 MMAs per k step accumulated in FP32 (the lo.lo term is below FP32 rounding).
+// Same structure as tc_gemm_ss_kernel: TMA producer warp, one MMA-issuing thread, four epilogue warps, persistent
+// over 128 x 128 output tiles with two accumulators in tensor memory. Prefill GEMMs of the FP32-parity modes.
+__global__ void __launch_bounds__(192, 1)
+    tc_gemm_ss3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_xlo,
+                       const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_wlo,
+                       TcGemmArgs a) {
+  using S = Ss3Smem;
+  constexpr int BN = S::BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* stages = base;  // per stage: x tile, x_lo tile, w tile, w_lo tile
+  float* epi_tiles = reinterpret_cast<float*>(base + (size_t)S::STAGES * S::STAGE_BYTES);
+  uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(epi_tiles) + S::EPI_BYTES);
+  uint64_t* empty = full + S::STAGES;
+  uint64_t* d_full = empty + S::STAGES;   // [2]: accumulator buffer holds a finished tile
+  uint64_t* d_empty = d_full + 2;         // [2]: the epilogue warps have read it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + 2);
+  volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  // Persistent over output tiles (tile = blockIdx.x, + gridDim.x, ...; column tiles of one row panel
+  // are neighbours, so the activation panel is reused from L2). Two accumulators in tensor memory:
+  // while the epilogue warps drain one tile, the MMAs of the next one already run.
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_n = (a.n + BN - 1) / BN, tiles = tiles_n * ((a.m + TILE_M - 1) / TILE_M);
+  const int nkb = a.k / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&d_full[i], 1);
+      mbar_init(&d_empty[i], 4);
+    }
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 2 * BN);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;  // stage counter over all tiles of this CTA
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        const int n0 = (tile % tiles_n) * BN, m0 = (tile / tiles_n) * TILE_M;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const uint32_t s = it % S::STAGES;
+          if (it >= S::STAGES) ok = mbar_wait(&empty[s], ((it / S::STAGES) - 1) & 1, failed, a.error_flag, 1);
+          if (!ok) break;
+          uint8_t* st = stages + (size_t)s * S::STAGE_BYTES;
+          mbar_expect_tx(&full[s], S::STAGE_BYTES);
+          tma_load_2d(st, &map_x, kb * BK, m0, &full[s]);
+          tma_load_2d(st + S::A_BYTES, &map_xlo, kb * BK, m0, &full[s]);
+          tma_load_2d(st + 2 * S::A_BYTES, &map_w, kb * BK, n0, &full[s]);
+          tma_load_2d(st + 2 * S::A_BYTES + S::B_BYTES, &map_wlo, kb * BK, n0, &full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_tf32(TILE_M, BN);
+      uint32_t it = 0, ti = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++ti) {
+        const uint32_t buf = ti & 1;
+        if (ti >= 2) ok = mbar_wait(&d_empty[buf], ((ti >> 1) - 1) & 1, failed, a.error_flag, 4);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
+          const uint32_t s = it % S::STAGES;
+          ok = mbar_wait(&full[s], (it / S::STAGES) & 1, failed, a.error_flag, 2);
+          if (!ok) break;
+          tc_fence_after();
+          uint8_t* st = stages + (size_t)s * S::STAGE_BYTES;
+          const uint64_t da = umma_desc_sw128(st), dal = umma_desc_sw128(st + S::A_BYTES);
+          const uint64_t db = umma_desc_sw128(st + 2 * S::A_BYTES), dbl = umma_desc_sw128(st + 2 * S::A_BYTES + S::B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 8; ++k)  // the small terms first, then hi . hi
+            umma_tf32_ss(tmem_d, dal + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+#pragma unroll
+          for (int k = 0; k < BK / 8; ++k) umma_tf32_ss(tmem_d, da + (uint64_t)(k * 2), dbl + (uint64_t)(k * 2), idesc, 1);
+#pragma unroll
+          for (int k = 0; k < BK / 8; ++k) umma_tf32_ss(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, 1);
+          umma_commit(&empty[s]);
+        }
+        if (ok) umma_commit(&d_full[buf]);
+      }
+    }
+  } else {
+    // TMEM lane = output row, but a row-per-thread store touches 32 cache lines per instruction:
+    // every 32x32 block goes through a padded shared-memory tile and leaves column-per-lane, so
+    // that residual loads and output stores are 128-byte coalesced.
+    const int q = warp & 3;
+    float* tile = epi_tiles + q * (32 * 33);
+    uint32_t ti = 0;
+    bool ok = true;
+    for (int tile_id = blockIdx.x; tile_id < tiles && ok; tile_id += gridDim.x, ++ti) {
+      const int n0 = (tile_id % tiles_n) * BN, m0 = (tile_id / tiles_n) * TILE_M;
+      const uint32_t buf = ti & 1;
+      const uint32_t tmem_d = tmem_base + buf * BN;
+      ok = mbar_wait(&d_full[buf], (ti >> 1) & 1, failed, a.error_flag, 3);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        const int col = n0 + c0 + lane;
+        // the block's 32 residual values of this lane's column go out first: they do not depend on
+        // the accumulator, and asked for one by one between the stores (which may alias them:
+        // the residual is updated in place) they would each cost a full memory round trip
+        float rv[32];
+        if (a.epilogue == EPI_RESID && col < a.n) {
+#pragma unroll
+          for (int rr = 0; rr < 32; ++rr) {
+            const int row = m0 + q * 32 + rr;
+            rv[rr] = row < a.m ? a.resid[(size_t)row * a.n + col] : 0.f;
+          }
+        }
+        float v[32];
+        tmem_ld32(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) tile[lane * 33 + j] = v[j];
+        __syncwarp();
+        const float bias = (a.bias && col < a.n) ? a.bias[col] : 0.f;
+        if (col < a.n) {
+#pragma unroll
+          for (int rr = 0; rr < 32; ++rr) {
+            const int row = m0 + q * 32 + rr;
+            if (row < a.m) {
+              float r = tile[rr * 33 + lane];
+              if (a.bias) r = bias + r;
+              if (a.epilogue == EPI_GELU) r = gelu_ref(r);
+              if (a.epilogue == EPI_RESID) r = rv[rr] + r;
+              a.out[(size_t)row * a.n + col] = r;
+            }
+          }
+        }
+        __syncwarp();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&d_empty[buf]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
+}
+
+// ------------------------------------------------------------------ 3xTF32, weights via TMEM
+// grid (ceil(n / 128), splits) with thread-block clusters of (1, splits, 1): the CTAs of one
+// cluster share a 128-row weight tile and each covers 1/splits of k. 192 threads per CTA.
+// A shared-memory stage holds the raw FP32 weight tile (128 rows x 32 k) and the pre-split
+// activation tiles x_hi, x_lo (BN rows x 32 k). The four epilogue warps turn each weight tile
+// into hi/lo in tensor memory; the MMA warp then issues, per 8-wide k step, hi*hi, hi*lo and
+// lo*hi into the same accumulator. Split-K partials are exchanged through distributed shared
+// memory and added in split order, so the result does not depend on scheduling.
 template <int BN>
 struct X3 {
   static constexpr int STAGES = (BN == 64) ? 6 : (BN == 32) ? 8 : 10;  // shared-memory stages (TMA depth)
@@ -528,6 +703,22 @@ cudaError_t launch_tile_weights(const float* src, float* dst, int n, int k, cuda
   return cudaGetLastError();
 }
 
+// lo[i] = x[i] - hi(x[i]) with hi = the upper 19 bits the tensor core reads
+__global__ void __launch_bounds__(256) tf32_lo_kernel(const float4* __restrict__ x, float4* __restrict__ lo, size_t n4) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+    const float4 v = x[i];
+    lo[i] = make_float4(v.x - tf32_hi(v.x), v.y - tf32_hi(v.y), v.z - tf32_hi(v.z), v.w - tf32_hi(v.w));
+  }
+}
+
+cudaError_t launch_tf32_lo(const float* x, float* lo, size_t n, cudaStream_t s) {
+  if (n % 4 != 0) return cudaErrorInvalidValue;
+  const size_t n4 = n / 4;
+  const int blocks = (int)std::min<size_t>((n4 + 255) / 256, 148 * 8);
+  tf32_lo_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const float4*>(x), reinterpret_cast<float4*>(lo), n4);
+  return cudaGetLastError();
+}
+
 static bool g_cluster16_ok = false;  // set by init_tc_kernel_attributes
 
 bool tc_gemm_supported(int m, int n, int k) {
@@ -541,6 +732,8 @@ cudaError_t init_tc_kernel_attributes() {
   e = cudaFuncSetAttribute(tc_gemm_ss_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SsSmem<128>::BYTES);
   if (e != cudaSuccess) return e;
   e = cudaFuncSetAttribute(tc_gemm_ss_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SsSmem<256>::BYTES);
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(tc_gemm_ss3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Ss3Smem::BYTES);
   if (e != cudaSuccess) return e;
 #define PG_X3_ATTR(BN_, SP_)                                                                                  \
   e = cudaFuncSetAttribute(tc_gemm_x3_kernel<BN_, SP_>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
@@ -589,6 +782,25 @@ cudaError_t launch_tc_gemm_tf32(const TcGemmArgs& a, cudaStream_t s) {
   dim3 grid((unsigned)std::min(tiles, sms));
   if (bn == 256) return launch_ex(tc_gemm_ss_kernel<256>, grid, SsSmem<256>::BYTES, s, false, params);
   return launch_ex(tc_gemm_ss_kernel<128>, grid, SsSmem<128>::BYTES, s, false, params);
+}
+
+cudaError_t launch_tc_gemm_tf32x3_rows(const TcGemmArgs& a, cudaStream_t s) {
+  if (!tc_gemm_supported(a.m, a.n, a.k) || !a.x || !a.x_lo || !a.w || !a.w_lo) return cudaErrorInvalidValue;
+  CUtensorMap mx, mxl, mw, mwl;
+  if (!make_map(&mx, a.x, a.m, a.k, TILE_M) || !make_map(&mxl, a.x_lo, a.m, a.k, TILE_M) ||
+      !make_map(&mw, a.w, a.n, a.k, Ss3Smem::BN) || !make_map(&mwl, a.w_lo, a.n, a.k, Ss3Smem::BN))
+    return cudaErrorInvalidValue;
+  TcGemmArgs args = a;
+  void* params[5] = {&mx, &mxl, &mw, &mwl, &args};
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  const int tiles = ((a.n + Ss3Smem::BN - 1) / Ss3Smem::BN) * ((a.m + TILE_M - 1) / TILE_M);
+  dim3 grid((unsigned)std::min(tiles, sms));
+  return launch_ex(tc_gemm_ss3_kernel, grid, Ss3Smem::BYTES, s, false, params);
 }
 
 int tc_gemm_x3_splits(int n, int k, int num_sms) {

@@ -111,6 +111,7 @@ struct TcGemmArgs {
   const float* x;     // [m, k] activations (x3: the hi part)
   const float* x_lo;  // [m, k] lo part (x3 only)
   const float* w;     // [n, k] row-major; for the x3 kernel the tiled copy made by launch_tile_weights
+  const float* w_lo;  // [n, k] row-major lo parts of w (launch_tc_gemm_tf32x3_rows only)
   const float* bias;  // [n] or nullptr
   const float* resid; // [m, n], EPI_RESID
   float* out;         // [m, n] (may be nullptr in x3 when only the split outputs are wanted)
@@ -128,6 +129,9 @@ size_t tc_tiled_weight_floats(int n, int k);
 cudaError_t launch_tile_weights(const float* src, float* dst, int n, int k, cudaStream_t s);
 // single TF32 pass, any m (prefill)
 cudaError_t launch_tc_gemm_tf32(const TcGemmArgs& a, cudaStream_t s);
+// three TF32 passes (FP32-grade), any m (prefill): x_lo and w_lo hold v - hi(v) of x and w (launch_tf32_lo)
+cudaError_t launch_tc_gemm_tf32x3_rows(const TcGemmArgs& a, cudaStream_t s);
+cudaError_t launch_tf32_lo(const float* x, float* lo, size_t n, cudaStream_t s);
 // three TF32 passes (FP32-grade), m <= 64 (decode)
 int tc_gemm_x3_splits(int n, int k, int num_sms);
 cudaError_t launch_tc_gemm_x3(const TcGemmArgs& a, int splits, bool pdl, cudaStream_t s);

@@ -33,6 +33,9 @@ struct LayerWeights {
   float *ln1_g, *ln1_b, *w_qkv, *b_qkv, *w_proj, *b_proj, *ln2_g, *ln2_b, *w_fc, *b_fc, *w_proj2, *b_proj2;
   // copies in the tiled layout of the tensor-core decode kernel (nullptr in fp32 mode)
   float *t_qkv = nullptr, *t_proj = nullptr, *t_fc = nullptr, *t_proj2 = nullptr;
+  // lo parts (w - hi(w), hi = the upper 19 bits a TF32 tensor core reads) of the four matrices, [out, in] row-major:
+  // second operand of the FP32-grade prefill GEMM (nullptr in fp32 mode)
+  float *l_qkv = nullptr, *l_proj = nullptr, *l_fc = nullptr, *l_proj2 = nullptr;
   // packed copies for the single-kernel decode step (BF16 or row-quantised int8 weights), [out, in] rows, and,
   // for int8, one scale per output row
   void *p_qkv = nullptr, *p_proj = nullptr, *p_fc = nullptr, *p_proj2 = nullptr;
@@ -58,6 +61,7 @@ struct pg_model {
   float* tiled_arena = nullptr;  // second copy of the dense matrices, tiled for TMA (tensor-core modes)
   size_t tiled_floats = 0;
   float* t_wte = nullptr;
+  float* lo_arena = nullptr;
   size_t arena_floats = 0;
   int stream_weight_type = STREAM_W_F32;  // what the single-kernel decode step streams
   unsigned char* packed_arena = nullptr;  // BF16 / int8 copies of the dense matrices and of wte
@@ -84,6 +88,7 @@ struct pg_model {
       cudaSetDevice(device);
       cudaFree(arena);
       if (tiled_arena) cudaFree(tiled_arena);
+      if (lo_arena) cudaFree(lo_arena);
       if (packed_arena) cudaFree(packed_arena);
       if (scale_arena) cudaFree(scale_arena);
       if (head_deq) cudaFree(head_deq);
@@ -275,6 +280,23 @@ static int build_model(const pg_gpt2_config& cfg, const float* const* tensors, c
       if (int r = tile(w.w_proj2, C, F, &w.t_proj2)) return r;
     }
     if (int r = tile(m->head_w, V, C, &m->t_wte)) return r;
+    if (C % 4 == 0 && F % 4 == 0) {
+      const size_t per_lo = (size_t)3 * C * C + (size_t)C * C + 2 * (size_t)C * F;
+      PG_CUDA_TRY(cudaMalloc(&m->lo_arena, per_lo * cfg.n_layer * sizeof(float)));
+      float* q = m->lo_arena;
+      auto lo = [&](const float* src, size_t n, float** dst) -> int {
+        *dst = q;
+        PG_CUDA_TRY(launch_tf32_lo(src, q, n, 0));
+        q += n;
+        return PG_OK;
+      };
+      for (auto& w : m->layers) {
+        if (int r = lo(w.w_qkv, (size_t)3 * C * C, &w.l_qkv)) return r;
+        if (int r = lo(w.w_proj, (size_t)C * C, &w.l_proj)) return r;
+        if (int r = lo(w.w_fc, (size_t)C * F, &w.l_fc)) return r;
+        if (int r = lo(w.w_proj2, (size_t)C * F, &w.l_proj2)) return r;
+      }
+    }
     PG_CUDA_TRY(cudaDeviceSynchronize());
   }
   *out = m.release();
@@ -335,7 +357,7 @@ struct pg_cache {
   int *h_ids = nullptr, *h_out = nullptr;  // pinned staging
   // prefill workspace (grow-only)
   size_t pre_rows = 0;
-  float *px = nullptr, *pnorm = nullptr, *pqkv = nullptr, *pattn = nullptr, *ph = nullptr;
+  float *px = nullptr, *pnorm = nullptr, *pqkv = nullptr, *pattn = nullptr, *ph = nullptr, *plo = nullptr;
   int* prow = nullptr;  // [4][pre_rows]: ids, pos, slot, (batch+1 seq_start / last rows)
   std::map<std::pair<int, int>, cudaGraphExec_t> graphs;  // (batch, splits) -> decode-step graph
   std::map<std::pair<int, int>, uint64_t> graphs_launches;  // kernel nodes in each graph
@@ -390,7 +412,7 @@ struct pg_cache {
     for (void* p : {(void*)kv_pool, (void*)d_table, (void*)d_ids, (void*)d_pos, (void*)d_argmax, (void*)d_token_log,
                     (void*)x, (void*)norm, (void*)qkv, (void*)attn, (void*)hbuf, (void*)logits, (void*)part_val,
                     (void*)part_idx, (void*)attn_part, (void*)attn_counters, (void*)topk_vals, (void*)topk_idx,
-                    (void*)px, (void*)pnorm, (void*)pqkv, (void*)pattn, (void*)ph, (void*)prow, (void*)norm_lo,
+                    (void*)px, (void*)pnorm, (void*)pqkv, (void*)pattn, (void*)ph, (void*)plo, (void*)prow, (void*)norm_lo,
                     (void*)attn_lo, (void*)h_lo, (void*)d_error, (void*)d_stream_ll, (void*)d_stream_epoch,
                     (void*)chain_partials, (void*)d_chain_barrier, (void*)d_chain_trace, (void*)d_chain_best})
       if (p) cudaFree(p);
@@ -910,9 +932,9 @@ struct PrefillPlan {
 static int grow_prefill_workspace(pg_cache* c, size_t rows) {
   if (rows <= c->pre_rows) return PG_OK;
   const pg_model* m = c->model;
-  for (void* p : {(void*)c->px, (void*)c->pnorm, (void*)c->pqkv, (void*)c->pattn, (void*)c->ph, (void*)c->prow})
+  for (void* p : {(void*)c->px, (void*)c->pnorm, (void*)c->pqkv, (void*)c->pattn, (void*)c->ph, (void*)c->plo, (void*)c->prow})
     if (p) cudaFree(p);
-  c->px = c->pnorm = c->pqkv = c->pattn = c->ph = nullptr;
+  c->px = c->pnorm = c->pqkv = c->pattn = c->ph = c->plo = nullptr;
   c->prow = nullptr;
   c->pre_rows = 0;
   const size_t C = m->c(), F = m->f();
@@ -921,6 +943,7 @@ static int grow_prefill_workspace(pg_cache* c, size_t rows) {
   PG_CUDA_TRY(cudaMalloc(&c->pqkv, rows * 3 * C * sizeof(float)));
   PG_CUDA_TRY(cudaMalloc(&c->pattn, rows * C * sizeof(float)));
   PG_CUDA_TRY(cudaMalloc(&c->ph, rows * F * sizeof(float)));
+  if (m->lo_arena) PG_CUDA_TRY(cudaMalloc(&c->plo, rows * std::max(C, F) * sizeof(float)));
   PG_CUDA_TRY(cudaMalloc(&c->prow, (rows * 3 + 2 * (size_t)c->max_batch + 2) * sizeof(int)));
   c->pre_rows = rows;
   return PG_OK;
@@ -931,6 +954,7 @@ static int grow_prefill_workspace(pg_cache* c, size_t rows) {
 // the paged cache. block_forward, rust.rs:1053-1134.
 struct BlockWorkspace {
   float *x, *norm, *qkv, *attn, *h;
+  float* lo;  // lo parts of the GEMM input in flight (FP32-grade tensor-core prefill), or nullptr
   const int *d_slot, *d_pos, *d_seq_start;
   int* d_error;  // error word of the tensor-core kernels (may be nullptr: then they are not used)
 };
@@ -939,12 +963,22 @@ static int run_blocks(const pg_model* m, const BlockWorkspace& ws, const Prefill
                       cudaStream_t s) {
   const int C = m->c(), F = m->f(), rows = plan.rows;
   const float eps = m->cfg.layer_norm_epsilon;
-  auto gemm = [&](const float* w, const float* bias, const float* x, float* out, int n_out, int k, int epi,
-                  const float* resid) -> cudaError_t {
+  const bool x3_mode = m->backend.math_mode == PG_MATH_TF32X3 || m->backend.math_mode == PG_MATH_BF16;
+  auto gemm = [&](const float* w, const float* w_lo, const float* bias, const float* x, float* out, int n_out, int k,
+                  int epi, const float* resid) -> cudaError_t {
     LinearArgs a{};
     a.w = w; a.bias = bias; a.x = x; a.out = out; a.resid = resid; a.eps = eps;
     a.m = rows; a.n = n_out; a.k = k;
     if (rows <= 16 && k % 4 == 0) return launch_linear_decode(a, epi, false, s, nullptr);
+    if (x3_mode && w_lo && ws.lo && ws.d_error && rows >= 128 && tc_gemm_supported(rows, n_out, k)) {
+      // FP32-grade product on the tensor cores: x.w + x.w_lo + x_lo.w as three TF32 MMAs per k step
+      cudaError_t e = launch_tf32_lo(x, ws.lo, (size_t)rows * k, s);
+      if (e != cudaSuccess) return e;
+      TcGemmArgs t{};
+      t.x = x; t.x_lo = ws.lo; t.w = w; t.w_lo = w_lo; t.bias = bias; t.resid = resid; t.out = out; t.error_flag = ws.d_error;
+      t.m = rows; t.n = n_out; t.k = k; t.epilogue = epi;
+      return launch_tc_gemm_tf32x3_rows(t, s);
+    }
     if (m->backend.math_mode == PG_MATH_TF32 && ws.d_error && rows >= 128 && tc_gemm_supported(rows, n_out, k)) {
       // single TF32 pass on the tensor cores: the fast prefill variant with its own looser bound
       TcGemmArgs t{};
@@ -958,7 +992,7 @@ static int run_blocks(const pg_model* m, const BlockWorkspace& ws, const Prefill
   for (int l = 0; l < m->layers_n(); ++l) {
     const LayerWeights& w = m->layers[l];
     PG_CUDA_TRY(launch_layernorm_rows(ws.x, w.ln1_g, w.ln1_b, eps, ws.norm, rows, C, false, s));
-    PG_CUDA_TRY(gemm(w.w_qkv, w.b_qkv, ws.norm, ws.qkv, 3 * C, C, EPI_NONE, nullptr));
+    PG_CUDA_TRY(gemm(w.w_qkv, w.l_qkv, w.b_qkv, ws.norm, ws.qkv, 3 * C, C, EPI_NONE, nullptr));
     if (cache)
       PG_CUDA_TRY(launch_kv_scatter(ws.qkv, ws.d_slot, ws.d_pos, cache->layer_pool(l), cache->d_table, cache->kv,
                                     rows, s));
@@ -969,10 +1003,10 @@ static int run_blocks(const pg_model* m, const BlockWorkspace& ws, const Prefill
       PG_CUDA_TRY(launch_prefill_attention_tc(pa, rows, ws.d_error, s));
     else
       PG_CUDA_TRY(launch_prefill_attention(pa, s));
-    PG_CUDA_TRY(gemm(w.w_proj, w.b_proj, ws.attn, ws.x, C, C, EPI_RESID, ws.x));
+    PG_CUDA_TRY(gemm(w.w_proj, w.l_proj, w.b_proj, ws.attn, ws.x, C, C, EPI_RESID, ws.x));
     PG_CUDA_TRY(launch_layernorm_rows(ws.x, w.ln2_g, w.ln2_b, eps, ws.norm, rows, C, false, s));
-    PG_CUDA_TRY(gemm(w.w_fc, w.b_fc, ws.norm, ws.h, F, C, EPI_GELU, nullptr));
-    PG_CUDA_TRY(gemm(w.w_proj2, w.b_proj2, ws.h, ws.x, C, F, EPI_RESID, ws.x));
+    PG_CUDA_TRY(gemm(w.w_fc, w.l_fc, w.b_fc, ws.norm, ws.h, F, C, EPI_GELU, nullptr));
+    PG_CUDA_TRY(gemm(w.w_proj2, w.l_proj2, w.b_proj2, ws.h, ws.x, C, F, EPI_RESID, ws.x));
   }
   return PG_OK;
 }
@@ -1120,7 +1154,7 @@ static int do_prefill(const pg_model* m, pg_cache* c, const int32_t* ids, const 
   PG_CUDA_TRY(cudaMemcpyAsync(d_start, plan.seq_start.data(), (batch + 1) * sizeof(int), cudaMemcpyHostToDevice, s));
   PG_CUDA_TRY(cudaMemcpyAsync(d_last, plan.last_rows.data(), batch * sizeof(int), cudaMemcpyHostToDevice, s));
   PG_CUDA_TRY(launch_embed(m->wte, m->wpe, d_ids, d_pos, c->px, plan.rows, m->c(), false, s));
-  BlockWorkspace ws{c->px, c->pnorm, c->pqkv, c->pattn, c->ph, d_slot, d_pos, d_start, c->d_error};
+  BlockWorkspace ws{c->px, c->pnorm, c->pqkv, c->pattn, c->ph, c->plo, d_slot, d_pos, d_start, c->d_error};
   if (int r = run_blocks(m, ws, plan, c, s)) return r;
   // last position of each prompt -> ln_f -> lm_head (the reference computes logits for every
   // prompt token and keeps the last, rust.rs:920-926; only the last is observable)
@@ -1235,7 +1269,7 @@ static int do_forward(const pg_model* m, const int32_t* ids, int t, float* logit
   hm[2 * R + 1] = t;
   PG_CUDA_TRY(cudaMemcpyAsync(ws.meta, hm.data(), hm.size() * sizeof(int), cudaMemcpyHostToDevice, s));
   PG_CUDA_TRY(launch_embed(m->wte, m->wpe, ws.meta, ws.meta + R, ws.x, t, (int)C, false, s));
-  BlockWorkspace bw{ws.x, ws.norm, ws.qkv, ws.attn, ws.h, nullptr, ws.meta + R, ws.meta + 2 * R, nullptr};
+  BlockWorkspace bw{ws.x, ws.norm, ws.qkv, ws.attn, ws.h, nullptr, nullptr, ws.meta + R, ws.meta + 2 * R, nullptr};
   if (int r = run_blocks(m, bw, plan, nullptr, s)) return r;
   const float* hidden = last_only ? ws.x + (R - 1) * C : ws.x;
   PG_CUDA_TRY(launch_layernorm_rows(hidden, m->lnf_g, m->lnf_b, m->cfg.layer_norm_epsilon, ws.norm, (int)out_rows, (int)C, false, s));
