@@ -247,8 +247,8 @@ int pg_cache_debug_expire_next_wait(pg_cache* cache, uint32_t spin_limit);
 /* One linear on host buffers, out[m, n] = x[m, k] . w[n, k]^T (+ bias[n]) then epilogue
  * (0 none, 1 tanh-GELU, 2 out = resid + value): transposed_dense_projection_into,
  * src/models/cpu.rs:58-75, with gelu_in_place / add_in_place (cpu.rs:145-171) fused. `w` is
- * already [out, in]. math_mode selects the kernel family (pg_math_mode; tf32x3 needs m <= 64,
- * the tensor-core modes need k % 32 == 0). With reps > 0 the kernel is launched reps more times,
+ * already [out, in]. math_mode selects the kernel family (pg_math_mode; the tensor-core modes need
+ * k % 32 == 0; tf32x3 runs the decode kernel up to 64 rows and the prefill kernel above). With reps > 0 the kernel is launched reps more times,
  * L2 flushed before each, and *seconds_per_launch receives the mean device time. */
 int pg_op_linear(const float* x, const float* w, const float* bias, const float* resid, int32_t m,
                  int32_t n, int32_t k, int32_t epilogue, int32_t math_mode, int32_t device,

@@ -48,13 +48,13 @@ extern "C" int pg_op_linear(const float* x, const float* w, const float* bias, c
   if (math_mode < PG_MATH_FP32 || math_mode > PG_MATH_TF32) return set_error(PG_INVALID_CONFIG, "math_mode must be fp32, tf32x3 or tf32");
   if (math_mode != PG_MATH_FP32 && !tc_gemm_supported(m, n, k))
     return set_error(PG_INVALID_INPUT, "tensor-core modes need k to be a multiple of 32");
-  if (math_mode == PG_MATH_TF32X3 && m > 64) return set_error(PG_INVALID_INPUT, "tf32x3 is the decode path: m <= 64");
+  const bool x3_rows = math_mode == PG_MATH_TF32X3 && m > 64;  // the FP32-grade prefill GEMM (both operands as hi + lo)
   if (int r = ensure_device(device)) return r;
   int rc = PG_OK;
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   const size_t xs = (size_t)m * k, ws = (size_t)n * k, os = (size_t)m * n;
-  DeviceBuf dx, dw, dwt, db, dr, dout, dhi, dlo, derr, dflush, dtrace, dpart, dbar;
+  DeviceBuf dx, dw, dwt, db, dr, dout, dhi, dlo, derr, dflush, dtrace, dpart, dbar, dwlo;
 #ifdef PG_DEV_TRACE
   const bool want_trace = getenv("PG_TRACE") != nullptr;  // developer aid: phase time stamps of the kernel, printed below
 #else
@@ -80,6 +80,12 @@ extern "C" int pg_op_linear(const float* x, const float* w, const float* bias, c
     if (math_mode == PG_MATH_TF32) {
       a.x = dx.as<float>();
       return launch_tc_gemm_tf32(a, st);
+    }
+    if (x3_rows) {  // the lo parts of the activations are made per call, as the prefill does; those of the weights once
+      cudaError_t e = launch_tf32_lo(dx.as<float>(), dlo.as<float>(), xs, st);
+      if (e != cudaSuccess) return e;
+      a.x = dx.as<float>(); a.x_lo = dlo.as<float>(); a.w_lo = dwlo.as<float>();
+      return launch_tc_gemm_tf32x3_rows(a, st);
     }
     cudaError_t e = launch_split_tf32(dx.as<float>(), dhi.as<float>(), dlo.as<float>(), xs, false, st);
     if (e != cudaSuccess) return e;
@@ -110,7 +116,15 @@ extern "C" int pg_op_linear(const float* x, const float* w, const float* bias, c
     PG_OP_TRY(cudaMalloc(&dr.p, os * 4));
     PG_OP_TRY(cudaMemcpyAsync(dr.p, resid, os * 4, cudaMemcpyHostToDevice, s));
   }
-  if (math_mode == PG_MATH_TF32X3) {
+  if (x3_rows) {
+    if (xs % 4 || ws % 4) {
+      rc = set_error(PG_INVALID_INPUT, "tf32x3 with more than 64 rows needs m * k and n * k to be multiples of 4");
+      goto done;
+    }
+    PG_OP_TRY(cudaMalloc(&dlo.p, xs * 4));
+    PG_OP_TRY(cudaMalloc(&dwlo.p, ws * 4));
+    PG_OP_TRY(launch_tf32_lo(dw.as<float>(), dwlo.as<float>(), ws, s));
+  } else if (math_mode == PG_MATH_TF32X3) {
     splits = tc_gemm_x3_splits(n, k, sms);
     PG_OP_TRY(cudaMalloc(&dhi.p, xs * 4));
     PG_OP_TRY(cudaMalloc(&dlo.p, xs * 4));

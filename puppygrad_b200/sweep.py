@@ -7,6 +7,7 @@
     python -m puppygrad_b200.sweep layernorm --m 1 64 4096 --k 1600
     python -m puppygrad_b200.sweep lm_head --m 1 8 --k 1600
     python -m puppygrad_b200.sweep xl_table        # every case of the GPT-2 XL kernel sweep as one markdown table
+    python -m puppygrad_b200.sweep decode --model small --batch 1 --prompt-len 32 --steps 60 [--weights fp32 bf16 int8]
 
 Prints one JSON line per case: seconds per launch, algorithmic GB/s (4*(k*n + m*k + m*n + n) bytes)
 and TFLOP/s (2*m*n*k), plus the largest deviation from a float64 product of the same inputs.
@@ -108,25 +109,27 @@ def lm_head_case(m, k, vocab, reps, seed=0):
             "argmax_equal_f64": bool((am == want.argmax(1)).all()), "max_rel_err_vs_f64": err}
 
 
-def xl_table(reps, hbm_gbs, tf32_tflops):
+def xl_table(reps, hbm_gbs, tf32_tflops, fp32_tflops=74.5):
     """Every case of the kernel sweep on GPT-2 XL shapes, one markdown row each: time, algorithmic GB/s or
     TFLOP/s, the fraction of the given peak that bounds the case, error against a float64 product."""
     c, f, v = XL["c"], XL["f"], 50257
     rows = ["| operator | shape | path | us | GB/s | TFLOP/s | bound | fraction of peak | max rel. error vs float64 |",
             "|---|---|---|---|---|---|---|---|---|"]
+    print("\n".join(rows), flush=True)
 
     def add(name, shape, path, r, bound):
-        frac = r["gbps"] / hbm_gbs if bound == "hbm" else r.get("tflops", 0.0) / tf32_tflops
+        frac = (r["gbps"] / hbm_gbs if bound == "hbm" else
+                r.get("tflops", 0.0) / (fp32_tflops if bound == "fp32 fma" else tf32_tflops))
         rows.append(f"| {name} | {shape} | {path} | {r['us']:.1f} | {r['gbps']:.0f} | {r.get('tflops', 0.0):.1f} | {bound} | "
                     f"{frac:.3f} | {r['max_rel_err_vs_f64']:.1e} |")
         print(rows[-1], flush=True)
 
     for m in (1, 8, 64, 512, 4096):
         for (n, k) in ((3 * c, c), (c, c), (f, c), (c, f)):
-            maths = ["fp32"] + (["tf32x3"] if 8 < m <= 64 else []) + (["tf32"] if m >= 128 else [])
+            maths = ["fp32"] + (["tf32x3"] if m > 8 else []) + (["tf32"] if m >= 128 else [])
             for math in maths:
                 r = linear_case(m, n, k, math, "none", reps)
-                add("linear", f"{m} x {k} -> {n}", math, r, "hbm" if m <= 64 else ("tensor" if math == "tf32" else "fp32 fma"))
+                add("linear", f"{m} x {k} -> {n}", math, r, "hbm" if m <= 64 else ("fp32 fma" if math == "fp32" else "tensor"))
     for b in (1, 32, 256):
         for kv in (128, 256, 512, 1024):
             sp = max(1, min(8, (2 * 148 + b * 25 - 1) // (b * 25), (kv + 128) // 128))
@@ -136,6 +139,36 @@ def xl_table(reps, hbm_gbs, tf32_tflops):
     for m in (1, 8):
         add("lm_head + arg-max", f"{m} x {c} -> {v}", "fp32", lm_head_case(m, c, v, reps), "hbm")
     return rows
+
+
+def decode_case(preset, batch, prompt_len, steps, math, weights, persistent, reps):
+    """Greedy decode fed back on the device: `steps` steps of `batch` sequences after seeded prompts; best of `reps`.
+    Algorithmic bytes per step: every weight once (at its stored width) + K and V of every sequence once."""
+    from . import synthetic
+    from .gpt2 import Gpt2CudaConfig, Gpt2Model
+    cfg = synthetic.preset(preset)
+    conf = Gpt2CudaConfig(math_mode="bf16" if weights == "bf16" else math, quantized_weights=weights == "int8",
+                          persistent_step=persistent)
+    model = Gpt2Model(cfg, synthetic.random_init_weights(cfg, 0), conf)
+    cache = model.new_kv_cache(max_batch=batch)
+    prompts = [synthetic.uniform_prompt(i + 1, prompt_len, cfg["vocab_size"]) for i in range(batch)]
+    best, launches = None, 0
+    for _ in range(reps):
+        _, first = model.prefill_batch(prompts, cache)
+        first = model.decode_greedy(first, cache, 4)[-1]
+        n0 = cache.kernel_launches()
+        cache.time_begin()
+        model.decode_greedy(first, cache, steps)
+        sec = cache.time_end()
+        launches = cache.kernel_launches() - n0
+        best = sec if best is None else min(best, sec)
+    mid = prompt_len + 4 + steps // 2
+    kv = batch * (2 * cfg["n_layer"] * (mid + 1) * cfg["n_embd"] * 4 + 2 * cfg["n_layer"] * cfg["n_embd"] * 4)
+    bytes_ = model.weight_bytes_per_step() + kv
+    return {"op": "decode", "preset": preset, "batch": batch, "prompt_len": prompt_len, "steps": steps, "math": math,
+            "weights": weights, "persistent_step": persistent, "us_per_step": best / steps * 1e6,
+            "tokens_per_s": batch * steps / best, "kernel_launches_per_step": launches / steps,
+            "bytes_per_step": bytes_, "gbps": bytes_ / (best / steps) / 1e9}
 
 
 def prefill_case(preset, seqs, prompt_len, math, reps):
@@ -164,7 +197,11 @@ def prefill_case(preset, seqs, prompt_len, math, reps):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["linear", "linear_q8", "attention", "prefill", "layernorm", "lm_head", "xl_table"])
+    ap.add_argument("op", choices=["linear", "linear_q8", "attention", "prefill", "layernorm", "lm_head", "xl_table", "decode"])
+    ap.add_argument("--steps", type=int, default=60, help="decode: timed steps")
+    ap.add_argument("--weights", nargs="+", default=["fp32"], choices=["fp32", "bf16", "int8"])
+    ap.add_argument("--persistent", default="auto", choices=["auto", "on", "off"],
+                    help="decode: the single-kernel step of small batches")
     ap.add_argument("--hbm-gbs", type=float, default=6534.5, help="xl_table: HBM peak the fractions are taken of")
     ap.add_argument("--tf32-tflops", type=float, default=838.0, help="xl_table: TF32 tensor peak (half the BF16 peak)")
     ap.add_argument("--vocab", type=int, default=50257)
@@ -183,6 +220,12 @@ def main():
     ap.add_argument("--epilogue", default="none")
     ap.add_argument("--reps", type=int, default=10)
     a = ap.parse_args()
+    if a.op == "decode":
+        pers = {"auto": None, "on": True, "off": False}[a.persistent]
+        for b in a.batch:
+            for wt in a.weights:
+                print(json.dumps(decode_case(a.model, b, a.prompt_len, a.steps, a.math[0], wt, pers, a.reps)), flush=True)
+        return
     if a.op == "xl_table":
         xl_table(a.reps, a.hbm_gbs, a.tf32_tflops)
         return
@@ -221,8 +264,6 @@ def main():
         shapes = [(m, n, k) for m in a.m for n in a.n for k in a.k]
     for (m, n, k) in shapes:
         for math in a.math:
-            if math == "tf32x3" and m > 64:
-                continue
             if math != "fp32" and k % 32:
                 continue
             print(json.dumps(linear_case(m, n, k, math, a.epilogue, a.reps)), flush=True)
