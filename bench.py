@@ -359,7 +359,8 @@ def run_ours(args):
         if rank == 0:
             print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K,
                               "warmup": W, "ms_per_step": sec_max / K * 1e3, "seqs_per_gpu": B,
-                              "gpu_launches": int(launches)}))
+                              "gpu_launches": int(launches),
+                              "streams_ok": sum(ch["ok"] for ch in checks), "streams_exact": sum(ch["exact"] for ch in checks)}))
         if world > 1:
             dist.destroy_process_group()
         return

@@ -185,14 +185,7 @@ __global__ void __launch_bounds__(192, 1)
   if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
 }
 
-// ------------------------------------------------------------------ 3xTF32, weights via TMEM
-// grid (ceil(n / 128), splits) with thread-block clusters of (1, splits, 1): the CTAs of one
-// cluster share a 128-row weight tile and each covers 1/splits of k. 192 threads per CTA.
-// A shared-memory stage holds the raw FP32 weight tile (128 rows x 32 k) and the pre-split
-// activation tiles x_hi, x_lo (BN rows x 32 k). The four epilogue warps turn each weight tile
-// into hi/lo in tensor memory; the MMA warp then issues, per 8-wide k step, hi*hi, hi*lo and
-// lo*hi into the same accumulator. Split-K partials are exchanged through distributed shared
-// memory and added in split order, so the result does not depend on scheduling.
+// ------------------------------------------------------------------ 3xTF32, both operands from shared memory
 struct Ss3Smem {
   static constexpr int BN = 128;
   static constexpr int STAGES = 3;
@@ -206,7 +199,7 @@ struct Ss3Smem {
 // every FP32 operand (its TF32 "hi" part), so with lo = v - hi(v) kept in a second array the product is
 // x.w + x.w_lo + x_lo.w, three TF32 MMAs per k step accumulated in FP32 (the lo.lo term is below FP32 rounding).
 // Same structure as tc_gemm_ss_kernel: TMA producer warp, one MMA-issuing thread, four epilogue warps, persistent
-// over 128 x 128 output tiles with two accumulators in tensor memory. Prefill GEMMs of the FP32-parity modes.
+// over 128 x 128 output tiles with two accumulator pairs in tensor memory. Prefill GEMMs of the FP32-parity modes.
 __global__ void __launch_bounds__(192, 1)
     tc_gemm_ss3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_xlo,
                        const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_wlo,
@@ -243,7 +236,7 @@ __global__ void __launch_bounds__(192, 1)
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(tmem_slot, 2 * BN);
+  if (warp == 1) tmem_alloc(tmem_slot, 4 * BN);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -278,7 +271,10 @@ __global__ void __launch_bounds__(192, 1)
         if (ti >= 2) ok = mbar_wait(&d_empty[buf], ((ti >> 1) - 1) & 1, failed, a.error_flag, 4);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + buf * BN;
+        // The tensor core adds into the accumulator with truncation, a bias that grows with the number of
+        // MMAs into one accumulator: the hi . hi products get an accumulator of their own and the two small
+        // terms share a second one (their magnitude, hence their bias, is 2^-11 of the first).
+        const uint32_t tmem_d = tmem_base + buf * (2 * BN), tmem_s = tmem_d + BN;
         for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
           const uint32_t s = it % S::STAGES;
           ok = mbar_wait(&full[s], (it / S::STAGES) & 1, failed, a.error_flag, 2);
@@ -288,12 +284,13 @@ __global__ void __launch_bounds__(192, 1)
           const uint64_t da = umma_desc_sw128(st), dal = umma_desc_sw128(st + S::A_BYTES);
           const uint64_t db = umma_desc_sw128(st + 2 * S::A_BYTES), dbl = umma_desc_sw128(st + 2 * S::A_BYTES + S::B_BYTES);
 #pragma unroll
-          for (int k = 0; k < BK / 8; ++k)  // the small terms first, then hi . hi
-            umma_tf32_ss(tmem_d, dal + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+          for (int k = 0; k < BK / 8; ++k)
+            umma_tf32_ss(tmem_s, dal + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
 #pragma unroll
-          for (int k = 0; k < BK / 8; ++k) umma_tf32_ss(tmem_d, da + (uint64_t)(k * 2), dbl + (uint64_t)(k * 2), idesc, 1);
+          for (int k = 0; k < BK / 8; ++k) umma_tf32_ss(tmem_s, da + (uint64_t)(k * 2), dbl + (uint64_t)(k * 2), idesc, 1);
 #pragma unroll
-          for (int k = 0; k < BK / 8; ++k) umma_tf32_ss(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, 1);
+          for (int k = 0; k < BK / 8; ++k)
+            umma_tf32_ss(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
           umma_commit(&empty[s]);
         }
         if (ok) umma_commit(&d_full[buf]);
@@ -310,7 +307,7 @@ __global__ void __launch_bounds__(192, 1)
     for (int tile_id = blockIdx.x; tile_id < tiles && ok; tile_id += gridDim.x, ++ti) {
       const int n0 = (tile_id % tiles_n) * BN, m0 = (tile_id / tiles_n) * TILE_M;
       const uint32_t buf = ti & 1;
-      const uint32_t tmem_d = tmem_base + buf * BN;
+      const uint32_t tmem_d = tmem_base + buf * (2 * BN);
       ok = mbar_wait(&d_full[buf], (ti >> 1) & 1, failed, a.error_flag, 3);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -329,10 +326,11 @@ __global__ void __launch_bounds__(192, 1)
             rv[rr] = row < a.m ? a.resid[(size_t)row * a.n + col] : 0.f;
           }
         }
-        float v[32];
+        float v[32], v2[32];
         tmem_ld32(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+        tmem_ld32(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(BN + c0), v2);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) tile[lane * 33 + j] = v[j];
+        for (int j = 0; j < 32; ++j) tile[lane * 33 + j] = v[j] + v2[j];
         __syncwarp();
         const float bias = (a.bias && col < a.n) ? a.bias[col] : 0.f;
         if (col < a.n) {
@@ -345,6 +343,7 @@ __global__ void __launch_bounds__(192, 1)
               if (a.epilogue == EPI_GELU) r = gelu_ref(r);
               if (a.epilogue == EPI_RESID) r = rv[rr] + r;
               a.out[(size_t)row * a.n + col] = r;
+              if (a.out_lo) a.out_lo[(size_t)row * a.n + col] = r - tf32_hi(r);  // lo part for the GEMM that reads `out`
             }
           }
         }
@@ -357,7 +356,7 @@ __global__ void __launch_bounds__(192, 1)
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
+  if (warp == 1) tmem_dealloc(tmem_base, 4 * BN);
 }
 
 // ------------------------------------------------------------------ 3xTF32, weights via TMEM

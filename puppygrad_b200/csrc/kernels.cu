@@ -39,6 +39,7 @@ __device__ __forceinline__ float dot4(float4 a, float4 b, float acc) {
   return acc;
 }
 
+__device__ __forceinline__ float tf32_trunc(float v) { return __uint_as_float(__float_as_uint(v) & 0xFFFFE000u); }
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(FULL, v, o);
@@ -339,6 +340,61 @@ __global__ void layernorm_rows_kernel(const float* x, const float* __restrict__ 
   q = warp_sum(q);
   float inv_std = 1.0f / sqrtf(q / (float)c + eps);
   for (int i = lane; i < c; i += 32) out[(size_t)r * c + i] = (xr[i] - mean) * inv_std * g[i] + b[i];
+}
+
+// One 128-thread CTA per row, 128-bit loads, row kept in registers between the passes (c % 4 == 0, c <= 4096):
+// the row is read from memory once. `lo` (optional) receives y - hi(y), hi = the upper 19 bits a TF32 tensor
+// core reads, for the FP32-grade GEMM that consumes the row.
+__global__ void __launch_bounds__(128) layernorm_rows_vec_kernel(const float* x, const float* __restrict__ g,
+                                                                 const float* __restrict__ b, float eps, float* out,
+                                                                 float* lo, int rows, int c) {
+  __shared__ float red[4];
+  pdl_launch();
+  pdl_wait();
+  const int r = blockIdx.x, tid = threadIdx.x;
+  if (r >= rows) return;
+  const int c4 = c >> 2;
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)r * c);
+  float4 v[8];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int idx = tid + i * 128;
+    v[i] = idx < c4 ? xr[idx] : make_float4(0, 0, 0, 0);
+    s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+  }
+  s = warp_sum(s);
+  if ((tid & 31) == 0) red[tid >> 5] = s;
+  __syncthreads();
+  const float mean = ((red[0] + red[1]) + (red[2] + red[3])) / (float)c;
+  __syncthreads();
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    if (tid + i * 128 < c4) {
+      const float d0 = v[i].x - mean, d1 = v[i].y - mean, d2 = v[i].z - mean, d3 = v[i].w - mean;
+      q += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+    }
+  }
+  q = warp_sum(q);
+  if ((tid & 31) == 0) red[tid >> 5] = q;
+  __syncthreads();
+  const float inv_std = 1.0f / sqrtf(((red[0] + red[1]) + (red[2] + red[3])) / (float)c + eps);
+  const float4* g4 = reinterpret_cast<const float4*>(g);
+  const float4* b4 = reinterpret_cast<const float4*>(b);
+  float4* o4 = reinterpret_cast<float4*>(out + (size_t)r * c);
+  float4* lo4 = lo ? reinterpret_cast<float4*>(lo + (size_t)r * c) : nullptr;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int idx = tid + i * 128;
+    if (idx < c4) {
+      const float4 gg = g4[idx], bb = b4[idx];
+      const float4 y = make_float4((v[i].x - mean) * inv_std * gg.x + bb.x, (v[i].y - mean) * inv_std * gg.y + bb.y,
+                                   (v[i].z - mean) * inv_std * gg.z + bb.z, (v[i].w - mean) * inv_std * gg.w + bb.w);
+      o4[idx] = y;
+      if (lo4) lo4[idx] = make_float4(y.x - tf32_trunc(y.x), y.y - tf32_trunc(y.y), y.z - tf32_trunc(y.z), y.w - tf32_trunc(y.w));
+    }
+  }
 }
 
 __global__ void split_tf32_kernel(const float* x, float* hi, float* lo, size_t n) {
@@ -885,8 +941,18 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(PrefillAttnArgs 
     if (qpos < len) {
       const float inv = 1.0f / l[i];
       float* orow = a.out + (size_t)(r0 + qpos) * c + h * D;
-      *reinterpret_cast<float4*>(orow + tx * 4) = make_float4(o[i][0] * inv, o[i][1] * inv, o[i][2] * inv, o[i][3] * inv);
-      *reinterpret_cast<float4*>(orow + 32 + tx * 4) = make_float4(o[i][4] * inv, o[i][5] * inv, o[i][6] * inv, o[i][7] * inv);
+      float y[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[e] = o[i][e] * inv;
+      *reinterpret_cast<float4*>(orow + tx * 4) = make_float4(y[0], y[1], y[2], y[3]);
+      *reinterpret_cast<float4*>(orow + 32 + tx * 4) = make_float4(y[4], y[5], y[6], y[7]);
+      if (a.out_lo) {
+        float* lrow = a.out_lo + (size_t)(r0 + qpos) * c + h * D;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] -= tf32_trunc(y[e]);
+        *reinterpret_cast<float4*>(lrow + tx * 4) = make_float4(y[0], y[1], y[2], y[3]);
+        *reinterpret_cast<float4*>(lrow + 32 + tx * 4) = make_float4(y[4], y[5], y[6], y[7]);
+      }
     }
   }
 }
@@ -1160,7 +1226,10 @@ cudaError_t launch_embed(const float* wte, const float* wpe, const int* ids, con
 }
 
 cudaError_t launch_layernorm_rows(const float* x, const float* g, const float* b, float eps, float* out, int rows,
-                                  int c, bool pdl, cudaStream_t s) {
+                                  int c, bool pdl, cudaStream_t s, float* lo) {
+  if (c % 4 == 0 && c <= 4096)
+    return launch(layernorm_rows_vec_kernel, dim3(rows), dim3(128), 0, s, pdl, x, g, b, eps, out, lo, rows, c);
+  if (lo) return cudaErrorInvalidValue;
   return launch(layernorm_rows_kernel, dim3((rows + 3) / 4), dim3(128), 0, s, pdl, x, g, b, eps, out, rows, c);
 }
 

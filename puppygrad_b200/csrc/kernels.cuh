@@ -38,9 +38,9 @@ int linear_decode_grid(int n, int num_sms);
 // out[r, :] = wte[ids[r]] + wpe[pos[r]]
 cudaError_t launch_embed(const float* wte, const float* wpe, const int* ids, const int* pos, float* out,
                          int rows, int c, bool pdl, cudaStream_t s);
-// out = LayerNorm(x) row-wise
+// out = LayerNorm(x) row-wise; lo (optional; needs c % 4 == 0 and c <= 4096) = out - hi(out), the TF32 lo part of the result
 cudaError_t launch_layernorm_rows(const float* x, const float* g, const float* b, float eps, float* out,
-                                  int rows, int c, bool pdl, cudaStream_t s);
+                                  int rows, int c, bool pdl, cudaStream_t s, float* lo = nullptr);
 // General FP32 GEMM out[m,n] = x[m,k] . w[n,k]^T (+bias)(+GELU | +resid), CUDA-core FMA.
 cudaError_t launch_gemm_f32(const LinearArgs& a, int epilogue, cudaStream_t s);
 // dst[o, i] = src[i, o]
@@ -64,6 +64,7 @@ cudaError_t launch_decode_attention(const DecodeAttnArgs& a, bool pdl, cudaStrea
 struct PrefillAttnArgs {
   const float* qkv;      // [rows, 3c], sequences concatenated
   float* out;            // [rows, c]
+  float* out_lo;         // optional (head_dim 64, FP32 kernel): out - hi(out), the lo part the FP32-grade GEMM after it reads
   const int* seq_start;  // [batch + 1] row offsets
   int n_head, head_dim, batch, max_len;
 };
@@ -116,7 +117,7 @@ struct TcGemmArgs {
   const float* resid; // [m, n], EPI_RESID
   float* out;         // [m, n] (may be nullptr in x3 when only the split outputs are wanted)
   float* out_hi;      // x3: optional TF32 hi/lo pair of the result, [m, n] each
-  float* out_lo;
+  float* out_lo;      // launch_tc_gemm_tf32x3_rows: optional, out - hi(out) (out_hi unused there)
   int* error_flag;    // set non-zero if a bounded wait inside the kernel expired
   unsigned long long* trace;  // optional tuning aid (x3 kernel): 16 words per CTA, phase timestamps and cycle counts
   int m, n, k, epilogue;

@@ -943,7 +943,7 @@ static int grow_prefill_workspace(pg_cache* c, size_t rows) {
   PG_CUDA_TRY(cudaMalloc(&c->pqkv, rows * 3 * C * sizeof(float)));
   PG_CUDA_TRY(cudaMalloc(&c->pattn, rows * C * sizeof(float)));
   PG_CUDA_TRY(cudaMalloc(&c->ph, rows * F * sizeof(float)));
-  if (m->lo_arena) PG_CUDA_TRY(cudaMalloc(&c->plo, rows * std::max(C, F) * sizeof(float)));
+  if (m->lo_arena) PG_CUDA_TRY(cudaMalloc(&c->plo, rows * (size_t)(C + F) * sizeof(float)));
   PG_CUDA_TRY(cudaMalloc(&c->prow, (rows * 3 + 2 * (size_t)c->max_batch + 2) * sizeof(int)));
   c->pre_rows = rows;
   return PG_OK;
@@ -954,7 +954,7 @@ static int grow_prefill_workspace(pg_cache* c, size_t rows) {
 // the paged cache. block_forward, rust.rs:1053-1134.
 struct BlockWorkspace {
   float *x, *norm, *qkv, *attn, *h;
-  float* lo;  // lo parts of the GEMM input in flight (FP32-grade tensor-core prefill), or nullptr
+  float* lo;  // FP32-grade tensor-core prefill: lo parts of the GEMM inputs, [rows, C] then [rows, F], or nullptr
   const int *d_slot, *d_pos, *d_seq_start;
   int* d_error;  // error word of the tensor-core kernels (may be nullptr: then they are not used)
 };
@@ -964,18 +964,23 @@ static int run_blocks(const pg_model* m, const BlockWorkspace& ws, const Prefill
   const int C = m->c(), F = m->f(), rows = plan.rows;
   const float eps = m->cfg.layer_norm_epsilon;
   const bool x3_mode = m->backend.math_mode == PG_MATH_TF32X3 || m->backend.math_mode == PG_MATH_BF16;
-  auto gemm = [&](const float* w, const float* w_lo, const float* bias, const float* x, float* out, int n_out, int k,
-                  int epi, const float* resid) -> cudaError_t {
+  // The FP32-grade tensor-core GEMM reads x and x - hi(x); whoever produces x (LayerNorm, attention, the GELU
+  // epilogue of the MLP's first GEMM) writes the lo part along with it, so no separate pass over x is needed.
+  const bool x3_rows = x3_mode && ws.lo && ws.d_error && rows >= 128 && m->lo_arena && m->head_dim() == 64 &&
+                       C % 4 == 0 && C <= 4096 && tc_gemm_supported(rows, C, C) && tc_gemm_supported(rows, C, F);
+  float* lo_c = x3_rows ? ws.lo : nullptr;                    // [rows, C]: LayerNorm or attention output
+  float* lo_f = x3_rows ? ws.lo + (size_t)rows * C : nullptr;  // [rows, F]: MLP hidden
+  auto gemm = [&](const float* w, const float* w_lo, const float* bias, const float* x, const float* x_lo, float* out,
+                  float* out_lo, int n_out, int k, int epi, const float* resid) -> cudaError_t {
     LinearArgs a{};
     a.w = w; a.bias = bias; a.x = x; a.out = out; a.resid = resid; a.eps = eps;
     a.m = rows; a.n = n_out; a.k = k;
     if (rows <= 16 && k % 4 == 0) return launch_linear_decode(a, epi, false, s, nullptr);
-    if (x3_mode && w_lo && ws.lo && ws.d_error && rows >= 128 && tc_gemm_supported(rows, n_out, k)) {
+    if (x3_rows && w_lo && x_lo) {
       // FP32-grade product on the tensor cores: x.w + x.w_lo + x_lo.w as three TF32 MMAs per k step
-      cudaError_t e = launch_tf32_lo(x, ws.lo, (size_t)rows * k, s);
-      if (e != cudaSuccess) return e;
       TcGemmArgs t{};
-      t.x = x; t.x_lo = ws.lo; t.w = w; t.w_lo = w_lo; t.bias = bias; t.resid = resid; t.out = out; t.error_flag = ws.d_error;
+      t.x = x; t.x_lo = x_lo; t.w = w; t.w_lo = w_lo; t.bias = bias; t.resid = resid; t.out = out; t.out_lo = out_lo;
+      t.error_flag = ws.d_error;
       t.m = rows; t.n = n_out; t.k = k; t.epilogue = epi;
       return launch_tc_gemm_tf32x3_rows(t, s);
     }
@@ -991,22 +996,24 @@ static int run_blocks(const pg_model* m, const BlockWorkspace& ws, const Prefill
   static const bool no_tc_attn = getenv("PG_NO_TC_ATTN") != nullptr;
   for (int l = 0; l < m->layers_n(); ++l) {
     const LayerWeights& w = m->layers[l];
-    PG_CUDA_TRY(launch_layernorm_rows(ws.x, w.ln1_g, w.ln1_b, eps, ws.norm, rows, C, false, s));
-    PG_CUDA_TRY(gemm(w.w_qkv, w.l_qkv, w.b_qkv, ws.norm, ws.qkv, 3 * C, C, EPI_NONE, nullptr));
+    PG_CUDA_TRY(launch_layernorm_rows(ws.x, w.ln1_g, w.ln1_b, eps, ws.norm, rows, C, false, s, lo_c));
+    PG_CUDA_TRY(gemm(w.w_qkv, w.l_qkv, w.b_qkv, ws.norm, lo_c, ws.qkv, nullptr, 3 * C, C, EPI_NONE, nullptr));
     if (cache)
       PG_CUDA_TRY(launch_kv_scatter(ws.qkv, ws.d_slot, ws.d_pos, cache->layer_pool(l), cache->d_table, cache->kv,
                                     rows, s));
     PrefillAttnArgs pa{};
     pa.qkv = ws.qkv; pa.out = ws.attn; pa.seq_start = ws.d_seq_start;
     pa.n_head = m->heads(); pa.head_dim = m->head_dim(); pa.batch = plan.batch; pa.max_len = plan.max_len;
-    if (m->backend.math_mode == PG_MATH_TF32 && ws.d_error && !no_tc_attn && prefill_attention_tc_supported(pa))
+    if (m->backend.math_mode == PG_MATH_TF32 && ws.d_error && !no_tc_attn && prefill_attention_tc_supported(pa)) {
       PG_CUDA_TRY(launch_prefill_attention_tc(pa, rows, ws.d_error, s));
-    else
+    } else {
+      pa.out_lo = lo_c;
       PG_CUDA_TRY(launch_prefill_attention(pa, s));
-    PG_CUDA_TRY(gemm(w.w_proj, w.l_proj, w.b_proj, ws.attn, ws.x, C, C, EPI_RESID, ws.x));
-    PG_CUDA_TRY(launch_layernorm_rows(ws.x, w.ln2_g, w.ln2_b, eps, ws.norm, rows, C, false, s));
-    PG_CUDA_TRY(gemm(w.w_fc, w.l_fc, w.b_fc, ws.norm, ws.h, F, C, EPI_GELU, nullptr));
-    PG_CUDA_TRY(gemm(w.w_proj2, w.l_proj2, w.b_proj2, ws.h, ws.x, C, F, EPI_RESID, ws.x));
+    }
+    PG_CUDA_TRY(gemm(w.w_proj, w.l_proj, w.b_proj, ws.attn, lo_c, ws.x, nullptr, C, C, EPI_RESID, ws.x));
+    PG_CUDA_TRY(launch_layernorm_rows(ws.x, w.ln2_g, w.ln2_b, eps, ws.norm, rows, C, false, s, lo_c));
+    PG_CUDA_TRY(gemm(w.w_fc, w.l_fc, w.b_fc, ws.norm, lo_c, ws.h, lo_f, F, C, EPI_GELU, nullptr));
+    PG_CUDA_TRY(gemm(w.w_proj2, w.l_proj2, w.b_proj2, ws.h, lo_f, ws.x, nullptr, C, F, EPI_RESID, ws.x));
   }
   return PG_OK;
 }
