@@ -54,11 +54,12 @@ typedef struct {
  * the other modes are extensions with their own stated error bounds. */
 typedef enum {
   PG_MATH_FP32 = 0,   /* FP32 FMA everywhere */
-  PG_MATH_TF32X3 = 1, /* decode linears of 9..64 sequences on tensor cores as three TF32 products
-                         (hi*hi + hi*lo + lo*hi) with FP32 accumulation: FP32-grade, passes the same
-                         token-exact tests; everything else as PG_MATH_FP32 */
-  PG_MATH_TF32 = 2,   /* as TF32X3 for decode; single-pass TF32 is available per operator
-                         (pg_op_linear) with its looser bound */
+  PG_MATH_TF32X3 = 1, /* FP32-grade products on the tensor cores as three TF32 MMAs over hi and lo parts of both
+                         operands (x.w + x.w_lo + x_lo.w) with FP32 accumulation: the decode linears of 9..64
+                         sequences and prefill GEMMs of at least 128 rows; passes the same token-exact and
+                         1e-3 / 1e-4 logit tests as PG_MATH_FP32. Everything else as PG_MATH_FP32 */
+  PG_MATH_TF32 = 2,   /* as TF32X3 for decode; prefill GEMMs of at least 128 rows and prefill attention
+                         (head_dim 64) as single TF32 passes: a speed mode, bound 5e-3 of the logit span */
   PG_MATH_BF16 = 3    /* BF16 WEIGHTS, FP32 activations and sums: the four dense matrices of every block and the
                          tied embedding are rounded to BF16 (nearest even) at load; what the model computes is
                          the FP32 path of the reference on those rounded weights. Decode steps of at most 8
