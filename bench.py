@@ -446,7 +446,7 @@ def run_ours(args):
         else:
             lin_sec, lin_n = sum(prof[k][0] for k in lin_keys), sum(prof[k][1] for k in lin_keys)
             if lin_sec >= prof["attention"][0]:
-                kernel_name = "linear_decode_kernel" if B <= 8 else "tc_gemm_x3_kernel"
+                kernel_name = "linear_decode_kernel" if B <= 4 else "tc_gemm_x3_kernel"
                 dom_bytes, dom_sec, dom_n = weight_bytes_step, lin_sec, lin_n
             else:
                 kernel_name, dom_bytes, dom_sec, dom_n = "decode_attention_kernel", kv_prof, prof["attention"][0], prof["attention"][1]
@@ -469,7 +469,7 @@ def run_ours(args):
                                    f"{PROMPT_LEN}-token prompts, greedy decode; step = one decode step of every sequence "
                                    f"({total} tokens)",
                        "linears": ("fp32 weights and activations; products as 3xTF32 on tcgen05 tensor cores, "
-                                   "FP32 accumulate" if args.math == "tf32x3" and B > 8 else "fp32 CUDA-core FMA"),
+                                   "FP32 accumulate" if args.math == "tf32x3" and B > 4 else "fp32 CUDA-core FMA"),
                        "step_kernels": ("ONE persistent kernel per step: embedding, all layers, lm_head, arg-max, "
                                         "token feedback" if launches == K else f"{launches // K} kernels per step in a CUDA graph"),
                        "l2": "inputs larger than L2 (1.4 GB weights + KV per step and GPU)", "parallelism": f"replicas x{world}, batch-sharded"},
@@ -515,7 +515,7 @@ def main():
     ap.add_argument("--seqs", type=int, default=TOTAL_SEQS,
                     help="sequences in total (default 64, the benchmark workload; smaller for profiler captures)")
     ap.add_argument("--math", default="tf32x3", choices=["fp32", "tf32x3"],
-                    help="arithmetic of decode linears of 9..64 sequences per GPU: fp32 = CUDA-core FMA, tf32x3 = three TF32 "
+                    help="arithmetic of decode linears of 5..64 sequences per GPU: fp32 = CUDA-core FMA, tf32x3 = three TF32 "
                          "tensor-core products with FP32 accumulation (FP32-grade, token-exact against the oracle)")
     ap.add_argument("--no-xl", action="store_true", help="skip the GPT-2 XL sampling line under `also`")
     ap.add_argument("--no-also", action="store_true", help="skip every line under `also` but the weak-scaling one")

@@ -428,7 +428,7 @@ __device__ __forceinline__ void chain_final_phase(const ChainArgs& a, int j) {
 // The new token's own key and value are appended to the cache.
 
 struct AtCursor {  // where the warp is in issuing its block sequence; the same in every lane, except pg0 / pg1
-  int item, blk, nblk, t, b, h;
+  int item, blk, nblk, t, b, h;  // item = pair * parts + part; the warp walks blocks part, part + parts, ...
   int pg0, pg1;  // page table entries lane and lane + 32 of sequence b
   uint32_t issued;
 };
@@ -488,15 +488,26 @@ __device__ __forceinline__ void attn_qkv4(const ChainArgs& a, const ChainPhase& 
   v = out[2];
 }
 
-// Moves the issuing cursor of an attention warp to pair `item` (all lanes, identical control flow).
-__device__ __forceinline__ void at_cursor_load(const ChainArgs& a, AtCursor& cur, int item, int items, int lane) {
+// With few pairs (small batches) the keys of one pair are shared out over `parts` = 2, 4 or 8 warps of one
+// CTA, block i of the pair going to part i mod parts, so that no warp idles while another walks a whole
+// context alone: parts = the largest power of two with pairs * parts <= worker warps of the grid.
+__device__ __forceinline__ int at_parts_shift(int pairs, int grid) {
+  int sh = 0;
+  while (sh < 3 && (pairs << (sh + 1)) <= grid * 8) ++sh;
+  return sh;
+}
+
+// Moves the issuing cursor of an attention warp to `item` (all lanes, identical control flow).
+__device__ __forceinline__ void at_cursor_load(const ChainArgs& a, AtCursor& cur, int item, int items, int lane, int psh) {
   const int H = a.kv.n_head, pps = a.kv.pages_per_seq;
   cur.item = item;
   cur.blk = 0;
   cur.nblk = 0;
   if (item >= items) return;
-  cur.b = item / H;
-  cur.h = item - cur.b * H;
+  const int pair = item >> psh;
+  cur.b = pair / H;
+  cur.h = pair - cur.b * H;
+  cur.blk = item & ((1 << psh) - 1);
   cur.t = __ldg(a.pos + cur.b);
   cur.nblk = (cur.t + AT_ROWS - 1) / AT_ROWS;
   const int* table = a.page_table + (size_t)cur.b * pps;
@@ -509,7 +520,8 @@ __device__ __forceinline__ void at_cursor_load(const ChainArgs& a, AtCursor& cur
 // loads), so that the attention phase starts with its first copies. (Asking L2 for the pair's first
 // key / value blocks here with cp.async.bulk.prefetch.L2 measured slower, twice, and is not done.)
 __device__ __forceinline__ void chain_attn_prepare(const ChainArgs& a, int w8, int lane, AtCursor& cur, uint32_t consumed) {
-  at_cursor_load(a, cur, (int)blockIdx.x * 8 + w8, a.m * a.kv.n_head, lane);
+  const int psh = at_parts_shift(a.m * a.kv.n_head, (int)gridDim.x);
+  at_cursor_load(a, cur, (int)blockIdx.x * 8 + w8, (a.m * a.kv.n_head) << psh, lane, psh);
   cur.issued = consumed;
 }
 
@@ -523,13 +535,14 @@ __device__ __forceinline__ void chain_attn_phase(const ChainArgs& a, const Chain
   float4* qs = reinterpret_cast<float4*>(scratch_all + w8 * D);  // this pair's query, 16 float4
   const int H = a.kv.n_head, C = H * D, pt = a.kv.page_tokens, pps = a.kv.pages_per_seq;
   const int pt_shift = pt == 16 ? 4 : pt == 32 ? 5 : 6;
-  const int items = a.m * H, step = (int)gridDim.x * 8, first = (int)blockIdx.x * 8 + w8;
+  const int psh = at_parts_shift(a.m * H, (int)gridDim.x), parts = 1 << psh;
+  const int items = (a.m * H) << psh, step = (int)gridDim.x * 8, first = (int)blockIdx.x * 8 + w8;
   const ChRange r = chain_range(ph.n, ph.k, 0, (int)gridDim.x);  // shares of the QKV GEMM whose partials are read
   const float scale = 0.125f;  // 1 / sqrt(64)
   bool ok = live;
 
   if (!prepared) {
-    at_cursor_load(a, cur, first, items, lane);
+    at_cursor_load(a, cur, first, items, lane, psh);
     cur.issued = consumed;
   }
   // executed by all lanes with identical control flow; only lane 0 starts copies
@@ -537,7 +550,7 @@ __device__ __forceinline__ void chain_attn_phase(const ChainArgs& a, const Chain
     while (cur.issued < limit) {
       if (cur.blk >= cur.nblk) {
         if (cur.item >= items) break;
-        at_cursor_load(a, cur, cur.item + step, items, lane);
+        at_cursor_load(a, cur, cur.item + step, items, lane, psh);
         if (cur.item >= items) break;
         continue;
       }
@@ -556,7 +569,7 @@ __device__ __forceinline__ void chain_attn_phase(const ChainArgs& a, const Chain
         if (lane < 2) bulk_load(dst, src, bytes, &kv_full[slot]);
       }
       ++cur.issued;
-      ++cur.blk;
+      cur.blk += parts;
     }
   };
   if (ok) issue_upto(consumed + AT_SLOTS);
@@ -564,7 +577,8 @@ __device__ __forceinline__ void chain_attn_phase(const ChainArgs& a, const Chain
   const int key = lane >> 1, half = lane & 1;  // scores: two lanes per key, 32 dims each
   const int d4 = lane & 15, kh = lane >> 4;    // values: sixteen lanes per row, two key halves
   for (int item = first; item < items; item += step) {
-    const int b = item / H, h = item - b * H;
+    const int pair = item >> psh, part = item & (parts - 1);
+    const int b = pair / H, h = pair - b * H;
     const int t = __ldg(a.pos + b);
     const int nblk = (t + RB - 1) / RB;
     // q, k, v of the new token: lanes 0-15 each own four of the head's 64 features
@@ -581,7 +595,7 @@ __device__ __forceinline__ void chain_attn_phase(const ChainArgs& a, const Chain
     __syncwarp();
     float m = -INFINITY, l = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int i = 0; i < nblk; ++i) {
+    for (int i = part; i < nblk; i += parts) {
       const int rows = min(RB, t - i * RB);
       const uint32_t slot = consumed % AT_SLOTS;
       const uint8_t* blk = stage + (size_t)slot * AT_SLOT_BYTES;  // key rows, then value rows
@@ -641,20 +655,65 @@ __device__ __forceinline__ void chain_attn_phase(const ChainArgs& a, const Chain
       __syncwarp();
       if (ok) issue_upto(consumed + AT_SLOTS);  // this block's slot is free
     }
-    // ---- the new token itself, then the two key halves and the lanes' partial sums
-    const float m_fin = fmaxf(m, sn);
-    const float corr = (m == -INFINITY) ? 0.f : expf(m - m_fin);
-    const float pn = expf(sn - m_fin);
-    acc.x *= corr;
-    acc.y *= corr;
-    acc.z *= corr;
-    acc.w *= corr;
-    acc.x += __shfl_xor_sync(0xffffffffu, acc.x, 16);
-    acc.y += __shfl_xor_sync(0xffffffffu, acc.y, 16);
-    acc.z += __shfl_xor_sync(0xffffffffu, acc.z, 16);
-    acc.w += __shfl_xor_sync(0xffffffffu, acc.w, 16);
-    const float ls = warp_sum_f(l) * corr + pn;
-    if (lane < 16 && ok) {
+    float ls, pn;
+    if (parts > 1) {
+      // ---- the two key halves and the lanes' partial sums of this warp's share
+      acc.x += __shfl_xor_sync(0xffffffffu, acc.x, 16);
+      acc.y += __shfl_xor_sync(0xffffffffu, acc.y, 16);
+      acc.z += __shfl_xor_sync(0xffffffffu, acc.z, 16);
+      acc.w += __shfl_xor_sync(0xffffffffu, acc.w, 16);
+      l = warp_sum_f(l);
+      // The parts of a pair are neighbouring warps of this CTA. Every warp has at most one item per phase
+      // here (that is how `parts` is chosen), so no copy is in flight and the warp's own staging area is
+      // free: (m, l, acc) go there, the warps of the pair meet at a named barrier, and part 0 adds the
+      // shares in part order (the same result whichever warp finishes first), then the new token itself.
+      float* mine = reinterpret_cast<float*>(stage);
+      if (lane < 16) reinterpret_cast<float4*>(mine)[lane] = acc;
+      if (lane == 0) {
+        mine[64] = m;
+        mine[65] = l;
+      }
+      asm volatile("bar.sync %0, %1;" ::"r"(2 + (w8 >> psh)), "r"(32 << psh) : "memory");
+      float mm = fmaxf(m, sn);
+      if (part == 0) {
+        for (int q = 1; q < parts; ++q)
+          mm = fmaxf(mm, reinterpret_cast<const float*>(stage + (size_t)q * AT_SLOTS * AT_SLOT_BYTES)[64]);
+        const float c0 = (m == -INFINITY) ? 0.f : expf(m - mm);
+        acc.x *= c0;
+        acc.y *= c0;
+        acc.z *= c0;
+        acc.w *= c0;
+        l *= c0;
+        for (int q = 1; q < parts; ++q) {
+          const float* other = reinterpret_cast<const float*>(stage + (size_t)q * AT_SLOTS * AT_SLOT_BYTES);
+          const float mq = other[64];
+          const float cq = (mq == -INFINITY) ? 0.f : expf(mq - mm);
+          const float4 aq = reinterpret_cast<const float4*>(other)[lane & 15];
+          acc.x = fmaf(cq, aq.x, acc.x);
+          acc.y = fmaf(cq, aq.y, acc.y);
+          acc.z = fmaf(cq, aq.z, acc.z);
+          acc.w = fmaf(cq, aq.w, acc.w);
+          l = fmaf(cq, other[65], l);
+        }
+      }
+      pn = expf(sn - mm);
+      ls = l + pn;
+    } else {
+      // ---- the new token itself, then the two key halves and the lanes' partial sums
+      const float m_fin = fmaxf(m, sn);
+      const float corr = (m == -INFINITY) ? 0.f : expf(m - m_fin);
+      pn = expf(sn - m_fin);
+      acc.x *= corr;
+      acc.y *= corr;
+      acc.z *= corr;
+      acc.w *= corr;
+      acc.x += __shfl_xor_sync(0xffffffffu, acc.x, 16);
+      acc.y += __shfl_xor_sync(0xffffffffu, acc.y, 16);
+      acc.z += __shfl_xor_sync(0xffffffffu, acc.z, 16);
+      acc.w += __shfl_xor_sync(0xffffffffu, acc.w, 16);
+      ls = warp_sum_f(l) * corr + pn;
+    }
+    if (lane < 16 && ok && part == 0) {
       const float inv = 1.0f / ls;
       const float y[4] = {fmaf(pn, vn.x, acc.x) * inv, fmaf(pn, vn.y, acc.y) * inv, fmaf(pn, vn.z, acc.z) * inv,
                           fmaf(pn, vn.w, acc.w) * inv};
@@ -668,7 +727,7 @@ __device__ __forceinline__ void chain_attn_phase(const ChainArgs& a, const Chain
       *reinterpret_cast<float4*>(ph.out_hi + idx) = make_float4(hi[0], hi[1], hi[2], hi[3]);
       *reinterpret_cast<float4*>(ph.out_lo + idx) = make_float4(lo[0], lo[1], lo[2], lo[3]);
     }
-    if (lane < 16) {  // append the new K and V rows
+    if (lane < 16 && part == 0) {  // append the new K and V rows
       const int off = t & (pt - 1);
       reinterpret_cast<float4*>(ph.kv_pool + ((((size_t)app_page * 2 + 0) * H + h) * pt + off) * D)[lane] = kn;
       reinterpret_cast<float4*>(ph.kv_pool + ((((size_t)app_page * 2 + 1) * H + h) * pt + off) * D)[lane] = vn;
