@@ -73,6 +73,8 @@ cudaError_t launch_prefill_attention(const PrefillAttnArgs& a, cudaStream_t s);
 // rows = rows of the QKV matrix; error_flag receives a code when a bounded wait runs out.
 bool prefill_attention_tc_supported(const PrefillAttnArgs& a);
 cudaError_t launch_prefill_attention_tc(const PrefillAttnArgs& a, int rows, int* error_flag, cudaStream_t s);
+// The same at FP32 grade (three TF32 products per term, lo parts formed inside the kernel): the FP32-parity modes.
+cudaError_t launch_prefill_attention_x3(const PrefillAttnArgs& a, int rows, int* error_flag, cudaStream_t s);
 cudaError_t init_attn_tc_attributes();
 // Copies K,V of every prompt row into the paged cache.
 cudaError_t launch_kv_scatter(const float* qkv, const int* row_slot, const int* row_pos, float* kv_pool,

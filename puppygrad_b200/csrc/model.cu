@@ -1009,6 +1009,9 @@ static int run_blocks(const pg_model* m, const BlockWorkspace& ws, const Prefill
     pa.n_head = m->heads(); pa.head_dim = m->head_dim(); pa.batch = plan.batch; pa.max_len = plan.max_len;
     if (m->backend.math_mode == PG_MATH_TF32 && ws.d_error && !no_tc_attn && prefill_attention_tc_supported(pa)) {
       PG_CUDA_TRY(launch_prefill_attention_tc(pa, rows, ws.d_error, s));
+    } else if (x3_rows && !no_tc_attn && prefill_attention_tc_supported(pa)) {
+      pa.out_lo = lo_c;
+      PG_CUDA_TRY(launch_prefill_attention_x3(pa, rows, ws.d_error, s));
     } else {
       pa.out_lo = lo_c;
       PG_CUDA_TRY(launch_prefill_attention(pa, s));
