@@ -347,25 +347,53 @@ __global__ void __launch_bounds__(192, 2)
 // tensor memory and V_lo^T while they transpose V. P keeps its full FP32 value in registers, 2^x is the
 // hardware approximation (2 ulp). The hi.hi products of P.V and its two small terms have an accumulator
 // each (the tensor core adds with truncation; the bias grows with the MMAs per accumulator). All 512
-// tensor-memory columns: one CTA per SM.
+// tensor-memory columns: one CTA per SM, so nothing overlaps the softmax of a tile but the work of its
+// own warps: EIGHT softmax warps, two per quarter of the tensor-memory lanes (a warp reaches the lanes
+// 32 * (warp % 4) ..), each with half of the tile's 128 key columns, half of a row of Q, K, V in the
+// conversions and transposition, and O or O_small when the maximum moves. The two threads of a row
+// exchange their partial row maxima through shared memory at a 64-thread named barrier per tile.
 constexpr size_t AT_X3_SMEM = (size_t)AT_TILE_BYTES * 5 + 1024;
 constexpr uint32_t X3_S_COL = 0, X3_PLO_COL = 128, X3_O_COL = 256, X3_OS_COL = 320, X3_Q_COL = 384, X3_QLO_COL = 448,
                    X3_TMEM_COLS = 512;
+constexpr int X3_THREADS = 320, X3_HC = AT_K / 2;  // threads per CTA; key columns per softmax thread
 
 __device__ __forceinline__ uint32_t lo_bits(uint32_t v) {
   return __float_as_uint(__uint_as_float(v) - __uint_as_float(v & 0xFFFFE000u));
 }
 
-// s <- P = 2^(s * sl2 - mn) at full FP32 precision; returns the row sum
+__device__ __forceinline__ void x3_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+// Row maximum of this thread's X3_HC raw scores (keys kt + cb ..); MASK: keys after the query do not count.
 template <bool MASK>
-__device__ __forceinline__ float at_exp_rows_full(uint32_t (&s)[128], int kt, int qpos, float sl2, float mn) {
+__device__ __forceinline__ float x3_row_max(const uint32_t (&s)[X3_HC], int k0, int qpos) {
+  float tmax = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < X3_HC; ++j)
+    if (!MASK || k0 + j <= qpos) tmax = fmaxf(tmax, __uint_as_float(s[j]));
+  return tmax;
+}
+
+// s <- P = 2^(s * sl2 - mn) at full FP32 precision; returns the sum of the thread's columns
+template <bool MASK>
+__device__ __forceinline__ float x3_exp_rows(uint32_t (&s)[X3_HC], int k0, int qpos, float sl2, float mn) {
   float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
-  for (int j = 0; j < AT_K; j += 2) {
+  for (int j = 0; j < X3_HC; j += 2) {
     float p0 = ex2_approx(fmaf(__uint_as_float(s[j]), sl2, -mn));
     float p1 = ex2_approx(fmaf(__uint_as_float(s[j + 1]), sl2, -mn));
-    if (MASK && kt + j > qpos) p0 = 0.f;
-    if (MASK && kt + j + 1 > qpos) p1 = 0.f;
+    if (MASK && k0 + j > qpos) p0 = 0.f;
+    if (MASK && k0 + j + 1 > qpos) p1 = 0.f;
     ps0 += p0;
     ps1 += p1;
     s[j] = __float_as_uint(p0);
@@ -374,7 +402,7 @@ __device__ __forceinline__ float at_exp_rows_full(uint32_t (&s)[128], int kt, in
   return ps0 + ps1;
 }
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(X3_THREADS, 1)
     prefill_attention_x3_kernel(const __grid_constant__ CUtensorMap map_qkv, PrefillAttnArgs a, int* error_flag) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int h = blockIdx.x, b = blockIdx.y, qb = (int)gridDim.z - 1 - (int)blockIdx.z;
@@ -391,6 +419,7 @@ __global__ void __launch_bounds__(192, 1)
   __shared__ uint64_t bars[9];
   __shared__ uint32_t tmem_slot;
   __shared__ int failed_word;
+  __shared__ float xmax[2][2][AT_Q];  // [tile parity][column half][row]: partial row maxima; at the end the partial sums
   uint64_t* q_full = &bars[0];
   uint64_t* q_ready = &bars[1];    // Q and Q_lo are in tensor memory
   uint64_t* k_full = &bars[2];
@@ -408,14 +437,14 @@ __global__ void __launch_bounds__(192, 1)
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    mbar_init(q_ready, 4);
+    mbar_init(q_ready, 8);
     mbar_init(k_full, 1);
     mbar_init(v_full, 1);
-    mbar_init(v_free, 4);
+    mbar_init(v_free, 8);
     mbar_init(s_full, 1);
-    mbar_init(p_ready, 4);
+    mbar_init(p_ready, 8);
     mbar_init(pv_done, 1);
-    mbar_init(klo_ready, 4);
+    mbar_init(klo_ready, 8);
     failed_word = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -486,51 +515,48 @@ __global__ void __launch_bounds__(192, 1)
       }
     }
   } else {
-    const int q = warp & 3;
-    const int r = q * 32 + lane;  // query row of the tile == tensor-memory lane == key handled in the transposition
+    const int q = warp & 3;          // quarter of the tensor-memory lanes this warp reaches
+    const int hf = (warp - 2) >> 2;  // which half of the key columns / of a row of Q, K, V this thread handles
+    const int r = q * 32 + lane;     // query row of the tile == tensor-memory lane == key handled in the transposition
+    const int cb = hf * X3_HC;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    const uint32_t s_addr = tmem_base + X3_S_COL + lane_addr, plo_addr = tmem_base + X3_PLO_COL + lane_addr;
-    const uint32_t o_addr = tmem_base + X3_O_COL + lane_addr, os_addr = tmem_base + X3_OS_COL + lane_addr;
+    const uint32_t s_addr = tmem_base + X3_S_COL + lane_addr + (uint32_t)cb;
+    const uint32_t plo_addr = tmem_base + X3_PLO_COL + lane_addr + (uint32_t)cb;
+    const uint32_t o_addr = tmem_base + (hf ? X3_OS_COL : X3_O_COL) + lane_addr;  // rescaled by this thread when the maximum moves
     const int qpos = q0 + r;
     const float sl2 = 0.125f * 1.4426950408889634f;  // 1 / sqrt(64), in powers of two
-    float m = -INFINITY, l = 0.f;                    // running maximum (log2 units) and sum
-    const float4* row_lo = reinterpret_cast<const float4*>(v_s + (size_t)r * 128);
-    const float4* row_hi = reinterpret_cast<const float4*>(v_s + AT_TILE_BYTES / 2 + (size_t)r * 128);
-    // K_lo of the tile in k_s: element by element at the same (swizzled) place, row r by this thread
+    float m = -INFINITY, l = 0.f;                    // running maximum (log2 units) and this thread's part of the sum
+    // this thread's half (32 floats = 128 bytes, one swizzle row) of row r of the Q / V tile and of the K tile
+    const float4* vrow = reinterpret_cast<const float4*>(v_s + hf * (AT_TILE_BYTES / 2) + (size_t)r * 128);
+    const float4* krow = reinterpret_cast<const float4*>(k_s + hf * (AT_TILE_BYTES / 2) + (size_t)r * 128);
+    float4* klrow = reinterpret_cast<float4*>(klo_s + hf * (AT_TILE_BYTES / 2) + (size_t)r * 128);
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory"); };
+    // K_lo of the tile in k_s: element by element at the same (swizzled) place
     auto make_klo = [&]() {
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const float4* src = reinterpret_cast<const float4*>(k_s + half * (AT_TILE_BYTES / 2) + (size_t)r * 128);
-        float4* dst = reinterpret_cast<float4*>(klo_s + half * (AT_TILE_BYTES / 2) + (size_t)r * 128);
-#pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-          const int cidx = jj ^ (r & 7);
-          const float4 x = src[cidx];
-          dst[cidx] = make_float4(__uint_as_float(lo_bits(__float_as_uint(x.x))), __uint_as_float(lo_bits(__float_as_uint(x.y))),
+      for (int jj = 0; jj < 8; ++jj) {
+        const int cidx = jj ^ (r & 7);
+        const float4 x = krow[cidx];
+        klrow[cidx] = make_float4(__uint_as_float(lo_bits(__float_as_uint(x.x))), __uint_as_float(lo_bits(__float_as_uint(x.y))),
                                   __uint_as_float(lo_bits(__float_as_uint(x.z))), __uint_as_float(lo_bits(__float_as_uint(x.w))));
-        }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // K_lo is read by the tensor core
     };
     bool ok = warp_wait_all(q_full, 0, failed, error_flag, 56);
     if (ok) {  // Q: shared memory -> tensor memory, as it is (the MMA reads its hi part) and its lo part
+      uint32_t w[32];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const float4* src = half ? row_hi : row_lo;
-        uint32_t w[32];
-#pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-          const float4 x = src[jj ^ (r & 7)];
-          w[4 * jj + 0] = __float_as_uint(x.x);
-          w[4 * jj + 1] = __float_as_uint(x.y);
-          w[4 * jj + 2] = __float_as_uint(x.z);
-          w[4 * jj + 3] = __float_as_uint(x.w);
-        }
-        tmem_st32(tmem_base + X3_Q_COL + lane_addr + (uint32_t)(half * 32), w);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) w[j] = lo_bits(w[j]);
-        tmem_st32(tmem_base + X3_QLO_COL + lane_addr + (uint32_t)(half * 32), w);
+      for (int jj = 0; jj < 8; ++jj) {
+        const float4 x = vrow[jj ^ (r & 7)];
+        w[4 * jj + 0] = __float_as_uint(x.x);
+        w[4 * jj + 1] = __float_as_uint(x.y);
+        w[4 * jj + 2] = __float_as_uint(x.z);
+        w[4 * jj + 3] = __float_as_uint(x.w);
       }
+      tmem_st32(tmem_base + X3_Q_COL + lane_addr + (uint32_t)(hf * 32), w);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) w[j] = lo_bits(w[j]);
+      tmem_st32(tmem_base + X3_QLO_COL + lane_addr + (uint32_t)(hf * 32), w);
       tmem_wait_st();
       tc_fence_before();
     }
@@ -546,16 +572,24 @@ __global__ void __launch_bounds__(192, 1)
     for (int i = 0; i < ntiles; ++i) {
       const int kt = i * AT_K;
       const bool diag = kt + AT_K - 1 > q0;  // some key of the tile lies after some query: mask
+      uint32_t s[X3_HC];
+      float part_max = -INFINITY;
       if (ok) ok = warp_wait_all(s_full, i & 1, failed, error_flag, 58);
       if (ok) {
         tc_fence_after();
-        uint32_t s[128];
-        at_ld32<0>(s_addr, s);
-        at_ld32<32>(s_addr, s);
-        at_ld32<64>(s_addr, s);
-        at_ld32<96>(s_addr, s);
+        x3_ld32(s_addr, s);
+        x3_ld32(s_addr + 32u, s + 32);
         at_wait_ld();
-        const float tmax = (diag ? at_row_max<true>(s, kt, qpos) : at_row_max<false>(s, kt, qpos)) * sl2;
+        part_max = diag ? x3_row_max<true>(s, kt + cb, qpos) : x3_row_max<false>(s, kt + cb, qpos);
+      }
+      // the row maximum is over both halves: every softmax thread comes here once per tile, whatever `ok` says
+      xmax[i & 1][hf][r] = part_max;
+      pair_sync();
+      if (ok) {
+        const float tmax = fmaxf(part_max, xmax[i & 1][hf ^ 1][r]) * sl2;
+        // The maximum is only moved (and O rescaled) when some row of the warp outgrew it by 2^8 (the same
+        // decision in both warps of the pair: they hold the same rows); key kt is visible to every row of
+        // the tile, so the first tile sets a finite maximum.
         const bool move = __any_sync(0xffffffffu, tmax > m + 8.0f);
         float corr = 1.0f;
         if (move) {
@@ -564,13 +598,13 @@ __global__ void __launch_bounds__(192, 1)
           l *= corr;
           m = mn;
         }
-        l += diag ? at_exp_rows_full<true>(s, kt, qpos, sl2, m) : at_exp_rows_full<false>(s, kt, qpos, sl2, m);
+        l += diag ? x3_exp_rows<true>(s, kt + cb, qpos, sl2, m) : x3_exp_rows<false>(s, kt + cb, qpos, sl2, m);
         // the PV MMAs of the previous tile read P, P_lo, V^T, V_lo^T and write O: wait for them
         if (i > 0) ok = warp_wait_all(pv_done, (i - 1) & 1, failed, error_flag, 59);
         if (ok) {
           tc_fence_after();
 #pragma unroll
-          for (int c0 = 0; c0 < AT_K; c0 += 32) {
+          for (int c0 = 0; c0 < X3_HC; c0 += 32) {
             uint32_t w[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) w[j] = s[c0 + j] & 0xFFFFE000u;
@@ -581,7 +615,7 @@ __global__ void __launch_bounds__(192, 1)
           }
           if (move && i > 0) {
 #pragma unroll 1
-            for (int c0 = 0; c0 < 2 * AT_D; c0 += 32) {  // O and O_small are neighbours
+            for (int c0 = 0; c0 < AT_D; c0 += 32) {  // column half 0 rescales O, half 1 O_small
               float v[32];
               uint32_t w[32];
               tmem_ld32(o_addr + (uint32_t)c0, v);
@@ -590,7 +624,7 @@ __global__ void __launch_bounds__(192, 1)
               tmem_st32(o_addr + (uint32_t)c0, w);
             }
           }
-          // V^T and V_lo^T: this thread moves key r of the tile
+          // V^T and V_lo^T: this thread moves 32 of the 64 values of key r
           ok = warp_wait_all(v_full, i & 1, failed, error_flag, 60);
         }
         if (ok) {
@@ -598,19 +632,15 @@ __global__ void __launch_bounds__(192, 1)
           float* vtl = reinterpret_cast<float*>(vtlo_s + (r >> 5) * 8192);
           const int kc = (r & 31) >> 2, kw = r & 3;  // 16-byte chunk and word of this key inside a V^T row
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            const float4* src = half ? row_hi : row_lo;
+          for (int jj = 0; jj < 8; ++jj) {
+            const float4 x = vrow[jj ^ (r & 7)];
+            const float xs[4] = {x.x, x.y, x.z, x.w};
+            const int d = hf * 32 + jj * 4;
 #pragma unroll
-            for (int jj = 0; jj < 8; ++jj) {
-              const float4 x = src[jj ^ (r & 7)];
-              const float xs[4] = {x.x, x.y, x.z, x.w};
-              const int d = half * 32 + jj * 4;
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int o = (d + e) * 32 + ((kc ^ ((d + e) & 7)) << 2) + kw;
-                vt[o] = xs[e];
-                vtl[o] = __uint_as_float(lo_bits(__float_as_uint(xs[e])));
-              }
+            for (int e = 0; e < 4; ++e) {
+              const int o = (d + e) * 32 + ((kc ^ ((d + e) & 7)) << 2) + kw;
+              vt[o] = xs[e];
+              vtl[o] = __uint_as_float(lo_bits(__float_as_uint(xs[e])));
             }
           }
           tmem_wait_st();
@@ -631,28 +661,29 @@ __global__ void __launch_bounds__(192, 1)
         if (lane == 0) mbar_arrive(klo_ready);
       }
     }
-    // ---- result: (O + O_small) / l
+    // ---- result: (O + O_small) / l, l = the sum over both column halves; each thread writes 32 of the 64 values
+    xmax[ntiles & 1][hf][r] = l;
+    pair_sync();
+    l += xmax[ntiles & 1][hf ^ 1][r];
     if (ok) ok = warp_wait_all(pv_done, (ntiles - 1) & 1, failed, error_flag, 62);
     if (ok) {
       tc_fence_after();
       const float inv = 1.0f / l;
-      float* orow = a.out + (size_t)(r0 + qpos) * c + h * AT_D;
-      float* lrow = a.out_lo ? a.out_lo + (size_t)(r0 + qpos) * c + h * AT_D : nullptr;
-#pragma unroll 1
-      for (int c0 = 0; c0 < AT_D; c0 += 32) {
-        float v[32], v2[32];
-        tmem_ld32(o_addr + (uint32_t)c0, v);
-        tmem_ld32(os_addr + (uint32_t)c0, v2);
-        if (qpos < len) {
+      const int c0 = hf * 32;
+      float* orow = a.out + (size_t)(r0 + qpos) * c + h * AT_D + c0;
+      float* lrow = a.out_lo ? a.out_lo + (size_t)(r0 + qpos) * c + h * AT_D + c0 : nullptr;
+      float v[32], v2[32];
+      tmem_ld32(tmem_base + X3_O_COL + lane_addr + (uint32_t)c0, v);
+      tmem_ld32(tmem_base + X3_OS_COL + lane_addr + (uint32_t)c0, v2);
+      if (qpos < len) {
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            const float y0 = (v[j] + v2[j]) * inv, y1 = (v[j + 1] + v2[j + 1]) * inv, y2 = (v[j + 2] + v2[j + 2]) * inv,
-                        y3 = (v[j + 3] + v2[j + 3]) * inv;
-            *reinterpret_cast<float4*>(orow + c0 + j) = make_float4(y0, y1, y2, y3);
-            if (lrow)
-              *reinterpret_cast<float4*>(lrow + c0 + j) =
-                  make_float4(y0 - tf32_hi(y0), y1 - tf32_hi(y1), y2 - tf32_hi(y2), y3 - tf32_hi(y3));
-          }
+        for (int j = 0; j < 32; j += 4) {
+          const float y0 = (v[j] + v2[j]) * inv, y1 = (v[j + 1] + v2[j + 1]) * inv, y2 = (v[j + 2] + v2[j + 2]) * inv,
+                      y3 = (v[j + 3] + v2[j + 3]) * inv;
+          *reinterpret_cast<float4*>(orow + j) = make_float4(y0, y1, y2, y3);
+          if (lrow)
+            *reinterpret_cast<float4*>(lrow + j) =
+                make_float4(y0 - tf32_hi(y0), y1 - tf32_hi(y1), y2 - tf32_hi(y2), y3 - tf32_hi(y3));
         }
       }
     }
@@ -690,7 +721,7 @@ cudaError_t launch_prefill_attention_x3(const PrefillAttnArgs& a, int rows, int*
   CUtensorMap map;
   if (!make_map(&map, a.qkv, (uint64_t)rows, (uint64_t)3 * c, 128)) return cudaErrorInvalidValue;
   dim3 grid(a.n_head, a.batch, (a.max_len + AT_Q - 1) / AT_Q);
-  prefill_attention_x3_kernel<<<grid, 192, AT_X3_SMEM, s>>>(map, a, error_flag);
+  prefill_attention_x3_kernel<<<grid, X3_THREADS, AT_X3_SMEM, s>>>(map, a, error_flag);
   return cudaGetLastError();
 }
 

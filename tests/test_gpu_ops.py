@@ -48,6 +48,21 @@ def test_linear_tf32x3_matches_oracle(oracle, m, n, k, epilogue):
     np.testing.assert_allclose(got, oracle_linear(oracle, x, w, b, epilogue, r), rtol=1e-3, atol=1e-4)
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 1600, 1600), (512, 4800, 1600), (300, 1600, 6400), (1000, 777, 256)])
+@pytest.mark.parametrize("epilogue", ["none", "gelu", "resid"])
+def test_linear_tf32x3_prefill_sized_matches_oracle(oracle, m, n, k, epilogue):
+    """More than 64 rows: hi and lo parts of both operands from shared memory, three TF32 MMAs per k step into
+    two accumulators (the hi.hi products and the small terms). Same bound as the FP32 path; row and column
+    counts that are not multiples of the 128 x 128 tile included."""
+    rng = np.random.default_rng(m * 13 + n * 5 + k + 2)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.05)
+    b = rng.standard_normal(n, dtype=np.float32)
+    r = rng.standard_normal((m, n), dtype=np.float32)
+    got, _ = ops.linear(x, w, b, r if epilogue == "resid" else None, epilogue, "tf32x3")
+    np.testing.assert_allclose(got, oracle_linear(oracle, x, w, b, epilogue, r), rtol=1e-3, atol=1e-4)
+
+
 @pytest.mark.parametrize("m,n,k", [(16, 1600, 1600), (64, 6400, 1600), (33, 1600, 6400), (40, 1000, 256)])
 @pytest.mark.parametrize("epilogue", ["none", "gelu", "resid"])
 def test_linear_tf32x3_one_launch_per_gemm_kernel_matches_oracle(oracle, monkeypatch, m, n, k, epilogue):
