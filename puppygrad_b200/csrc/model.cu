@@ -595,8 +595,11 @@ struct StepProfiler {
   }
 };
 
-static ChainArgs chain_base_args(const pg_cache* c, int batch) {
+// Arguments of the chain kernel for `batch` sequences starting at slot 64 * chunk (steps of more than 64
+// sequences run as one launch per 64: the activation buffers are reused, what belongs to a slot is offset).
+static ChainArgs chain_base_args(const pg_cache* c, int batch, int chunk = 0) {
   const pg_model* m = c->model;
+  const size_t s0 = (size_t)chunk * 64;
   ChainArgs base{};
   base.m = batch; base.eps = m->cfg.layer_norm_epsilon; base.arena = m->tiled_arena; base.arena_floats = m->tiled_floats;
   base.act_hi[CH_ACT_NORM] = c->norm; base.act_lo[CH_ACT_NORM] = c->norm_lo; base.act_k[CH_ACT_NORM] = m->c();
@@ -604,9 +607,10 @@ static ChainArgs chain_base_args(const pg_cache* c, int batch) {
   base.act_hi[CH_ACT_H] = c->hbuf; base.act_lo[CH_ACT_H] = c->h_lo; base.act_k[CH_ACT_H] = m->f();
   base.partials = c->chain_partials; base.barrier = c->d_chain_barrier; base.error_flag = c->d_error;
   base.trace = c->d_chain_trace;
-  base.kv = c->kv; base.page_table = c->d_table; base.pos = c->d_pos;
-  base.wte = m->wte; base.wpe = m->wpe; base.ids = c->d_ids; base.pos_rw = c->d_pos; base.argmax_out = c->d_argmax;
-  base.token_log = c->d_token_log; base.n_positions = m->positions(); base.best = c->d_chain_best;
+  base.kv = c->kv; base.page_table = c->d_table + s0 * c->kv.pages_per_seq; base.pos = c->d_pos + s0;
+  base.wte = m->wte; base.wpe = m->wpe; base.ids = c->d_ids + s0; base.pos_rw = c->d_pos + s0;
+  base.argmax_out = c->d_argmax + s0;
+  base.token_log = c->d_token_log + s0 * m->positions(); base.n_positions = m->positions(); base.best = c->d_chain_best;
   return base;
 }
 
@@ -614,9 +618,13 @@ static ChainArgs chain_base_args(const pg_cache* c, int batch) {
 // kernel and uploads it: per layer QKV projection, attention, attention-output projection with
 // residual and LayerNorm, MLP with GELU, residual and the next LayerNorm; then the lm_head.
 // block_forward_one_profiled (rust.rs:1136-1250), forward_one tail (rust.rs:981-1003).
-static int ensure_chain_program(pg_cache* c, int batch) {
-  if (c->chain_ctas <= 0 || batch < c->chain_min_batch || batch > 64 || !c->norm_lo) return PG_OK;
-  if (c->chain_programs.count(batch)) return PG_OK;
+static int chain_program_key(int rows, int chunk) { return rows + 100 * chunk; }
+
+static int ensure_chain_program(pg_cache* c, int batch, int chunk = 0) {
+  if (c->chain_ctas <= 0 || batch < 1 || batch > 64 || !c->norm_lo) return PG_OK;
+  if (chunk == 0 && batch < c->chain_min_batch) return PG_OK;
+  const int key = chain_program_key(batch, chunk);
+  if (c->chain_programs.count(key)) return PG_OK;
   const pg_model* m = c->model;
   const int C = m->c(), F = m->f(), V = m->v(), L = m->layers_n();
   std::vector<ChainPhase> ph;
@@ -671,7 +679,7 @@ static int ensure_chain_program(pg_cache* c, int batch) {
   }
   cur_b = B_LOGITS;
   gemm(m->t_wte, V, C, CH_ACT_NORM);
-  elem(V, C, nullptr, 0, c->logits, nullptr, nullptr);
+  elem(V, C, nullptr, 0, c->logits + (size_t)chunk * 64 * V, nullptr, nullptr);
   ph.back().best = c->d_chain_best;  // the reduce phase of the lm_head also finds the row arg-max
   {
     ChainPhase p{};
@@ -679,7 +687,7 @@ static int ensure_chain_program(pg_cache* c, int batch) {
     ph.push_back(p);
     bucket.push_back(B_OTHER);
   }
-  ChainArgs a = chain_base_args(c, batch);
+  ChainArgs a = chain_base_args(c, batch, chunk);
   a.n_phases = (int)ph.size();
   pg_cache::ChainProgram prog;
   prog.n = (int)ph.size();
@@ -695,7 +703,15 @@ static int ensure_chain_program(pg_cache* c, int batch) {
     PG_CUDA_TRY(cudaMalloc(&prog.dev_argmax_only, lean.size() * sizeof(ChainPhase)));
     PG_CUDA_TRY(cudaMemcpy(prog.dev_argmax_only, lean.data(), lean.size() * sizeof(ChainPhase), cudaMemcpyHostToDevice));
   }
-  c->chain_programs[batch] = prog;
+  c->chain_programs[key] = prog;
+  return PG_OK;
+}
+
+// More than 64 sequences: a program per chunk of 64 (the last one may be smaller).
+static int ensure_chain_programs(pg_cache* c, int batch) {
+  if (batch <= 64) return ensure_chain_program(c, batch);
+  for (int k = 0; k * 64 < batch; ++k)
+    if (int r = ensure_chain_program(c, std::min(64, batch - k * 64), k)) return r;
   return PG_OK;
 }
 
@@ -766,8 +782,30 @@ static cudaError_t enqueue_decode_step(pg_cache* c, int batch, int splits, cudaS
     if (e != cudaSuccess) return e;                                      \
     if (prof && (e = prof->mark(s, -1)) != cudaSuccess) return e;        \
   } while (0)
+  if (m->t_wte && batch > 64 && !prof) {
+    // more than 64 sequences: the same kernel once per 64 sequences, one after the other (each launch streams
+    // the weights again: a step is bound by its chain of phases, not by bytes)
+    bool all = true;
+    for (int k = 0; k * 64 < batch && all; ++k) {
+      auto prog = c->chain_programs.find(chain_program_key(std::min(64, batch - k * 64), k));
+      all = prog != c->chain_programs.end() && prog->second.dev;
+    }
+    if (all) {
+      for (int k = 0; k * 64 < batch; ++k) {
+        const int rows = std::min(64, batch - k * 64);
+        const auto& prog = c->chain_programs[chain_program_key(rows, k)];
+        ChainArgs a = chain_base_args(c, rows, k);
+        a.phases_dev = c->step_wants_logits ? prog.dev : prog.dev_argmax_only;
+        a.n_phases = prog.n;
+        cur_bucket = B_OTHER;
+        PG_E(launch_chain(a, c->chain_ctas, s));
+      }
+      if (launches) *launches = n;
+      return cudaSuccess;
+    }
+  }
   {
-    auto prog = c->chain_programs.find(batch);
+    auto prog = c->chain_programs.find(batch <= 64 ? chain_program_key(batch, 0) : -1);
     if (m->t_wte && prog != c->chain_programs.end() && prog->second.dev) {
       // the whole step, from the embedding to the token fed back, as one persistent cooperative kernel
       ChainArgs a = chain_base_args(c, batch);
@@ -891,7 +929,7 @@ static int run_decode_step(pg_cache* c, int batch) {
   const bool graphs = m->backend.use_graphs != 2 && !env_flag("PG_NO_GRAPHS");
   uint64_t launches = 0;
   if (m->t_wte) {
-    if (int r = ensure_chain_program(c, batch)) return r;
+    if (int r = ensure_chain_programs(c, batch)) return r;
   }
   if (!graphs || c->dbg_poison) {
     cudaError_t e = enqueue_decode_step(c, batch, splits, c->stream, &launches);

@@ -192,7 +192,7 @@ def test_token_by_token_prefill_equals_batched_prefill(midi):
 
 @pytest.mark.parametrize("batch,math_mode", [(2, "fp32"), (5, "fp32"), (8, "fp32"), (12, "fp32"),
                                              (5, "tf32x3"), (8, "tf32x3"), (12, "tf32x3"), (20, "tf32x3"),
-                                             (33, "tf32x3"), (64, "tf32x3")])
+                                             (33, "tf32x3"), (64, "tf32x3"), (70, "tf32x3"), (130, "tf32x3")])
 def test_ragged_batches_match_single_sequences(midi, oracle, batch, math_mode):
     cfg, w, g, o = midi
     if math_mode != "fp32":  # linears as three TF32 tensor-core products with FP32 accumulation
@@ -210,11 +210,20 @@ def test_ragged_batches_match_single_sequences(midi, oracle, batch, math_mode):
     cur = am.copy()
     assert list(cur) == [oracle.argmax_logits(l) for l in olog]
     for step in range(6):
+        n0 = cache.kernel_launches()
         logits, am, _, _ = g.forward_one_batch(cur, cache, want_logits=True)
+        if math_mode != "fp32" and batch >= 5:  # one persistent kernel per 64 sequences
+            assert cache.kernel_launches() - n0 == (batch + 63) // 64
         ol = np.stack([o.forward_one(int(cur[i]), ocaches[i]) for i in range(batch)])
         assert_logits_close(logits, ol)
         assert list(am) == [oracle.argmax_logits(l) for l in ol]
         cur = am.copy()
+    if batch > 64:  # the device-fed loop over several launches per step
+        toks = g.decode_greedy(cur, cache, 3)
+        for step in range(3):
+            ol = [o.forward_one(int(cur[i]), ocaches[i]) for i in range(batch)]
+            cur = np.array([oracle.argmax_logits(l) for l in ol], dtype=np.int32)
+            assert list(toks[step]) == list(cur)
 
 
 def test_device_fed_greedy_equals_oracle_stream(midi):
