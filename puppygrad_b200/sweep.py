@@ -203,7 +203,7 @@ def main():
     ap.add_argument("--persistent", default="auto", choices=["auto", "on", "off"],
                     help="decode: the single-kernel step of small batches")
     ap.add_argument("--hbm-gbs", type=float, default=6534.5, help="xl_table: HBM peak the fractions are taken of")
-    ap.add_argument("--tf32-tflops", type=float, default=838.0, help="xl_table: TF32 tensor peak (half the BF16 peak)")
+    ap.add_argument("--tf32-tflops", type=float, default=725.0, help="xl_table: TF32 tensor peak (library GEMM at 8192^3 on B200)")
     ap.add_argument("--vocab", type=int, default=50257)
     ap.add_argument("--model", default="small", help="prefill: model preset")
     ap.add_argument("--seqs", type=int, default=8, help="prefill: prompts per call")
