@@ -223,6 +223,12 @@ __global__ void __launch_bounds__(192, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_n = (a.n + BN - 1) / BN, tiles = tiles_n * ((a.m + TILE_M - 1) / TILE_M);
   const int nkb = a.k / BK;
+  // Long reductions are cut into chunks of at most 56 k blocks, each accumulated in tensor memory on its own and
+  // added to the result by the epilogue warps in FP32 (round to nearest): the accumulate inside the tensor core
+  // truncates, and its bias grows with the length of one accumulation. Not with GELU (not additive; its GEMM
+  // has k = n_embd, short enough).
+  const int nchunk = (a.epilogue == EPI_GELU) ? 1 : (nkb + 55) / 56;
+  const int kc = (nkb + nchunk - 1) / nchunk;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; ++s) {
@@ -248,7 +254,7 @@ __global__ void __launch_bounds__(192, 1)
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
         const int n0 = (tile % tiles_n) * BN, m0 = (tile / tiles_n) * TILE_M;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        for (int kb = 0; kb < nkb; ++kb, ++it) {  // chunk boundaries do not matter to the operand stream
           const uint32_t s = it % S::STAGES;
           if (it >= S::STAGES) ok = mbar_wait(&empty[s], ((it / S::STAGES) - 1) & 1, failed, a.error_flag, 1);
           if (!ok) break;
@@ -266,7 +272,9 @@ __global__ void __launch_bounds__(192, 1)
       const uint32_t idesc = umma_idesc_tf32(TILE_M, BN);
       uint32_t it = 0, ti = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++ti) {
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x)
+      for (int kb0 = 0; kb0 < nkb && ok; kb0 += kc, ++ti) {
+        const int kb1 = min(nkb, kb0 + kc);
         const uint32_t buf = ti & 1;
         if (ti >= 2) ok = mbar_wait(&d_empty[buf], ((ti >> 1) - 1) & 1, failed, a.error_flag, 4);
         if (!ok) break;
@@ -275,7 +283,7 @@ __global__ void __launch_bounds__(192, 1)
         // MMAs into one accumulator: the hi . hi products get an accumulator of their own and the two small
         // terms share a second one (their magnitude, hence their bias, is 2^-11 of the first).
         const uint32_t tmem_d = tmem_base + buf * (2 * BN), tmem_s = tmem_d + BN;
-        for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
           const uint32_t s = it % S::STAGES;
           ok = mbar_wait(&full[s], (it / S::STAGES) & 1, failed, a.error_flag, 2);
           if (!ok) break;
@@ -285,12 +293,12 @@ __global__ void __launch_bounds__(192, 1)
           const uint64_t db = umma_desc_sw128(st + 2 * S::A_BYTES), dbl = umma_desc_sw128(st + 2 * S::A_BYTES + S::B_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / 8; ++k)
-            umma_tf32_ss(tmem_s, dal + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+            umma_tf32_ss(tmem_s, dal + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb != kb0) || k != 0);
 #pragma unroll
           for (int k = 0; k < BK / 8; ++k) umma_tf32_ss(tmem_s, da + (uint64_t)(k * 2), dbl + (uint64_t)(k * 2), idesc, 1);
 #pragma unroll
           for (int k = 0; k < BK / 8; ++k)
-            umma_tf32_ss(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+            umma_tf32_ss(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb != kb0) || k != 0);
           umma_commit(&empty[s]);
         }
         if (ok) umma_commit(&d_full[buf]);
@@ -304,7 +312,9 @@ __global__ void __launch_bounds__(192, 1)
     float* tile = epi_tiles + q * (32 * 33);
     uint32_t ti = 0;
     bool ok = true;
-    for (int tile_id = blockIdx.x; tile_id < tiles && ok; tile_id += gridDim.x, ++ti) {
+    for (int tile_id = blockIdx.x; tile_id < tiles && ok; tile_id += gridDim.x)
+    for (int ch = 0; ch < nchunk && ok; ++ch, ++ti) {
+      const bool first = ch == 0, last = ch == nchunk - 1;
       const int n0 = (tile_id % tiles_n) * BN, m0 = (tile_id / tiles_n) * TILE_M;
       const uint32_t buf = ti & 1;
       const uint32_t tmem_d = tmem_base + buf * (2 * BN);
@@ -318,12 +328,14 @@ __global__ void __launch_bounds__(192, 1)
         // the block's 32 residual values of this lane's column go out first: they do not depend on
         // the accumulator, and asked for one by one between the stores (which may alias them:
         // the residual is updated in place) they would each cost a full memory round trip
+        // (a later chunk of a long reduction adds to what the chunks before it left in `out`)
         float rv[32];
-        if (a.epilogue == EPI_RESID && col < a.n) {
+        const float* prev = first ? (a.epilogue == EPI_RESID ? a.resid : nullptr) : a.out;
+        if (prev && col < a.n) {
 #pragma unroll
           for (int rr = 0; rr < 32; ++rr) {
             const int row = m0 + q * 32 + rr;
-            rv[rr] = row < a.m ? a.resid[(size_t)row * a.n + col] : 0.f;
+            rv[rr] = row < a.m ? prev[(size_t)row * a.n + col] : 0.f;
           }
         }
         float v[32], v2[32];
@@ -339,11 +351,11 @@ __global__ void __launch_bounds__(192, 1)
             const int row = m0 + q * 32 + rr;
             if (row < a.m) {
               float r = tile[rr * 33 + lane];
-              if (a.bias) r = bias + r;
+              if (a.bias && first) r = bias + r;
               if (a.epilogue == EPI_GELU) r = gelu_ref(r);
-              if (a.epilogue == EPI_RESID) r = rv[rr] + r;
+              if (prev) r = rv[rr] + r;
               a.out[(size_t)row * a.n + col] = r;
-              if (a.out_lo) a.out_lo[(size_t)row * a.n + col] = r - tf32_hi(r);  // lo part for the GEMM that reads `out`
+              if (a.out_lo && last) a.out_lo[(size_t)row * a.n + col] = r - tf32_hi(r);  // lo part for the GEMM that reads `out`
             }
           }
         }
