@@ -55,7 +55,7 @@ typedef struct {
 typedef enum {
   PG_MATH_FP32 = 0,   /* FP32 FMA everywhere */
   PG_MATH_TF32X3 = 1, /* FP32-grade products on the tensor cores as three TF32 MMAs over hi and lo parts of both
-                         operands (x.w + x.w_lo + x_lo.w) with FP32 accumulation: the decode linears of 5..64
+                         operands (x.w + x.w_lo + x_lo.w) with FP32 accumulation: the decode linears of 9..64
                          sequences and prefill GEMMs of at least 128 rows; passes the same token-exact and
                          1e-3 / 1e-4 logit tests as PG_MATH_FP32. Everything else as PG_MATH_FP32 */
   PG_MATH_TF32 = 2,   /* as TF32X3 for decode; prefill GEMMs of at least 128 rows and prefill attention

@@ -289,6 +289,195 @@ __global__ void __launch_bounds__(LIN_THREADS) linear_decode_kernel(LinearArgs a
 }
 
 
+// ------------------------------------------------------------------ decode linear, activations in shared memory
+// The same operator as one persistent CTA of 16 warps per SM: with several input rows the kernel above
+// re-reads the activations from L1 once per input row and 16 weights, and starts a CTA (and, fused, a
+// LayerNorm) per four weight rows. Here a CTA stages the input rows once ([MT][k] floats, LayerNorm applied
+// in place when asked for) and its warps then walk units of (four weight rows, one of `kparts` parts of
+// k): 128-bit streaming loads of the weights, activations from shared memory (consecutive lanes,
+// consecutive 16-byte units: no bank conflict), one folding warp reduction per unit. With kparts = 1 the
+// lanes that hold the sums finish the rows; otherwise the parts of a row group, which are neighbouring
+// warps of one CTA, leave their sums in shared memory and after a CTA barrier the first threads add them
+// in part order. kparts is chosen so that all 16 x 148 warps have a unit when the matrix has few rows.
+constexpr int LR_THREADS = 512;
+constexpr int LR_WARPS = LR_THREADS / 32;
+constexpr int LR_ROWS = 4;
+constexpr size_t LR_MAX_SMEM = 208 * 1024;  // [MT][k] floats
+
+template <int MT, int EPI>
+__global__ void __launch_bounds__(LR_THREADS, 1) linear_rows_smem_kernel(LinearArgs a, int kp_shift) {
+  extern __shared__ float4 dyn_smem4[];
+  float4* xs4 = dyn_smem4;  // [MT][k / 4]
+  constexpr int NV = LR_ROWS * MT;
+  constexpr int SH = (NV == 32) ? 0 : (NV == 16) ? 1 : (NV == 8) ? 2 : 3;  // 5 - log2(NV)
+  __shared__ float part[LR_WARPS][NV];
+  __shared__ float best_v[LR_WARPS][NV];
+  __shared__ int best_i[LR_WARPS][NV];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int k4 = a.k >> 2;
+  const int groups = (a.n + LR_ROWS - 1) / LR_ROWS;
+  const int kparts = 1 << kp_shift;
+  const int gpc = LR_WARPS >> kp_shift;           // row groups a CTA works on at a time
+  const int wg = warp >> kp_shift, kp = warp & (kparts - 1);  // this warp's group slot and part of k
+  const int c_beg = (int)(((long long)k4 * kp) >> kp_shift), c_end = (int)(((long long)k4 * (kp + 1)) >> kp_shift);
+  const float4* w4 = reinterpret_cast<const float4*>(a.w);
+  const int g_first = (int)blockIdx.x * gpc + wg, g_stride = (int)gridDim.x * gpc;
+
+  pdl_launch();
+  // weights do not depend on the previous kernel: the warp's first loads go out before the dependency wait
+  float4 wpre[LR_ROWS];
+#pragma unroll
+  for (int r = 0; r < LR_ROWS; ++r)
+    wpre[r] = (g_first < groups && c_beg + lane < c_end)
+                  ? ldg_stream(w4 + (size_t)min(g_first * LR_ROWS + r, a.n - 1) * k4 + c_beg + lane)
+                  : make_float4(0, 0, 0, 0);
+  pdl_wait();
+
+  {
+    const float4* x4 = reinterpret_cast<const float4*>(a.x);
+    for (int idx = tid; idx < MT * k4; idx += LR_THREADS) {
+      const int r = idx / k4;
+      xs4[idx] = r < a.m ? x4[idx] : make_float4(0, 0, 0, 0);
+    }
+  }
+  __syncthreads();
+  if (a.ln_g) {  // LayerNorm of each row, by one warp (layer_norm_in_place, src/models/cpu.rs:119-143, tree sums)
+    const float4* g4 = reinterpret_cast<const float4*>(a.ln_g);
+    const float4* b4 = reinterpret_cast<const float4*>(a.ln_b);
+    for (int r = warp; r < a.m && r < MT; r += LR_WARPS) {
+      float4* row = xs4 + (size_t)r * k4;
+      float sum = 0.f;
+      for (int c = lane; c < k4; c += 32) {
+        const float4 v = row[c];
+        sum += (v.x + v.y) + (v.z + v.w);
+      }
+      const float mean = warp_sum(sum) / (float)a.k;
+      float q = 0.f;
+      for (int c = lane; c < k4; c += 32) {
+        const float4 v = row[c];
+        const float d0 = v.x - mean, d1 = v.y - mean, d2 = v.z - mean, d3 = v.w - mean;
+        q += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+      }
+      const float inv_std = 1.0f / sqrtf(warp_sum(q) / (float)a.k + a.eps);
+      for (int c = lane; c < k4; c += 32) {
+        const float4 g = g4[c], b = b4[c];
+        float4 v = row[c];
+        v.x = (v.x - mean) * inv_std * g.x + b.x;
+        v.y = (v.y - mean) * inv_std * g.y + b.y;
+        v.z = (v.z - mean) * inv_std * g.z + b.z;
+        v.w = (v.w - mean) * inv_std * g.w + b.w;
+        row[c] = v;
+      }
+    }
+    __syncthreads();
+  }
+
+  // after the warp reduction the lanes with (lane & (2^SH - 1)) == 0 hold sum number lane >> SH = r * MT + m
+  const bool holder = (lane & ((1 << SH) - 1)) == 0;
+  // who finishes a sum: with kparts = 1 the holder lanes of the warp, else thread t < gpc * NV for (group slot, sum)
+  const bool finisher = kparts == 1 ? holder : tid < gpc * NV;
+  const int fs = kparts == 1 ? (lane >> SH) : tid % NV;  // sum number
+  const int fslot = kparts == 1 ? wg : tid / NV;         // group slot
+  const int fr = fs / MT, fm = fs % MT;
+  float run_best = -INFINITY;  // lm_head arg-max partial of this finisher's (row in group, input row) pair
+  int run_idx = INT_MAX;
+
+  // every warp of the CTA makes the same number of rounds (the CTA barrier inside needs all of them)
+  const int rounds = (groups - (int)blockIdx.x * gpc + g_stride - 1) / g_stride;
+  for (int it = 0; it < rounds; ++it) {
+    const int g = g_first + it * g_stride;
+    const bool live = g < groups;
+    const int row0 = g * LR_ROWS;
+    // what the epilogue needs from memory, asked for before the loop
+    const int orow = ((int)blockIdx.x * gpc + fslot + it * g_stride) * LR_ROWS + fr;
+    const bool fin = finisher && orow < a.n && fm < a.m && ((int)blockIdx.x * gpc + fslot + it * g_stride) < groups;
+    float bias_v = 0.f, resid_v = 0.f;
+    if (fin) {
+      if (a.bias) bias_v = a.bias[orow];
+      if (EPI == EPI_RESID) resid_v = a.resid[(size_t)fm * a.n + orow];
+    }
+    float acc[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) acc[i] = 0.f;
+    if (live) {
+      const float4* wrow[LR_ROWS];
+#pragma unroll
+      for (int r = 0; r < LR_ROWS; ++r) wrow[r] = w4 + (size_t)min(row0 + r, a.n - 1) * k4;
+      auto accumulate = [&](const float4 (&w)[LR_ROWS], int c) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          const float4 xv = xs4[(size_t)m * k4 + c];
+#pragma unroll
+          for (int r = 0; r < LR_ROWS; ++r) acc[r * MT + m] = dot4(w[r], xv, acc[r * MT + m]);
+        }
+      };
+      int c = c_beg + lane;
+      if (it == 0) {
+        if (c < c_end) accumulate(wpre, c);
+        c += 32;
+      }
+#pragma unroll 2
+      for (; c < c_end; c += 32) {
+        float4 w[LR_ROWS];
+#pragma unroll
+        for (int r = 0; r < LR_ROWS; ++r) w[r] = ldg_stream(wrow[r] + c);
+        accumulate(w, c);
+      }
+      WarpMultiReduce<NV, 16>::run(acc, lane);
+    }
+    float total = acc[0];
+    if (kparts > 1) {
+      if (holder) part[warp][lane >> SH] = acc[0];
+      __syncthreads();
+      if (fin) {
+        total = 0.f;
+        for (int q = 0; q < kparts; ++q) total += part[(fslot << kp_shift) + q][fs];  // in part order
+      }
+    }
+    if (fin) {
+      float v = a.bias ? bias_v + total : total;
+      if (EPI == EPI_GELU) v = gelu_ref(v);
+      if (EPI == EPI_RESID) v = resid_v + v;
+      a.out[(size_t)fm * a.n + orow] = v;
+      if (a.part_val && v > run_best) {
+        run_best = v;
+        run_idx = orow;
+      }
+    }
+    if (kparts > 1) __syncthreads();  // `part` is rewritten in the next round
+  }
+
+  if (a.part_val) {
+    // finishers: kparts = 1: holder lanes of every warp, sum number lane >> SH; else threads t < gpc * NV
+    if (kparts == 1) {
+      if (holder) {
+        best_v[warp][lane >> SH] = run_best;
+        best_i[warp][lane >> SH] = run_idx;
+      }
+    } else if (tid < gpc * NV) {
+      best_v[tid / NV][tid % NV] = run_best;
+      best_i[tid / NV][tid % NV] = run_idx;
+    }
+    __syncthreads();
+    if (tid < MT && tid < a.m) {
+      float bv = -INFINITY;
+      int bi = INT_MAX;
+      for (int w = 0; w < gpc; ++w)
+#pragma unroll
+        for (int r = 0; r < LR_ROWS; ++r) {
+          const float v = best_v[w][r * MT + tid];
+          const int i = best_i[w][r * MT + tid];
+          if (v > bv || (v == bv && i < bi)) {
+            bv = v;
+            bi = i;
+          }
+        }
+      a.part_val[(size_t)tid * gridDim.x + blockIdx.x] = bv;
+      a.part_idx[(size_t)tid * gridDim.x + blockIdx.x] = bi;
+    }
+  }
+}
+
 // Any k (no alignment requirement): one thread per output element. Only shapes whose inner
 // dimension is not a multiple of 4 take this path.
 __global__ void linear_generic_kernel(LinearArgs a, int epi) {
@@ -1202,6 +1391,11 @@ int linear_decode_grid(int n, int sms) {
   return groups < cap ? groups : cap;
 }
 
+// smallest row count class (1, 2, 4, 8) that takes the shared-memory kernel (one input row is faster on the
+// kernel above: GPT-2 medium steps of 1 / 2 / 4 / 8 sequences took 747 / 893 / 1113 / 1580 us with it and
+// 758 / 789 / 921 / 1091 us with the shared-memory kernel); PG_LR_MIN_MT overrides it for tuning
+static int g_lr_min_mt = [] { const char* e = getenv("PG_LR_MIN_MT"); return e ? atoi(e) : 2; }();
+
 cudaError_t launch_linear_decode(const LinearArgs& a, int epilogue, bool pdl, cudaStream_t s, int* grid_out) {
   if (a.k % 4 != 0 || (a.ln_g && (a.m > 8 || a.k > 2048)) || (a.part_val && a.m > 8)) {
     if (a.ln_g || a.part_val) return cudaErrorInvalidValue;  // callers un-fuse these cases
@@ -1210,6 +1404,28 @@ cudaError_t launch_linear_decode(const LinearArgs& a, int epilogue, bool pdl, cu
     return launch(linear_generic_kernel, dim3((unsigned)((total + 127) / 128)), dim3(128), 0, s, pdl, a, epilogue);
   }
   int mt = a.m <= 1 ? 1 : a.m <= 2 ? 2 : a.m <= 4 ? 4 : 8;
+  if (a.m <= 8 && mt >= g_lr_min_mt && (size_t)mt * a.k * sizeof(float) <= LR_MAX_SMEM) {
+    // activations staged in shared memory, one persistent CTA per SM; k is shared out over the warps of a
+    // CTA when the matrix has too few rows to give every warp of the chip a row group
+    const int groups = (a.n + LR_ROWS - 1) / LR_ROWS, k4 = a.k / 4;
+    int kp_shift = 0;
+    while (kp_shift < 4 && (groups << (kp_shift + 1)) <= num_sms() * LR_WARPS && (k4 >> (kp_shift + 1)) >= 32) ++kp_shift;
+    const int gpc = LR_WARPS >> kp_shift;
+    const int grid = std::max(1, std::min(num_sms(), (groups + gpc - 1) / gpc));
+    if (grid_out) *grid_out = grid;
+    const size_t smem = (size_t)mt * a.k * sizeof(float);
+#define PG_LR(MT_)                                                                                                        \
+  switch (epilogue) {                                                                                                      \
+    case EPI_GELU: return launch(linear_rows_smem_kernel<MT_, EPI_GELU>, dim3(grid), dim3(LR_THREADS), smem, s, pdl, a, kp_shift);   \
+    case EPI_RESID: return launch(linear_rows_smem_kernel<MT_, EPI_RESID>, dim3(grid), dim3(LR_THREADS), smem, s, pdl, a, kp_shift); \
+    default: return launch(linear_rows_smem_kernel<MT_, EPI_NONE>, dim3(grid), dim3(LR_THREADS), smem, s, pdl, a, kp_shift);         \
+  }
+    if (mt == 1) { PG_LR(1) }
+    if (mt == 2) { PG_LR(2) }
+    if (mt == 4) { PG_LR(4) }
+    PG_LR(8)
+#undef PG_LR
+  }
   int grid = linear_decode_grid(a.n, num_sms());
   if (grid_out) *grid_out = grid;
   bool ln = a.ln_g != nullptr;
@@ -1325,6 +1541,12 @@ cudaError_t init_kernel_attributes() {
   PG_SET((linear_decode_kernel<4, EPI_NONE, true>), ln_smem / 2)
   PG_SET((linear_decode_kernel<4, EPI_GELU, true>), ln_smem / 2)
   PG_SET((linear_decode_kernel<4, EPI_RESID, true>), ln_smem / 2)
+#define PG_SET_LR(MT_)                                              \
+  PG_SET((linear_rows_smem_kernel<MT_, EPI_NONE>), LR_MAX_SMEM)    \
+  PG_SET((linear_rows_smem_kernel<MT_, EPI_GELU>), LR_MAX_SMEM)    \
+  PG_SET((linear_rows_smem_kernel<MT_, EPI_RESID>), LR_MAX_SMEM)
+  PG_SET_LR(1) PG_SET_LR(2) PG_SET_LR(4) PG_SET_LR(8)
+#undef PG_SET_LR
   PG_SET(decode_attention_kernel<64>, 64 * 1024)
   PG_SET(prefill_attention_kernel<64>, PA_SMEM)
   PG_SET(decode_attention_generic_kernel, 64 * 1024)

@@ -328,7 +328,7 @@ struct pg_cache {
   unsigned* attn_counters = nullptr;
   float* topk_vals = nullptr;
   int* topk_idx = nullptr;
-  // tensor-core decode path (5..64 sequences): TF32 hi/lo pairs of the GEMM inputs, split-K scratch
+  // tensor-core decode path (9..64 sequences): TF32 hi/lo pairs of the GEMM inputs, split-K scratch
   float *norm_lo = nullptr, *attn_lo = nullptr, *h_lo = nullptr;
   int* d_error = nullptr;
   // persistent chain kernel of the tensor-core decode path: partial tiles, grid-barrier word
@@ -337,8 +337,8 @@ struct pg_cache {
   unsigned long long* d_chain_best = nullptr;  // row arg-max accumulators of the lm_head phase
   unsigned long long* d_chain_trace = nullptr;  // developer aid: only allocated in builds with -DPG_DEV_TRACE
   int chain_ctas = 0;
-  int chain_min_batch = 5;  // smallest batch whose decode step runs as the chain kernel in the tensor-core modes (measured on
-                            // B200, GPT-2 medium, 8 sequences: 1.34 ms against 1.58 ms for one kernel per operation)
+  int chain_min_batch = 9;  // smallest batch whose decode step runs as the chain kernel in the tensor-core modes (measured on
+                            // B200, GPT-2 medium, 8 sequences: 1.34 ms as the chain kernel, 1.09 ms as one kernel per operation)
   struct ChainProgram {  // whole-step phase list of the persistent chain kernel for one batch size
     ChainPhase* dev = nullptr;            // in device memory (nullptr: this batch size is not supported)
     ChainPhase* dev_argmax_only = nullptr;  // the same list whose lm_head reduce phase keeps the row arg-max but stores no logits
