@@ -303,6 +303,7 @@ constexpr int LR_THREADS = 512;
 constexpr int LR_WARPS = LR_THREADS / 32;
 constexpr int LR_ROWS = 4;
 constexpr size_t LR_MAX_SMEM = 208 * 1024;  // [MT][k] floats
+constexpr int LR_ONE_ROW_MIN_N = 16384;      // one input row takes this kernel only for the lm_head
 
 template <int MT, int EPI>
 __global__ void __launch_bounds__(LR_THREADS, 1) linear_rows_smem_kernel(LinearArgs a, int kp_shift) {
@@ -416,7 +417,8 @@ __global__ void __launch_bounds__(LR_THREADS, 1) linear_rows_smem_kernel(LinearA
         if (c < c_end) accumulate(wpre, c);
         c += 32;
       }
-#pragma unroll 2
+      constexpr int UNR = MT >= 4 ? 2 : 4;  // iterations whose loads are in flight together (registers permitting)
+#pragma unroll(UNR)
       for (; c < c_end; c += 32) {
         float4 w[LR_ROWS];
 #pragma unroll
@@ -1404,7 +1406,7 @@ cudaError_t launch_linear_decode(const LinearArgs& a, int epilogue, bool pdl, cu
     return launch(linear_generic_kernel, dim3((unsigned)((total + 127) / 128)), dim3(128), 0, s, pdl, a, epilogue);
   }
   int mt = a.m <= 1 ? 1 : a.m <= 2 ? 2 : a.m <= 4 ? 4 : 8;
-  if (a.m <= 8 && mt >= g_lr_min_mt && (size_t)mt * a.k * sizeof(float) <= LR_MAX_SMEM) {
+  if (a.m <= 8 && (mt >= g_lr_min_mt || a.n >= LR_ONE_ROW_MIN_N) && (size_t)mt * a.k * sizeof(float) <= LR_MAX_SMEM) {
     // activations staged in shared memory, one persistent CTA per SM; k is shared out over the warps of a
     // CTA when the matrix has too few rows to give every warp of the chip a row group
     const int groups = (a.n + LR_ROWS - 1) / LR_ROWS, k4 = a.k / 4;
