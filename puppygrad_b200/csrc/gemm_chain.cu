@@ -93,18 +93,24 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volati
 // Grid barrier of the worker warps: arrival count only grows during a launch, barrier b (1-based)
 // is passed when it reaches grid * b. Returns the same verdict to every worker thread.
 __device__ __forceinline__ bool chain_grid_barrier(unsigned* counter, unsigned target, volatile int* failed, int* err,
-                                                   int wt, volatile int* verdict) {
+                                                   int wt, volatile int* verdict, int fence_first) {
   workers_sync();
   if (wt == 0) {
     if (!*failed) {
-      __threadfence();
-      asm volatile("fence.proxy.async;" ::: "memory");  // results written here are read by other CTAs' TMA loads
+      // The arrival is a release at GPU scope and release is cumulative: what the other workers of this CTA
+      // wrote before the CTA barrier above is ordered before it, so no separate fence is needed for them.
+      if (fence_first & 1) __threadfence();
+      if (!(fence_first & 2)) asm volatile("fence.proxy.async;" ::: "memory");  // results written here are read by other CTAs' TMA loads
       asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
       uint32_t spins = 0;
       for (;;) {
         unsigned v;
-        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
-        if (v >= target) break;
+        if (fence_first & 4) asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+        else asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+        if (v >= target) {
+          if (fence_first & 4) asm volatile("fence.acq_rel.gpu;" ::: "memory");
+          break;
+        }
         if (++spins > (1u << 22) || *failed) {
           *failed = 1;
           atomicCAS(err, 0, 30);
@@ -1009,7 +1015,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
       if (wt == 0 && p < 10) chain_trace(a, 10 + p);
       if (p + 1 < a.n_phases) {
         ++barriers;
-        live = chain_grid_barrier(a.barrier, (unsigned)grid * barriers, failed, a.error_flag, wt, verdict);
+        live = chain_grid_barrier(a.barrier, (unsigned)grid * barriers, failed, a.error_flag, wt, verdict, a.tune_fence);
         ok = ok && live;
       }
       if (wt == 0 && p < 10) chain_trace(a, p);

@@ -611,6 +611,7 @@ static ChainArgs chain_base_args(const pg_cache* c, int batch, int chunk = 0) {
   base.wte = m->wte; base.wpe = m->wpe; base.ids = c->d_ids + s0; base.pos_rw = c->d_pos + s0;
   base.argmax_out = c->d_argmax + s0;
   base.token_log = c->d_token_log + s0 * m->positions(); base.n_positions = m->positions(); base.best = c->d_chain_best;
+  { static const int f = getenv("PG_CHAIN_FENCE") ? atoi(getenv("PG_CHAIN_FENCE")) : 0; base.tune_fence = f; }
   return base;
 }
 
