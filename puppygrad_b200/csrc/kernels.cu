@@ -933,15 +933,17 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attention_kernel(DecodeAtt
     mypart[0] = (k1 > k0) ? mx : -INFINITY;
     mypart[1] = (k1 > k0) ? total : 0.f;
   }
-  __threadfence();
+  // The arrival is an acquire-release atomic at GPU scope: with the CTA barriers around it, it orders this
+  // CTA's partial before the arrival and, for the last arriver, every other split's partial before the merge
+  // (a separate fence by every thread cost more than the atomic).
   __syncthreads();
   if (tid == 0) {
-    unsigned old = atomicAdd(&a.counters[b * a.kv.n_head + h], 1u);
+    unsigned old;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(&a.counters[b * a.kv.n_head + h]) : "memory");
     is_last = (old == (unsigned)a.splits - 1);
   }
   __syncthreads();
   if (is_last) {
-    __threadfence();
     merge_splits(a.part + (size_t)(b * a.kv.n_head + h) * a.splits * (D + 2), a.splits, D, a.out, a.out_lo,
                  (size_t)b * c + h * D);
     if (tid == 0) a.counters[b * a.kv.n_head + h] = 0;
