@@ -61,6 +61,7 @@ constexpr size_t CH_SMEM = (size_t)CH_W_STAGES * CH_W_BYTES + (size_t)CH_X_STAGE
                            2 * AT_SCRATCH_FLOATS * 4 + 1024;
 static_assert(CH_SMEM <= 232448, "shared memory of one CTA");
 static_assert(CH_UB == 2, "one MMA issuer per k block of a unit");
+static_assert(sizeof(ChainPhase) % 8 == 0 && 384 + 2 * sizeof(ChainPhase) <= 1024, "two phase descriptors behind the barriers");
 constexpr size_t CH_PART_TILE = (size_t)CH_BN * TILE_M;  // floats of one partial tile: [token][row]
 
 // Share of one CTA in units: [g0, g1) of the phase's tiles * nkb units (row tile major); per = units per CTA.
@@ -82,9 +83,23 @@ __device__ __host__ inline ChRange chain_range(int n, int k, int cta, int grid) 
   return r;
 }
 
+// The same share from the fields chain_prepare_phases filled in: no division.
+__device__ __forceinline__ ChRange chain_range_ph(const ChainPhase& ph, int cta) {
+  ChRange r;
+  r.nkb = ph.r_nkb;
+  r.per = ph.r_per;
+  const int total = ((ph.n + TILE_M - 1) >> 7) * r.nkb;
+  r.g0 = min(cta * r.per, total);
+  r.g1 = min(r.g0 + r.per, total);
+  return r;
+}
+static_assert(TILE_M == 128, "row tiles by shift");
+
 __device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // All lanes wait; the verdict is made warp-uniform because aligned tcgen05 instructions follow.
+// All lanes wait (one polling lane with a shuffle behind it measured 2.5% slower here); the verdict is made
+// warp-uniform because aligned tcgen05 instructions follow.
 __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* failed, int* err, int code) {
   const bool ok = mbar_wait(bar, parity, failed, err, code);
   return __all_sync(0xffffffffu, ok);
@@ -236,7 +251,7 @@ __device__ __forceinline__ float warp_sum_f(float v) {
 // as a TF32 hi/lo pair. One CTA per token; wt = worker thread 0..255; n % 4 == 0, n <= 4096.
 __device__ __forceinline__ void chain_rows_phase(const ChainArgs& a, const ChainPhase& ph, int j, int wt, float* red, bool embed) {
   const int n = ph.n, n4 = n >> 2;
-  const ChRange r = chain_range(ph.n, ph.k, 0, (int)gridDim.x);
+  const ChRange r = chain_range_ph(ph, 0);
   const bool aligned = r.nkb % r.per == 0;
   const int cnt = r.nkb / r.per;
   float4 v[4];
@@ -257,7 +272,7 @@ __device__ __forceinline__ void chain_rows_phase(const ChainArgs& a, const Chain
       float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
       if (ph.bias) b = __ldg(reinterpret_cast<const float4*>(ph.bias) + u);
       const float4 acc = aligned ? sum_partials_aligned<16>(a.partials, u * 4, j, cnt)
-                                 : sum_partials<16>(a.partials, u * 4, j, r.nkb, fast_div(r.per), fast_div(r.nkb));
+                                 : sum_partials<16>(a.partials, u * 4, j, r.nkb, FastDiv{ph.r_magic_per, (unsigned)r.per}, FastDiv{ph.r_magic_nkb, (unsigned)r.nkb});
       v[i].x = xv.x + (b.x + acc.x);
       v[i].y = xv.y + (b.y + acc.y);
       v[i].z = xv.z + (b.z + acc.z);
@@ -312,12 +327,12 @@ __device__ __forceinline__ void chain_rows_phase(const ChainArgs& a, const Chain
 // ELEM phase: out[j, f] = act(bias[f] + sum of partials), all CTAs, four features per thread.
 __device__ __forceinline__ void chain_elem_phase(const ChainArgs& a, const ChainPhase& ph, int wt, unsigned long long* best_s) {
   const int n = ph.n, n4 = (n + 3) >> 2;
-  const ChRange r = chain_range(ph.n, ph.k, 0, (int)gridDim.x);
+  const ChRange r = chain_range_ph(ph, 0);
   const int total = a.m * n4;
   const bool vec = (n & 3) == 0;
   const bool aligned = r.nkb % r.per == 0;
   const int cnt = r.nkb / r.per;
-  const FastDiv by_per = fast_div(r.per), by_nkb = fast_div(r.nkb);
+  const FastDiv by_per = {ph.r_magic_per, (unsigned)r.per}, by_nkb = {ph.r_magic_nkb, (unsigned)r.nkb};
   // Every CTA takes one contiguous run of (token, four features) units, its threads interleaved over
   // it: a thread's units then lie in one row, rarely two, so the row arg-max is a running maximum
   // per thread that goes to shared memory only when the row changes.
@@ -441,7 +456,7 @@ struct AtCursor {  // where the warp is in issuing its block sequence; the same 
 
 __device__ __forceinline__ float4 attn_feature4(const ChainArgs& a, const ChainPhase& ph, const ChRange& r, int f, int j) {
   const float4 acc = (r.nkb % r.per == 0) ? sum_partials_aligned<8>(a.partials, f, j, r.nkb / r.per)
-                                          : sum_partials<8>(a.partials, f, j, r.nkb, fast_div(r.per), fast_div(r.nkb));
+                                          : sum_partials<8>(a.partials, f, j, r.nkb, FastDiv{ph.r_magic_per, (unsigned)r.per}, FastDiv{ph.r_magic_nkb, (unsigned)r.nkb});
   float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
   if (ph.bias) b = __ldg(reinterpret_cast<const float4*>(ph.bias + f));
   return make_float4(b.x + acc.x, b.y + acc.y, b.z + acc.z, b.w + acc.w);
@@ -543,7 +558,7 @@ __device__ __forceinline__ void chain_attn_phase(const ChainArgs& a, const Chain
   const int pt_shift = pt == 16 ? 4 : pt == 32 ? 5 : 6;
   const int psh = at_parts_shift(a.m * H, (int)gridDim.x), parts = 1 << psh;
   const int items = (a.m * H) << psh, step = (int)gridDim.x * 8, first = (int)blockIdx.x * 8 + w8;
-  const ChRange r = chain_range(ph.n, ph.k, 0, (int)gridDim.x);  // shares of the QKV GEMM whose partials are read
+  const ChRange r = chain_range_ph(ph, 0);  // shares of the QKV GEMM whose partials are read
   const float scale = 0.125f;  // 1 / sqrt(64)
   bool ok = live;
 
@@ -769,6 +784,9 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* verdict = reinterpret_cast<volatile int*>(tmem_slot + 2);
   float* red = reinterpret_cast<float*>(tmem_slot + 4);  // 8 floats
+  // the descriptor of the current and of the next phase, copied here ahead of the barrier before the phase: what a
+  // phase needs first is then a shared-memory read away instead of a chain of L2 reads
+  ChainPhase* ph_s = reinterpret_cast<ChainPhase*>(reinterpret_cast<uint8_t*>(w_full) + 384);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta = (int)blockIdx.x, grid = (int)gridDim.x;
@@ -811,7 +829,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
       bool ok = true;
       for (int p = 0; p < a.n_phases && ok; ++p) {
         if (phase_at(a, p).kind != CH_GEMM) continue;
-        const ChRange r = chain_range(phase_at(a, p).n, phase_at(a, p).k, cta, grid);
+        const ChRange r = chain_range_ph(phase_at(a, p), cta);
         const uint32_t b0 = phase_at(a, p).w_block0;
         for (int g = r.g0; g < r.g1 && ok; ++g, ++wi) {
           const uint32_t s = wi % CH_W_STAGES;
@@ -836,7 +854,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
       bool ok = true;
       for (int p = 0; p < a.n_phases && ok; ++p) {
         if (phase_at(a, p).kind != CH_GEMM) continue;
-        const ChRange r = chain_range(phase_at(a, p).n, phase_at(a, p).k, cta, grid);
+        const ChRange r = chain_range_ph(phase_at(a, p), cta);
         for (int g = r.g0; g < r.g1 && ok;) {
           const int tile = g / r.nkb;
           const int gend = min(r.g1, (tile + 1) * r.nkb);
@@ -873,7 +891,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
       bool ok = true;
       for (int p = 0; p < a.n_phases && ok; ++p) {
         if (phase_at(a, p).kind != CH_GEMM) continue;
-        const ChRange r = chain_range(phase_at(a, p).n, phase_at(a, p).k, cta, grid);
+        const ChRange r = chain_range_ph(phase_at(a, p), cta);
         const int act = phase_at(a, p).act;
         const CUtensorMap* mh = act == 0 ? &map_hi0 : act == 1 ? &map_hi1 : &map_hi2;
         const CUtensorMap* ml = act == 0 ? &map_lo0 : act == 1 ? &map_lo1 : &map_lo2;
@@ -906,7 +924,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
     bool ok = true;
     for (int p = 0; p < a.n_phases && ok; ++p) {
       if (phase_at(a, p).kind != CH_GEMM) continue;
-      const ChRange r = chain_range(phase_at(a, p).n, phase_at(a, p).k, cta, grid);
+      const ChRange r = chain_range_ph(phase_at(a, p), cta);
       for (int g = r.g0; g < r.g1 && ok; ++g, ++wi) {
         const uint32_t s = wi % CH_W_STAGES, xs = wi % CH_X_STAGES;
         ok = warp_wait(&w_full[s], (wi / CH_W_STAGES) & 1, failed, a.error_flag, 27);
@@ -965,15 +983,20 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
     bool at_prepared = false;
     at_cur.item = at_cur.blk = at_cur.nblk = at_cur.t = at_cur.b = at_cur.h = at_cur.pg0 = at_cur.pg1 = 0;
     at_cur.issued = 0;
+    constexpr int PH_WORDS = (int)(sizeof(ChainPhase) / 4);
+    const bool ph_staged = !(a.tune_fence & 4);
+    if (wt < PH_WORDS) reinterpret_cast<uint32_t*>(&ph_s[0])[wt] = reinterpret_cast<const uint32_t*>(&phase_at(a, 0))[wt];
+    workers_sync();
     for (int p = 0; p < a.n_phases; ++p) {
-      const int kind = phase_at(a, p).kind;
+      const ChainPhase& ph = ph_staged ? ph_s[p & 1] : phase_at(a, p);
+      const int kind = ph.kind;
       if (kind == CH_GEMM) {
         if (wt == 0) mbar_arrive(go);  // inputs of this phase exist (previous kernel, or the barrier just passed)
         if (live && p + 1 < a.n_phases && phase_at(a, p + 1).kind == CH_ATTN) {
           chain_attn_prepare(a, ww, lane, at_cur, at_consumed);
           at_prepared = true;
         }
-        const ChRange r = chain_range(phase_at(a, p).n, phase_at(a, p).k, cta, grid);
+        const ChRange r = chain_range_ph(ph, cta);
         int seg = 0;
         for (int g = r.g0; g < r.g1; ++seg) {
           const int tile = g / r.nkb;
@@ -1003,17 +1026,19 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
           g = gend;
         }
       } else if (kind == CH_ATTN) {
-        chain_attn_phase(a, phase_at(a, p), wt, act_ring, kv_full, at_scratch, at_consumed, at_cur, at_prepared, failed, live);
+        chain_attn_phase(a, ph, wt, act_ring, kv_full, at_scratch, at_consumed, at_cur, at_prepared, failed, live);
         at_prepared = false;
       } else if (kind == CH_ROWS || kind == CH_EMBED) {
-        if (live && cta < a.m) chain_rows_phase(a, phase_at(a, p), cta, wt, red, kind == CH_EMBED);
+        if (live && cta < a.m) chain_rows_phase(a, ph, cta, wt, red, kind == CH_EMBED);
       } else if (kind == CH_FINAL) {
         if (live && cta == 0 && wt < a.m) chain_final_phase(a, wt);
       } else {
-        if (live) chain_elem_phase(a, phase_at(a, p), wt, reinterpret_cast<unsigned long long*>(at_scratch));
+        if (live) chain_elem_phase(a, ph, wt, reinterpret_cast<unsigned long long*>(at_scratch));
       }
       if (wt == 0 && p < 10) chain_trace(a, 10 + p);
       if (p + 1 < a.n_phases) {
+        if (wt < PH_WORDS)  // the next phase's descriptor; the barrier's first CTA barrier orders it before its readers
+          reinterpret_cast<uint32_t*>(&ph_s[(p + 1) & 1])[wt] = reinterpret_cast<const uint32_t*>(&phase_at(a, p + 1))[wt];
         ++barriers;
         live = chain_grid_barrier(a.barrier, (unsigned)grid * barriers, failed, a.error_flag, wt, verdict, a.tune_fence);
         ok = ok && live;
@@ -1062,6 +1087,20 @@ int chain_grid(int num_sms) {
 size_t chain_partial_floats(int grid) { return (size_t)grid * CH_MAX_SEG * CH_PART_TILE; }
 
 unsigned long long chain_argmax_init() { return argmax_key(0xff800000u, 0u); }
+
+void chain_prepare_phases(ChainPhase* phases, int n_phases, int grid) {
+  for (int p = 0; p < n_phases; ++p) {
+    ChainPhase& ph = phases[p];
+    ph.r_nkb = ph.r_per = 0;
+    ph.r_magic_per = ph.r_magic_nkb = 0;
+    if (ph.kind == CH_FINAL || ph.k < BK * CH_UB || ph.n < 1) continue;
+    const ChRange r = chain_range(ph.n, ph.k, 0, grid);
+    ph.r_nkb = r.nkb;
+    ph.r_per = r.per;
+    ph.r_magic_per = r.per > 1 ? (unsigned)((0x100000000ull + (unsigned)r.per - 1) / (unsigned)r.per) : 0u;
+    ph.r_magic_nkb = r.nkb > 1 ? (unsigned)((0x100000000ull + (unsigned)r.nkb - 1) / (unsigned)r.nkb) : 0u;
+  }
+}
 
 bool chain_supported(const ChainArgs& a, int grid, const ChainPhase* host_phases) {
   const ChainPhase* phs = host_phases ? host_phases : a.ph;
@@ -1120,6 +1159,7 @@ cudaError_t launch_chain(const ChainArgs& a, int grid, cudaStream_t s) {
       return cudaErrorInvalidValue;
   }
   ChainArgs args = a;
+  if (!args.phases_dev) chain_prepare_phases(args.ph, args.n_phases, grid);
   void* params[8] = {&maps[0], &maps[1], &maps[2], &maps[3], &maps[4], &maps[5], &maps[6], &args};
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);

@@ -165,6 +165,11 @@ struct ChainPhase {
   float* out_lo;
   float* kv_pool;     // ATTN: this layer's page pool (n, k, bias: those of the QKV GEMM right before it)
   unsigned long long* best;  // ELEM: optional row arg-max accumulator [m] (packed value | index, see CH_FINAL)
+  // derived by chain_prepare_phases (share arithmetic of the phase's GEMM for the launch grid, so that no thread
+  // divides when a phase starts): 32 KB weight units per row tile, units per CTA, multiply-high reciprocals of both
+  int r_nkb, r_per;
+  unsigned r_magic_per, r_magic_nkb;
+  int reserved_[2];
 };
 constexpr int CHAIN_MAX_PHASES = 10;
 struct ChainArgs {
@@ -197,7 +202,8 @@ struct ChainArgs {
   float* partials;     // chain_partial_floats(grid) floats
   unsigned* barrier;   // one word, zero before the first launch (the kernel leaves it zero)
   int* error_flag;     // set non-zero when a bounded wait expired
-  int tune_fence;      // tuning: bit 0 = a separate __threadfence(), bit 1 = a proxy fence before the arrival at the grid barrier (0: the release alone)
+  int tune_fence;      // tuning: bit 0 = a separate __threadfence(), bit 1 = a proxy fence before the arrival at the grid barrier
+                       // (0: the release alone); bit 2 = phase descriptors read from global memory instead of the staged copy
   unsigned long long* phase_times;  // optional: n_phases + 1 %globaltimer stamps written by CTA 0 (start, then after each phase)
   unsigned long long* trace;  // optional tuning aid, 32 words per CTA: [p] when worker thread 0 left phase p, [10 + p]
                               // when its work of phase p was done, [20..25] wait / issue cycle counts, [31] start
@@ -210,6 +216,8 @@ unsigned long long chain_argmax_init();
 // True when every phase fits the kernel's limits for a grid of `grid` CTAs. `host_phases` is the
 // host copy of the phase list (a.ph when nullptr).
 bool chain_supported(const ChainArgs& a, int grid, const ChainPhase* host_phases = nullptr);
+// Fills the derived fields of a phase list for a grid of `grid` CTAs (before chain_supported / the upload).
+void chain_prepare_phases(ChainPhase* phases, int n_phases, int grid);
 cudaError_t launch_chain(const ChainArgs& a, int grid, cudaStream_t s);
 
 // Whole decode step for at most 8 sequences (head_dim 64) as one persistent cooperative kernel

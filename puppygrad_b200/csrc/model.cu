@@ -688,6 +688,7 @@ static int ensure_chain_program(pg_cache* c, int batch, int chunk = 0) {
     ph.push_back(p);
     bucket.push_back(B_OTHER);
   }
+  chain_prepare_phases(ph.data(), (int)ph.size(), c->chain_ctas);
   ChainArgs a = chain_base_args(c, batch, chunk);
   a.n_phases = (int)ph.size();
   pg_cache::ChainProgram prog;
