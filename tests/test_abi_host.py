@@ -298,3 +298,42 @@ def test_generation_stats_rates():
     assert s.total_tokens_per_second() == 5.0 and s.average_decode_token_time() == 0.1
     z = pg.GenerationStats()
     assert z.decode_tokens_per_second() == 0.0 and z.average_decode_token_time() is None
+
+
+def test_struct_layouts_of_the_binding_match_the_header(tmp_path):
+    """The ctypes structures (and with them the `#[repr(C)]` structs of the Rust binding, which list the
+    same fields in the same order and types) are pinned to the header: a C program compiled against
+    include/puppygrad_b200.h prints the size and every field offset of each struct."""
+    import shutil
+    import subprocess
+    if shutil.which("gcc") is None:
+        pytest.skip("no C compiler")
+    structs = {
+        "pg_gpt2_config": N.PgConfig, "pg_backend_config": N.PgBackendConfig,
+        "pg_generation_config": N.PgGenerationConfig, "pg_generation_stats": N.PgGenerationStats,
+        "pg_operation_profile": N.PgOperationProfile,
+    }
+    lines = ['#include <stddef.h>', '#include <stdio.h>', '#include "puppygrad_b200.h"', "int main(void) {"]
+    for cname, st in structs.items():
+        lines.append(f'  printf("{cname} size %zu\\n", sizeof({cname}));')
+        for field, _ in st._fields_:
+            lines.append(f'  printf("{cname} {field} %zu\\n", offsetof({cname}, {field}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    include = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include")
+    subprocess.run(["gcc", "-std=c11", "-I", include, str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split("\n")
+    seen = 0
+    for line in out:
+        if not line:
+            continue
+        cname, field, value = line.split()
+        st = structs[cname]
+        if field == "size":
+            assert C.sizeof(st) == int(value), cname
+        else:
+            assert getattr(st, field).offset == int(value), (cname, field)
+        seen += 1
+    assert seen == sum(len(st._fields_) + 1 for st in structs.values())
