@@ -380,6 +380,12 @@ int pg_sampler_select_next_token(pg_sampler* sampler, const float* logits, size_
 int pg_sampler_select_from_topk(pg_sampler* sampler, const float* topk_vals,
                                 const int32_t* topk_idx, size_t k,
                                 const pg_generation_config* cfg, uint64_t* out_token);
+/* The same for a batch in one call: sampler i draws from row i of the [batch, k] top-k arrays that
+ * pg_forward_one filled; out_tokens[i] receives its token. One RNG draw per sampler, as `batch` calls of
+ * pg_sampler_select_from_topk in order (a serving loop pays one foreign call per step instead of one per
+ * sequence). No reference counterpart: the reference samples one sequence at a time. */
+int pg_sampler_select_from_topk_batch(pg_sampler* const* samplers, const float* topk_vals, const int32_t* topk_idx,
+                                      size_t batch, size_t k, const pg_generation_config* cfg, uint64_t* out_tokens);
 
 #ifdef __cplusplus
 }

@@ -123,6 +123,8 @@ SIGNATURES = {
     "pg_sampler_select_next_token": (C.c_int, [_vp, _fp, C.c_size_t, _u64p, C.c_size_t,
                                                C.POINTER(PgGenerationConfig), _u64p]),
     "pg_sampler_select_from_topk": (C.c_int, [_vp, _fp, _ip, C.c_size_t, C.POINTER(PgGenerationConfig), _u64p]),
+    "pg_sampler_select_from_topk_batch": (C.c_int, [C.POINTER(C.c_void_p), _fp, _ip, C.c_size_t, C.c_size_t,
+                                                      C.POINTER(PgGenerationConfig), _u64p]),
 }
 
 

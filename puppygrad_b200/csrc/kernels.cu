@@ -1279,7 +1279,9 @@ __device__ __forceinline__ int total_key(float f) {
 
 // k rounds of block-wide arg-max over the row held in shared memory. Candidates are the finite
 // logits; order is descending total_cmp, ties by lower index (the stable sort of sample_logits,
-// src/models/generation.rs:305-318). Rows shorter than k are padded with -inf / -1.
+// src/models/generation.rs:305-318). Rows shorter than k are padded with -inf / -1. Every thread keeps the
+// best of its own keys (i = tid, tid + 1024, ...) in registers; a round reduces those 1024 candidates and only
+// the thread that owned the winner scans its keys again.
 __global__ void __launch_bounds__(1024) topk_rows_kernel(const float* logits, int m, int n, int k, float* vals,
                                                          int* idx) {
   extern __shared__ float4 dyn_smem4[];
@@ -1289,20 +1291,18 @@ __global__ void __launch_bounds__(1024) topk_rows_kernel(const float* logits, in
   __shared__ int win_i;
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * n;
+  int my_k = INT_MIN, my_i = INT_MAX;  // best of this thread's keys; scanning upwards keeps the lower index on ties
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     float v = row[i];
-    keys[i] = isfinite(v) ? total_key(v) : INT_MIN;
-  }
-  __syncthreads();
-  for (int round = 0; round < k; ++round) {
-    int bk = INT_MIN, bi = INT_MAX;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-      int kk = keys[i];
-      if (kk > bk) {
-        bk = kk;
-        bi = i;
-      }
+    const int kk = isfinite(v) ? total_key(v) : INT_MIN;
+    keys[i] = kk;
+    if (kk > my_k) {
+      my_k = kk;
+      my_i = i;
     }
+  }
+  for (int round = 0; round < k; ++round) {
+    int bk = my_k, bi = my_i;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       int ok = __shfl_xor_sync(FULL, bk, o);
@@ -1317,25 +1317,45 @@ __global__ void __launch_bounds__(1024) topk_rows_kernel(const float* logits, in
       si[threadIdx.x >> 5] = bi;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
-        if (sk[w] > bk || (sk[w] == bk && si[w] < bi)) {
-          bk = sk[w];
-          bi = si[w];
+    if (threadIdx.x < 32) {
+      bk = threadIdx.x < (blockDim.x >> 5) ? sk[threadIdx.x] : INT_MIN;
+      bi = threadIdx.x < (blockDim.x >> 5) ? si[threadIdx.x] : INT_MAX;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        int ok = __shfl_xor_sync(FULL, bk, o);
+        int oi = __shfl_xor_sync(FULL, bi, o);
+        if (ok > bk || (ok == bk && oi < bi)) {
+          bk = ok;
+          bi = oi;
         }
-      if (bk == INT_MIN) {
-        vals[(size_t)r * k + round] = -INFINITY;
-        idx[(size_t)r * k + round] = -1;
-        win_i = -1;
-      } else {
-        vals[(size_t)r * k + round] = row[bi];
-        idx[(size_t)r * k + round] = bi;
-        win_i = bi;
+      }
+      if (threadIdx.x == 0) {
+        if (bk == INT_MIN) {
+          vals[(size_t)r * k + round] = -INFINITY;
+          idx[(size_t)r * k + round] = -1;
+          win_i = -1;
+        } else {
+          vals[(size_t)r * k + round] = row[bi];
+          idx[(size_t)r * k + round] = bi;
+          win_i = bi;
+        }
       }
     }
     __syncthreads();
-    if (threadIdx.x == 0 && win_i >= 0) keys[win_i] = INT_MIN;
-    __syncthreads();
+    const int w = win_i;
+    if (w >= 0 && (w % (int)blockDim.x) == (int)threadIdx.x) {  // the owner removes it and looks for its next best
+      keys[w] = INT_MIN;
+      my_k = INT_MIN;
+      my_i = INT_MAX;
+      for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int kk = keys[i];
+        if (kk > my_k) {
+          my_k = kk;
+          my_i = i;
+        }
+      }
+    }
+    // sk / si / win_i are rewritten only after the next round's first barrier has been passed by everyone who read them
   }
 }
 

@@ -188,4 +188,14 @@ int pg_sampler_select_from_topk(pg_sampler* sampler, const float* topk_vals, con
   return sampler->select_from_sorted(topk_vals, topk_idx, k, *cfg, out_token);
 }
 
+int pg_sampler_select_from_topk_batch(pg_sampler* const* samplers, const float* topk_vals, const int32_t* topk_idx,
+                                      size_t batch, size_t k, const pg_generation_config* cfg, uint64_t* out_tokens) {
+  if (!samplers || !topk_vals || !topk_idx || !cfg || !out_tokens) return pg::set_error(PG_INVALID_INPUT, "null argument");
+  for (size_t i = 0; i < batch; ++i) {
+    if (!samplers[i]) return pg::set_error(PG_INVALID_INPUT, "null sampler at index " + std::to_string(i));
+    if (int r = samplers[i]->select_from_sorted(topk_vals + i * k, topk_idx + i * k, k, *cfg, out_tokens + i)) return r;
+  }
+  return PG_OK;
+}
+
 }  // extern "C"

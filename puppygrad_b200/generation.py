@@ -117,6 +117,22 @@ class LogitsSampler:
                                                 C.byref(out)))
         return int(out.value)
 
+    @staticmethod
+    def select_from_topk_batch(samplers, vals, idx, config: TextGenerationConfig) -> np.ndarray:
+        """One draw per sampler from row i of the [batch, k] top-k arrays, in one native call."""
+        v = np.ascontiguousarray(vals, np.float32)
+        i = np.ascontiguousarray(idx, np.int32)
+        n, k = v.shape
+        if len(samplers) != n:
+            raise ValueError("one sampler per row")
+        handles = (C.c_void_p * n)(*[s_._h for s_ in samplers])
+        g = config.to_native()
+        out = np.empty(n, np.uint64)
+        check(N.lib.pg_sampler_select_from_topk_batch(handles, v.ctypes.data_as(C.POINTER(C.c_float)),
+                                                      i.ctypes.data_as(C.POINTER(C.c_int32)), n, k, C.byref(g),
+                                                      out.ctypes.data_as(C.POINTER(C.c_uint64))))
+        return out
+
 
 __all__ = ["TextGenerationConfig", "GenerationStats", "LogitsSampler", "argmax_logits", "Gpt2Error",
            "gpt2_generation_config", "GPT2_EOS_TOKEN_ID"]

@@ -372,6 +372,8 @@ class Gpt2Model:
                 tv[i], ti[i] = logits[i, order], order
         for step in range(config.max_new_tokens):
             nxt = np.zeros(n, np.int32)
+            # all draws of the step in one native call when every sequence is still running
+            drawn = LogitsSampler.select_from_topk_batch(samplers, tv, ti, config) if use_topk and not any(done) else None
             for i in range(n):
                 if done[i]:
                     nxt[i] = history[i][-1]
@@ -383,7 +385,7 @@ class Gpt2Model:
                 if use_argmax:
                     tok = int(am[i])
                 elif use_topk:
-                    tok = samplers[i].select_from_topk(tv[i], ti[i], config)
+                    tok = int(drawn[i]) if drawn is not None else samplers[i].select_from_topk(tv[i], ti[i], config)
                 else:
                     tok = samplers[i].select_next_token(logits[i], history[i], config)
                 if config.eos_token_id is not None and tok == config.eos_token_id:

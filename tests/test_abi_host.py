@@ -337,3 +337,22 @@ def test_struct_layouts_of_the_binding_match_the_header(tmp_path):
             assert getattr(st, field).offset == int(value), (cname, field)
         seen += 1
     assert seen == sum(len(st._fields_) + 1 for st in structs.values())
+
+
+def test_batch_draw_from_topk_rows_equals_one_call_per_sampler():
+    """pg_sampler_select_from_topk_batch: sampler i draws from row i exactly as a call of its own would
+    (sample_logits over a pre-sorted top-k list, src/models/generation.rs:300-362), one RNG draw each."""
+    from puppygrad_b200.generation import LogitsSampler
+    rng = np.random.default_rng(3)
+    n, k = 7, 40
+    vals = -np.sort(-rng.standard_normal((n, k)).astype(np.float32), axis=1)
+    idx = np.stack([rng.permutation(5000)[:k] for _ in range(n)]).astype(np.int32)
+    conf = pg.TextGenerationConfig(4, temperature=0.8, top_k=40, seed=11)
+    a = [LogitsSampler(100 + i) for i in range(n)]
+    b = [LogitsSampler(100 + i) for i in range(n)]
+    for _ in range(5):
+        want = [a[i].select_from_topk(vals[i], idx[i], conf) for i in range(n)]
+        got = LogitsSampler.select_from_topk_batch(b, vals, idx, conf)
+        assert [int(t) for t in got] == want
+    with pytest.raises(ValueError):
+        LogitsSampler.select_from_topk_batch(b[:3], vals, idx, conf)
