@@ -161,6 +161,17 @@ __device__ __forceinline__ const ChainPhase& phase_at(const ChainArgs& a, int p)
   return a.phases_dev ? a.phases_dev[p] : a.ph[p];
 }
 
+// Tiled load with an L2 eviction-priority hint: the weight stream is read once per step and should not push
+// the partial tiles, activations and keys / values of the running step out of L2.
+__device__ __forceinline__ void tma_load_2d_hint(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
+
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                    smem_u32(smem_dst)),
@@ -825,6 +836,9 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
     // ---------------------------------------------------------------- weight producer
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      uint64_t evict_first;
+      asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(evict_first));
+      const bool hint = (a.tune_fence & 8) == 0;
       uint32_t wi = 0;
       bool ok = true;
       for (int p = 0; p < a.n_phases && ok; ++p) {
@@ -837,7 +851,10 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
           if (!ok) break;
           // one unit = CH_UB consecutive 16 KB blocks of the tiled arena = one box of CH_UB * 128 rows
           mbar_expect_tx(&w_full[s], CH_W_BYTES);
-          tma_load_2d(w_ring + (size_t)s * CH_W_BYTES, &map_w, 0, (int)((b0 + (uint32_t)g * CH_UB) * TILE_M), &w_full[s]);
+          if (hint)
+            tma_load_2d_hint(w_ring + (size_t)s * CH_W_BYTES, &map_w, 0, (int)((b0 + (uint32_t)g * CH_UB) * TILE_M), &w_full[s], evict_first);
+          else
+            tma_load_2d(w_ring + (size_t)s * CH_W_BYTES, &map_w, 0, (int)((b0 + (uint32_t)g * CH_UB) * TILE_M), &w_full[s]);
         }
       }
     }
