@@ -108,7 +108,11 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volati
 // Grid barrier of the worker warps: arrival count only grows during a launch, barrier b (1-based)
 // is passed when it reaches grid * b. Returns the same verdict to every worker thread.
 __device__ __forceinline__ bool chain_grid_barrier(unsigned* counter, unsigned target, volatile int* failed, int* err,
-                                                   int wt, volatile int* verdict, int fence_first) {
+                                                   int wt, volatile int* verdict, int fence_first, uint64_t* go,
+                                                   const int* next_kind) {
+  // thread 0 alone needs to know whether a GEMM follows; the load overlaps the CTA barrier
+  uint64_t* go_next = nullptr;
+  if (wt == 0 && next_kind && !(fence_first & 16) && *next_kind == CH_GEMM) go_next = go;
   workers_sync();
   if (wt == 0) {
     if (!*failed) {
@@ -125,7 +129,11 @@ __device__ __forceinline__ bool chain_grid_barrier(unsigned* counter, unsigned t
         unsigned v;
         // (polling with relaxed loads and one acquire fence at the end measured 4% slower)
         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
-        if (v >= target) break;
+        if (v >= target) {
+          // the next phase is a GEMM: its activation producer may start before the other workers have been told
+          if (go_next) mbar_arrive(go_next);
+          break;
+        }
         if (++spins > (1u << 22) || *failed) {
           *failed = 1;
           atomicCAS(err, 0, 30);
@@ -1008,7 +1016,9 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
       const ChainPhase& ph = ph_staged ? ph_s[p & 1] : phase_at(a, p);
       const int kind = ph.kind;
       if (kind == CH_GEMM) {
-        if (wt == 0) mbar_arrive(go);  // inputs of this phase exist (previous kernel, or the barrier just passed)
+        // inputs of this phase exist: previous kernel (first phase), or the barrier just passed, whose polling
+        // thread has told the activation producer already
+        if (wt == 0 && (p == 0 || (a.tune_fence & 16))) mbar_arrive(go);
         if (live && p + 1 < a.n_phases && phase_at(a, p + 1).kind == CH_ATTN) {
           chain_attn_prepare(a, ww, lane, at_cur, at_consumed);
           at_prepared = true;
@@ -1057,7 +1067,8 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
         if (wt < PH_WORDS)  // the next phase's descriptor; the barrier's first CTA barrier orders it before its readers
           reinterpret_cast<uint32_t*>(&ph_s[(p + 1) & 1])[wt] = reinterpret_cast<const uint32_t*>(&phase_at(a, p + 1))[wt];
         ++barriers;
-        live = chain_grid_barrier(a.barrier, (unsigned)grid * barriers, failed, a.error_flag, wt, verdict, a.tune_fence);
+        live = chain_grid_barrier(a.barrier, (unsigned)grid * barriers, failed, a.error_flag, wt, verdict, a.tune_fence, go,
+                                  &phase_at(a, p + 1).kind);
         ok = ok && live;
       }
       if (wt == 0 && p < 10) chain_trace(a, p);

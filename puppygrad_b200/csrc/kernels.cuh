@@ -204,7 +204,8 @@ struct ChainArgs {
   int* error_flag;     // set non-zero when a bounded wait expired
   int tune_fence;      // tuning: bit 0 = a separate __threadfence(), bit 1 = a proxy fence before the arrival at the grid barrier
                        // (0: the release alone); bit 2 = phase descriptors read from global memory instead of the staged copy;
-                       // bit 3 = weight loads without the L2 evict-first hint
+                       // bit 3 = weight loads without the L2 evict-first hint; bit 4 = the activation producer of a GEMM phase is
+                       // told by the first worker thread after the barrier instead of by the polling thread inside it
   unsigned long long* phase_times;  // optional: n_phases + 1 %globaltimer stamps written by CTA 0 (start, then after each phase)
   unsigned long long* trace;  // optional tuning aid, 32 words per CTA: [p] when worker thread 0 left phase p, [10 + p]
                               // when its work of phase p was done, [20..25] wait / issue cycle counts, [31] start
