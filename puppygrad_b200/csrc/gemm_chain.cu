@@ -11,14 +11,13 @@
 //               activations, so this warp never waits for a phase to begin: while the other warps
 //               reduce, normalise, attend or wait at the grid barrier it already fetches the next
 //               GEMM's units.
-//   warps 4-7   splitters: lo part (w - hi(w), hi = the upper 19 bits the tensor core reads) of the FP32 weight
-//               tile into tensor memory (tcgen05.st); they run ahead as far as tensor memory stages are free.
+//   warps 4-7   splitters: FP32 weight tile -> TF32 hi/lo pair in tensor memory (tcgen05.st); they
+//               run ahead as far as tensor memory stages are free.
 //   warp 2      activation producer: after the phase's inputs exist (grid barrier), TMA loads of
 //               the 64-token x 32 hi and lo tiles.
 //   warps 1, 3  MMA issuers, one per k block of a unit, an accumulator in tensor memory each: per
-//               8-wide k slice one tcgen05.mma of N = 128 (w_hi . [x_hi | x_lo], the weight tile read from the
-//               ring as it came from memory) and one of N = 64 (w_lo . x_hi, w_lo from tensor memory). A ring
-//               stage is free again when both issuers' MMAs on it have completed (tcgen05.commit).
+//               8-wide k slice one tcgen05.mma of N = 128 (w_hi . [x_hi | x_lo]) and one of N = 64
+//               (w_lo . x_hi).
 //   warps 8-15  workers: drain the accumulators into per-CTA partial tiles (global memory, L2
 //               resident), take part in the grid barrier, run the reduce phases, the attention
 //               phases (one warp per sequence-head pair), the embedding and the end-of-step phase.
@@ -814,7 +813,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
   if (threadIdx.x == 0) {
     for (int s = 0; s < CH_W_STAGES; ++s) {
       mbar_init(&w_full[s], 1);
-      mbar_init(&w_empty[s], 2);  // both MMA issuers commit: the MMAs read the raw weight tile from the ring
+      mbar_init(&w_empty[s], 4);
     }
     for (int s = 0; s < CH_X_STAGES; ++s) {
       mbar_init(&ready[s], 5);  // four splitter warps + the activation producer's expect_tx arrival
@@ -888,23 +887,19 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
           if (!ok) break;
           tc_fence_after();
           for (int gb = g; gb < gend && ok; ++gb, ++wi) {
-            const uint32_t xs = wi % CH_X_STAGES, ws = wi % CH_W_STAGES;
+            const uint32_t xs = wi % CH_X_STAGES;
             ok = mbar_wait(&ready[xs], (wi / CH_X_STAGES) & 1, failed, a.error_flag, 23);
-            if (ok) ok = mbar_wait(&w_full[ws], (wi / CH_W_STAGES) & 1, failed, a.error_flag, 24);  // long complete: the splitters waited for it
             if (!ok) break;
             tc_fence_after();
-            // block b of the unit: x_hi rows then x_lo rows in shared memory; the weight tile as it came from
-            // memory in the ring (the tensor core reads its upper 19 bits: w_hi), w_lo columns in tensor memory
+            // block b of the unit: x_hi rows then x_lo rows in shared memory, w_hi | w_lo columns in tensor memory
             const uint64_t dx = umma_desc_sw128(act_ring + (size_t)xs * CH_ACT_BYTES + (size_t)b * (CH_ACT_BYTES / CH_UB));
-            const uint64_t dw = umma_desc_sw128(w_ring + (size_t)ws * CH_W_BYTES + (size_t)b * (TILE_M * BK * 4));
-            const uint32_t alo = tmem_base + CH_A_COL0 + xs * (32 * CH_UB) + b * 32;
+            const uint32_t ahi = tmem_base + CH_A_COL0 + xs * (64 * CH_UB) + b * 64, alo = ahi + 32;
 #pragma unroll
             for (int k = 0; k < BK / 8; ++k) {
-              umma_tf32_ss(dcol, dw + (uint64_t)(k * 2), dx + (uint64_t)(k * 2), idesc2, (gb != g || k != 0) ? 1u : 0u);
+              umma_tf32_ts(dcol, ahi + k * 8, dx + (uint64_t)(k * 2), idesc2, (gb != g || k != 0) ? 1u : 0u);
               umma_tf32_ts(dcol, alo + k * 8, dx + (uint64_t)(k * 2), idesc1, 1u);
             }
             umma_commit(&done[xs]);
-            umma_commit(&w_empty[ws]);
           }
           if (ok) umma_commit(d_full);
           ++si;
@@ -967,16 +962,24 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
         for (int b = 0; b < CH_UB; ++b) {
           const float4* rowp = reinterpret_cast<const float4*>(w_ring + (size_t)s * CH_W_BYTES + (size_t)b * (TILE_M * BK * 4) +
                                                                (size_t)row * 128);
-          uint32_t lo[32];
+          uint32_t hi[32], lo[32];
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const float4 v = rowp[j ^ (row & 7)];  // undo the 128-byte swizzle: conflict-free per quarter warp
             const float f[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) lo[j * 4 + e] = __float_as_uint(f[e] - tf32_hi(f[e]));
+            for (int e = 0; e < 4; ++e) {
+              const float h = tf32_hi(f[e]);
+              hi[j * 4 + e] = __float_as_uint(h);
+              lo[j * 4 + e] = __float_as_uint(f[e] - h);
+            }
           }
-          tmem_st32(tmem_base + CH_A_COL0 + xs * (32 * CH_UB) + b * 32 + lane_addr, lo);
+          const uint32_t col = tmem_base + CH_A_COL0 + xs * (64 * CH_UB) + b * 64 + lane_addr;
+          tmem_st32(col, hi);
+          tmem_st32(col + 32, lo);
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&w_empty[s]);  // the unit is in registers / tensor memory: the stage may be refilled
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
