@@ -189,16 +189,11 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* src, uint3
 
 // Sum of the partial tiles covering features [f, f + 4) of token j, in k order. Loads go out in
 // batches of NB before the first add, so that their L2 latencies overlap.
-// x / d for the small non-negative operands of the share arithmetic (x * d < 2^32): one multiply-high.
+// x / d for the small non-negative operands of the share arithmetic (x * d < 2^32): one multiply-high with the
+// reciprocal chain_prepare_phases computed on the host (ceil(2^32 / d); d = 1 divides by nothing).
 struct FastDiv {
   unsigned magic, d;
 };
-__device__ __forceinline__ FastDiv fast_div(int d) {
-  FastDiv f;
-  f.d = (unsigned)d;
-  f.magic = d > 1 ? (unsigned)((0x100000000ull + (unsigned)d - 1) / (unsigned)d) : 0u;
-  return f;
-}
 __device__ __forceinline__ int div_by(int x, FastDiv f) { return f.d > 1 ? (int)__umulhi((unsigned)x, f.magic) : x; }
 
 template <int NB>
