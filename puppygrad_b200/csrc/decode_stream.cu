@@ -46,7 +46,7 @@ constexpr int ST_RELEASER = ST_CT - 1;     // the computing thread that hands ri
 constexpr int ST_STAGE = 16384;            // bytes of one ring slot
 constexpr int ST_STAGE_SHIFT = 14;
 constexpr int ST_MAX_STAGES = 13;
-constexpr int ST_BLOCK_ROWS = 16;          // most weight rows handed over at once
+constexpr int ST_BLOCK_ROWS = 32;          // most weight rows handed over at once (16 unless a block may span five or six ring slots)
 constexpr int ST_MAX_SPLITS = 8;
 constexpr int ST_PART_WORDS = 66;          // attention partial: max, sum, 64 values
 constexpr int ST_KEEP = 16;                // residual values a CTA keeps per sequence: its rows of the next residual phase
@@ -262,7 +262,8 @@ __device__ __noinline__ float4 ll_poll4(const u64* base, int stride, int n, unsi
 // ------------------------------------------------------------------ the weight stream
 __device__ __host__ inline int rows_per_block(int k, int elem_bytes, int block_stages) {
   int rb = (block_stages * ST_STAGE) / (k * elem_bytes);
-  if (rb > ST_BLOCK_ROWS) rb = ST_BLOCK_ROWS;
+  const int cap = block_stages >= 5 ? ST_BLOCK_ROWS : ST_BLOCK_ROWS / 2;
+  if (rb > cap) rb = cap;
   if (rb >= 4) rb &= ~3;
   return rb;
 }
@@ -365,8 +366,10 @@ struct Elem<WT_I8> {
 
 // log2 of the k parts a block of `rows` rows is cut into: (row groups of four) x parts <= 15 warps.
 __device__ __forceinline__ int block_lkp(int rows, int ls) {
+  // row groups of four x parts of k = items, one per warp, at most 15: 1 group -> 8 parts, 2 or 3 -> 4,
+  // 4..7 -> 2, 8 -> 1
   const int rg_n = (rows + 3) >> 2;
-  const int l = rg_n == 1 ? 3 : rg_n == 4 ? 1 : 2;
+  const int l = rg_n == 1 ? 3 : rg_n <= 3 ? 2 : rg_n <= 7 ? 1 : 0;
   return min(l, ls);
 }
 
@@ -1038,7 +1041,12 @@ static bool stream_geometry(int m, int c, int f, int weight_type, int* ns_out, i
   if (fixed + 3 * (size_t)ST_STAGE > ST_DYN_SMEM_MAX) return false;
   int ns = (int)((ST_DYN_SMEM_MAX - fixed) / ST_STAGE);
   ns = std::min(ns, ST_MAX_STAGES);
-  const int bs = std::max(1, std::min(4, ns / 2));
+  // Rows of a CTA's share are handed over in blocks of at most four ring slots and 16 rows; with narrow rows
+  // (at most 3 KB: GPT-2 small in FP32, wider models with packed weights) and one or two sequences, blocks of up to
+  // six slots (half the ring) and 32 rows, which take the CTA's rows of every layer linear of GPT-2 small in one round and halve the
+  // rounds of the lm_head (one sequence: 283 against 293 us per token; GPT-2 medium and four sequences lose 1%)
+  const bool wide_blocks = mt_of(m) <= 2 && (size_t)c * decode_stream_elem_bytes(weight_type) <= 3072 && ns >= 10;
+  const int bs = std::max(1, std::min(wide_blocks ? 6 : 4, ns / 2));
   const int eb = decode_stream_elem_bytes(weight_type);
   if (rows_per_block(c, eb, bs) < 1 || rows_per_block(f, eb, bs) < 1) return false;
   *ns_out = ns;
