@@ -68,13 +68,14 @@ constexpr size_t CH_PART_TILE = (size_t)CH_BN * TILE_M;  // floats of one partia
 struct ChRange {
   int g0, g1, nkb, per;
 };
-__device__ __host__ inline ChRange chain_range(int n, int k, int cta, int grid) {
+__device__ __host__ inline ChRange chain_range(int n, int k, int cta, int grid, bool whole_tiles = false) {
   const int tiles = (n + TILE_M - 1) / TILE_M, nkb = k / (BK * CH_UB);  // units per row tile
   const int total = tiles * nkb;
   int per = (total + grid - 1) / grid;
   // one block more per CTA when that makes shares line up with row tiles: fewer partial tiles to
   // write and to add, at the price of a few idle SMs
   if (nkb % per != 0 && nkb % (per + 1) == 0) per += 1;
+  if (whole_tiles) per = nkb * ((tiles + grid - 1) / grid);
   ChRange r;
   r.nkb = nkb;
   r.per = per;
@@ -97,7 +98,6 @@ static_assert(TILE_M == 128, "row tiles by shift");
 
 __device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
-// All lanes wait; the verdict is made warp-uniform because aligned tcgen05 instructions follow.
 // All lanes wait (one polling lane with a shuffle behind it measured 2.5% slower here); the verdict is made
 // warp-uniform because aligned tcgen05 instructions follow.
 __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* failed, int* err, int code) {
@@ -1003,6 +1003,19 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
     bool at_prepared = false;
     at_cur.item = at_cur.blk = at_cur.nblk = at_cur.t = at_cur.b = at_cur.h = at_cur.pg0 = at_cur.pg1 = 0;
     at_cur.issued = 0;
+    // Sums of token columns [c0, c0 + 16) of this thread's row: two accumulators (k block 0 and 1 of every unit),
+    // each with hi*hi + lo*hi and hi*lo columns; the four loads are in flight together
+    auto ld_acc = [&](int c0, float* y) {
+      uint32_t v[16], v2[16], u[16], u2[16];
+      tmem_ld16_issue(tmem_base + lane_addr + (uint32_t)c0, v);
+      tmem_ld16_issue(tmem_base + lane_addr + (uint32_t)(CH_BN + c0), v2);
+      tmem_ld16_issue(tmem_base + CH_D_COLS + lane_addr + (uint32_t)c0, u);
+      tmem_ld16_issue(tmem_base + CH_D_COLS + lane_addr + (uint32_t)(CH_BN + c0), u2);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        y[j] = (__uint_as_float(v[j]) + __uint_as_float(v2[j])) + (__uint_as_float(u[j]) + __uint_as_float(u2[j]));
+    };
     constexpr int PH_WORDS = (int)(sizeof(ChainPhase) / 4);
     const bool ph_staged = !(a.tune_fence & 4);
     if (wt < PH_WORDS) reinterpret_cast<uint32_t*>(&ph_s[0])[wt] = reinterpret_cast<const uint32_t*>(&phase_at(a, 0))[wt];
@@ -1019,26 +1032,57 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
           at_prepared = true;
         }
         const ChRange r = chain_range_ph(ph, cta);
+        unsigned long long* best_s = reinterpret_cast<unsigned long long*>(at_scratch);
+        if (ph.whole_tiles && ph.best) {
+          if (wt < CH_BN) best_s[wt] = 0ull;
+          workers_sync();
+        }
         int seg = 0;
         for (int g = r.g0; g < r.g1; ++seg) {
           const int tile = g / r.nkb;
           const int gend = min(r.g1, (tile + 1) * r.nkb);
           if (ok) ok = warp_wait(d_full, si & 1, failed, a.error_flag, 29);
-          if (ok) {
+          if (ok && ph.whole_tiles) {
+            // finished sums (the share is whole row tiles): store them and fold them into the row arg-max;
+            // the accumulator is handed back as soon as it is in registers, so the next tile's MMAs overlap the rest
+            tc_fence_after();
+            const int feat = tile * TILE_M + row;
+            const bool valid = feat < ph.n;
+            float y[32];
+#pragma unroll
+            for (int cc = 0; cc < 32; cc += 16) {
+              const int c0 = half * 32 + cc;
+              ld_acc(c0, &y[cc]);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(d_empty);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int tok = half * 32 + j;
+              if (tok >= a.m) continue;  // the same for the whole warp
+              if (ph.out && valid) ph.out[(size_t)tok * ph.n + feat] = y[j];
+              if (!ph.best) continue;
+              // NaN never wins; -0 counts as +0; 0 = no candidate (the high word of a key is never 0 for a number)
+              const unsigned bits = y[j] == 0.f ? 0u : __float_as_uint(y[j]);
+              const unsigned ord = (valid && y[j] == y[j]) ? ((bits & 0x80000000u) ? ~bits : (bits | 0x80000000u)) : 0u;
+              const unsigned mx = __reduce_max_sync(0xffffffffu, ord);
+              const unsigned who = __ballot_sync(0xffffffffu, ord == mx);
+              if (mx != 0u && lane == 0)  // lowest lane = lowest feature among equals
+                atomicMax(best_s + tok, ((unsigned long long)mx << 32) |
+                                            (unsigned long long)(0xffffffffu - (unsigned)(tile * TILE_M + q * 32 + __ffs((int)who) - 1)));
+            }
+          } else if (ok) {
             tc_fence_after();
             float* dst = a.partials + ((size_t)(cta * CH_MAX_SEG + seg) * CH_BN) * TILE_M + row;
 #pragma unroll
             for (int cc = 0; cc < 32; cc += 16) {
               const int c0 = half * 32 + cc;
-              // two accumulators (k block 0 and 1 of every unit), each with hi*hi + lo*hi and hi*lo columns
-              float v[16], v2[16], u[16], u2[16];
-              tmem_ld16(tmem_base + lane_addr + (uint32_t)c0, v);
-              tmem_ld16(tmem_base + lane_addr + (uint32_t)(CH_BN + c0), v2);
-              tmem_ld16(tmem_base + CH_D_COLS + lane_addr + (uint32_t)c0, u);
-              tmem_ld16(tmem_base + CH_D_COLS + lane_addr + (uint32_t)(CH_BN + c0), u2);
+              float y[16];
+              ld_acc(c0, y);
 #pragma unroll
               for (int j = 0; j < 16; ++j)
-                if (c0 + j < a.m) dst[(size_t)(c0 + j) * TILE_M] = (v[j] + v2[j]) + (u[j] + u2[j]);
+                if (c0 + j < a.m) dst[(size_t)(c0 + j) * TILE_M] = y[j];
             }
             tc_fence_before();
             __syncwarp();
@@ -1046,6 +1090,10 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
           }
           ++si;
           g = gend;
+        }
+        if (ph.whole_tiles && ph.best) {
+          workers_sync();
+          if (live && wt < a.m && best_s[wt]) atomicMax(ph.best + wt, best_s[wt]);
         }
       } else if (kind == CH_ATTN) {
         chain_attn_phase(a, ph, wt, act_ring, kv_full, at_scratch, at_consumed, at_cur, at_prepared, failed, live);
@@ -1117,7 +1165,7 @@ void chain_prepare_phases(ChainPhase* phases, int n_phases, int grid) {
     ph.r_nkb = ph.r_per = 0;
     ph.r_magic_per = ph.r_magic_nkb = 0;
     if (ph.kind == CH_FINAL || ph.k < BK * CH_UB || ph.n < 1) continue;
-    const ChRange r = chain_range(ph.n, ph.k, 0, grid);
+    const ChRange r = chain_range(ph.n, ph.k, 0, grid, ph.kind == CH_GEMM && ph.whole_tiles);
     ph.r_nkb = r.nkb;
     ph.r_per = r.per;
     ph.r_magic_per = r.per > 1 ? (unsigned)((0x100000000ull + (unsigned)r.per - 1) / (unsigned)r.per) : 0u;
@@ -1140,7 +1188,8 @@ bool chain_supported(const ChainArgs& a, int grid, const ChainPhase* host_phases
     }
     if (ph.kind == CH_FINAL) {
       if (!a.best || !a.argmax_out || !a.ids || !a.pos_rw || !a.token_log || a.n_positions < 1) return false;
-      if (p == 0 || phs[p - 1].kind != CH_ELEM || phs[p - 1].best != a.best) return false;
+      if (p == 0 || phs[p - 1].best != a.best) return false;
+      if (phs[p - 1].kind != CH_ELEM && !(phs[p - 1].kind == CH_GEMM && phs[p - 1].whole_tiles)) return false;
       continue;
     }
     if (ph.k < BK * CH_UB || ph.k % (BK * CH_UB) != 0 || ph.n < 1) return false;
@@ -1149,8 +1198,11 @@ bool chain_supported(const ChainArgs& a, int grid, const ChainPhase* host_phases
       if (!a.wte || !a.wpe || !a.ids || !a.pos) return false;
       continue;
     }
-    const ChRange r = chain_range(ph.n, ph.k, 0, grid);
-    if ((r.per + r.nkb - 2) / r.nkb + 1 > CH_MAX_SEG) return false;
+    const bool whole = ph.kind == CH_GEMM && ph.whole_tiles;
+    const ChRange r = chain_range(ph.n, ph.k, 0, grid, whole);
+    if (!whole && (r.per + r.nkb - 2) / r.nkb + 1 > CH_MAX_SEG) return false;  // partial tiles of one CTA
+    if (whole && (ph.bias || ph.gelu || ph.out_hi || (p + 1 < a.n_phases && phs[p + 1].kind != CH_FINAL))) return false;
+    if (!whole && ph.kind == CH_GEMM && (ph.best || ph.out)) return false;
     if (ph.kind == CH_GEMM) {
       if (ph.act < 0 || ph.act > 2 || !a.act_hi[ph.act] || !a.act_lo[ph.act] || a.act_k[ph.act] != ph.k) return false;
       const unsigned long long rows = ((unsigned long long)ph.w_block0 + (unsigned long long)((ph.n + TILE_M - 1) / TILE_M) * r.nkb * CH_UB) * TILE_M;

@@ -164,12 +164,15 @@ struct ChainPhase {
   float* out_hi;      // ROWS: LayerNorm result, ELEM / ATTN: result, as a TF32 hi/lo pair (or nullptr)
   float* out_lo;
   float* kv_pool;     // ATTN: this layer's page pool (n, k, bias: those of the QKV GEMM right before it)
-  unsigned long long* best;  // ELEM: optional row arg-max accumulator [m] (packed value | index, see CH_FINAL)
+  unsigned long long* best;  // ELEM, whole-tile GEMM: optional row arg-max accumulator [m] (packed value | index, see CH_FINAL)
   // derived by chain_prepare_phases (share arithmetic of the phase's GEMM for the launch grid, so that no thread
   // divides when a phase starts): 32 KB weight units per row tile, units per CTA, multiply-high reciprocals of both
   int r_nkb, r_per;
   unsigned r_magic_per, r_magic_nkb;
-  int reserved_[2];
+  // GEMM without a reduce phase behind it (the lm_head): every CTA takes whole row tiles, so an accumulator holds
+  // finished sums, and the drain stores them to `out` (or nowhere) and folds them into `best`; no bias, no partial tiles
+  int whole_tiles;
+  int reserved_;
 };
 constexpr int CHAIN_MAX_PHASES = 10;
 struct ChainArgs {

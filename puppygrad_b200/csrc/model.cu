@@ -680,8 +680,17 @@ static int ensure_chain_program(pg_cache* c, int batch, int chunk = 0) {
   }
   cur_b = B_LOGITS;
   gemm(m->t_wte, V, C, CH_ACT_NORM);
-  elem(V, C, nullptr, 0, c->logits + (size_t)chunk * 64 * V, nullptr, nullptr);
-  ph.back().best = c->d_chain_best;  // the reduce phase of the lm_head also finds the row arg-max
+  // The lm_head in whole row tiles per CTA: its drain stores the logits and finds the row arg-max, and there is no
+  // reduce phase (measured on GPT-2 medium, 64 sequences: 38 + 37 us for GEMM + reduce with equal shares).
+  // PG_CHAIN_LM_HEAD_REDUCE=1 brings the equal shares and the reduce phase back.
+  static const bool lm_head_reduce = getenv("PG_CHAIN_LM_HEAD_REDUCE") && atoi(getenv("PG_CHAIN_LM_HEAD_REDUCE")) != 0;
+  if (lm_head_reduce) {
+    elem(V, C, nullptr, 0, c->logits + (size_t)chunk * 64 * V, nullptr, nullptr);
+  } else {
+    ph.back().whole_tiles = 1;
+    ph.back().out = c->logits + (size_t)chunk * 64 * V;
+  }
+  ph.back().best = c->d_chain_best;  // together with the row arg-max
   {
     ChainPhase p{};
     p.kind = CH_FINAL;
@@ -701,7 +710,7 @@ static int ensure_chain_program(pg_cache* c, int batch, int chunk = 0) {
     // 12.9 MB of logits per step of 64 sequences that greedy decoding never reads
     std::vector<ChainPhase> lean = ph;
     for (ChainPhase& p : lean)
-      if (p.kind == CH_ELEM && p.best) p.out = nullptr;
+      if (p.best) p.out = nullptr;
     PG_CUDA_TRY(cudaMalloc(&prog.dev_argmax_only, lean.size() * sizeof(ChainPhase)));
     PG_CUDA_TRY(cudaMemcpy(prog.dev_argmax_only, lean.data(), lean.size() * sizeof(ChainPhase), cudaMemcpyHostToDevice));
   }

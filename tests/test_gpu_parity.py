@@ -765,6 +765,38 @@ def test_persistent_step_when_shares_straddle_row_tiles(oracle):
         cur = am.copy()
 
 
+def test_persistent_step_breaks_logit_ties_towards_the_lowest_index(oracle):
+    """argmax_logits (generation.rs:269-279) keeps the first strict maximum. With a tied embedding whose rows
+    repeat (row v = row v + 1 for even v, and again 400 and 800 rows further on), every logit occurs six times:
+    in neighbouring lanes of one warp, in other warps and in other row tiles of the lm_head. Every row tile sums
+    in the same order, so the six are equal bit for bit and the answer must be the even index below 400."""
+    cfg = dict(vocab_size=1200, n_positions=64, n_embd=256, n_layer=2, n_head=4, n_inner=1024,
+               layer_norm_epsilon=1e-5)
+    w = synthetic.perturbed_weights(cfg, 43)
+    base = w["wte.weight"][:200].copy()
+    w["wte.weight"] = np.ascontiguousarray(base[(np.arange(1200) % 400) // 2])
+    g = pg.Gpt2Model(cfg, w, pg.Gpt2CudaConfig(math_mode="tf32x3"))
+    o = oracle.Model(cfg, w, threads=4)
+    batch = 12
+    prompts = [synthetic.uniform_prompt(900 + i, 2 + 3 * i, cfg["vocab_size"]) for i in range(batch)]
+    cache = g.new_kv_cache(max_batch=batch)
+    _, cur = g.prefill_batch(prompts, cache)
+    ocaches = [o.new_kv_cache() for _ in prompts]
+    ocur = [oracle.argmax_logits(o.prefill(p, c)) for p, c in zip(prompts, ocaches)]
+    assert list(cur) == ocur
+    for step in range(4):
+        n0 = cache.kernel_launches()
+        logits, am, _, _ = g.forward_one_batch(cur, cache, want_logits=step % 2 == 0)
+        assert cache.kernel_launches() - n0 == 1
+        ol = np.stack([o.forward_one(int(cur[i]), ocaches[i]) for i in range(batch)])
+        if logits is not None:
+            assert_logits_close(logits, ol)
+            assert np.array_equal(logits[:, :400], logits[:, 400:800]) and np.array_equal(logits[:, :400], logits[:, 800:])
+        assert all(int(t) < 400 and int(t) % 2 == 0 for t in am)
+        assert list(am) == [oracle.argmax_logits(l) for l in ol]
+        cur = am.copy()
+
+
 # ------------------------------------------------------------------ narrow weights: int8 rows (the reference's variant), BF16
 @pytest.mark.parametrize("batch,math_mode", [(1, "fp32"), (3, "fp32"), (8, "fp32"), (12, "tf32x3")])
 def test_quantized_weights_model_matches_the_quantized_oracle(oracle, batch, math_mode):
