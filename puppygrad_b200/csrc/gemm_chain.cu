@@ -15,9 +15,11 @@
 //               run ahead as far as tensor memory stages are free.
 //   warp 2      activation producer: after the phase's inputs exist (grid barrier), TMA loads of
 //               the 64-token x 32 hi and lo tiles.
-//   warps 1, 3  MMA issuers, one per k block of a unit, an accumulator in tensor memory each: per
-//               8-wide k slice one tcgen05.mma of N = 128 (w_hi . [x_hi | x_lo]) and one of N = 64
-//               (w_lo . x_hi).
+//   warps 1, 3  MMA issuers, one per k block of a unit, a 64-column accumulator in tensor memory each:
+//               per 8-wide k slice three tcgen05.mma of N = 64 into it (w_hi . x_hi, w_lo . x_hi,
+//               w_hi . x_lo). One accumulator for the three products leaves tensor memory for three
+//               stages of split weights (two stages and separate columns for w_hi . x_lo measured
+//               1% slower: a stage comes back only when its MMAs have completed).
 //   warps 8-15  workers: drain the accumulators into per-CTA partial tiles (global memory, L2
 //               resident), take part in the grid barrier, run the reduce phases, the attention
 //               phases (one warp per sequence-head pair), the embedding and the end-of-step phase.
@@ -40,13 +42,15 @@ constexpr int CH_THREADS = 512;
 // so fewer, larger hand-overs keep the tensor pipe busier.
 constexpr int CH_UB = 2;
 constexpr int CH_W_STAGES = 3;    // weight units in flight per SM (32 KB each)
-constexpr int CH_X_STAGES = 2;    // units whose activation tiles (shared memory) and split weights (tensor memory) are staged
+constexpr int CH_X_STAGES = 3;    // units whose activation tiles (shared memory) and split weights (tensor memory) are staged
 constexpr int CH_BN = 64;
 constexpr int CH_W_BYTES = CH_UB * TILE_M * BK * 4;
 constexpr int CH_ACT_BYTES = CH_UB * 2 * CH_BN * BK * 4;  // per block: x_hi tile then x_lo tile
 constexpr int CH_MAX_SEG = 4;     // row tiles one CTA's share may touch
 constexpr int CH_WORKERS = 256;
-constexpr uint32_t CH_D_COLS = 128, CH_A_COL0 = 256, CH_TMEM_COLS = 512;
+// tensor memory: two accumulators of CH_BN columns, then CH_X_STAGES stages of w_hi | w_lo for the unit's two k blocks
+constexpr uint32_t CH_D_COLS = 64, CH_A_COL0 = 128, CH_TMEM_COLS = 512;
+static_assert(CH_D_COLS == CH_BN && CH_A_COL0 == 2 * CH_D_COLS && CH_A_COL0 + CH_X_STAGES * 64 * CH_UB <= CH_TMEM_COLS, "tensor memory columns");
 // Attention phases stage key / value rows in the (then idle) activation ring plus an extra region:
 // each of the eight worker warps has AT_SLOTS slots, each holding AT_ROWS key rows and the AT_ROWS
 // value rows of the same positions (one mbarrier per slot: one wait per block of keys).
@@ -868,7 +872,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
     // into an accumulator of its own; the drain adds the two.
     if (lane == 0) {
       const int b = warp == 1 ? 0 : 1;
-      const uint32_t idesc1 = umma_idesc_tf32(TILE_M, CH_BN), idesc2 = umma_idesc_tf32(TILE_M, 2 * CH_BN);
+      const uint32_t idesc1 = umma_idesc_tf32(TILE_M, CH_BN);
       const uint32_t dcol = tmem_base + (uint32_t)b * CH_D_COLS;
       uint32_t wi = 0, si = 0;
       bool ok = true;
@@ -888,11 +892,13 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
             tc_fence_after();
             // block b of the unit: x_hi rows then x_lo rows in shared memory, w_hi | w_lo columns in tensor memory
             const uint64_t dx = umma_desc_sw128(act_ring + (size_t)xs * CH_ACT_BYTES + (size_t)b * (CH_ACT_BYTES / CH_UB));
+            const uint64_t dxl = umma_desc_sw128(act_ring + (size_t)xs * CH_ACT_BYTES + (size_t)b * (CH_ACT_BYTES / CH_UB) + CH_BN * BK * 4);
             const uint32_t ahi = tmem_base + CH_A_COL0 + xs * (64 * CH_UB) + b * 64, alo = ahi + 32;
 #pragma unroll
             for (int k = 0; k < BK / 8; ++k) {
-              umma_tf32_ts(dcol, ahi + k * 8, dx + (uint64_t)(k * 2), idesc2, (gb != g || k != 0) ? 1u : 0u);
+              umma_tf32_ts(dcol, ahi + k * 8, dx + (uint64_t)(k * 2), idesc1, (gb != g || k != 0) ? 1u : 0u);
               umma_tf32_ts(dcol, alo + k * 8, dx + (uint64_t)(k * 2), idesc1, 1u);
+              umma_tf32_ts(dcol, ahi + k * 8, dxl + (uint64_t)(k * 2), idesc1, 1u);
             }
             umma_commit(&done[xs]);
           }
@@ -1003,18 +1009,15 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
     bool at_prepared = false;
     at_cur.item = at_cur.blk = at_cur.nblk = at_cur.t = at_cur.b = at_cur.h = at_cur.pg0 = at_cur.pg1 = 0;
     at_cur.issued = 0;
-    // Sums of token columns [c0, c0 + 16) of this thread's row: two accumulators (k block 0 and 1 of every unit),
-    // each with hi*hi + lo*hi and hi*lo columns; the four loads are in flight together
+    // Sums of token columns [c0, c0 + 16) of this thread's row: two accumulators (k block 0 and 1 of every unit);
+    // the two loads are in flight together
     auto ld_acc = [&](int c0, float* y) {
-      uint32_t v[16], v2[16], u[16], u2[16];
+      uint32_t v[16], u[16];
       tmem_ld16_issue(tmem_base + lane_addr + (uint32_t)c0, v);
-      tmem_ld16_issue(tmem_base + lane_addr + (uint32_t)(CH_BN + c0), v2);
       tmem_ld16_issue(tmem_base + CH_D_COLS + lane_addr + (uint32_t)c0, u);
-      tmem_ld16_issue(tmem_base + CH_D_COLS + lane_addr + (uint32_t)(CH_BN + c0), u2);
       tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 16; ++j)
-        y[j] = (__uint_as_float(v[j]) + __uint_as_float(v2[j])) + (__uint_as_float(u[j]) + __uint_as_float(u2[j]));
+      for (int j = 0; j < 16; ++j) y[j] = __uint_as_float(v[j]) + __uint_as_float(u[j]);
     };
     constexpr int PH_WORDS = (int)(sizeof(ChainPhase) / 4);
     const bool ph_staged = !(a.tune_fence & 4);
