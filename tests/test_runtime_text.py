@@ -207,8 +207,46 @@ def test_runtime_errors_with_a_stand_in_model(tokenizer):
         r.stream_token_ids_with_stats("the quick", pg.TextGenerationConfig(4), on_token)
 
 
+def test_command_output_with_a_stand_in_model(tokenizer, monkeypatch):
+    """run-gpt2 (main.rs:1305-1388): text to stdout and the speed line to stderr; with --stream-raw-tokens one
+    `phase TAB id TAB token` line per prompt and generated token; --stats prints the statistics block;
+    --no-eos-stop and --eos-token-id set the end-of-sequence token of the generation."""
+    cont = tokenizer.encode(" jumps over the lazy dog")
+    seen = {}
+
+    def from_dir_with_backend(model_dir, backend, use_tuning=True, tuning_file=None):
+        seen.update(model_dir=model_dir, backend=backend, use_tuning=use_tuning)
+        return pg.Gpt2Runtime(StandInModel(50257, cont), tokenizer)  # room for the default end-of-sequence id
+
+    monkeypatch.setattr(rt.Gpt2Runtime, "from_dir_with_backend", staticmethod(from_dir_with_backend))
+    prompt = "the quick brown fox"
+    out, err = io.StringIO(), io.StringIO()
+    assert rt.run_gpt2(["--model-dir", "/m", "--prompt", prompt, "--max-new-tokens", "4", "--no-tuning"], out, err) == 0
+    assert out.getvalue() == prompt + tokenizer.decode(cont[:4]) + "\n"
+    assert "loading GPT-2 from /m" in err.getvalue() and "tokens/sec: " in err.getvalue() and "stats:" not in err.getvalue()
+    assert seen == {"model_dir": "/m", "backend": None, "use_tuning": False}
+
+    out, err = io.StringIO(), io.StringIO()
+    assert rt.run_gpt2(["--model-dir", "/m", "--prompt", prompt, "--max-new-tokens", "3", "--stream-raw-tokens", "--stats",
+                        "--math-mode", "tf32x3", "--quantized-weights"], out, err) == 0
+    rows = [l.split("\t") for l in out.getvalue().splitlines()]
+    ids = tokenizer.encode(prompt)
+    assert [(r[0], int(r[1])) for r in rows] == [("prompt", t) for t in ids] + [("generated", t) for t in cont[:3]]
+    assert all(r[2] == pg.escape_raw_token(tokenizer.raw_token(int(r[1]))) for r in rows)
+    assert "stats:" in err.getvalue() and "    tokenization: " in err.getvalue()
+    assert seen["backend"].math_mode == "tf32x3" and seen["backend"].quantized_weights and seen["use_tuning"]
+
+    out, err = io.StringIO(), io.StringIO()  # the third token of the continuation as end-of-sequence token
+    assert rt.run_gpt2(["--model-dir", "/m", "--prompt", prompt, "--max-new-tokens", "8", "--eos-token-id", str(cont[2])],
+                       out, err) == 0
+    assert out.getvalue() == prompt + tokenizer.decode(cont[:2]) + "\n"
+    with pytest.raises(pg.Gpt2Error):  # validated before anything is loaded
+        rt.run_gpt2(["--model-dir", "/m", "--prompt", prompt, "--top-p", "0"], io.StringIO(), io.StringIO())
+
+
 @pytest.mark.gpu
 def test_runtime_from_dir_generates_text_end_to_end(tmp_path):
+
     vocab = make_tokenizer_json(tmp_path / "tokenizer.json")
     cfg = dict(vocab_size=vocab, n_positions=64, n_embd=64, n_layer=2, n_head=1, n_inner=256, layer_norm_epsilon=1e-5)
     w = synthetic.perturbed_weights(cfg, 77)
