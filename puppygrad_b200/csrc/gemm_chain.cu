@@ -169,6 +169,18 @@ __device__ __forceinline__ void chain_trace(const ChainArgs& a, int slot) {
   }
 }
 
+// Developer aid, compiled in only with -DPG_DEV_TRACE (and then active only when the trace buffer exists): clock64()
+// stamps of the first 48 weight units of CTA 0 in the whole-tile GEMM (the lm_head), eight events per unit, behind the
+// per-CTA slots of the buffer: 0 weight copy issued, 1 splitters saw the weights, 2 ... the free tensor-memory stage,
+// 3 split weights stored, 4 activation copy issued, 5 issuer saw the unit ready, 6 its MMAs committed, 7 issuer began
+// to wait. Slots 20-22 of every CTA: globaltimer at the start and at the end of its lm_head work, and its SM.
+#ifdef PG_DEV_TRACE
+__device__ __forceinline__ void unit_trace(const ChainArgs& a, bool on, int u, int e) {
+  if (on && a.trace && u < 48) a.trace[(size_t)gridDim.x * 32 + (size_t)u * 8 + e] = (unsigned long long)clock64();
+}
+#else
+__device__ __forceinline__ void unit_trace(const ChainArgs&, bool, int, int) {}
+#endif
 __device__ __forceinline__ const ChainPhase& phase_at(const ChainArgs& a, int p) {
   return a.phases_dev ? a.phases_dev[p] : a.ph[p];
 }
@@ -852,10 +864,12 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
         if (phase_at(a, p).kind != CH_GEMM) continue;
         const ChRange r = chain_range_ph(phase_at(a, p), cta);
         const uint32_t b0 = phase_at(a, p).w_block0;
+        const bool tr = cta == 0 && phase_at(a, p).whole_tiles;
         for (int g = r.g0; g < r.g1 && ok; ++g, ++wi) {
           const uint32_t s = wi % CH_W_STAGES;
           if (wi >= CH_W_STAGES) ok = mbar_wait(&w_empty[s], ((wi / CH_W_STAGES) - 1) & 1, failed, a.error_flag, 21);
           if (!ok) break;
+          unit_trace(a, tr, g - r.g0, 0);
           // one unit = CH_UB consecutive 16 KB blocks of the tiled arena = one box of CH_UB * 128 rows
           mbar_expect_tx(&w_full[s], CH_W_BYTES);
           if (hint)
@@ -887,8 +901,11 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
           tc_fence_after();
           for (int gb = g; gb < gend && ok; ++gb, ++wi) {
             const uint32_t xs = wi % CH_X_STAGES;
+            const bool tr = cta == 0 && b == 0 && phase_at(a, p).whole_tiles;
+            unit_trace(a, tr, gb - r.g0, 7);
             ok = mbar_wait(&ready[xs], (wi / CH_X_STAGES) & 1, failed, a.error_flag, 23);
             if (!ok) break;
+            unit_trace(a, tr, gb - r.g0, 5);
             tc_fence_after();
             // block b of the unit: x_hi rows then x_lo rows in shared memory, w_hi | w_lo columns in tensor memory
             const uint64_t dx = umma_desc_sw128(act_ring + (size_t)xs * CH_ACT_BYTES + (size_t)b * (CH_ACT_BYTES / CH_UB));
@@ -901,6 +918,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
               umma_tf32_ts(dcol, ahi + k * 8, dxl + (uint64_t)(k * 2), idesc1, 1u);
             }
             umma_commit(&done[xs]);
+            unit_trace(a, tr, gb - r.g0, 6);
           }
           if (ok) umma_commit(d_full);
           ++si;
@@ -929,6 +947,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
           const uint32_t s = wi % CH_X_STAGES;
           if (wi >= CH_X_STAGES) ok = mbar_wait(&done[s], ((wi / CH_X_STAGES) - 1) & 1, failed, a.error_flag, 26);
           if (!ok) break;
+          unit_trace(a, cta == 0 && phase_at(a, p).whole_tiles, g - r.g0, 4);
           const int kb = (g % r.nkb) * CH_UB;
           uint8_t* dst = act_ring + (size_t)s * CH_ACT_BYTES;
           mbar_expect_tx(&ready[s], CH_ACT_BYTES);
@@ -953,11 +972,14 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
       const ChRange r = chain_range_ph(phase_at(a, p), cta);
       for (int g = r.g0; g < r.g1 && ok; ++g, ++wi) {
         const uint32_t s = wi % CH_W_STAGES, xs = wi % CH_X_STAGES;
+        const bool tr = cta == 0 && warp == 4 && lane == 0 && phase_at(a, p).whole_tiles;
         ok = warp_wait(&w_full[s], (wi / CH_W_STAGES) & 1, failed, a.error_flag, 27);
         if (!ok) break;
+        unit_trace(a, tr, g - r.g0, 1);
         // the tensor-memory stage is free once the MMAs of the unit that used it last have completed
         if (wi >= CH_X_STAGES) ok = warp_wait(&done[xs], ((wi / CH_X_STAGES) - 1) & 1, failed, a.error_flag, 28);
         if (!ok) break;
+        unit_trace(a, tr, g - r.g0, 2);
         tc_fence_after();
 #pragma unroll
         for (int b = 0; b < CH_UB; ++b) {
@@ -982,6 +1004,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
         __syncwarp();
         if (lane == 0) mbar_arrive(&w_empty[s]);  // the unit is in registers / tensor memory: the stage may be refilled
         tmem_wait_st();
+        unit_trace(a, tr, g - r.g0, 3);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&ready[xs]);
@@ -1109,6 +1132,14 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
         if (live) chain_elem_phase(a, ph, wt, reinterpret_cast<unsigned long long*>(at_scratch));
       }
       if (wt == 0 && p < 10) chain_trace(a, 10 + p);
+#ifdef PG_DEV_TRACE
+      if (wt == 0 && a.trace && kind == CH_GEMM && ph.whole_tiles) {
+        chain_trace(a, 21);
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        a.trace[(size_t)blockIdx.x * 32 + 22] = smid;
+      }
+#endif
       if (p + 1 < a.n_phases) {
         if (wt < PH_WORDS)  // the next phase's descriptor; the barrier's first CTA barrier orders it before its readers
           reinterpret_cast<uint32_t*>(&ph_s[(p + 1) & 1])[wt] = reinterpret_cast<const uint32_t*>(&phase_at(a, p + 1))[wt];
@@ -1118,6 +1149,9 @@ __global__ void __launch_bounds__(CH_THREADS, 1)
         ok = ok && live;
       }
       if (wt == 0 && p < 10) chain_trace(a, p);
+#ifdef PG_DEV_TRACE
+      if (wt == 0 && p + 1 < a.n_phases && phase_at(a, p + 1).kind == CH_GEMM && phase_at(a, p + 1).whole_tiles) chain_trace(a, 20);
+#endif
       if (wt == 0 && cta == 0 && a.phase_times) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

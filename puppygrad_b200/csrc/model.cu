@@ -402,6 +402,17 @@ struct pg_cache {
           }
           fprintf(stderr, "chain trace phase %d: work done %6llu..%6llu ns, barrier passed %6llu..%6llu ns\n", sl, wlo, whi, lo, hi);
         }
+        // the lm_head of the last step: per CTA its SM and the time its share took; then CTA 0's units (see unit_trace)
+        for (int i = 0; i < chain_ctas; ++i) {
+          const unsigned long long* r = t.data() + (size_t)i * 32;
+          fprintf(stderr, "chain trace lm_head cta %3d sm %3llu work %7lld ns\n", i, r[22], (long long)(r[21] - r[20]));
+        }
+        const unsigned long long* u = t.data() + (size_t)chain_ctas * 32;
+        for (int i = 0; i < 48; ++i) {
+          fprintf(stderr, "chain trace unit %2d:", i);
+          for (int e = 0; e < 8; ++e) fprintf(stderr, " %7lld", u[i * 8 + e] ? (long long)(u[i * 8 + e] - u[0]) : -1LL);
+          fprintf(stderr, "\n");
+        }
       }
     }
 #endif
