@@ -62,6 +62,10 @@ class GenerationStats:
                                    self.decode_time, self.total_generation_time,
                                    -1.0 if self.first_token_time is None else self.first_token_time)
 
+    def with_profile(self, profile) -> "ProfiledGenerationStats":
+        """generation.rs:141-146"""
+        return ProfiledGenerationStats(self, profile)
+
     def total_model_tokens(self) -> int:
         return int(N.lib.pg_generation_stats_total_model_tokens(C.byref(self.to_native())))
 
@@ -77,6 +81,16 @@ class GenerationStats:
     def average_decode_token_time(self) -> Optional[float]:
         t = float(N.lib.pg_generation_stats_average_decode_token_time(C.byref(self.to_native())))
         return None if t < 0 else t
+
+
+@dataclass
+class ProfiledGenerationStats:
+    """generation.rs:182-196: the common statistics with a model's own profile beside them."""
+    common: GenerationStats
+    profile: object
+
+    def split(self):
+        return self.common, self.profile
 
 
 def argmax_logits(values: Sequence[float]) -> int:

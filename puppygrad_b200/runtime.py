@@ -22,7 +22,7 @@ from dataclasses import dataclass, field
 from typing import Callable, List, Optional, Sequence, TextIO, Tuple
 
 from .errors import Gpt2Error
-from .generation import GenerationStats, TextGenerationConfig, gpt2_generation_config
+from .generation import GenerationStats, ProfiledGenerationStats, TextGenerationConfig, gpt2_generation_config
 from .gpt2 import Gpt2CudaConfig, Gpt2Model
 from .streaming import IncrementalTextStreamer, escape_raw_token
 
@@ -109,6 +109,14 @@ class Gpt2GenerationStats:
     """rust.rs:329-374: the common statistics plus the operation profile; attributes of `common` read through."""
     common: GenerationStats = field(default_factory=GenerationStats)
     operation_profile: Gpt2OperationProfile = field(default_factory=Gpt2OperationProfile)
+
+    @classmethod
+    def new(cls, common: GenerationStats, operation_profile: Gpt2OperationProfile) -> "Gpt2GenerationStats":
+        common, operation_profile = common.with_profile(operation_profile).split()
+        return cls(common, operation_profile)
+
+    def as_profiled(self) -> ProfiledGenerationStats:
+        return ProfiledGenerationStats(self.common, self.operation_profile)
 
     def __getattr__(self, name):  # Deref<Target = GenerationStats>
         return getattr(object.__getattribute__(self, "common"), name)

@@ -302,3 +302,26 @@ def test_pool_chunk_to_worker_mapping(oracle):
     assert oracle.pool_worker_chunks(2, 10, 3, 1) == [1, 3]
     assert oracle.pool_worker_chunks(1, 10, 3, 0) == [0, 1, 2, 3]
     assert oracle.pool_worker_chunks(4, 0, 3, 0) == []
+
+
+def _pool_chunks(oracle, threads, length, chunk_size):
+    """What parallel_chunks returns, in chunk order: the (start, end) every worker was given, merged by chunk index."""
+    owned = sorted(c for w in range(threads) for c in oracle.pool_worker_chunks(threads, length, chunk_size, w))
+    return [(c * chunk_size, min(length, (c + 1) * chunk_size)) for c in owned]
+
+
+def test_parallel_chunks_preserves_order(oracle):
+    """thread_pool.rs:230-237"""
+    chunks = _pool_chunks(oracle, 4, 10, 3)
+    assert [v for a, b in chunks for v in range(a, b)] == list(range(10))
+
+
+def test_single_thread_chunks_preserve_order(oracle):
+    """thread_pool.rs:239-245"""
+    assert [sum(range(a, b)) for a, b in _pool_chunks(oracle, 1, 7, 2)] == [1, 5, 9, 6]
+
+
+def test_cloned_pool_reuses_workers(oracle):
+    """thread_pool.rs:247-256: chunk sizes of (4, 1) on two workers; a clone is the same pool, so the same mapping."""
+    assert [b - a for a, b in _pool_chunks(oracle, 2, 4, 1)] == [1, 1, 1, 1]
+    assert _pool_chunks(oracle, 2, 4, 1) == _pool_chunks(oracle, 2, 4, 1)

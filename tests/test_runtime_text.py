@@ -122,6 +122,29 @@ def test_raw_token_events_and_durations(tokenizer):
     assert rt.format_duration(3e-6) == "3.00us"
 
 
+def test_generic_generation_stats_report_token_rates():
+    """rust.rs:2040-2060"""
+    stats = pg.GenerationStats(prompt_tokens=4, generated_tokens=6, tokenize_time=0.005, prefill_time=0.020,
+                               decode_time=0.030, total_generation_time=0.050, first_token_time=0.022)
+    assert stats.total_model_tokens() == 10
+    assert stats.prefill_tokens_per_second() == pytest.approx(200.0)
+    assert stats.decode_tokens_per_second() == pytest.approx(200.0)
+    assert stats.total_tokens_per_second() == pytest.approx(200.0)
+    assert stats.average_decode_token_time() == pytest.approx(0.005)
+
+
+def test_gpt2_operation_profile_attaches_to_generic_stats():
+    """rust.rs:2062-2080"""
+    stats = pg.Gpt2GenerationStats.new(pg.GenerationStats(prompt_tokens=2, generated_tokens=3),
+                                       pg.Gpt2OperationProfile(qkv_projection=0.007))
+    profiled = stats.as_profiled()
+    assert profiled.common.total_model_tokens() == 5
+    assert profiled.profile.qkv_projection == 0.007
+    common, profile = profiled.split()
+    assert common is stats.common and profile is stats.operation_profile
+    assert stats.generated_tokens == 3 and stats.total_model_tokens() == 5  # reads through to the common part
+
+
 class StandInModel:
     """Emits a fixed continuation the way the library's calls do: callback per token, abort when it returns True."""
 
