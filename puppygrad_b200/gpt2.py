@@ -76,6 +76,11 @@ class Gpt2CudaConfig:
     persistent_step: Optional[bool] = None
     quantized_weights: bool = False  # Gpt2RustConfig::quantized_weights: row-wise int8 dense matrices and lm_head
 
+    def describe(self) -> str:
+        """Gpt2BackendConfig::describe (options.rs:36-50), the `backend:` line of run-gpt2."""
+        weights = "int8" if self.quantized_weights else "bf16" if self.math_mode == "bf16" else "f32"
+        return f"cuda (device={self.device}, math={self.math_mode}, page_tokens={self.page_tokens}, weights={weights})"
+
     def to_native(self) -> N.PgBackendConfig:
         if self.math_mode not in _MATH:
             raise Gpt2Error("InvalidConfig", f"cuda math_mode {self.math_mode!r} must be one of {sorted(_MATH)}")

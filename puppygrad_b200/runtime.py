@@ -325,11 +325,12 @@ def run_gpt2(argv: Optional[Sequence[str]] = None, stdout: TextIO = sys.stdout, 
     backend = None
     if a.math_mode is not None or a.quantized_weights:
         backend = Gpt2CudaConfig(math_mode=a.math_mode or "fp32", quantized_weights=a.quantized_weights)
-    stderr.write(f"backend: cuda ({'tuning file or defaults' if backend is None else backend})\n")
     stderr.write(f"loading GPT-2 from {a.model_dir}\n")
     t0 = time.perf_counter()
     runtime = Gpt2Runtime.from_dir_with_backend(a.model_dir, backend, use_tuning=not a.no_tuning, tuning_file=a.tuning_file)
     load_time = time.perf_counter() - t0
+    used = getattr(runtime.model, "cuda_config", None)  # the tuning file's when no backend was given
+    stderr.write(f"backend: {used.describe() if used is not None else 'cuda'}\n")
     if a.stream_raw_tokens:
         for token_id in runtime.tokenizer.encode(a.prompt):
             write_raw_token_event(stdout, None, "prompt", token_id, runtime.tokenizer)

@@ -258,6 +258,8 @@ def test_command_output_with_a_stand_in_model(tokenizer, monkeypatch):
     assert all(r[2] == pg.escape_raw_token(tokenizer.raw_token(int(r[1]))) for r in rows)
     assert "stats:" in err.getvalue() and "    tokenization: " in err.getvalue()
     assert seen["backend"].math_mode == "tf32x3" and seen["backend"].quantized_weights and seen["use_tuning"]
+    assert seen["backend"].describe() == "cuda (device=0, math=tf32x3, page_tokens=32, weights=int8)"
+    assert pg.Gpt2CudaConfig().describe() == "cuda (device=0, math=fp32, page_tokens=32, weights=f32)"
 
     out, err = io.StringIO(), io.StringIO()  # the third token of the continuation as end-of-sequence token
     assert rt.run_gpt2(["--model-dir", "/m", "--prompt", prompt, "--max-new-tokens", "8", "--eos-token-id", str(cont[2])],
